@@ -1,0 +1,766 @@
+"""`CudaBackend`: the device backend behind the op interface, standing in for `WebGPUBackend`
+(src/backend/webgpu.ts). Same public surface: `install/uninstall`, the 14 ops of `OpsBackend`, the
+`RegionBackend` trio, `uploadParams`, `sync`, `reclaimStepTransients`, `residentBytes`, the raw-buffer
+calls the optimizers and checkpoints use, and the introspection fields its tests read. Every method
+is a thin enqueue through the C ABI of libgguftrain_cuda.so; nothing here computes.
+
+Differences that are deliberate:
+ * Gradient buffers are not cleared and then `+=`-ed into. Each entry tracks whether its gradient
+   has been written in the current graph; the first writer overwrites, later ones accumulate. The
+   values are the ones a cleared buffer plus `+=` would hold, without the clear's memory traffic.
+   `gradClearsIssued` counts only the clears that still happen (a gradient that is read before
+   anything was written to it, the scatter-add target of the embedding).
+ * Work can be captured once into a CUDA graph and replayed (`beginCapture/endCapture`), which is
+   what removes the per-op host cost the reference is bound by.
+ * `setBatch(B, T)` lets one call carry B sequences as [B*T] rows.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import weakref
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+
+from . import _lib
+from . import autograd as ag
+from .autograd import Tensor
+
+_EW = {"add": 0, "mul": 1, "silu": 2, "gelu": 3, "scale": 4}
+_KIND = {"NT": 0, "NN": 1, "TN": 2}
+PRECISION = {"fp32": 0, "tf32": 1, "bf16": 2}
+
+
+class _Entry:
+    __slots__ = ("data", "grad", "bytes", "external", "gradLive", "size")
+
+    def __init__(self, data: int, grad: int, nbytes: int, external: bool, size: int):
+        self.data = data
+        self.grad = grad          # 0 for a frozen external (webgpu.ts frozenGradStub)
+        self.bytes = nbytes
+        self.external = external
+        self.gradLive = False     # has anything been written to grad in the current graph?
+        self.size = size
+
+
+class CapturedGraph:
+    """One recorded stretch of device work, replayable with new integer inputs."""
+
+    def __init__(self, gpu: "CudaBackend", handle: int, inputs, owned, outputs):
+        self.gpu = gpu
+        self.handle = handle
+        self.inputs = inputs      # [(addr, count)] in upload order
+        self.owned = owned        # [(addr, size)] transients pinned to this graph
+        self.outputs = outputs    # {name: (addr, count)}
+
+    def launch(self, inputs: Sequence[np.ndarray]):
+        if len(inputs) != len(self.inputs):
+            raise ValueError(f"graph takes {len(self.inputs)} integer inputs, got {len(inputs)}")
+        g = self.gpu
+        for (addr, count), arr in zip(self.inputs, inputs):
+            a = _as_u32(arr)
+            if a.size != count:
+                raise ValueError(f"graph input has {a.size} elements, recorded {count}")
+            g._check(g.lib.gt_write(g.ctx, addr, a.ctypes.data, a.nbytes))
+        g._check(g.lib.gt_graph_launch(g.ctx, self.handle))
+
+    def destroy(self):
+        g = self.gpu
+        g._check(g.lib.gt_graph_destroy(g.ctx, self.handle))
+        for addr, _size in self.owned:
+            g._check(g.lib.gt_free(g.ctx, addr))
+        self.owned = []
+
+
+def _as_u32(values) -> np.ndarray:
+    """-1 uploads as 0xffffffff, the marker the kernels test for (webgpu.ts:1636-1646)."""
+    a = np.asarray(values)
+    if a.dtype != np.uint32:
+        a = a.astype(np.int64).astype(np.uint32) if a.dtype.kind != "u" else a.astype(np.uint32)
+    return np.ascontiguousarray(a)
+
+
+class CudaBackend:
+    def __init__(self, device: int = 0, precision: str = "fp32"):
+        self.lib = _lib.load()
+        ctx = C.c_void_p()
+        st = self.lib.gt_init(device, C.byref(ctx))
+        if st != 0:
+            raise _lib.GtError(st, self.lib.gt_last_error(None).decode())
+        self.ctx = ctx
+        self.device = device
+        name = C.create_string_buffer(256)
+        self._check(self.lib.gt_device_name(self.ctx, name, 256))
+        self.adapterName = name.value.decode()
+        self.timestampSupported = True
+        self.lastSyncReadbackBytes = 0
+        self.gradClearsIssued = 0
+        self.precision = precision
+        self._check(self.lib.gt_set_precision(self.ctx, PRECISION[precision]))
+        self._entries: "weakref.WeakKeyDictionary[Tensor, _Entry]" = weakref.WeakKeyDictionary()
+        self._touched: Dict[int, Tensor] = {}
+        self._keptOnDevice: "weakref.WeakSet[Tensor]" = weakref.WeakSet()
+        self._transients: List[tuple] = []     # (addr, size)
+        self._regionFree: List[tuple] = []
+        self._regionsOpened = 0
+        self._backwardBegun = False
+        self._graphSynced = False              # a sync() ran after the current graph was built
+        self._capturing = False
+        self._captureInputs: List[tuple] = []
+        self._captureMark = 0
+        self._batch = (0, 0)
+        self._stateBufs: Dict[int, int] = {}
+        self._readback = 0
+        self._seedBuf = 0
+        self._finalizer = weakref.finalize(self, _destroy_ctx, self.lib, self.ctx)
+
+    # ------------------------------------------------------------------ plumbing
+    def _check(self, status: int):
+        if status != 0:
+            raise _lib.GtError(status, self.lib.gt_last_error(self.ctx).decode())
+
+    def describeDevice(self) -> str:
+        return self.adapterName
+
+    def install(self):
+        ag.setOpsBackend(self)
+
+    def uninstall(self):
+        ag.setOpsBackend(None)
+
+    def destroy(self):
+        """webgpu.ts:764-767."""
+        if ag.opsBackend() is self:
+            self.uninstall()
+        if self._finalizer.alive:
+            self._finalizer()
+        self.ctx = None
+
+    def setPrecision(self, precision: str):
+        self.precision = precision
+        self._check(self.lib.gt_set_precision(self.ctx, PRECISION[precision]))
+
+    def setBatch(self, batch: int, seq_len: int = 0):
+        """Rows passed to the ops are `batch` sequences of `seq_len` rows; 0 restores one sequence per call."""
+        self._check(self.lib.gt_set_batch(self.ctx, batch, seq_len))
+        self._batch = (batch, seq_len if batch else 0)
+
+    def stats(self):
+        out = (C.c_uint64 * 4)()
+        self._check(self.lib.gt_stats(self.ctx, out))
+        return {"pool": int(out[0]), "state": int(out[1]), "readback": int(out[2]), "launches": int(out[3])}
+
+    def residentBytes(self):
+        """webgpu.ts:774-777."""
+        s = self.stats()
+        return {"pool": s["pool"], "state": s["state"], "total": s["pool"] + s["state"]}
+
+    def kernelLaunches(self) -> int:
+        return self.stats()["launches"]
+
+    # ------------------------------------------------------------------ memory
+    def _alloc(self, nbytes: int) -> tuple:
+        out = C.c_uint64()
+        self._check(self.lib.gt_alloc(self.ctx, max(nbytes, 4), C.byref(out)))
+        size = max(256, (max(nbytes, 4) + 255) // 256 * 256)
+        return int(out.value), size
+
+    def _acquirePersistent(self, nbytes: int) -> int:
+        return self._alloc(nbytes)[0]
+
+    def _acquireTransient(self, nbytes: int) -> int:
+        addr, size = self._alloc(nbytes)
+        self._transients.append((addr, size))
+        return addr
+
+    def _acquireRecycled(self, nbytes: int) -> int:
+        """Best fit from the region free-list, else a fresh transient (webgpu.ts acquireRecycled)."""
+        want = max(256, (max(nbytes, 4) + 255) // 256 * 256)
+        best = -1
+        for i, (_a, size) in enumerate(self._regionFree):
+            if size >= want and (best < 0 or size < self._regionFree[best][1]):
+                best = i
+        if best < 0:
+            return self._acquireTransient(nbytes)
+        tr = self._regionFree.pop(best)
+        self._transients.append(tr)
+        return tr[0]
+
+    def _write(self, addr: int, arr: np.ndarray):
+        arr = np.ascontiguousarray(arr)
+        self._check(self.lib.gt_write(self.ctx, addr, arr.ctypes.data, arr.nbytes))
+
+    def _read(self, addr: int, out: np.ndarray):
+        assert out.flags["C_CONTIGUOUS"]
+        self._check(self.lib.gt_read(self.ctx, addr, out.ctypes.data, out.nbytes))
+        self._readback += out.nbytes
+
+    def _uploadU32(self, values) -> int:
+        a = _as_u32(values)
+        if self._capturing:
+            # a replayed graph reads its integer inputs from fixed buffers the launcher rewrites
+            addr = self._acquirePersistent(a.nbytes)
+            self._captureInputs.append((addr, a.size))
+            return addr
+        addr = self._acquireTransient(a.nbytes)
+        self._write(addr, a)
+        return addr
+
+    def _uploadF32(self, values) -> int:
+        a = np.ascontiguousarray(np.asarray(values, dtype=np.float32))
+        if self._capturing:
+            raise _lib.GtError(4, "float uploads are not replayable; this op cannot be captured")
+        addr = self._acquireTransient(a.nbytes)
+        self._write(addr, a)
+        return addr
+
+    def _entryFor(self, t: Tensor) -> _Entry:
+        """webgpu.ts:1539-1573: externals (params, test inputs) get persistent buffers on first use."""
+        e = self._entries.get(t)
+        if e is None:
+            nbytes = t.size * 4
+            if self._capturing:
+                raise _lib.GtError(4, "a tensor first reached the device inside a graph capture; upload it first")
+            e = _Entry(self._acquirePersistent(nbytes), self._acquirePersistent(nbytes) if t.requiresGrad else 0,
+                       nbytes, True, t.size)
+            self._entries[t] = e
+            self._write(e.data, t.data)
+        if e.external and id(t) not in self._touched:
+            self._touched[id(t)] = t
+        return e
+
+    def _makeOut(self, shape, prev) -> tuple:
+        t = Tensor.zeros(shape)
+        t._prev = list(prev)
+        nbytes = t.size * 4
+        e = _Entry(self._acquireRecycled(nbytes), self._acquireRecycled(nbytes), nbytes, False, t.size)
+        self._entries[t] = e
+        return t, e
+
+    def _gradTarget(self, t: Tensor, e: _Entry):
+        """(grad address or 0, accum flag) for a backward kernel about to write into t's gradient."""
+        if e.grad == 0 or (e.external and not t.requiresGrad):
+            return 0, 0
+        acc = 1 if e.gradLive else 0
+        e.gradLive = True
+        return e.grad, acc
+
+    def _gradSource(self, e: _Entry) -> int:
+        """The upstream gradient of an op output. Never written means it is exactly zero."""
+        if not e.gradLive:
+            self._check(self.lib.gt_zero(self.ctx, e.grad, e.bytes))
+            self.gradClearsIssued += 1
+            e.gradLive = True
+        return e.grad
+
+    # ------------------------------------------------------------------ data movement
+    def uploadParams(self, tensors: Sequence[Tensor]):
+        """webgpu.ts:406-411."""
+        for t in tensors:
+            e = self._entryFor(t)
+            self._write(e.data, t.data)
+
+    def reserveGradArena(self, tensors: Sequence[Tensor]) -> tuple:
+        """Give the listed trainable tensors gradient buffers carved, in order, from one contiguous
+        block, so a data-parallel step can sum them across ranks in a few large buckets.
+        Returns (address, element count, [offset per tensor])."""
+        total = 0
+        offs = []
+        for t in tensors:
+            if t in self._entries:
+                raise _lib.GtError(4, "reserveGradArena must run before the tensors are first used")
+            offs.append(total)
+            total += (t.size + 63) // 64 * 64   # 256-byte aligned slices
+        base = self.createStateBuffer(total * 4)
+        for t, off in zip(tensors, offs):
+            nbytes = t.size * 4
+            e = _Entry(self._acquirePersistent(nbytes), base + off * 4, nbytes, True, t.size)
+            self._entries[t] = e
+            self._write(e.data, t.data)
+        return base, total, offs
+
+    def sync(self, reads: Sequence[Tensor] = ()):
+        """webgpu.ts:419-576: flush, copy back `reads` and the gradients of every touched external that
+        requires grad and is not kept on device, recycle the transients."""
+        if self._capturing:
+            raise _lib.GtError(4, "sync() inside a graph capture")
+        self._readback = 0
+        seen = set()
+        for t in reads:
+            if id(t) in seen:
+                continue
+            seen.add(id(t))
+            e = self._entries.get(t)
+            if e is None:
+                continue
+            self._read(e.data, t.data)
+        for t in list(self._touched.values()):
+            e = self._entries.get(t)
+            if e is None:
+                continue
+            if t.requiresGrad and e.grad:
+                if not e.gradLive:
+                    # touched by a forward, never written by a backward: the reference's cleared buffer
+                    self._check(self.lib.gt_zero(self.ctx, e.grad, e.bytes))
+                    self.gradClearsIssued += 1
+                if t not in self._keptOnDevice:
+                    self._read(e.grad, t.grad)
+            e.gradLive = False   # the next graph's first writer overwrites (the deferred clear)
+        self._check(self.lib.gt_sync(self.ctx))
+        self.lastSyncReadbackBytes = self._readback
+        for addr, _size in self._transients:
+            self._check(self.lib.gt_free(self.ctx, addr))
+        self._transients = []
+        for addr, _size in self._regionFree:
+            self._check(self.lib.gt_free(self.ctx, addr))
+        self._regionFree = []
+        self._touched.clear()
+        self._backwardBegun = False
+        self._graphSynced = True
+
+    def reclaimStepTransients(self, keep: Sequence[Tensor] = ()):
+        """webgpu.ts:612-633: recycle this micro-batch's transients without the readback."""
+        keepBufs = set()
+        for t in keep:
+            e = self._entries.get(t)
+            if e is not None:
+                keepBufs.add(e.data)
+        retained = []
+        for tr in self._transients:
+            if tr[0] in keepBufs:
+                retained.append(tr)
+            else:
+                self._check(self.lib.gt_free(self.ctx, tr[0]))
+        self._transients = retained
+        for addr, _size in self._regionFree:
+            self._check(self.lib.gt_free(self.ctx, addr))
+        self._regionFree = []
+
+    # ------------------------------------------------------------------ regions (RegionBackend)
+    def beginRegion(self) -> int:
+        self._regionsOpened += 1
+        return len(self._transients)
+
+    def regionCount(self) -> int:
+        return self._regionsOpened
+
+    def endRegion(self, mark: int, keep: Sequence[Tensor]):
+        """webgpu.ts:659-702."""
+        if mark > len(self._transients):
+            raise RuntimeError(
+                f"endRegion: mark {mark} is past the {len(self._transients)} live transients; "
+                f"a sync() or reclaim ran inside the region")
+        keepBufs = set()
+        for t in keep:
+            e = self._entries.get(t)
+            if e is not None:
+                keepBufs.add(e.data)
+                keepBufs.add(e.grad)
+        retained = self._transients[:mark]
+        for tr in self._transients[mark:]:
+            if tr[0] in keepBufs:
+                retained.append(tr)
+            else:
+                self._regionFree.append(tr)
+        self._transients = retained
+
+    def seedGradFrom(self, dst: Tensor, src: Tensor):
+        """webgpu.ts:748-761."""
+        self._ensureBackwardBegun()
+        ed, es = self._entries.get(dst), self._entries.get(src)
+        if ed is None or es is None:
+            raise RuntimeError("seedGradFrom: tensor has no GPU buffers")
+        if dst.size != src.size:
+            raise RuntimeError(f"seedGradFrom: size mismatch {dst.size} vs {src.size}")
+        self._check(self.lib.gt_copy(self.ctx, ed.grad, self._gradSource(es), src.size * 4))
+        ed.gradLive = True
+
+    def seedGradFromHost(self, t: Tensor):
+        """webgpu.ts:1432-1437."""
+        self._ensureBackwardBegun()
+        e = self._entries.get(t)
+        if e is None:
+            raise RuntimeError("seedGradFromHost: tensor has no GPU buffers")
+        self._write(e.grad, t.grad)
+        e.gradLive = True
+
+    def _beginForwardOp(self):
+        self._backwardBegun = False
+        self._graphSynced = False
+
+    def _ensureBackwardBegun(self):
+        """webgpu.ts:1397-1429. A sync() between a graph's forward and its backward recycled the graph's
+        buffers; refuse to accumulate into them."""
+        if self._backwardBegun:
+            return
+        if self._graphSynced:
+            raise RuntimeError(
+                "backward over a graph built before a sync(): that sync recycled the graph's "
+                "gradient buffers and discarded their clears, so this backward would "
+                "accumulate into pool garbage")
+        self._backwardBegun = True
+
+    # ------------------------------------------------------------------ raw buffers (optimizers, checkpoints)
+    def buffersFor(self, t: Tensor):
+        e = self._entryFor(t)
+        return {"data": e.data, "grad": e.grad}
+
+    def keepGradOnDevice(self, t: Tensor):
+        self._keptOnDevice.add(t)
+
+    def createStateBuffer(self, nbytes: int) -> int:
+        out = C.c_uint64()
+        self._check(self.lib.gt_alloc_state(self.ctx, nbytes, C.byref(out)))
+        self._stateBufs[int(out.value)] = nbytes
+        return int(out.value)
+
+    def writeStateBuffer(self, buf: int, f32: np.ndarray):
+        self._write(buf, np.ascontiguousarray(f32, dtype=np.float32))
+
+    def readStateBuffer(self, buf: int, n: int) -> np.ndarray:
+        out = np.empty(n, np.float32)
+        self._read(buf, out)
+        return out
+
+    # ------------------------------------------------------------------ graph capture
+    def beginCapture(self, seed: float = 1.0, accumulate: bool = True):
+        """Start recording device work into a replayable graph. Run the same work once eagerly first:
+        recording cannot allocate (the pool, RoPE tables and scratch must already be warm).
+        `seed` is the loss seed the recorded backward uses. With `accumulate` the recorded backward adds
+        into the parameter gradients (replay it once per micro-batch after zeroing them); without, its
+        first write to each parameter gradient overwrites (one replay per step)."""
+        if self._capturing:
+            raise _lib.GtError(4, "beginCapture: already capturing")
+        if self._seedBuf == 0:
+            self._seedBuf = self.createStateBuffer(4)
+        self._write(self._seedBuf, np.array([seed], np.float32))
+        for t, e in list(self._entries.items()):
+            if e.external and e.grad:
+                e.gradLive = bool(accumulate)
+        self._check(self.lib.gt_graph_begin(self.ctx))
+        self._capturing = True
+        self._captureInputs = []
+        self._captureMark = len(self._transients)
+
+    def endCapture(self, outputs: Optional[Dict[str, Tensor]] = None) -> CapturedGraph:
+        h = C.c_uint64()
+        self._capturing = False
+        self._check(self.lib.gt_graph_end(self.ctx, C.byref(h)))
+        owned = self._transients[self._captureMark:] + self._regionFree
+        self._transients = self._transients[:self._captureMark]
+        self._regionFree = []
+        owned = owned + [(a, n * 4) for a, n in self._captureInputs]
+        outs = {}
+        for name, t in (outputs or {}).items():
+            e = self._entries[t]
+            outs[name] = (e.data, t.size)
+        g = CapturedGraph(self, int(h.value), list(self._captureInputs), owned, outs)
+        self._captureInputs = []
+        # externals touched while recording keep their accumulate-or-overwrite state as recorded
+        return g
+
+    def readGraphOutput(self, g: CapturedGraph, name: str) -> np.ndarray:
+        addr, n = g.outputs[name]
+        out = np.empty(n, np.float32)
+        self._read(addr, out)
+        return out
+
+    # ------------------------------------------------------------------ events
+    def recordEvent(self, slot: int):
+        self._check(self.lib.gt_event_record(self.ctx, slot))
+
+    def elapsedMs(self, a: int, b: int) -> float:
+        ms = C.c_float()
+        self._check(self.lib.gt_event_elapsed_ms(self.ctx, a, b, C.byref(ms)))
+        return float(ms.value)
+
+    # ------------------------------------------------------------------ ops (OpsBackend)
+    def _gemm(self, kind: str, accum: int, M: int, N: int, K: int, a: int, b: int, c: int):
+        self._check(self.lib.gt_gemm(self.ctx, _KIND[kind], accum, M, N, K, a, b, c))
+
+    def linear(self, x: Tensor, w: Tensor) -> Tensor:
+        """webgpu.ts:884-903."""
+        self._beginForwardOp()
+        T, inDim = x.shape
+        outDim = w.shape[0]
+        ex, ew = self._entryFor(x), self._entryFor(w)
+        out, eo = self._makeOut([T, outDim], [x, w])
+        self._gemm("NT", 0, T, outDim, inDim, ex.data, ew.data, eo.data)
+
+        def _bw():
+            self._ensureBackwardBegun()
+            go = self._gradSource(eo)
+            gx, ax = self._gradTarget(x, ex)
+            if gx:
+                self._gemm("NN", ax, T, inDim, outDim, go, ew.data, gx)
+            if w.requiresGrad:
+                gw, aw = self._gradTarget(w, ew)
+                if gw:
+                    self._gemm("TN", aw, outDim, inDim, T, go, ex.data, gw)
+
+        out._backward = _bw
+        return out
+
+    def _elementwise(self, op: str, a: Tensor, b: Optional[Tensor], c: float) -> Tensor:
+        self._beginForwardOp()
+        ea = self._entryFor(a)
+        eb = self._entryFor(b) if b is not None else None
+        out, eo = self._makeOut(a.shape, [a, b] if b is not None else [a])
+        n = a.size
+        code = _EW[op]
+        self._check(self.lib.gt_ew_fwd(self.ctx, code, n, ea.data, eb.data if eb else 0, c, eo.data))
+
+        def _bw():
+            self._ensureBackwardBegun()
+            go = self._gradSource(eo)
+            if eb is not None and eb is ea:
+                # add(t,t) / mul(t,t): both contributions land in one buffer, summed in one write
+                ga, aa = self._gradTarget(a, ea)
+                self._check(self.lib.gt_ew_bwd(self.ctx, code, n, ea.data, ea.data, c, go, ga, aa, ga, aa))
+                return
+            ga, aa = self._gradTarget(a, ea)
+            gb, ab = self._gradTarget(b, eb) if eb is not None else (0, 0)
+            self._check(self.lib.gt_ew_bwd(self.ctx, code, n, ea.data, eb.data if eb else 0, c, go, ga, aa, gb, ab))
+
+        out._backward = _bw
+        return out
+
+    def add(self, a, b):
+        return self._elementwise("add", a, b, 0.0)
+
+    def mul(self, a, b):
+        return self._elementwise("mul", a, b, 0.0)
+
+    def silu(self, x):
+        return self._elementwise("silu", x, None, 0.0)
+
+    def gelu(self, x):
+        return self._elementwise("gelu", x, None, 0.0)
+
+    def scale(self, x, c):
+        return self._elementwise("scale", x, None, float(c))
+
+    def _rmsNormRows(self, x: Tensor, w: Tensor, rows: int, d: int, eps: float, shape) -> Tensor:
+        """webgpu.ts:1673-1701."""
+        self._beginForwardOp()
+        ex, ew = self._entryFor(x), self._entryFor(w)
+        out, eo = self._makeOut(shape, [x, w])
+        rinv = self._acquireRecycled(rows * 4)
+        self._check(self.lib.gt_rmsnorm_fwd(self.ctx, rows, d, ex.data, ew.data, eps, eo.data, rinv))
+
+        def _bw():
+            self._ensureBackwardBegun()
+            go = self._gradSource(eo)
+            gx, ax = self._gradTarget(x, ex)
+            gw, aw = self._gradTarget(w, ew) if w.requiresGrad else (0, 0)
+            self._check(self.lib.gt_rmsnorm_bwd(self.ctx, rows, d, ex.data, ew.data, rinv, go, gx, ax, gw, aw))
+
+        out._backward = _bw
+        return out
+
+    def rmsNorm(self, x, weight, eps):
+        T, d = x.shape
+        return self._rmsNormRows(x, weight, T, d, eps, [T, d])
+
+    def rmsNormHeads(self, x, weight, T, H, hd, eps):
+        return self._rmsNormRows(x, weight, T * H, hd, eps, [T, H * hd])
+
+    def embedding(self, weight: Tensor, ids) -> Tensor:
+        """webgpu.ts:1090-1108."""
+        self._beginForwardOp()
+        d = weight.shape[1]
+        T = len(ids)
+        ew = self._entryFor(weight)
+        idBuf = self._uploadU32(ids)
+        out, eo = self._makeOut([T, d], [weight])
+        self._check(self.lib.gt_embedding_fwd(self.ctx, T, d, ew.data, idBuf, eo.data))
+
+        def _bw():
+            self._ensureBackwardBegun()
+            if not weight.requiresGrad or not ew.grad:
+                return
+            go = self._gradSource(eo)
+            if not ew.gradLive:
+                self._check(self.lib.gt_zero(self.ctx, ew.grad, ew.bytes))
+                self.gradClearsIssued += 1
+                ew.gradLive = True
+            self._check(self.lib.gt_embedding_bwd(self.ctx, T, d, go, idBuf, ew.grad))
+
+        out._backward = _bw
+        return out
+
+    def _checkT(self, T: int, rows: int, where: str):
+        b, sl = self._batch
+        if b and T != b * sl:
+            raise ValueError(f"{where}: T={T} but the batch is {b} x {sl}")
+        if not b and T != rows:
+            raise ValueError(f"{where}: T={T} but the tensor has {rows} rows")
+
+    def rope(self, x: Tensor, T: int, H: int, hd: int, base: float, posOffset: int = 0) -> Tensor:
+        self._beginForwardOp()
+        self._checkT(T, x.shape[0], "rope")
+        ex = self._entryFor(x)
+        out, eo = self._makeOut([T, H * hd], [x])
+        self._check(self.lib.gt_rope_fwd(self.ctx, T, H, hd, float(base), posOffset, ex.data, eo.data))
+
+        def _bw():
+            self._ensureBackwardBegun()
+            go = self._gradSource(eo)
+            gx, ax = self._gradTarget(x, ex)
+            self._check(self.lib.gt_rope_bwd(self.ctx, T, H, hd, float(base), posOffset, go, gx, ax))
+
+        out._backward = _bw
+        return out
+
+    def attention(self, q: Tensor, k: Tensor, v: Tensor, T: int, Hq: int, Hkv: int, hd: int, window: int) -> Tensor:
+        """webgpu.ts:1125-1192."""
+        self._beginForwardOp()
+        self._checkT(T, q.shape[0], "attention")
+        eq, ek, ev = self._entryFor(q), self._entryFor(k), self._entryFor(v)
+        out, eo = self._makeOut([T, Hq * hd], [q, k, v])
+        lse = self._acquireRecycled(Hq * T * 4)
+        self._check(self.lib.gt_attention_fwd(self.ctx, T, Hq, Hkv, hd, window, eq.data, ek.data, ev.data, eo.data, lse))
+
+        def _bw():
+            self._ensureBackwardBegun()
+            go = self._gradSource(eo)
+            gq, aq = self._gradTarget(q, eq)
+            gk, ak = self._gradTarget(k, ek)
+            gv, av = self._gradTarget(v, ev)
+            self._check(self.lib.gt_attention_bwd(self.ctx, T, Hq, Hkv, hd, window, eq.data, ek.data, ev.data, eo.data,
+                                                  lse, go, gq, aq, gk, ak, gv, av))
+
+        out._backward = _bw
+        return out
+
+    def _nseq(self) -> int:
+        return self._batch[0] if self._batch[0] else 1
+
+    def _lossOut(self, prev):
+        """The scalar loss tensor plus its device-side companions: [1+nseq] losses and [nseq] 1/kept."""
+        nseq = self._nseq()
+        loss = Tensor.zeros([1])
+        loss._prev = list(prev)
+        e = _Entry(self._acquireRecycled((1 + nseq) * 4), self._acquireRecycled(4), 4, False, 1)
+        self._entries[loss] = e
+        invKept = self._acquireRecycled(nseq * 4)
+        return loss, e, invKept
+
+    def _lossGrad(self, loss: Tensor, e: _Entry) -> int:
+        """backward(loss, seed) wrote the seed into the HOST grad array; push it to the device
+        (webgpu.ts:1316-1320). A captured graph instead reads the seed from a fixed buffer that
+        beginCapture filled, since a host write cannot be replayed."""
+        if self._capturing:
+            return self._seedBuf
+        if not e.gradLive:
+            self._write(e.grad, loss.grad[:1])
+            e.gradLive = True
+        return e.grad
+
+    def crossEntropy(self, logits: Tensor, targets, kept: int) -> Tensor:
+        """webgpu.ts:1295-1329. `kept` was counted above the dispatch; the device derives the same
+        count from the uploaded targets, so nothing host-computed is baked into a replayable graph."""
+        self._beginForwardOp()
+        T, V = logits.shape
+        el = self._entryFor(logits)
+        tgt = self._uploadU32(targets)
+        stats = self._acquireRecycled(T * 16)
+        loss, eo, invKept = self._lossOut([logits])
+        self._check(self.lib.gt_ce_fwd(self.ctx, T, V, el.data, tgt, stats, eo.data, invKept))
+
+        def _bw():
+            self._ensureBackwardBegun()
+            seed = self._lossGrad(loss, eo)
+            gl, al = self._gradTarget(logits, el)
+            self._check(self.lib.gt_ce_bwd(self.ctx, T, V, el.data, tgt, stats, invKept, seed, gl, al))
+
+        loss._backward = _bw
+        return loss
+
+    def fusedCrossEntropy(self, hidden: Tensor, w: Tensor, targets, chunk: int, kept: int) -> Tensor:
+        """webgpu.ts:1214-1278: per vocab span, logits = hidden·W[span]ᵀ then online (max, sum, target
+        logit); backward recomputes each span, forms dlogits in place and feeds the two products."""
+        self._beginForwardOp()
+        T, H = hidden.shape
+        V = w.shape[0]
+        eh, ew = self._entryFor(hidden), self._entryFor(w)
+        tgt = self._uploadU32(targets)
+        run = self._acquireRecycled(T * 12)
+        width = min(chunk, V)
+        ch = self._acquireRecycled(T * width * 4)
+        loss, eo, invKept = self._lossOut([hidden, w])
+        for v0 in range(0, V, chunk):
+            n = min(chunk, V - v0)
+            self._gemm("NT", 0, T, n, H, eh.data, ew.data + v0 * H * 4, ch)
+            self._check(self.lib.gt_ce_chunk_stats(self.ctx, T, n, v0, 1 if v0 == 0 else 0, ch, tgt, run))
+        self._check(self.lib.gt_ce_loss_from_stats(self.ctx, T, run, tgt, eo.data, invKept))
+
+        def _bw():
+            self._ensureBackwardBegun()
+            seed = self._lossGrad(loss, eo)
+            gh, ah = self._gradTarget(hidden, eh)
+            gw, aw = self._gradTarget(w, ew) if w.requiresGrad else (0, 0)
+            for v0 in range(0, V, chunk):
+                n = min(chunk, V - v0)
+                self._gemm("NT", 0, T, n, H, eh.data, ew.data + v0 * H * 4, ch)
+                self._check(self.lib.gt_ce_chunk_grad(self.ctx, T, n, v0, ch, tgt, run, invKept, seed))
+                if gh:
+                    self._gemm("NN", ah, T, H, n, ch, ew.data + v0 * H * 4, gh)
+                    ah = 1
+                if gw:
+                    # rows [v0, v0+n) of dW; each span is written by exactly one product
+                    self._gemm("TN", aw, n, H, T, ch, eh.data, gw + v0 * H * 4)
+
+        loss._backward = _bw
+        return loss
+
+    def softCrossEntropy(self, logits: Tensor, teacherIds, teacherProbs, k: int, kept: int) -> Tensor:
+        """webgpu.ts:1331-1378."""
+        self._beginForwardOp()
+        T, V = logits.shape
+        el = self._entryFor(logits)
+        ids = self._uploadU32(teacherIds)
+        probs = self._uploadF32(teacherProbs)
+        stats = self._acquireRecycled(T * 16)
+        loss, eo, invKept = self._lossOut([logits])
+        self._check(self.lib.gt_soft_ce_fwd(self.ctx, T, V, k, el.data, ids, probs, stats, eo.data, invKept))
+
+        def _bw():
+            self._ensureBackwardBegun()
+            seed = self._lossGrad(loss, eo)
+            gl, al = self._gradTarget(logits, el)
+            self._check(self.lib.gt_soft_ce_bwd(self.ctx, T, V, k, el.data, ids, probs, stats, invKept, seed, gl, al))
+
+        loss._backward = _bw
+        return loss
+
+    # ------------------------------------------------------------------ per-sequence losses of a batched call
+    def sequenceLosses(self, loss: Tensor) -> np.ndarray:
+        """The per-sequence losses behind a loss tensor produced under setBatch (blocks)."""
+        e = self._entries[loss]
+        out = np.empty(1 + self._nseq(), np.float32)
+        self._read(e.data, out)
+        return out[1:]
+
+
+def _destroy_ctx(lib, ctx):
+    try:
+        lib.gt_destroy(ctx)
+    except Exception:
+        pass
+
+
+def initCuda(device: int = 0, precision: str = "fp32") -> Optional[CudaBackend]:
+    """`initWebGPU()` (webgpu.ts:1812-1870): a backend, or None when there is no GPU so suites can SKIP."""
+    try:
+        return CudaBackend(device, precision)
+    except _lib.GtError:
+        return None
+
+
+def requireGPU(purpose: str, device: int = 0, precision: str = "fp32") -> CudaBackend:
+    """webgpu.ts:1872-1888."""
+    gpu = initCuda(device, precision)
+    if gpu is None:
+        raise RuntimeError(f"no GPU adapter found, and {purpose} needs one")
+    return gpu

@@ -1,0 +1,85 @@
+// Shared declarations for libgguftrain_cuda.so (internal; the public ABI is include/gguftrain.h).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <map>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/gguftrain.h"
+
+struct GtAdamW;
+struct GtMuon;
+struct GtDp;
+
+struct gt_ctx {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  std::string err;
+  int precision = GT_PREC_FP32;
+  int batch = 0, seq_len = 0;  // gt_set_batch
+  int sm_count = 148;
+  // pool (BufferPool, webgpu.ts:214-262): exact-size free lists, 256-byte buckets
+  std::map<uint64_t, std::vector<void*>> free_lists;
+  std::unordered_map<void*, uint64_t> live;   // allocation -> bucket size (pooled)
+  std::unordered_map<void*, uint64_t> state;  // allocation -> bytes (state buffers)
+  uint64_t pool_bytes = 0, state_bytes = 0, readback_bytes = 0, launches = 0;
+  // rope tables keyed by (T, hd, base, posOffset)
+  struct RopeKey {
+    int T, hd, off;
+    double base;
+    bool operator<(const RopeKey& o) const {
+      if (T != o.T) return T < o.T;
+      if (hd != o.hd) return hd < o.hd;
+      if (off != o.off) return off < o.off;
+      return base < o.base;
+    }
+  };
+  std::map<RopeKey, float*> rope_tables;  // [T, hd/2, 2] (cos, sin)
+  // small scratch for reductions (never pooled)
+  float* scratch = nullptr;
+  uint64_t scratch_bytes = 0;
+  // staging
+  void* pinned = nullptr;
+  uint64_t pinned_bytes = 0, pinned_cursor = 0;
+  bool capturing = false;
+  std::vector<GtAdamW*> adamws;
+  std::vector<GtMuon*> muons;
+  std::vector<cudaGraphExec_t> graphs;
+  cudaEvent_t events[64] = {};
+  GtDp* dp = nullptr;
+};
+
+gt_status gt_fail(gt_ctx* ctx, gt_status code, const char* fmt, ...);
+gt_status gt_check_cuda(gt_ctx* ctx, cudaError_t e, const char* what);
+// scratch of at least `bytes` (grows outside graph capture only)
+gt_status gt_scratch(gt_ctx* ctx, uint64_t bytes, float** out);
+
+#define GT_CUDA(ctx, call)                                              \
+  do {                                                                  \
+    cudaError_t _e = (call);                                            \
+    if (_e != cudaSuccess) return gt_check_cuda(ctx, _e, #call);        \
+  } while (0)
+#define GT_LAUNCHED(ctx, name)                                          \
+  do {                                                                  \
+    (ctx)->launches++;                                                  \
+    cudaError_t _e = cudaPeekAtLastError();                             \
+    if (_e != cudaSuccess) return gt_check_cuda(ctx, _e, name);         \
+  } while (0)
+#define GT_REQUIRE(ctx, cond, ...)                                      \
+  do {                                                                  \
+    if (!(cond)) return gt_fail(ctx, GT_ERR_ARG, __VA_ARGS__);          \
+  } while (0)
+
+template <typename T>
+static inline T* gt_ptr(gt_buf b) { return reinterpret_cast<T*>(static_cast<uintptr_t>(b)); }
+static inline int gt_cdiv(long a, long b) { return (int)((a + b - 1) / b); }
+
+// internal cross-file entry points
+gt_status gt_gemm_simt(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c);
+gt_status gt_gemm_tc(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c,
+                     bool* handled);
+void gt_optim_destroy(gt_ctx* ctx);
+void gt_dp_teardown(gt_ctx* ctx);

@@ -1,0 +1,124 @@
+// Strict-f32 matrix product: f32 loads, FFMA, f32 accumulate. This is the precision mode whose results
+// must stay within 1e-5 relative L2 of the reference's f64-accumulating loops (src/model/autograd.ts:348-377);
+// the tensor-core path lives in gemm_tc.cu. Covers the three operand layouts of WebGPUBackend.gemm
+// (src/backend/webgpu.ts:1654-1671) with ragged edges in every dimension.
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 16, TM = 8, TN = 8, PAD = 4;
+
+// Element (m,k) of A is a[m*sam + k*sak]; element (n,k) of B is b[n*sbn + k*sbk].
+template <bool A_KCONTIG, bool B_KCONTIG>
+__global__ void __launch_bounds__(256) gemm_f32_kernel(int M, int N, int K, const float* __restrict__ a, long sam, long sak,
+                                                       const float* __restrict__ b, long sbn, long sbk,
+                                                       float* __restrict__ c, int accum, int ksplit) {
+  __shared__ __align__(16) float As[BK][BM + PAD];
+  __shared__ __align__(16) float Bs[BK][BN + PAD];
+  const int tid = threadIdx.x;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int tx = tid % 16, ty = tid / 16;
+  // split-K: slice z covers k in [kb, ke)
+  const int kper = ((K + ksplit - 1) / ksplit + BK - 1) / BK * BK;
+  const int kb = blockIdx.z * kper;
+  const int ke = min(K, kb + kper);
+
+  float acc[TM][TN];
+#pragma unroll
+  for (int i = 0; i < TM; i++)
+#pragma unroll
+    for (int j = 0; j < TN; j++) acc[i][j] = 0.f;
+
+  for (int k0 = kb; k0 < ke; k0 += BK) {
+#pragma unroll
+    for (int i = 0; i < (BM * BK) / 256; i++) {
+      int idx = tid + i * 256;
+      int mm, kk;
+      if (A_KCONTIG) { kk = idx % BK; mm = idx / BK; } else { mm = idx % BM; kk = idx / BM; }
+      int gm = m0 + mm, gk = k0 + kk;
+      As[kk][mm] = (gm < M && gk < ke) ? a[(long)gm * sam + (long)gk * sak] : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < (BN * BK) / 256; i++) {
+      int idx = tid + i * 256;
+      int nn, kk;
+      if (B_KCONTIG) { kk = idx % BK; nn = idx / BK; } else { nn = idx % BN; kk = idx / BN; }
+      int gn = n0 + nn, gk = k0 + kk;
+      Bs[kk][nn] = (gn < N && gk < ke) ? b[(long)gn * sbn + (long)gk * sbk] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; kk++) {
+      float av[TM], bv[TN];
+      // two float4 per operand: rows ty*4..+3 and 64+ty*4..+3 (same for columns)
+      *(float4*)&av[0] = *(const float4*)&As[kk][ty * 4];
+      *(float4*)&av[4] = *(const float4*)&As[kk][64 + ty * 4];
+      *(float4*)&bv[0] = *(const float4*)&Bs[kk][tx * 4];
+      *(float4*)&bv[4] = *(const float4*)&Bs[kk][64 + tx * 4];
+#pragma unroll
+      for (int i = 0; i < TM; i++)
+#pragma unroll
+        for (int j = 0; j < TN; j++) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int i = 0; i < TM; i++) {
+    int gm = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + i - 4);
+    if (gm >= M) continue;
+#pragma unroll
+    for (int j = 0; j < TN; j++) {
+      int gn = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + j - 4);
+      if (gn >= N) continue;
+      float* dst = c + (long)gm * N + gn;
+      if (ksplit > 1) atomicAdd(dst, acc[i][j]);
+      else *dst = accum ? *dst + acc[i][j] : acc[i][j];
+    }
+  }
+}
+
+}  // namespace
+
+gt_status gt_gemm_simt(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c) {
+  dim3 grid(gt_cdiv(N, BN), gt_cdiv(M, BM), 1);
+  // Few output tiles and a deep K (the dW product, K = rows): split K across CTAs and reduce with
+  // f32 atomics into C. Order of the partial sums then varies run to run at the 1e-7 level.
+  int ksplit = 1;
+  long tiles = (long)grid.x * grid.y;
+  if (tiles < ctx->sm_count && K >= 1024) {
+    ksplit = (int)min((long)(2 * ctx->sm_count / tiles), (long)(K / 256));
+    if (ksplit < 1) ksplit = 1;
+  }
+  if (ksplit > 1 && !accum) {
+    cudaError_t e = cudaMemsetAsync(c, 0, sizeof(float) * (size_t)M * N, ctx->stream);
+    if (e != cudaSuccess) return gt_check_cuda(ctx, e, "gemm split-K clear");
+  }
+  grid.z = ksplit;
+  switch (kind) {
+    case GT_GEMM_NT:
+      gemm_f32_kernel<true, true><<<grid, 256, 0, ctx->stream>>>(M, N, K, a, K, 1, b, K, 1, c, accum, ksplit);
+      break;
+    case GT_GEMM_NN:
+      gemm_f32_kernel<true, false><<<grid, 256, 0, ctx->stream>>>(M, N, K, a, K, 1, b, 1, N, c, accum, ksplit);
+      break;
+    case GT_GEMM_TN:
+      gemm_f32_kernel<false, false><<<grid, 256, 0, ctx->stream>>>(M, N, K, a, 1, M, b, 1, N, c, accum, ksplit);
+      break;
+    default:
+      return gt_fail(ctx, GT_ERR_ARG, "gt_gemm: unknown kind %d", kind);
+  }
+  GT_LAUNCHED(ctx, "gemm_f32_kernel");
+  return GT_OK;
+}
+
+extern "C" gt_status gt_gemm(gt_ctx* ctx, int32_t kind, int32_t accum, int32_t M, int32_t N, int32_t K, gt_buf a, gt_buf b, gt_buf c) {
+  GT_REQUIRE(ctx, M > 0 && N > 0 && K > 0, "gt_gemm: empty product %dx%dx%d", M, N, K);
+  GT_REQUIRE(ctx, a && b && c, "gt_gemm: null operand");
+  if (ctx->precision != GT_PREC_FP32) {
+    bool handled = false;
+    gt_status s = gt_gemm_tc(ctx, kind, accum, M, N, K, gt_ptr<const float>(a), gt_ptr<const float>(b), gt_ptr<float>(c), &handled);
+    if (s != GT_OK || handled) return s;
+  }
+  return gt_gemm_simt(ctx, kind, accum, M, N, K, gt_ptr<const float>(a), gt_ptr<const float>(b), gt_ptr<float>(c));
+}

@@ -1,0 +1,148 @@
+// RMSNorm over the last dimension of a [rows, d] view, forward and backward
+// (src/model/autograd.ts:472-545; srcRmsNormFwd/BwdX/BwdW src/backend/wgsl.ts:217-303).
+// The per-head variant (rmsNormHeads) is the same kernels on the [T*H, hd] view with a shared w[hd].
+// HBM-bound. One warp owns a row: the row lives in registers between the reduction and the
+// write, so x is read once. Backward produces dx and the column sums for dw in the same pass
+// (the reference re-reads x and g once per column in srcRmsNormBwdW).
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// NPL = elements per lane (d <= 32*NPL)
+template <int NPL>
+__global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(int rows, int d, const float* __restrict__ x,
+                                                          const float* __restrict__ w, float eps,
+                                                          float* __restrict__ y, float* __restrict__ rinv) {
+  const int lane = threadIdx.x & 31;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  float wv[NPL];
+#pragma unroll
+  for (int i = 0; i < NPL; i++) { int j = lane + 32 * i; wv[i] = j < d ? w[j] : 0.f; }
+  for (int row = warp; row < rows; row += nwarps) {
+    const float* xr = x + (size_t)row * d;
+    float v[NPL];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NPL; i++) { int j = lane + 32 * i; v[i] = j < d ? xr[j] : 0.f; ss = fmaf(v[i], v[i], ss); }
+    ss = warp_sum(ss);
+    float r = 1.f / sqrtf(ss / (float)d + eps);
+    if (lane == 0) rinv[row] = r;
+    float* yr = y + (size_t)row * d;
+#pragma unroll
+    for (int i = 0; i < NPL; i++) { int j = lane + 32 * i; if (j < d) yr[j] = v[i] * r * wv[i]; }
+  }
+}
+
+template <int NPL>
+__global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(int rows, int d, const float* __restrict__ x,
+                                                          const float* __restrict__ w, const float* __restrict__ rinv,
+                                                          const float* __restrict__ g, float* gx, int accum_x,
+                                                          float* gw) {
+  extern __shared__ float sdw[];  // [d] block-level column partials
+  const int lane = threadIdx.x & 31;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  if (gw) {
+    for (int j = threadIdx.x; j < d; j += blockDim.x) sdw[j] = 0.f;
+    __syncthreads();
+  }
+  float wv[NPL], dwv[NPL];
+#pragma unroll
+  for (int i = 0; i < NPL; i++) { int j = lane + 32 * i; wv[i] = j < d ? w[j] : 0.f; dwv[i] = 0.f; }
+  const float invd = 1.f / (float)d;
+  for (int row = warp; row < rows; row += nwarps) {
+    const float* xr = x + (size_t)row * d;
+    const float* gr = g + (size_t)row * d;
+    float xv[NPL], gv[NPL];
+    float S = 0.f;
+#pragma unroll
+    for (int i = 0; i < NPL; i++) {
+      int j = lane + 32 * i;
+      xv[i] = j < d ? xr[j] : 0.f;
+      gv[i] = j < d ? gr[j] : 0.f;
+      S = fmaf(gv[i] * wv[i], xv[i], S);
+    }
+    S = warp_sum(S);
+    const float r = rinv[row];
+    const float k = r * r * r * S * invd;
+    if (gx) {
+      float* o = gx + (size_t)row * d;
+#pragma unroll
+      for (int i = 0; i < NPL; i++) {
+        int j = lane + 32 * i;
+        if (j < d) {
+          float v = wv[i] * r * gv[i] - xv[i] * k;
+          o[j] = accum_x ? o[j] + v : v;
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < NPL; i++) dwv[i] = fmaf(gv[i] * xv[i], r, dwv[i]);
+  }
+  if (gw) {
+#pragma unroll
+    for (int i = 0; i < NPL; i++) { int j = lane + 32 * i; if (j < d) atomicAdd(&sdw[j], dwv[i]); }
+    __syncthreads();
+    for (int j = threadIdx.x; j < d; j += blockDim.x) atomicAdd(&gw[j], sdw[j]);
+  }
+}
+
+template <int NPL>
+gt_status launch_fwd(gt_ctx* ctx, int rows, int d, const float* x, const float* w, float eps, float* y, float* rinv) {
+  int blocks = min(gt_cdiv(rows, 8), ctx->sm_count * 8);
+  rmsnorm_fwd_kernel<NPL><<<blocks, 256, 0, ctx->stream>>>(rows, d, x, w, eps, y, rinv);
+  GT_LAUNCHED(ctx, "rmsnorm_fwd_kernel");
+  return GT_OK;
+}
+template <int NPL>
+gt_status launch_bwd(gt_ctx* ctx, int rows, int d, const float* x, const float* w, const float* rinv, const float* g,
+                     float* gx, int accum_x, float* gw) {
+  // fewer, fatter blocks when dw is wanted: each block ends with d global atomics
+  int blocks = min(gt_cdiv(rows, 8), ctx->sm_count * (gw ? 4 : 8));
+  rmsnorm_bwd_kernel<NPL><<<blocks, 256, sizeof(float) * d, ctx->stream>>>(rows, d, x, w, rinv, g, gx, accum_x, gw);
+  GT_LAUNCHED(ctx, "rmsnorm_bwd_kernel");
+  return GT_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+gt_status gt_rmsnorm_fwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf x, gt_buf w, float eps, gt_buf y, gt_buf rinv) {
+  GT_REQUIRE(ctx, rows > 0 && d > 0 && d <= 2048, "gt_rmsnorm_fwd: rows %d d %d (d must be in 1..2048)", rows, d);
+  GT_REQUIRE(ctx, x && w && y && rinv, "gt_rmsnorm_fwd: null operand");
+  const float* px = gt_ptr<const float>(x); const float* pw = gt_ptr<const float>(w);
+  float* py = gt_ptr<float>(y); float* pr = gt_ptr<float>(rinv);
+  if (d <= 64) return launch_fwd<2>(ctx, rows, d, px, pw, eps, py, pr);
+  if (d <= 128) return launch_fwd<4>(ctx, rows, d, px, pw, eps, py, pr);
+  if (d <= 256) return launch_fwd<8>(ctx, rows, d, px, pw, eps, py, pr);
+  if (d <= 640) return launch_fwd<20>(ctx, rows, d, px, pw, eps, py, pr);
+  if (d <= 1024) return launch_fwd<32>(ctx, rows, d, px, pw, eps, py, pr);
+  return launch_fwd<64>(ctx, rows, d, px, pw, eps, py, pr);
+}
+
+gt_status gt_rmsnorm_bwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf x, gt_buf w, gt_buf rinv, gt_buf gy, gt_buf gx,
+                         int32_t accum_x, gt_buf gw, int32_t accum_w) {
+  GT_REQUIRE(ctx, rows > 0 && d > 0 && d <= 2048, "gt_rmsnorm_bwd: rows %d d %d (d must be in 1..2048)", rows, d);
+  GT_REQUIRE(ctx, x && w && rinv && gy, "gt_rmsnorm_bwd: null operand");
+  if (!gx && !gw) return GT_OK;
+  const float* px = gt_ptr<const float>(x); const float* pw = gt_ptr<const float>(w);
+  const float* pr = gt_ptr<const float>(rinv); const float* pg = gt_ptr<const float>(gy);
+  float* pgx = gt_ptr<float>(gx); float* pgw = gt_ptr<float>(gw);
+  if (pgw && !accum_w) GT_CUDA(ctx, cudaMemsetAsync(pgw, 0, sizeof(float) * d, ctx->stream));
+  if (d <= 64) return launch_bwd<2>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw);
+  if (d <= 128) return launch_bwd<4>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw);
+  if (d <= 256) return launch_bwd<8>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw);
+  if (d <= 640) return launch_bwd<20>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw);
+  if (d <= 1024) return launch_bwd<32>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw);
+  return launch_bwd<64>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw);
+}
+
+}  // extern "C"

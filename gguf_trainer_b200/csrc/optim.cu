@@ -1,0 +1,439 @@
+// Device-resident optimizers: AdamW with global-norm clipping and Muon with quintic Newton-Schulz
+// (src/train/adam.ts:46-82, src/train/muon.ts:69-158; GPU forms src/backend/adamw-gpu.ts:32-129 and
+// src/backend/muon-gpu.ts:51-252). AdamW is HBM-bound at 28 B/parameter (read g, m, v, w; write m, v, w):
+// one multi-tensor launch covers the whole group through a chunk table, 128-bit accesses. The
+// Newton-Schulz products go through the same matrix-product path as the model's linears.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int CHUNK = 32768;  // elements per CTA
+constexpr int OT = 256;
+
+struct Chunk { int tensor; uint32_t start; uint32_t count; };
+
+__device__ __forceinline__ float block_sum(float v, float* sh) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = 0.f;
+  if (threadIdx.x < 32) {
+    r = threadIdx.x < (blockDim.x >> 5) ? sh[threadIdx.x] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+  }
+  return r;  // valid in thread 0
+}
+
+__global__ void __launch_bounds__(OT) sumsq_partial_kernel(const Chunk* __restrict__ chunks, float* const* __restrict__ grads,
+                                                           float* __restrict__ partials) {
+  __shared__ float sh[OT / 32];
+  const Chunk c = chunks[blockIdx.x];
+  const float* g = grads[c.tensor] + c.start;
+  float s = 0.f;
+  const uint32_t n4 = ((((uintptr_t)g) & 15) == 0) ? c.count / 4 : 0;
+  for (uint32_t i = threadIdx.x; i < n4; i += OT) {
+    float4 x = ((const float4*)g)[i];
+    s = fmaf(x.x, x.x, s); s = fmaf(x.y, x.y, s); s = fmaf(x.z, x.z, s); s = fmaf(x.w, x.w, s);
+  }
+  for (uint32_t i = n4 * 4 + threadIdx.x; i < c.count; i += OT) s = fmaf(g[i], g[i], s);
+  s = block_sum(s, sh);
+  if (threadIdx.x == 0) partials[blockIdx.x] = s;
+}
+
+// same reduction over one plain array; CTA b covers elements [b*CHUNK, (b+1)*CHUNK)
+__global__ void __launch_bounds__(OT) sumsq_direct_kernel(const float* __restrict__ g, size_t n, float* __restrict__ partials) {
+  __shared__ float sh[OT / 32];
+  size_t start = (size_t)blockIdx.x * CHUNK;
+  size_t end = start + CHUNK < n ? start + CHUNK : n;
+  float s = 0.f;
+  for (size_t i = start + threadIdx.x; i < end; i += OT) s = fmaf(g[i], g[i], s);
+  s = block_sum(s, sh);
+  if (threadIdx.x == 0) partials[blockIdx.x] = s;
+}
+
+// mode 0: out[0] = clip scale (norm > clip ? clip/(norm+1e-12) : 1)   (adam.ts:51-62)
+// mode 1: out[0] = 1/(sqrt(sum)+1e-7)                                  (muon.ts:140-141)
+__global__ void __launch_bounds__(1024) sumsq_final_kernel(int n, const float* __restrict__ partials, int mode, float clip,
+                                                           float* __restrict__ out) {
+  __shared__ double sh[32];
+  double s = 0.0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) s += (double)partials[i];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    for (int i = 0; i < (int)(blockDim.x >> 5); i++) t += sh[i];
+    double norm = sqrt(t);
+    if (mode == 0) out[0] = norm > (double)clip ? (float)((double)clip / (norm + 1e-12)) : 1.f;
+    else out[0] = (float)(1.0 / (norm + 1e-7));
+  }
+}
+
+__global__ void __launch_bounds__(OT) adamw_kernel(const Chunk* __restrict__ chunks, float* const* __restrict__ datas,
+                                                   float* const* __restrict__ grads, float* const* __restrict__ ms,
+                                                   float* const* __restrict__ vs, const float* __restrict__ scale_p, float lr,
+                                                   float bc1, float bc2, float b1, float b2, float eps, float wd) {
+  const Chunk c = chunks[blockIdx.x];
+  float* w = datas[c.tensor] + c.start;
+  const float* g = grads[c.tensor] + c.start;
+  float* m = ms[c.tensor] + c.start;
+  float* v = vs[c.tensor] + c.start;
+  const float scale = scale_p ? scale_p[0] : 1.f;
+  const float ib1 = 1.f / bc1, ib2 = 1.f / bc2;
+  auto upd = [&](float gi, float& mi, float& vi, float& wi) {
+    float gg = gi * scale;
+    mi = b1 * mi + (1.f - b1) * gg;
+    vi = b2 * vi + (1.f - b2) * gg * gg;
+    float u = (mi * ib1) / (sqrtf(vi * ib2) + eps);
+    if (wd > 0.f) u += wd * wi;
+    wi -= lr * u;
+  };
+  const bool al = (((uintptr_t)w | (uintptr_t)g | (uintptr_t)m | (uintptr_t)v) & 15) == 0;
+  const uint32_t n4 = al ? c.count / 4 : 0;
+  for (uint32_t i = threadIdx.x; i < n4; i += OT) {
+    float4 G = ((const float4*)g)[i], M = ((float4*)m)[i], V = ((float4*)v)[i], W = ((float4*)w)[i];
+    upd(G.x, M.x, V.x, W.x); upd(G.y, M.y, V.y, W.y); upd(G.z, M.z, V.z, W.z); upd(G.w, M.w, V.w, W.w);
+    ((float4*)m)[i] = M; ((float4*)v)[i] = V; ((float4*)w)[i] = W;
+  }
+  for (uint32_t i = n4 * 4 + threadIdx.x; i < c.count; i += OT) {
+    float M = m[i], V = v[i], W = w[i];
+    upd(g[i], M, V, W);
+    m[i] = M; v[i] = V; w[i] = W;
+  }
+}
+
+// ---- Muon elementwise pieces ----
+// buf = mu*buf + g ; U = nesterov ? g + mu*buf : buf     (muon.ts:78-85, srcMomentum muon-gpu.ts:51-64)
+__global__ void muon_momentum_kernel(size_t n, const float* __restrict__ g, float* __restrict__ buf, float* __restrict__ U,
+                                     float mu, int nesterov) {
+  size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    float b = mu * buf[i] + g[i];
+    buf[i] = b;
+    U[i] = nesterov ? g[i] + mu * b : b;
+  }
+}
+// X[r,c] = (flip ? U^T : U) * inv[0], U is [m,n]   (srcNormalize muon-gpu.ts:100-135)
+__global__ void muon_normalize_kernel(int m, int n, int flip, const float* __restrict__ U, const float* __restrict__ inv,
+                                      float* __restrict__ X) {
+  size_t total = (size_t)m * n, stride = (size_t)gridDim.x * blockDim.x;
+  const float s = inv[0];
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    if (!flip) { X[i] = U[i] * s; }
+    else { size_t a = i / m, b = i % m; X[i] = U[b * n + a] * s; }  // X is [n, m]: X[a][b] = U[b][a]
+  }
+}
+// out = ca*a + cb*b
+__global__ void axpby_kernel(size_t n, float ca, const float* __restrict__ a, float cb, const float* __restrict__ b, float* out) {
+  size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) out[i] = ca * a[i] + cb * b[i];
+}
+// W[m,n] -= lr*scale * (flip ? X^T : X)    (srcApply muon-gpu.ts:173-190)
+__global__ void muon_apply_kernel(int m, int n, int flip, float f, const float* __restrict__ X, float* __restrict__ W) {
+  size_t total = (size_t)m * n, stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    float o;
+    if (!flip) o = X[i];
+    else { size_t a = i / n, b = i % n; o = X[b * m + a]; }  // W[a][b] uses X[b][a], X is [n, m]
+    W[i] -= f * o;
+  }
+}
+
+inline int egrid(gt_ctx* ctx, size_t n) {
+  size_t want = (n + 255) / 256, cap = (size_t)ctx->sm_count * 8;
+  return (int)(want < 1 ? 1 : (want > cap ? cap : want));
+}
+
+}  // namespace
+
+struct GtAdamW {
+  int n = 0;
+  std::vector<float*> data, grad, m, v;
+  std::vector<uint64_t> sizes;
+  float lr, b1, b2, eps, wd, clip;
+  int t = 0;
+  int nchunks = 0;
+  Chunk* d_chunks = nullptr;
+  float** d_ptrs = nullptr;  // [4][n]: data, grad, m, v
+  float* d_partials = nullptr;
+  float* d_scale = nullptr;
+};
+
+struct GtMuon {
+  int n = 0;
+  std::vector<float*> data, grad, buf;
+  std::vector<int> rows, cols;
+  float lr, mu;
+  int nesterov, ns;
+  // workspaces sized for the largest matrix
+  float *U = nullptr, *X = nullptr, *BX = nullptr, *A = nullptr, *AA = nullptr, *partials = nullptr, *inv = nullptr;
+  size_t maxel = 0;
+  int maxr = 0;
+};
+
+static gt_status dev_alloc(gt_ctx* ctx, void** p, size_t bytes, bool zero) {
+  GT_CUDA(ctx, cudaMalloc(p, bytes < 256 ? 256 : bytes));
+  if (zero) GT_CUDA(ctx, cudaMemsetAsync(*p, 0, bytes, ctx->stream));
+  ctx->state_bytes += bytes;
+  return GT_OK;
+}
+
+// Newton-Schulz on X [r,c] in place using A, AA [r,r] and BX [r,c]  (muon.ts:143-155, muon-gpu.ts:224-252)
+static gt_status ns_iterations(gt_ctx* ctx, int r, int c, int steps, float* X, float* A, float* AA, float* BX) {
+  for (int s = 0; s < steps; s++) {
+    gt_status st = gt_gemm(ctx, GT_GEMM_NT, 0, r, r, c, (gt_buf)(uintptr_t)X, (gt_buf)(uintptr_t)X, (gt_buf)(uintptr_t)A);
+    if (st) return st;
+    st = gt_gemm(ctx, GT_GEMM_NN, 0, r, r, r, (gt_buf)(uintptr_t)A, (gt_buf)(uintptr_t)A, (gt_buf)(uintptr_t)AA);
+    if (st) return st;
+    axpby_kernel<<<egrid(ctx, (size_t)r * r), 256, 0, ctx->stream>>>((size_t)r * r, -4.7750f, A, 2.0315f, AA, AA);
+    GT_LAUNCHED(ctx, "axpby_kernel");
+    st = gt_gemm(ctx, GT_GEMM_NN, 0, r, c, r, (gt_buf)(uintptr_t)AA, (gt_buf)(uintptr_t)X, (gt_buf)(uintptr_t)BX);
+    if (st) return st;
+    axpby_kernel<<<egrid(ctx, (size_t)r * c), 256, 0, ctx->stream>>>((size_t)r * c, 3.4445f, X, 1.f, BX, X);
+    GT_LAUNCHED(ctx, "axpby_kernel");
+  }
+  return GT_OK;
+}
+
+// inv[0] = 1/(||U||_F + 1e-7) for one array of n elements, using `partials` (>= ceil(n/CHUNK) floats)
+static gt_status frob_inv(gt_ctx* ctx, const float* U, size_t n, float* partials, float* inv) {
+  int nch = gt_cdiv((long)n, CHUNK);
+  sumsq_direct_kernel<<<nch, OT, 0, ctx->stream>>>(U, n, partials);
+  GT_LAUNCHED(ctx, "sumsq_direct_kernel");
+  sumsq_final_kernel<<<1, 1024, 0, ctx->stream>>>(nch, partials, 1, 0.f, inv);
+  GT_LAUNCHED(ctx, "sumsq_final_kernel");
+  return GT_OK;
+}
+
+void gt_optim_destroy(gt_ctx* ctx) {
+  for (GtAdamW* a : ctx->adamws) {
+    if (!a) continue;
+    for (float* p : a->m) cudaFree(p);
+    for (float* p : a->v) cudaFree(p);
+    cudaFree(a->d_chunks); cudaFree(a->d_ptrs); cudaFree(a->d_partials); cudaFree(a->d_scale);
+    delete a;
+  }
+  ctx->adamws.clear();
+  for (GtMuon* m : ctx->muons) {
+    if (!m) continue;
+    for (float* p : m->buf) cudaFree(p);
+    cudaFree(m->U); cudaFree(m->X); cudaFree(m->BX); cudaFree(m->A); cudaFree(m->AA); cudaFree(m->partials); cudaFree(m->inv);
+    delete m;
+  }
+  ctx->muons.clear();
+}
+
+extern "C" {
+
+gt_status gt_adamw_create(gt_ctx* ctx, int32_t n, const gt_buf* data, const gt_buf* grad, const uint64_t* sizes, float lr,
+                          float beta1, float beta2, float eps, float weight_decay, float clip, uint64_t* out_handle) {
+  GT_REQUIRE(ctx, n >= 0 && out_handle, "gt_adamw_create: bad argument");
+  if (ctx->capturing) return gt_fail(ctx, GT_ERR_STATE, "gt_adamw_create inside a graph capture");
+  GtAdamW* a = new GtAdamW();
+  a->n = n; a->lr = lr; a->b1 = beta1; a->b2 = beta2; a->eps = eps; a->wd = weight_decay; a->clip = clip;
+  std::vector<Chunk> chunks;
+  for (int i = 0; i < n; i++) {
+    if (!data[i] || !grad[i] || sizes[i] == 0 || sizes[i] > 0xffffffffull) {
+      delete a;
+      return gt_fail(ctx, GT_ERR_ARG, "gt_adamw_create: tensor %d has a null buffer or an unsupported size", i);
+    }
+    a->data.push_back(gt_ptr<float>(data[i]));
+    a->grad.push_back(gt_ptr<float>(grad[i]));
+    a->sizes.push_back(sizes[i]);
+    float *m = nullptr, *v = nullptr;
+    gt_status s = dev_alloc(ctx, (void**)&m, sizeof(float) * sizes[i], true);
+    if (!s) s = dev_alloc(ctx, (void**)&v, sizeof(float) * sizes[i], true);
+    if (s) { delete a; return s; }
+    a->m.push_back(m); a->v.push_back(v);
+    for (uint64_t st = 0; st < sizes[i]; st += CHUNK)
+      chunks.push_back(Chunk{i, (uint32_t)st, (uint32_t)(st + CHUNK <= sizes[i] ? CHUNK : sizes[i] - st)});
+  }
+  a->nchunks = (int)chunks.size();
+  if (n > 0) {
+    gt_status s = dev_alloc(ctx, (void**)&a->d_chunks, sizeof(Chunk) * chunks.size(), false);
+    if (!s) s = dev_alloc(ctx, (void**)&a->d_ptrs, sizeof(float*) * 4 * n, false);
+    if (!s) s = dev_alloc(ctx, (void**)&a->d_partials, sizeof(float) * chunks.size(), false);
+    if (!s) s = dev_alloc(ctx, (void**)&a->d_scale, 256, true);
+    if (s) { delete a; return s; }
+    std::vector<float*> ptrs;
+    ptrs.insert(ptrs.end(), a->data.begin(), a->data.end());
+    ptrs.insert(ptrs.end(), a->grad.begin(), a->grad.end());
+    ptrs.insert(ptrs.end(), a->m.begin(), a->m.end());
+    ptrs.insert(ptrs.end(), a->v.begin(), a->v.end());
+    GT_CUDA(ctx, cudaMemcpyAsync(a->d_chunks, chunks.data(), sizeof(Chunk) * chunks.size(), cudaMemcpyHostToDevice, ctx->stream));
+    GT_CUDA(ctx, cudaMemcpyAsync(a->d_ptrs, ptrs.data(), sizeof(float*) * ptrs.size(), cudaMemcpyHostToDevice, ctx->stream));
+    GT_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  }
+  ctx->adamws.push_back(a);
+  *out_handle = ctx->adamws.size();
+  return GT_OK;
+}
+
+static GtAdamW* adamw_of(gt_ctx* ctx, uint64_t h) {
+  if (h < 1 || h > ctx->adamws.size()) return nullptr;
+  return ctx->adamws[h - 1];
+}
+
+gt_status gt_adamw_set_lr(gt_ctx* ctx, uint64_t h, float lr) {
+  GtAdamW* a = adamw_of(ctx, h);
+  GT_REQUIRE(ctx, a, "gt_adamw_set_lr: bad handle");
+  a->lr = lr;
+  return GT_OK;
+}
+
+gt_status gt_adamw_step(gt_ctx* ctx, uint64_t h) {
+  GtAdamW* a = adamw_of(ctx, h);
+  GT_REQUIRE(ctx, a, "gt_adamw_step: bad handle");
+  a->t += 1;
+  if (a->n == 0) return GT_OK;
+  float** P = a->d_ptrs;
+  const float* scale = nullptr;
+  if (a->clip > 0.f) {
+    sumsq_partial_kernel<<<a->nchunks, OT, 0, ctx->stream>>>(a->d_chunks, P + a->n, a->d_partials);
+    GT_LAUNCHED(ctx, "sumsq_partial_kernel");
+    sumsq_final_kernel<<<1, 1024, 0, ctx->stream>>>(a->nchunks, a->d_partials, 0, a->clip, a->d_scale);
+    GT_LAUNCHED(ctx, "sumsq_final_kernel");
+    scale = a->d_scale;
+  }
+  float bc1 = (float)(1.0 - pow((double)a->b1, (double)a->t));
+  float bc2 = (float)(1.0 - pow((double)a->b2, (double)a->t));
+  adamw_kernel<<<a->nchunks, OT, 0, ctx->stream>>>(a->d_chunks, P, P + a->n, P + 2 * a->n, P + 3 * a->n, scale, a->lr, bc1, bc2,
+                                                   a->b1, a->b2, a->eps, a->wd);
+  GT_LAUNCHED(ctx, "adamw_kernel");
+  return GT_OK;
+}
+
+gt_status gt_adamw_state(gt_ctx* ctx, uint64_t h, int32_t i, gt_buf* m, gt_buf* v) {
+  GtAdamW* a = adamw_of(ctx, h);
+  GT_REQUIRE(ctx, a && i >= 0 && i < a->n, "gt_adamw_state: bad handle or index");
+  *m = (gt_buf)(uintptr_t)a->m[i];
+  *v = (gt_buf)(uintptr_t)a->v[i];
+  return GT_OK;
+}
+gt_status gt_adamw_get_t(gt_ctx* ctx, uint64_t h, int32_t* t) {
+  GtAdamW* a = adamw_of(ctx, h);
+  GT_REQUIRE(ctx, a, "gt_adamw_get_t: bad handle");
+  *t = a->t;
+  return GT_OK;
+}
+gt_status gt_adamw_set_t(gt_ctx* ctx, uint64_t h, int32_t t) {
+  GtAdamW* a = adamw_of(ctx, h);
+  GT_REQUIRE(ctx, a && t >= 0, "gt_adamw_set_t: bad handle or step");
+  a->t = t;
+  return GT_OK;
+}
+
+gt_status gt_muon_create(gt_ctx* ctx, int32_t n, const gt_buf* data, const gt_buf* grad, const int32_t* rows, const int32_t* cols,
+                         float lr, float momentum, int32_t nesterov, int32_t ns_steps, uint64_t* out_handle) {
+  GT_REQUIRE(ctx, n >= 0 && out_handle && ns_steps >= 0, "gt_muon_create: bad argument");
+  if (ctx->capturing) return gt_fail(ctx, GT_ERR_STATE, "gt_muon_create inside a graph capture");
+  GtMuon* m = new GtMuon();
+  m->n = n; m->lr = lr; m->mu = momentum; m->nesterov = nesterov; m->ns = ns_steps;
+  for (int i = 0; i < n; i++) {
+    if (!data[i] || !grad[i] || rows[i] <= 0 || cols[i] <= 0) { delete m; return gt_fail(ctx, GT_ERR_ARG, "gt_muon_create: matrix %d is malformed", i); }
+    m->data.push_back(gt_ptr<float>(data[i]));
+    m->grad.push_back(gt_ptr<float>(grad[i]));
+    m->rows.push_back(rows[i]); m->cols.push_back(cols[i]);
+    size_t el = (size_t)rows[i] * cols[i];
+    float* b = nullptr;
+    gt_status s = dev_alloc(ctx, (void**)&b, sizeof(float) * el, true);
+    if (s) { delete m; return s; }
+    m->buf.push_back(b);
+    if (el > m->maxel) m->maxel = el;
+    int r = rows[i] < cols[i] ? rows[i] : cols[i];
+    if (r > m->maxr) m->maxr = r;
+  }
+  if (n > 0) {
+    size_t e = sizeof(float) * m->maxel, rr = sizeof(float) * (size_t)m->maxr * m->maxr;
+    gt_status s = dev_alloc(ctx, (void**)&m->U, e, false);
+    if (!s) s = dev_alloc(ctx, (void**)&m->X, e, false);
+    if (!s) s = dev_alloc(ctx, (void**)&m->BX, e, false);
+    if (!s) s = dev_alloc(ctx, (void**)&m->A, rr, false);
+    if (!s) s = dev_alloc(ctx, (void**)&m->AA, rr, false);
+    if (!s) s = dev_alloc(ctx, (void**)&m->partials, sizeof(float) * (m->maxel / CHUNK + 2), false);
+    if (!s) s = dev_alloc(ctx, (void**)&m->inv, 256, true);
+    if (s) { delete m; return s; }
+  }
+  ctx->muons.push_back(m);
+  *out_handle = ctx->muons.size();
+  return GT_OK;
+}
+
+static GtMuon* muon_of(gt_ctx* ctx, uint64_t h) {
+  if (h < 1 || h > ctx->muons.size()) return nullptr;
+  return ctx->muons[h - 1];
+}
+
+gt_status gt_muon_set_lr(gt_ctx* ctx, uint64_t h, float lr) {
+  GtMuon* m = muon_of(ctx, h);
+  GT_REQUIRE(ctx, m, "gt_muon_set_lr: bad handle");
+  m->lr = lr;
+  return GT_OK;
+}
+
+gt_status gt_muon_step(gt_ctx* ctx, uint64_t h) {
+  GtMuon* m = muon_of(ctx, h);
+  GT_REQUIRE(ctx, m, "gt_muon_step: bad handle");
+  for (int i = 0; i < m->n; i++) {
+    const int rows = m->rows[i], cols = m->cols[i];
+    const size_t el = (size_t)rows * cols;
+    const int flip = rows > cols;
+    const int r = flip ? cols : rows, c = flip ? rows : cols;
+    muon_momentum_kernel<<<egrid(ctx, el), 256, 0, ctx->stream>>>(el, m->grad[i], m->buf[i], m->U, m->mu, m->nesterov);
+    GT_LAUNCHED(ctx, "muon_momentum_kernel");
+    gt_status s = frob_inv(ctx, m->U, el, m->partials, m->inv);
+    if (s) return s;
+    muon_normalize_kernel<<<egrid(ctx, el), 256, 0, ctx->stream>>>(rows, cols, flip, m->U, m->inv, m->X);
+    GT_LAUNCHED(ctx, "muon_normalize_kernel");
+    s = ns_iterations(ctx, r, c, m->ns, m->X, m->A, m->AA, m->BX);
+    if (s) return s;
+    float f = m->lr * sqrtf(fmaxf(1.f, (float)rows / (float)cols));
+    muon_apply_kernel<<<egrid(ctx, el), 256, 0, ctx->stream>>>(rows, cols, flip, f, m->X, m->data[i]);
+    GT_LAUNCHED(ctx, "muon_apply_kernel");
+  }
+  return GT_OK;
+}
+
+gt_status gt_muon_state(gt_ctx* ctx, uint64_t h, int32_t i, gt_buf* momentum) {
+  GtMuon* m = muon_of(ctx, h);
+  GT_REQUIRE(ctx, m && i >= 0 && i < m->n, "gt_muon_state: bad handle or index");
+  *momentum = (gt_buf)(uintptr_t)m->buf[i];
+  return GT_OK;
+}
+
+gt_status gt_newton_schulz(gt_ctx* ctx, int32_t mm, int32_t nn, int32_t steps, gt_buf g, gt_buf out) {
+  GT_REQUIRE(ctx, mm > 0 && nn > 0 && steps >= 0 && g && out, "gt_newton_schulz: bad argument");
+  if (ctx->capturing) return gt_fail(ctx, GT_ERR_STATE, "gt_newton_schulz inside a graph capture");
+  const size_t el = (size_t)mm * nn;
+  const int flip = mm > nn;
+  const int r = flip ? nn : mm, c = flip ? mm : nn;
+  float *X, *BX, *A, *AA, *partials, *inv;
+  GT_CUDA(ctx, cudaMalloc(&X, sizeof(float) * el)); GT_CUDA(ctx, cudaMalloc(&BX, sizeof(float) * el));
+  GT_CUDA(ctx, cudaMalloc(&A, sizeof(float) * r * r)); GT_CUDA(ctx, cudaMalloc(&AA, sizeof(float) * r * r));
+  GT_CUDA(ctx, cudaMalloc(&partials, sizeof(float) * (el / CHUNK + 2))); GT_CUDA(ctx, cudaMalloc(&inv, 256));
+  gt_status s = frob_inv(ctx, gt_ptr<const float>(g), el, partials, inv);
+  if (!s) {
+    muon_normalize_kernel<<<egrid(ctx, el), 256, 0, ctx->stream>>>(mm, nn, flip, gt_ptr<const float>(g), inv, X);
+    ctx->launches++;
+    s = ns_iterations(ctx, r, c, steps, X, A, AA, BX);
+  }
+  if (!s) {
+    // out = 0 - (-1) * (flip ? X^T : X): the apply kernel with factor -1 into a zeroed tensor (muon-gpu.ts:270-279)
+    cudaMemsetAsync(gt_ptr<float>(out), 0, sizeof(float) * el, ctx->stream);
+    muon_apply_kernel<<<egrid(ctx, el), 256, 0, ctx->stream>>>(mm, nn, flip, -1.f, X, gt_ptr<float>(out));
+    ctx->launches++;
+  }
+  cudaStreamSynchronize(ctx->stream);
+  cudaFree(X); cudaFree(BX); cudaFree(A); cudaFree(AA); cudaFree(partials); cudaFree(inv);
+  if (s) return s;
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? GT_OK : gt_check_cuda(ctx, e, "gt_newton_schulz");
+}
+
+}  // extern "C"

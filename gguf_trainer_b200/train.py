@@ -1,0 +1,197 @@
+"""Step loops. `trainLMGpuResident` mirrors src/backend/train-gpu.ts:162-258 call for call (rng order,
+masks, two syncs per step, checkpoint cadence). `trainLMCuda` is its batched twin for this backend:
+the B sequences of a step travel as one [B*T]-row call, the forward+backward is captured once as a
+CUDA graph and replayed, and with several ranks the gradients are summed over NCCL before the
+optimizer step. Both consume the rng in the same order, so a given seed draws the same windows.
+"""
+from __future__ import annotations
+
+import math
+import time
+from typing import Callable, Dict, List, Optional, Sequence
+
+import numpy as np
+
+from . import autograd as ag
+from .autograd import Tensor, backward, crossEntropy, fusedCrossEntropy
+from .backend import CudaBackend
+from .qk_clip import applyQKClip
+
+
+def sequenceLoss(model, inputIds, targetIds, lossChunk: int = 0) -> Tensor:
+    """src/train/loss.ts:104-115."""
+    if lossChunk > 0 and hasattr(model, "forwardToReadout"):
+        r = model.forwardToReadout(inputIds)
+        return fusedCrossEntropy(r["hidden"], r["readout"], targetIds, lossChunk)
+    return crossEntropy(model.forward(inputIds), targetIds)
+
+
+def maskWindow(targetIds: np.ndarray, supervised: np.ndarray, start: int) -> np.ndarray:
+    """src/train/trainer.ts:45-49: in place, target -> -1 where the supervision mask is 0."""
+    m = supervised[start:start + len(targetIds)]
+    targetIds[m == 0] = -1
+    return targetIds
+
+
+def trainLMGpuResident(model, gpu: CudaBackend, tokens: np.ndarray, seqLen: int, steps: int, batchPerStep: int,
+                       optimizer, logEvery: int = 20, rng: Optional[Callable[[], float]] = None,
+                       onLog=None, schedule=None, qkClipTau: float = 0.0, onStepTime=None,
+                       supervised: Optional[np.ndarray] = None, checkpointEvery: int = 0,
+                       checkpointEveryMs: float = 0.0, onCheckpoint=None, reclaimTransients: bool = False,
+                       lossChunk: int = 0):
+    """src/backend/train-gpu.ts:162-258."""
+    import random
+    rng = rng or random.random
+    tokens = np.asarray(tokens)
+    maxStart = len(tokens) - seqLen - 1
+    if maxStart <= 0:
+        raise ValueError("Not enough tokens for one training window")
+    history = []
+    lastCheckpointAt = time.perf_counter()
+    normTensors: List[Tensor] = []
+    if qkClipTau:
+        qk = model.qkNorms() if hasattr(model, "qkNorms") else None
+        for L in (qk["pairs"] if qk else []):
+            normTensors.extend([L["qNorm"], L["kNorm"]])
+    gpu.install()
+    try:
+        for step in range(steps):
+            t0 = time.perf_counter()
+            if schedule:
+                optimizer.setLrScale(schedule(step))
+            optimizer.zeroGrad()
+            losses: List[Tensor] = []
+            for b in range(batchPerStep):
+                start = math.floor(rng() * maxStart)
+                inputIds = tokens[start:start + seqLen].astype(np.int64)
+                targetIds = tokens[start + 1:start + 1 + seqLen].astype(np.int64)
+                if supervised is not None:
+                    maskWindow(targetIds, supervised, start + 1)
+                loss = sequenceLoss(model, inputIds, targetIds, lossChunk)
+                backward(loss, 1 / batchPerStep)
+                losses.append(loss)
+                if reclaimTransients and b < batchPerStep - 1:
+                    gpu.reclaimStepTransients(losses)
+            gpu.sync(losses)
+            readback = gpu.lastSyncReadbackBytes
+            t1 = time.perf_counter()
+            optimizer.recordStep()
+            gpu.sync(normTensors)
+            if qkClipTau:
+                applyQKClip(model, qkClipTau)
+                gpu.uploadParams(normTensors)
+            if onStepTime:
+                onStepTime((t1 - t0) * 1e3, (time.perf_counter() - t1) * 1e3, readback)
+            avg = float(sum(float(l.data[0]) for l in losses) / batchPerStep)
+            if step % logEvery == 0 or step == steps - 1:
+                history.append({"step": step, "loss": avg})
+                if onLog:
+                    onLog(step, avg)
+            dueByStep = bool(checkpointEvery) and step % checkpointEvery == 0
+            dueByTime = bool(checkpointEveryMs) and (time.perf_counter() - lastCheckpointAt) * 1e3 >= checkpointEveryMs
+            if onCheckpoint and step > 0 and (dueByStep or dueByTime):
+                optimizer.syncWeightsToHost()
+                onCheckpoint(step)
+                lastCheckpointAt = time.perf_counter()
+    finally:
+        gpu.uninstall()
+    optimizer.syncWeightsToHost()
+    return history
+
+
+class DataParallel:
+    """One process per GPU. Rank r runs micro-batches [r*B, (r+1)*B) of each step's global draw order;
+    the only exchange is an f32 sum of the gradient arena over NCCL, in buckets, on a side stream."""
+
+    def __init__(self, gpu: CudaBackend, rank: int, world: int, unique_id: bytes):
+        import ctypes as C
+        self.gpu, self.rank, self.world = gpu, rank, world
+        buf = (C.c_uint8 * 128).from_buffer_copy(unique_id)
+        gpu._check(gpu.lib.gt_dp_init(gpu.ctx, rank, world, buf))
+
+    @staticmethod
+    def uniqueId() -> bytes:
+        import ctypes as C
+        from . import _lib
+        lib = _lib.load()
+        buf = (C.c_uint8 * 128)()
+        st = lib.gt_dp_unique_id(buf)
+        if st != 0:
+            raise _lib.GtError(st, lib.gt_last_error(None).decode())
+        return bytes(buf)
+
+    def allreduce(self, addr: int, count: int, bucketElems: int = 8 << 20):
+        """Sum `count` f32 at `addr` across ranks in buckets, then make the compute stream wait."""
+        off = 0
+        while off < count:
+            n = min(bucketElems, count - off)
+            self.gpu._check(self.gpu.lib.gt_dp_allreduce_start(self.gpu.ctx, addr + off * 4, n))
+            off += n
+        self.gpu._check(self.gpu.lib.gt_dp_wait(self.gpu.ctx))
+
+    def start(self, addr: int, count: int):
+        self.gpu._check(self.gpu.lib.gt_dp_allreduce_start(self.gpu.ctx, addr, count))
+
+    def wait(self):
+        self.gpu._check(self.gpu.lib.gt_dp_wait(self.gpu.ctx))
+
+
+def drawWindows(rng, n: int, maxStart: int) -> List[int]:
+    """`floor(rng() * maxStart)` n times, the reference's draw (train-gpu.ts:206)."""
+    return [math.floor(rng() * maxStart) for _ in range(n)]
+
+
+class CudaStep:
+    """The forward+backward of one step recorded once and replayed: `batch` sequences of `seqLen` rows in
+    a single [batch*seqLen]-row call. Each sequence's loss is its own mean over kept rows and the step
+    loss is their mean, so gradients equal `batch` reference micro-batches seeded with 1/batch."""
+
+    def __init__(self, model, gpu: CudaBackend, batch: int, seqLen: int, lossChunk: int = 0, world: int = 1,
+                 capture: bool = True):
+        self.model, self.gpu, self.batch, self.seqLen, self.lossChunk = model, gpu, batch, seqLen, lossChunk
+        self.world = world
+        self.capture = capture
+        self.graph = None
+        self.lossTensor: Optional[Tensor] = None
+        self.launchesPerReplay = 0
+
+    def _once(self, ids: np.ndarray, targets: np.ndarray, seed: float) -> Tensor:
+        loss = sequenceLoss(self.model, ids, targets, self.lossChunk)
+        backward(loss, seed)
+        return loss
+
+    def run(self, ids: np.ndarray, targets: np.ndarray) -> None:
+        """Enqueue forward+backward for ids/targets of shape [batch*seqLen]; gradients overwrite."""
+        gpu = self.gpu
+        seed = 1.0 / self.world
+        gpu.install()
+        gpu.setBatch(self.batch, self.seqLen)
+        try:
+            if not self.capture:
+                self.lossTensor = self._once(ids, targets, seed)
+                return
+            if self.graph is None:
+                # eager once (warms the pool, RoPE tables, scratch), then record
+                warm = self._once(ids, targets, seed)
+                gpu.sync([warm])
+                before = gpu.kernelLaunches()
+                gpu.beginCapture(seed=seed, accumulate=False)
+                loss = self._once(ids, targets, seed)
+                self.graph = gpu.endCapture({"loss": loss})
+                self.launchesPerReplay = gpu.kernelLaunches() - before
+                self.lossTensor = loss
+            self.graph.launch(self.graphInputs(ids, targets))
+        finally:
+            gpu.setBatch(0)
+            gpu.uninstall()
+
+    def graphInputs(self, ids, targets):
+        return [ids, targets]
+
+    def losses(self) -> np.ndarray:
+        """[mean over sequences, per-sequence...] of the last run (blocks)."""
+        gpu = self.gpu
+        e = gpu._entries[self.lossTensor]
+        out = np.empty(1 + self.batch, np.float32)
+        gpu._read(e.data, out)
+        return out

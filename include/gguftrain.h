@@ -1,0 +1,160 @@
+/*
+ * libgguftrain_cuda.so - C ABI of the B200 (sm_100a) training backend for gguf-trainer.
+ *
+ * The library stands in for the WebGPU device behind gguf-trainer's op interface
+ * (`OpsBackend` + the `WebGPUBackend` buffer/sync API, src/backend/webgpu.ts). The
+ * host (TypeScript through Deno.dlopen, or the Python mirror in this repository)
+ * owns the tensors and the tape; this library owns device memory and the kernels.
+ *
+ * Conventions
+ *  - Every function returns a gt_status (0 = ok). gt_last_error() gives the text.
+ *    Nothing aborts, nothing throws across the boundary, no device traps.
+ *  - gt_buf is a device address inside an allocation made by this library. Adding a
+ *    byte offset to it is allowed (the chunked readout addresses row blocks that way).
+ *  - All work is enqueued on the context's stream in call order (the WebGPU queue
+ *    ordering the reference relies on); only gt_read, gt_sync, gt_graph_end and
+ *    gt_profile_stop block.
+ *  - Host pointers are borrowed for the duration of the call only.
+ *  - One context per process per GPU, called from one thread.
+ *  - Layout: row-major f32; activations [rows, features]; weights [out, in]; heads
+ *    packed [rows, H*hd]; ids/targets are u32 with 0xffffffff as the ignore marker
+ *    (webgpu.ts:1636-1646 maps -1 to it).
+ *  - Backward entry points take an `accum` flag per gradient output: 1 adds into the
+ *    buffer (the reference's `+=`), 0 overwrites it (what the reference gets from a
+ *    cleared buffer followed by `+=`). A zero gradient handle skips that output (a
+ *    frozen input, webgpu.ts:898-901).
+ */
+#ifndef GGUFTRAIN_H
+#define GGUFTRAIN_H
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct gt_ctx gt_ctx;
+typedef uint64_t gt_buf;
+typedef int32_t gt_status;
+
+enum { GT_OK = 0, GT_ERR_CUDA = 1, GT_ERR_ARG = 2, GT_ERR_OOM = 3, GT_ERR_STATE = 4, GT_ERR_NCCL = 5, GT_ERR_UNSUPPORTED = 6 };
+enum { GT_GEMM_NT = 0, GT_GEMM_NN = 1, GT_GEMM_TN = 2 };
+enum { GT_PREC_FP32 = 0, GT_PREC_TF32 = 1, GT_PREC_BF16 = 2 };
+enum { GT_EW_ADD = 0, GT_EW_MUL = 1, GT_EW_SILU = 2, GT_EW_GELU = 3, GT_EW_SCALE = 4 };
+
+/* ---- construction: initWebGPU / requireGPU / destroy (webgpu.ts:1812-1888, 764-767) ---- */
+gt_status gt_init(int32_t device, gt_ctx** out);
+gt_status gt_destroy(gt_ctx* ctx);
+const char* gt_last_error(gt_ctx* ctx);            /* ctx may be NULL: last init error */
+gt_status gt_device_name(gt_ctx* ctx, char* out, int32_t cap); /* adapterName / describeDevice */
+/* Matrix-product precision: strict f32 FMA, or TF32 / BF16 tensor cores with f32 accumulation. */
+gt_status gt_set_precision(gt_ctx* ctx, int32_t mode);
+/* Rows handed to the ops are `batch` independent sequences of `seq_len` rows each (RoPE
+ * positions wrap, attention is block-diagonal, losses are per sequence). batch=0 restores the
+ * reference behaviour: one sequence of however many rows the op is given. */
+gt_status gt_set_batch(gt_ctx* ctx, int32_t batch, int32_t seq_len);
+
+/* ---- memory: BufferPool.acquire/release, createStateBuffer, writeBuffer, staging reads
+ *      (webgpu.ts:214-262, 1465-1503) ---- */
+gt_status gt_alloc(gt_ctx* ctx, uint64_t bytes, gt_buf* out);       /* pooled, contents undefined */
+gt_status gt_alloc_state(gt_ctx* ctx, uint64_t bytes, gt_buf* out); /* zero-filled, never pooled */
+gt_status gt_free(gt_ctx* ctx, gt_buf buf);                         /* back to the pool */
+gt_status gt_write(gt_ctx* ctx, gt_buf dst, const void* host, uint64_t bytes);
+gt_status gt_read(gt_ctx* ctx, gt_buf src, void* host, uint64_t bytes); /* blocks until the data is on the host */
+gt_status gt_zero(gt_ctx* ctx, gt_buf buf, uint64_t bytes);             /* clearBuffer */
+gt_status gt_copy(gt_ctx* ctx, gt_buf dst, gt_buf src, uint64_t bytes); /* seedGradFrom, webgpu.ts:748-761 */
+gt_status gt_sync(gt_ctx* ctx);                                         /* submit + wait; surfaces latched errors */
+/* out[0] pooled bytes, out[1] state bytes, out[2] bytes read back since the last gt_sync,
+ * out[3] kernels launched since gt_init (residentBytes / lastSyncReadbackBytes) */
+gt_status gt_stats(gt_ctx* ctx, uint64_t* out4);
+
+/* ---- ops (OpsBackend, src/model/autograd.ts:103-151; kernels src/backend/wgsl.ts) ---- */
+/* C[M,N] (+)= op(A)*op(B): NT A[M,K] B[N,K]; NN A[M,K] B[K,N]; TN A[K,M] B[K,N]
+ * (WebGPUBackend.gemm, webgpu.ts:1654-1671; srcGemm wgsl.ts:87-196). */
+gt_status gt_gemm(gt_ctx* ctx, int32_t kind, int32_t accum, int32_t M, int32_t N, int32_t K, gt_buf a, gt_buf b, gt_buf c);
+/* add/mul/silu/gelu/scale (webgpu.ts:905-1078, srcElementwise wgsl.ts:199-209) */
+gt_status gt_ew_fwd(gt_ctx* ctx, int32_t op, uint64_t n, gt_buf a, gt_buf b, float c, gt_buf out);
+gt_status gt_ew_bwd(gt_ctx* ctx, int32_t op, uint64_t n, gt_buf a, gt_buf b, float c, gt_buf gout,
+                    gt_buf ga, int32_t accum_a, gt_buf gb, int32_t accum_b);
+/* rmsNorm and rmsNormHeads ([rows, d] view; webgpu.ts:1673-1701, wgsl.ts:217-303) */
+gt_status gt_rmsnorm_fwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf x, gt_buf w, float eps, gt_buf y, gt_buf rinv);
+gt_status gt_rmsnorm_bwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf x, gt_buf w, gt_buf rinv, gt_buf gy,
+                         gt_buf gx, int32_t accum_x, gt_buf gw, int32_t accum_w);
+/* embedding gather / scatter-add (webgpu.ts:1090-1108, wgsl.ts:305-344); gw always accumulates */
+gt_status gt_embedding_fwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf w, gt_buf ids, gt_buf out);
+gt_status gt_embedding_bwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf gy, gt_buf ids, gt_buf gw);
+/* NeoX RoPE, x:[rows, H*hd], position = row (mod seq_len when a batch is set) + pos_offset (wgsl.ts:346-384) */
+gt_status gt_rope_fwd(gt_ctx* ctx, int32_t rows, int32_t H, int32_t hd, double base, int32_t pos_offset, gt_buf x, gt_buf y);
+gt_status gt_rope_bwd(gt_ctx* ctx, int32_t rows, int32_t H, int32_t hd, double base, int32_t pos_offset, gt_buf gy,
+                      gt_buf gx, int32_t accum);
+/* causal GQA attention with optional sliding window; lse:[Hq, rows] in log2 units
+ * (webgpu.ts:1125-1192; srcAttnFwd/BwdD/BwdDq/BwdDkv wgsl.ts:657-918) */
+gt_status gt_attention_fwd(gt_ctx* ctx, int32_t rows, int32_t Hq, int32_t Hkv, int32_t hd, int32_t window,
+                           gt_buf q, gt_buf k, gt_buf v, gt_buf out, gt_buf lse);
+gt_status gt_attention_bwd(gt_ctx* ctx, int32_t rows, int32_t Hq, int32_t Hkv, int32_t hd, int32_t window,
+                           gt_buf q, gt_buf k, gt_buf v, gt_buf out, gt_buf lse, gt_buf gout,
+                           gt_buf gq, int32_t accum_q, gt_buf gk, int32_t accum_k, gt_buf gv, int32_t accum_v);
+/* cross entropy over logits [rows, V] (webgpu.ts:1295-1329; srcCeFwd/Reduce/Bwd wgsl.ts:936-996, 1112-1133).
+ * stats: [rows, 2] (row max, 1/sum). loss: [1 + nseq] floats, loss[0] = mean over sequences of the
+ * per-sequence kept-row means, loss[1+s] = sequence s; inv_kept: [nseq] = 1/max(kept_s, 1). */
+gt_status gt_ce_fwd(gt_ctx* ctx, int32_t rows, int32_t V, gt_buf logits, gt_buf targets, gt_buf stats,
+                    gt_buf loss, gt_buf inv_kept);
+gt_status gt_ce_bwd(gt_ctx* ctx, int32_t rows, int32_t V, gt_buf logits, gt_buf targets, gt_buf stats,
+                    gt_buf inv_kept, gt_buf gloss, gt_buf glogits, int32_t accum);
+/* chunked readout+CE (webgpu.ts:1214-1278; srcCeChunkStats/LossFromStats/ChunkGrad wgsl.ts:1153-1247).
+ * run: [rows, 3] running (max, sum, target logit); chunk logits [rows, n] cover vocab [v0, v0+n). */
+gt_status gt_ce_chunk_stats(gt_ctx* ctx, int32_t rows, int32_t n, int32_t v0, int32_t first, gt_buf chunk,
+                            gt_buf targets, gt_buf run);
+gt_status gt_ce_loss_from_stats(gt_ctx* ctx, int32_t rows, gt_buf run, gt_buf targets, gt_buf loss, gt_buf inv_kept);
+gt_status gt_ce_chunk_grad(gt_ctx* ctx, int32_t rows, int32_t n, int32_t v0, gt_buf chunk, gt_buf targets,
+                           gt_buf run, gt_buf inv_kept, gt_buf gloss);
+/* sparse-teacher soft CE (webgpu.ts:1331-1378; srcSoftCeFwd/BwdP/BwdQ wgsl.ts:1004-1110).
+ * tids/tprobs: [rows, k]; a row whose first id is 0xffffffff is ignored. */
+gt_status gt_soft_ce_fwd(gt_ctx* ctx, int32_t rows, int32_t V, int32_t k, gt_buf logits, gt_buf tids, gt_buf tprobs,
+                         gt_buf stats, gt_buf loss, gt_buf inv_kept);
+gt_status gt_soft_ce_bwd(gt_ctx* ctx, int32_t rows, int32_t V, int32_t k, gt_buf logits, gt_buf tids, gt_buf tprobs,
+                         gt_buf stats, gt_buf inv_kept, gt_buf gloss, gt_buf glogits, int32_t accum);
+
+/* ---- optimizers (AdamWGpu src/backend/adamw-gpu.ts:131-251; MuonGpu src/backend/muon-gpu.ts:351-470) ---- */
+/* A parameter group: n tensors given as parallel host arrays of device addresses and element counts.
+ * Moments are allocated zeroed by the library (createStateBuffer). */
+gt_status gt_adamw_create(gt_ctx* ctx, int32_t n, const gt_buf* data, const gt_buf* grad, const uint64_t* sizes,
+                          float lr, float beta1, float beta2, float eps, float weight_decay, float clip, uint64_t* out_handle);
+gt_status gt_adamw_set_lr(gt_ctx* ctx, uint64_t h, float lr);     /* setLrScale: host passes base*scale */
+gt_status gt_adamw_step(gt_ctx* ctx, uint64_t h);                 /* recordStep: clip-norm reduce + fused update */
+gt_status gt_adamw_state(gt_ctx* ctx, uint64_t h, int32_t i, gt_buf* m, gt_buf* v); /* exportState/importState buffers */
+gt_status gt_adamw_get_t(gt_ctx* ctx, uint64_t h, int32_t* t);
+gt_status gt_adamw_set_t(gt_ctx* ctx, uint64_t h, int32_t t);
+/* Muon over n matrices [rows_i, cols_i]: momentum, Frobenius normalise, quintic Newton-Schulz, apply. */
+gt_status gt_muon_create(gt_ctx* ctx, int32_t n, const gt_buf* data, const gt_buf* grad, const int32_t* rows,
+                         const int32_t* cols, float lr, float momentum, int32_t nesterov, int32_t ns_steps,
+                         uint64_t* out_handle);
+gt_status gt_muon_set_lr(gt_ctx* ctx, uint64_t h, float lr);
+gt_status gt_muon_step(gt_ctx* ctx, uint64_t h);
+gt_status gt_muon_state(gt_ctx* ctx, uint64_t h, int32_t i, gt_buf* momentum);
+/* newtonSchulzGpu (muon-gpu.ts:258-282): out[m,n] = NS_steps(g[m,n]) */
+gt_status gt_newton_schulz(gt_ctx* ctx, int32_t m, int32_t n, int32_t steps, gt_buf g, gt_buf out);
+
+/* ---- replay: one micro-batch's recorded work as a CUDA graph (the role prepareDispatch plays for
+ *      the optimizers, webgpu.ts:1512-1537, extended to the whole forward+backward) ---- */
+gt_status gt_graph_begin(gt_ctx* ctx);
+gt_status gt_graph_end(gt_ctx* ctx, uint64_t* out_graph);
+gt_status gt_graph_launch(gt_ctx* ctx, uint64_t graph);
+gt_status gt_graph_destroy(gt_ctx* ctx, uint64_t graph);
+
+/* ---- profiling: startProfile/stopProfile/readProfile (webgpu.ts:817-880). Events on the stream. ---- */
+gt_status gt_event_record(gt_ctx* ctx, int32_t slot);            /* slots 0..63 */
+gt_status gt_event_elapsed_ms(gt_ctx* ctx, int32_t start_slot, int32_t end_slot, float* ms); /* blocks on end_slot */
+
+/* ---- data parallel: no counterpart in the reference (single device). One process per GPU;
+ *      gradients are summed across ranks with NCCL on a side stream. ---- */
+gt_status gt_dp_unique_id(uint8_t* out128);                       /* rank 0 creates, host broadcasts */
+gt_status gt_dp_init(gt_ctx* ctx, int32_t rank, int32_t world, const uint8_t* id128);
+/* Start summing count f32 at buf across ranks, ordered after everything enqueued so far on the compute
+ * stream; later compute does not wait for it until gt_dp_wait. */
+gt_status gt_dp_allreduce_start(gt_ctx* ctx, gt_buf buf, uint64_t count);
+gt_status gt_dp_wait(gt_ctx* ctx);                                /* compute stream waits for all started reductions */
+gt_status gt_dp_destroy(gt_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
