@@ -109,8 +109,13 @@ def test_config1_tiny_llama_full_step(gpu, oracle):
     for i, g in enumerate(grads):
         compare(f"grad[{i}]", g, om.grad(i), BWD)
     om.opt_step()
+    # AdamW's first update is g/(|g|+eps), a sign function wherever |g| >> 1e-8: an element whose gradient
+    # sits at the f32 rounding floor of its own accumulation can land on either side, which moves that
+    # weight by up to 2*lr whatever the kernels do. Gradients above are held to 1e-5; the stepped weights
+    # to the element tolerances and 5e-5 relative L2 (tests/test_gpu_optim.py holds the update itself to
+    # 1e-6 when both sides are fed identical gradients).
     for i, p in enumerate(m.params()):
-        compare(f"post-step weight[{i}]", p.data, om.data(i), FWD)
+        compare(f"post-step weight[{i}]", p.data, om.data(i), FWD, 5e-5)
 
 
 def test_two_micro_batch_accumulation(gpu, oracle):
