@@ -245,3 +245,28 @@ gt_status gt_attention_bwd_simt(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, i
   }
   return GT_OK;
 }
+
+// The same backward launches with the row-dot scratch D supplied by the caller instead of taken from the
+// context's growable scratch block (used by the entry point that must not allocate).
+gt_status gt_attention_bwd_simt_scratch(gt_ctx* ctx, float* D, int rows, int T, int Hq, int Hkv, int hd, int window,
+                                        const float* q, const float* k, const float* v, const float* out, const float* lse,
+                                        const float* go, float* gq, int accum_q, float* gk, int accum_k, float* gv,
+                                        int accum_v) {
+  const float scale = 1.f / sqrtf((float)hd);
+  const float scale2 = 1.4426950408889634f * scale;
+  long warps = (long)rows * Hq;
+  attn_bwd_d_kernel<<<gt_cdiv(warps * 32, 256), 256, 0, ctx->stream>>>(rows, Hq, hd, go, out, D);
+  GT_LAUNCHED(ctx, "attn_bwd_d_kernel");
+  if (gq) {
+    attn_bwd_dq_kernel<<<gt_cdiv(warps, WARPS), WARPS * 32, sizeof(float) * WARPS * 2 * hd, ctx->stream>>>(
+        rows, T, Hq, Hkv, hd, window, scale2, scale, q, k, v, go, lse, D, gq, accum_q);
+    GT_LAUNCHED(ctx, "attn_bwd_dq_kernel");
+  }
+  if (gk || gv) {
+    long kw = (long)rows * Hkv;
+    attn_bwd_dkv_kernel<<<gt_cdiv(kw, WARPS), WARPS * 32, sizeof(float) * WARPS * 2 * hd, ctx->stream>>>(
+        rows, T, Hq, Hkv, hd, window, scale2, scale, q, k, v, go, lse, D, gk, accum_k, gv, accum_v);
+    GT_LAUNCHED(ctx, "attn_bwd_dkv_kernel");
+  }
+  return GT_OK;
+}

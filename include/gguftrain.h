@@ -92,6 +92,16 @@ gt_status gt_attention_fwd(gt_ctx* ctx, int32_t rows, int32_t Hq, int32_t Hkv, i
 gt_status gt_attention_bwd(gt_ctx* ctx, int32_t rows, int32_t Hq, int32_t Hkv, int32_t hd, int32_t window,
                            gt_buf q, gt_buf k, gt_buf v, gt_buf out, gt_buf lse, gt_buf gout,
                            gt_buf gq, int32_t accum_q, gt_buf gk, int32_t accum_k, gt_buf gv, int32_t accum_v);
+/* No counterpart in the reference. The same f32 attention backward as gt_attention_bwd for callers that
+ * cannot allocate device memory (hosts that give all of HBM to their own arena, or steps that cannot afford
+ * cudaMalloc's device-wide synchronisation): its only scratch, the per-(head,row) dot products dO.O, sits
+ * in a fixed 4 MiB array inside the library, so the call never allocates or frees. Limit: rows*Hq <=
+ * 1048576, larger shapes are refused with GT_ERR_ARG. Always f32, whatever gt_set_precision says. The
+ * first call on a device resolves the array's address (do it before any stream capture). All calls share
+ * the array: calls that overlap on the GPU race, so keep them on one stream. */
+gt_status gt_attention_bwd_static(gt_ctx* ctx, int32_t rows, int32_t Hq, int32_t Hkv, int32_t hd, int32_t window,
+                                  gt_buf q, gt_buf k, gt_buf v, gt_buf out, gt_buf lse, gt_buf gout,
+                                  gt_buf gq, int32_t accum_q, gt_buf gk, int32_t accum_k, gt_buf gv, int32_t accum_v);
 /* cross entropy over logits [rows, V] (webgpu.ts:1295-1329; srcCeFwd/Reduce/Bwd wgsl.ts:936-996, 1112-1133).
  * stats: [rows, 2] (row max, 1/sum). loss: [1 + nseq] floats, loss[0] = mean over sequences of the
  * per-sequence kept-row means, loss[1+s] = sequence s; inv_kept: [nseq] = 1/max(kept_s, 1). */
