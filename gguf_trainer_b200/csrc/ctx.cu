@@ -233,6 +233,8 @@ gt_status gt_sync(gt_ctx* ctx) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return gt_check_cuda(ctx, e, "gt_sync (latched)");
   ctx->readback_bytes = 0;
+  gt_status ts = gt_gemm_tc_check(ctx);
+  if (ts) return ts;
   return GT_OK;
 }
 

@@ -1,0 +1,98 @@
+"""The tcgen05 (TF32, f32 accumulate) matrix product through the C ABI against an f64 product of the same
+f32 inputs: all three operand layouts, ragged edges, accumulate, split-K; and a whole training step in
+tf32 mode against the CPU oracle. Bound: relative L2 <= 2e-3 (the tensor-core modes' stated tolerance)."""
+import numpy as np
+import pytest
+
+from gpu_harness import REL_L2_TC, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def gpu():
+    from gguf_trainer_b200.backend import requireGPU
+    g = requireGPU("the tensor-core suite", precision="tf32")
+    yield g
+    g.destroy()
+
+
+def _dev(gpu, a):
+    b = gpu.createStateBuffer(a.nbytes)
+    gpu.writeStateBuffer(b, a)
+    return b
+
+
+SHAPES = [(128, 128, 32), (128, 192, 64), (256, 192, 576), (300, 200, 100), (2048, 576, 576), (1000, 1536, 576),
+          (576, 1536, 2048), (192, 576, 4096), (2048, 64, 1536), (130, 16, 576), (4096, 576, 16)]
+
+
+@pytest.mark.parametrize("kind", ["NT", "NN", "TN"])
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_gemm_tf32(gpu, oracle, kind, M, N, K):
+    rng = oracle.Mulberry32(M * 7 + N * 3 + K)
+    A = rng.randn((M, K), 0.5)
+    B = rng.randn((N, K), 0.5)
+    C0 = rng.randn((M, N), 0.5)
+    want = A.astype(np.float64) @ B.astype(np.float64).T
+    a_store = A if kind != "TN" else np.ascontiguousarray(A.T)        # TN: A is [K, M]
+    b_store = B if kind == "NT" else np.ascontiguousarray(B.T)        # NN, TN: B is [K, N]
+    da, db = _dev(gpu, a_store), _dev(gpu, b_store)
+    launches = gpu.kernelLaunches()
+    for accum in (0, 1):
+        dc = _dev(gpu, C0)
+        gpu._gemm(kind, accum, M, N, K, da, db, dc)
+        got = gpu.readStateBuffer(dc, M * N).reshape(M, N)
+        ref = want + (C0.astype(np.float64) if accum else 0.0)
+        r = rel_l2(got, ref)
+        assert np.isfinite(got).all()
+        assert r <= REL_L2_TC, f"{kind} {M}x{N}x{K} accum={accum}: relative L2 {r:.3e}"
+        gpu._check(gpu.lib.gt_free(gpu.ctx, dc))
+    gpu.sync([])   # surfaces a pipeline-wait flag if one was raised
+    assert gpu.kernelLaunches() > launches
+    for b in (da, db):
+        gpu._check(gpu.lib.gt_free(gpu.ctx, b))
+
+
+def test_tf32_products_differ_from_strict_f32(gpu, oracle):
+    """Guards against the tensor-core path silently falling through to the f32 kernel."""
+    rng = oracle.Mulberry32(5)
+    M, N, K = 256, 192, 576
+    A, B = rng.randn((M, K), 0.5), rng.randn((N, K), 0.5)
+    da, db = _dev(gpu, A), _dev(gpu, B)
+    outs = {}
+    for mode in ("tf32", "fp32"):
+        gpu.setPrecision(mode)
+        dc = gpu.createStateBuffer(M * N * 4)
+        gpu._gemm("NT", 0, M, N, K, da, db, dc)
+        outs[mode] = gpu.readStateBuffer(dc, M * N)
+    gpu.setPrecision("tf32")
+    want = (A.astype(np.float64) @ B.astype(np.float64).T).ravel()
+    assert rel_l2(outs["fp32"], want) < 1e-6
+    assert 1e-5 < rel_l2(outs["tf32"], want) <= REL_L2_TC
+
+
+def test_config1_step_in_tf32_mode(gpu, oracle):
+    """Tiny llama (hidden 128, 2 layers, seq 128): loss and every gradient in tf32 mode vs the oracle."""
+    from gguf_trainer_b200 import autograd as ag
+    from gguf_trainer_b200.arch import buildModel, tinyLlama
+    from gguf_trainer_b200.train import sequenceLoss
+    cfg = tinyLlama()
+    om = oracle.Model(cfg.oracle_dict(), 1234)
+    m = buildModel(cfg, 1234)
+    for i, p in enumerate(m.params()):
+        p.data[:] = om.data(i).reshape(-1)
+    ids = oracle.Mulberry32(3).randint(128, cfg.vocabSize)
+    tg = oracle.Mulberry32(4).randint(128, cfg.vocabSize)
+    ref = float(om.loss_backward(ids, tg))
+    gpu.install()
+    try:
+        loss = sequenceLoss(m, ids, tg)
+        ag.backward(loss, 1.0)
+        gpu.sync([loss])
+    finally:
+        gpu.uninstall()
+    assert abs(float(loss.data[0]) - ref) <= 2e-3 * abs(ref)
+    for i, p in enumerate(m.params()):
+        r = rel_l2(p.grad, om.grad(i))
+        assert r <= REL_L2_TC, f"grad[{i}] {p.shape}: relative L2 {r:.3e}"
