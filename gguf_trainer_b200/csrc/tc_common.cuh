@@ -1,0 +1,124 @@
+// PTX wrappers shared by the tensor-core kernels (tcgen05 MMA, TMEM, TMA, mbarrier) and the host-side tensor-map
+// encoder. Internal to libgguftrain_cuda.so.
+#pragma once
+#include <cuda.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace tc {
+
+constexpr uint64_t WAIT_NS = 2000000000ull;  // every mbarrier wait gives up after 2 s of wall time
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint64_t gtimer() { uint64_t t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// false on timeout
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  if (mbar_try(bar, parity)) return true;
+  const uint64_t t0 = gtimer();
+  while (!mbar_try(bar, parity)) {
+    if (gtimer() - t0 > WAIT_NS) return false;
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
+               ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// the barrier receives one arrival when every MMA issued so far by this thread has completed
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
+      "%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor. Bits: [0,14) start>>4, [16,30) leading byte offset>>4, [32,46) stride byte
+// offset>>4, [46,48) version 1, [61,64) swizzle layout.
+// K-major tile (layout 2, 128-byte swizzle in 16-byte units): rows of 128 B (32 f32 of K), 8-row groups 1024 B
+//   apart (stride offset); the leading offset is not used for swizzled K-major tiles.
+// MN-major tile of 32-bit elements (layout 1, the 128-byte swizzle in 32-byte units, the only one tcgen05 accepts
+//   for MN-major tf32; TMA writes it with SWIZZLE_128B_ATOM_32B): chunks of 32 MN-elements x 32 K-rows (4096 B, one
+//   TMA box); a K row is 128 B, the swizzle pattern repeats every 4 K rows = 512 B (stride offset), chunks are
+//   4096 B apart (leading offset). One MMA (K = 8) reads two such 4-row groups.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3ffff) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)layout << 61;
+  return d;
+}
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) { return smem_desc(addr, 16, 1024, 2); }
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr) { return smem_desc(addr, 4096, 512, 1); }
+
+
+// Instruction descriptor (kind::tf32, f32 accumulate): [4,6) D format 1 = f32, [7,10) A format 2 = tf32,
+// [10,13) B format 2, bit 15 A is MN-major, bit 16 B is MN-major, [17,23) N>>3, [24,29) M>>4.
+__host__ __device__ constexpr uint32_t idesc_tf32(bool a_mn, bool b_mn, int m, int n) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// make generic-proxy shared-memory writes visible to the async proxy (TMA, tcgen05.mma operand reads)
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// kind::tf32 drops the low 13 mantissa bits of each f32 operand (truncation, not rounding), so every product is
+// biased low. For operands whose mantissas are log-uniform (generic data) the mean relative truncation error is
+// 2^-11 * E[1/m] = 2^-11 / (2 ln 2) = 3.52e-4 per operand: measured -7.05e-4 on the product of two. Multiplying an
+// accumulator by 1 + 2 * 3.52e-4 removes the systematic part and leaves the zero-mean part (relative L2 7.7e-4 ->
+// 3.1e-4 measured on a 576-deep product). For operands that happen to be exact in tf32 the factor itself is the
+// error: the same size as the bias it removes elsewhere, and inside the tensor-core modes' 2e-3 bound.
+constexpr float TRUNC_COMP = 1.000704f;
+
+// 2-D f32 tensor [outer, inner] with `inner` contiguous, tiled in boxes of [box_outer, 32 elements]; reads outside
+// the tensor give 0. kmajor tiles use the 128-byte swizzle in 16-byte units; MN-major tiles the 32-byte-unit variant.
+bool make_map_2d(CUtensorMap* map, const float* ptr, uint64_t inner, uint64_t outer, uint64_t row_pitch_elems,
+                 uint32_t box_outer, bool kmajor);
+
+// Device word the kernels set when a bounded wait expires (checked and cleared by gt_sync). Null while a graph is
+// being captured and the word does not exist yet.
+int* device_flag(gt_ctx* ctx);
+
+}  // namespace tc
