@@ -347,6 +347,61 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_micro(args):
+    """One op of the step at the benchmark shape, launched `--steps` times between two events: prints its
+    time and achieved algorithmic rate. Meant for `ncu` captures of a single kernel and for the per-kernel
+    roofline table; `--micro-batch` shrinks the row count (default: the full 8 x 2048)."""
+    from gguf_trainer_b200.backend import requireGPU
+    gpu = requireGPU("the micro benchmark", precision=args.precision)
+    B, T = args.micro_batch, args.seq
+    rows = B * T
+    h, q, kv, f, V, Hq, Hkv, hd = 576, 576, 192, 1536, 49152, 9, 3, 64
+    rng = np.random.default_rng(0)
+
+    def buf(n, fill=True):
+        b = gpu.createStateBuffer(n * 4)
+        if fill:
+            gpu.writeStateBuffer(b, (rng.standard_normal(n, dtype=np.float32) * 0.5))
+        return b
+
+    lib, ctx = gpu.lib, gpu.ctx
+    gpu.setBatch(B, T)
+    name = args.micro
+    pk = peaks()
+    if name == "attention":
+        Q, K, Vv, O, G = buf(rows * q), buf(rows * kv), buf(rows * kv), buf(rows * q, False), buf(rows * q)
+        L = buf(Hq * rows, False)
+        gq, gk, gv = buf(rows * q, False), buf(rows * kv, False), buf(rows * kv, False)
+        P = T * (T + 1) // 2
+        cases = [("attention fwd", lambda: lib.gt_attention_fwd(ctx, rows, Hq, Hkv, hd, args.window, Q, K, Vv, O, L), 4 * Hq * hd * P * B),
+                 ("attention bwd", lambda: lib.gt_attention_bwd(ctx, rows, Hq, Hkv, hd, args.window, Q, K, Vv, O, L, G, gq, 0, gk, 0, gv, 0), 10 * Hq * hd * P * B)]
+        unit, peak = "TFLOP/s", pk["tflops_sustained"]
+    elif name == "gemm":
+        cases = []
+        for out, inn in [(q, h), (kv, h), (f, h), (h, f)]:
+            x, w, y = buf(rows * inn), buf(out * inn), buf(rows * out)
+            dx, dw = buf(rows * inn, False), buf(out * inn, False)
+            fl = 2 * rows * inn * out
+            cases.append((f"NT {rows}x{out}x{inn}", (lambda x=x, w=w, y=y, out=out, inn=inn: lib.gt_gemm(ctx, 0, 0, rows, out, inn, x, w, y)), fl))
+            cases.append((f"NN {rows}x{inn}x{out}", (lambda w=w, y=y, dx=dx, out=out, inn=inn: lib.gt_gemm(ctx, 1, 0, rows, inn, out, y, w, dx)), fl))
+            cases.append((f"TN {out}x{inn}x{rows}", (lambda x=x, y=y, dw=dw, out=out, inn=inn: lib.gt_gemm(ctx, 2, 0, out, inn, rows, y, x, dw)), fl))
+        unit, peak = "TFLOP/s", pk["tflops_sustained"]
+    else:
+        raise SystemExit(f"unknown --micro {name}")
+    for label, fn, work in cases:
+        for _ in range(2):
+            gpu._check(fn())
+        gpu.recordEvent(30)
+        for _ in range(args.steps):
+            gpu._check(fn())
+        gpu.recordEvent(31)
+        ms = gpu.elapsedMs(30, 31) / args.steps
+        rate = work / (ms / 1e3) / 1e12
+        print(json.dumps({"micro": label, "ms": ms, "achieved": rate, "unit": unit, "peak": peak, "frac": rate / peak,
+                          "precision": args.precision, "rows": rows}), flush=True)
+    gpu.sync([])
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -360,8 +415,13 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=256)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--micro", default="", help="time one op of the step instead: attention | gemm")
+    ap.add_argument("--micro-batch", type=int, default=8)
+    ap.add_argument("--window", type=int, default=0)
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.micro:
+        run_micro(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

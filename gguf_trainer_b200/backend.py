@@ -80,6 +80,41 @@ def _as_u32(values) -> np.ndarray:
     return np.ascontiguousarray(a)
 
 
+class _ProfilingLib:
+    """Stand-in for the library handle while a profile is open: every enqueueing call is bracketed by two
+    events on the library's stream and attributed to its entry point (and, for products, its layout and
+    shape), the per-label GPU time the reference collects with timestamp queries (webgpu.ts:817-880)."""
+
+    _SKIP = ("gt_event_", "gt_read", "gt_write", "gt_sync", "gt_alloc", "gt_free", "gt_stats", "gt_last_error",
+             "gt_graph_", "gt_set_", "gt_device_name", "gt_adamw_state", "gt_muon_state", "gt_adamw_get_t",
+             "gt_adamw_set_", "gt_muon_set_", "gt_adamw_create", "gt_muon_create", "gt_dp_")
+
+    def __init__(self, lib, ctx, totals):
+        self._lib, self._ctx, self._totals = lib, ctx, totals
+
+    def __getattr__(self, name):
+        fn = getattr(self._lib, name)
+        if name.startswith(self._SKIP):
+            return fn
+        lib, ctx, totals = self._lib, self._ctx, self._totals
+
+        def timed(*args):
+            lib.gt_event_record(ctx, 62)
+            st = fn(*args)
+            lib.gt_event_record(ctx, 63)
+            ms = C.c_float()
+            lib.gt_event_elapsed_ms(ctx, 62, 63, C.byref(ms))
+            label = name
+            if name == "gt_gemm":
+                label = f"gt_gemm {('NT', 'NN', 'TN')[args[1]]} {args[3]}x{args[4]}x{args[5]}"
+            t = totals.setdefault(label, [0.0, 0])
+            t[0] += float(ms.value)
+            t[1] += 1
+            return st
+
+        return timed
+
+
 class CudaBackend:
     def __init__(self, device: int = 0, precision: str = "fp32"):
         self.lib = _lib.load()
@@ -121,6 +156,24 @@ class CudaBackend:
 
     def describeDevice(self) -> str:
         return self.adapterName
+
+    def startProfile(self):
+        """webgpu.ts:817-845. Per-label GPU time until stopProfile(); each call is synchronised, so use it to
+        see where time goes, not to measure throughput."""
+        if getattr(self, "_profTotals", None) is not None:
+            return
+        self._profTotals = {}
+        self._realLib = self.lib
+        self.lib = _ProfilingLib(self._realLib, self.ctx, self._profTotals)
+
+    def stopProfile(self):
+        """Returns {label: {"ms": total, "count": n}} and closes the profile (webgpu.ts:847-880)."""
+        totals = getattr(self, "_profTotals", None)
+        if totals is None:
+            return {}
+        self.lib = self._realLib
+        self._profTotals = None
+        return {k: {"ms": v[0], "count": v[1]} for k, v in totals.items()}
 
     def install(self):
         ag.setOpsBackend(self)

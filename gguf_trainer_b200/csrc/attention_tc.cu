@@ -53,8 +53,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + S::BAR_OFF + 64);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q0 = blockIdx.x * BQ;            // first query position of this tile inside its sequence
-  const int h = blockIdx.y, seq = blockIdx.z;
+  // Causal work grows with the query position: the heaviest tiles are launched first, and all (head, sequence)
+  // pairs of one tile index are adjacent, so the tail of the grid is made of the lightest tiles.
+  const int q0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * BQ;   // first query position of this tile inside its sequence
+  const int h = blockIdx.x % Hq, seq = blockIdx.x / Hq;
   const int kvh = h / (Hq / Hkv);
   const int row0 = seq * T;                  // first global row of the sequence
   const int q_last = min(q0 + BQ - 1, T - 1);
@@ -219,7 +221,7 @@ gt_status launch_fwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, 
   }
   // the S product's truncation bias is folded into the score scale
   const float scale2 = 1.4426950408889634f / sqrtf((float)HD) * TRUNC_COMP;
-  dim3 grid(gt_cdiv(T, BQ), Hq, rows / T);
+  dim3 grid(Hq * (rows / T), gt_cdiv(T, BQ), 1);
   kern<<<grid, 160, FwdSmem<HD>::TOTAL, ctx->stream>>>(mq, mk, mv, out, lse, rows, T, Hq, Hkv, window, scale2, flag);
   GT_LAUNCHED(ctx, "attn_fwd_tc_kernel");
   return GT_OK;
@@ -297,8 +299,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + S::BAR_OFF + 64);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int k0 = blockIdx.x * 128;
-  const int kvh = blockIdx.y, seq = blockIdx.z;
+  const int k0 = blockIdx.y * 128;            // early keys are read by the most queries: heaviest first
+  const int kvh = blockIdx.x % Hkv, seq = blockIdx.x / Hkv;
   const int group = Hq / Hkv;
   const int row0 = seq * T;
   const int k_last = min(k0 + 127, T - 1);
@@ -498,8 +500,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + S::BAR_OFF + 64);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q0 = blockIdx.x * 128;
-  const int h = blockIdx.y, seq = blockIdx.z;
+  const int q0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * 128;   // late queries read the most keys: heaviest first
+  const int h = blockIdx.x % Hq, seq = blockIdx.x / Hq;
   const int kvh = h / (Hq / Hkv);
   const int row0 = seq * T;
   const int q_last = min(q0 + 127, T - 1);
@@ -670,7 +672,7 @@ gt_status launch_bwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, 
       GT_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvSmem<HD, NQ>::TOTAL));
       attr_set[ctx->device] = true;
     }
-    dim3 grid(gt_cdiv(T, 128), Hkv, nseq);
+    dim3 grid(Hkv * nseq, gt_cdiv(T, 128), 1);
     kern<<<grid, 160, DkvSmem<HD, NQ>::TOTAL, ctx->stream>>>(mK, mV, mQk, mQm, mGk, mGm, lse, D, gk, accum_k, gv, accum_v, rows, T, Hq, Hkv,
                                                             window, scale2, scale, flag);
     GT_LAUNCHED(ctx, "attn_bwd_dkv_tc_kernel");
@@ -687,7 +689,7 @@ gt_status launch_bwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, 
       GT_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DqSmem<HD, NK>::TOTAL));
       attr_set[ctx->device] = true;
     }
-    dim3 grid(gt_cdiv(T, 128), Hq, nseq);
+    dim3 grid(Hq * nseq, gt_cdiv(T, 128), 1);
     kern<<<grid, 160, DqSmem<HD, NK>::TOTAL, ctx->stream>>>(mQ, mG, mKk, mVk, mKm, lse, D, gq, accum_q, rows, T, Hq, Hkv, window, scale2,
                                                            scale, flag);
     GT_LAUNCHED(ctx, "attn_bwd_dq_tc_kernel");
