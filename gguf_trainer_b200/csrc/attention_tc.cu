@@ -7,11 +7,14 @@
 // low mantissa bits; the mean truncation bias is compensated, see tc_common.cuh); softmax, masks and all
 // accumulation are f32.
 //
-// Forward: one CTA owns 128 query rows of one head. Per 64-key block: S = Q.K^T into TMEM (M=128, N=64);
-// four warps read it one row per thread (no shuffles), apply mask and online softmax, and write P as the
-// A operand of the second product; O_blk = P.V into TMEM; the same threads fold it into their register
-// accumulator with the rescale factor. One more warp issues TMA and MMA. K and V of the next block are
-// fetched while the current block's softmax runs.
+// All three kernels share one shape. A CTA owns 128 rows of the output (queries for forward and dQ, keys for
+// dK/dV) and walks the other axis in blocks. One warp issues TMA and MMA; eight warps do the element math, two
+// per TMEM lane quadrant, each taking half of a block's columns, one output row per thread (no shuffles). The
+// score products of block i+1 are issued before the element math of block i is waited for (their TMEM
+// accumulators are double-buffered), so the tensor pipe and the CUDA cores overlap; operand tiles of the next
+// block are fetched as soon as the products that read the current ones have completed.
+// Waits on mbarriers are bounded in wall time: on expiry a thread raises the device flag and from then on skips
+// every wait, so all threads still run the same control flow to the end and release TMEM.
 #include "common.cuh"
 #include "tc_common.cuh"
 
@@ -20,222 +23,260 @@ using namespace tc;
 namespace {
 
 constexpr float NEG = -3.0e38f;
-constexpr int BQ = 128, BKV = 64;
+constexpr int ROWS = 128;          // output rows per CTA = TMEM lanes
+constexpr int MATH_WARPS = 8;
+constexpr int THREADS = (MATH_WARPS + 1) * 32;
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                 "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, float* v) {
+  static_assert(N == 16 || N % 32 == 0, "column count");
+  if constexpr (N == 16) tmem_ld16(taddr, v);
+  else {
+#pragma unroll
+    for (int c = 0; c < N / 32; c++) tmem_ld32(taddr + c * 32, v + c * 32);
+  }
+}
+__device__ __forceinline__ void pair_sync(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
+
+// A bounded wait that becomes a no-op once any wait of this thread has expired.
+struct Waiter {
+  bool dead = false;
+  int* flag;
+  __device__ __forceinline__ void wait(uint32_t bar, uint32_t parity, int code) {
+    if (dead) return;
+    if (!mbar_wait(bar, parity)) { dead = true; atomicExch(flag, code); }
+  }
+};
+
+// Write NC consecutive f32 values, starting at column c0 (a multiple of 4), as row r of a K-major operand tile:
+// atoms of 32 columns, 128 rows each, rows 128 B apart, 16-byte chunks XOR (row mod 8).
+template <int NC>
+__device__ __forceinline__ void store_row_kmajor(uint8_t* tile, int r, int c0, const float* v) {
+#pragma unroll
+  for (int i = 0; i < NC / 4; i++) {
+    const int c4 = c0 / 4 + i;
+    const int atom = c4 / 8, chunk = (c4 % 8) ^ (r & 7);
+    *reinterpret_cast<float4*>(tile + atom * (ROWS * 128) + r * 128 + chunk * 16) = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Forward. Per 64-key block: S = Q.K^T (M=128, N=64) -> mask, online softmax -> P (A operand) -> O_blk = P.V,
+// folded into a register accumulator with the rescale factor. The two warps of a lane quadrant split the 64
+// keys for the softmax (exchanging their partial row maxima through shared memory) and the head dimension
+// for the accumulator.
+// ---------------------------------------------------------------------------------------------
+constexpr int BKV = 64;
 
 template <int HD>
 struct FwdSmem {
-  static constexpr int Q_BYTES = BQ * HD * 4;
-  static constexpr int K_BYTES = BKV * HD * 4;
-  static constexpr int V_BYTES = BKV * HD * 4;
-  static constexpr int P_BYTES = BQ * BKV * 4;
-  static constexpr int Q_OFF = 0, K_OFF = Q_BYTES, V_OFF = K_OFF + K_BYTES, P_OFF = V_OFF + V_BYTES;
-  static constexpr int BAR_OFF = P_OFF + P_BYTES;
+  static constexpr int Q_BYTES = ROWS * HD * 4, K_BYTES = BKV * HD * 4, V_BYTES = BKV * HD * 4, P_BYTES = ROWS * BKV * 4;
+  static constexpr int Q_OFF = 0, K_OFF = Q_BYTES, V_OFF = K_OFF + K_BYTES, P_OFF = V_OFF + V_BYTES, X_OFF = P_OFF + P_BYTES;
+  static constexpr int X_BYTES = 2 * 2 * ROWS * 4;   // partial row maxima [parity][half][row]
+  static constexpr int BAR_OFF = X_OFF + X_BYTES;
   static constexpr int TOTAL = BAR_OFF + 128 + 1024;
-  static constexpr uint32_t TMEM_COLS = (64 + HD) <= 128 ? 128 : 256;
+  static constexpr uint32_t TMEM_COLS = (2 * BKV + HD) <= 256 ? 256 : 512;
 };
 
-// Q: [rows, Hq*HD]; K, V: [rows, Hkv*HD]. Tensor maps: mapQ box [128 rows, 32], mapK box [64 rows, 32] (both 16-byte-atom
-// swizzle), mapV box [64 rows, 32] with the 32-byte-atom swizzle (V is the [keys, hd] operand with hd contiguous).
 template <int HD>
-__global__ void __launch_bounds__(160, 1)
+__global__ void __launch_bounds__(THREADS, HD <= 64 ? 2 : 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                    const __grid_constant__ CUtensorMap mapV, float* __restrict__ out, float* __restrict__ lse, int rows, int T,
                    int Hq, int Hkv, int window, float scale2, int* __restrict__ flag) {
   extern __shared__ uint8_t smem_raw[];
   using S = FwdSmem<HD>;
-  constexpr int ATOMS = HD / 32;
+  constexpr int ATOMS = HD / 32, HH = HD / 2;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t q_s = base + S::Q_OFF, k_s = base + S::K_OFF, v_s = base + S::V_OFF, p_s = base + S::P_OFF;
+  float* xch = reinterpret_cast<float*>(base_ptr + S::X_OFF);
   const uint32_t bars = base + S::BAR_OFF;
-  const uint32_t q_full = bars, k_full = bars + 8, v_full = bars + 16, s_full = bars + 24, p_full = bars + 32, o_full = bars + 40;
+  const uint32_t q_full = bars, k_full = bars + 8, v_full = bars + 16, s_full0 = bars + 24, s_full1 = bars + 32, p_full = bars + 40,
+                 o_full = bars + 48;
   const uint32_t tmem_slot = bars + 64;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + S::BAR_OFF + 64);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Causal work grows with the query position: the heaviest tiles are launched first, and all (head, sequence)
   // pairs of one tile index are adjacent, so the tail of the grid is made of the lightest tiles.
-  const int q0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * BQ;   // first query position of this tile inside its sequence
+  const int q0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * ROWS;
   const int h = blockIdx.x % Hq, seq = blockIdx.x / Hq;
   const int kvh = h / (Hq / Hkv);
-  const int row0 = seq * T;                  // first global row of the sequence
-  const int q_last = min(q0 + BQ - 1, T - 1);
+  const int row0 = seq * T;
+  const int q_last = min(q0 + ROWS - 1, T - 1);
   const int kb_lo = (window > 0 && q0 - window + 1 > 0) ? (q0 - window + 1) / BKV : 0;
   const int kb_hi = q_last / BKV;
   const int nkb = kb_hi - kb_lo + 1;
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1); mbar_init(k_full, 1); mbar_init(v_full, 1); mbar_init(s_full, 1); mbar_init(p_full, 128); mbar_init(o_full, 1);
+    mbar_init(q_full, 1); mbar_init(k_full, 1); mbar_init(v_full, 1); mbar_init(s_full0, 1); mbar_init(s_full1, 1);
+    mbar_init(p_full, MATH_WARPS * 32); mbar_init(o_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 4) tmem_alloc(tmem_slot, S::TMEM_COLS);
+  if (warp == MATH_WARPS) tmem_alloc(tmem_slot, S::TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot_ptr;
-  const uint32_t tm_s = tmem, tm_o = tmem + 64;
+  const uint32_t tm_o = tmem + 2 * BKV;
+  Waiter w{false, flag};
 
-  if (warp == 4) {
+  if (warp == MATH_WARPS) {
     if (lane == 0) {
-      // ---- TMA + MMA issue ----
-      constexpr uint32_t idesc_s = idesc_tf32(false, false, BQ, BKV);   // S = Q.K^T, both K-major
-      constexpr uint32_t idesc_o = idesc_tf32(false, true, BQ, HD);     // O = P.V, V is [keys, hd]
-      bool ok = true;
-      mbar_expect_tx(q_full, S::Q_BYTES);
-      for (int a = 0; a < ATOMS; a++) tma_load_2d(q_s + a * (BQ * 128), &mapQ, h * HD + 32 * a, row0 + q0, q_full);
-      auto load_k = [&](int kb) {
+      constexpr uint32_t idesc_s = idesc_tf32(false, false, ROWS, BKV);   // S = Q.K^T, both K-major
+      constexpr uint32_t idesc_o = idesc_tf32(false, true, ROWS, HD);     // O = P.V, V is [keys, hd]
+      auto load_k = [&](int i) {
         mbar_expect_tx(k_full, S::K_BYTES);
-        for (int a = 0; a < ATOMS; a++) tma_load_2d(k_s + a * (BKV * 128), &mapK, kvh * HD + 32 * a, row0 + kb * BKV, k_full);
+        for (int a = 0; a < ATOMS; a++) tma_load_2d(k_s + a * (BKV * 128), &mapK, kvh * HD + 32 * a, row0 + (kb_lo + i) * BKV, k_full);
       };
-      auto load_v = [&](int kb) {
+      auto load_v = [&](int i) {
         mbar_expect_tx(v_full, S::V_BYTES);
-        for (int a = 0; a < ATOMS; a++) tma_load_2d(v_s + a * (BKV * 128), &mapV, kvh * HD + 32 * a, row0 + kb * BKV, v_full);
+        for (int a = 0; a < ATOMS; a++) tma_load_2d(v_s + a * (BKV * 128), &mapV, kvh * HD + 32 * a, row0 + (kb_lo + i) * BKV, v_full);
       };
-      load_k(kb_lo);
-      load_v(kb_lo);
-      ok = mbar_wait(q_full, 0);
-      if (!ok) atomicExch(flag, 11);
-      for (int i = 0; i < nkb && ok; i++) {
-        const uint32_t par = i & 1;
-        ok = mbar_wait(k_full, par);
-        if (!ok) { atomicExch(flag, 12); break; }
-        tc_fence_after();
+      auto mma_s = [&](int i) {
+        const uint32_t tm_s = tmem + (i & 1) * BKV;
 #pragma unroll
         for (int a = 0; a < ATOMS; a++)
 #pragma unroll
           for (int j = 0; j < 4; j++)
-            umma_tf32(tm_s, desc_kmajor(q_s + a * (BQ * 128) + j * 32), desc_kmajor(k_s + a * (BKV * 128) + j * 32), idesc_s,
+            umma_tf32(tm_s, desc_kmajor(q_s + a * (ROWS * 128) + j * 32), desc_kmajor(k_s + a * (BKV * 128) + j * 32), idesc_s,
                       (a > 0 || j > 0) ? 1u : 0u);
-        umma_commit(s_full);
-        ok = mbar_wait(s_full, par);         // K tile has been read: fetch the next one under the softmax
-        if (!ok) { atomicExch(flag, 13); break; }
-        if (i + 1 < nkb) load_k(kb_lo + i + 1);
-        ok = mbar_wait(v_full, par) && mbar_wait(p_full, par);
-        if (!ok) { atomicExch(flag, 14); break; }
+        umma_commit((i & 1) ? s_full1 : s_full0);
+      };
+      mbar_expect_tx(q_full, S::Q_BYTES);
+      for (int a = 0; a < ATOMS; a++) tma_load_2d(q_s + a * (ROWS * 128), &mapQ, h * HD + 32 * a, row0 + q0, q_full);
+      load_k(0);
+      load_v(0);
+      w.wait(q_full, 0, 11);
+      w.wait(k_full, 0, 12);
+      tc_fence_after();
+      mma_s(0);
+      w.wait(s_full0, 0, 13);
+      if (nkb > 1) load_k(1);
+      for (int i = 0; i < nkb; i++) {
+        if (i + 1 < nkb) {                     // next block's scores, under this block's softmax
+          w.wait(k_full, (i + 1) & 1, 12);
+          tc_fence_after();
+          mma_s(i + 1);
+        }
+        w.wait(v_full, i & 1, 14);
+        w.wait(p_full, i & 1, 14);
         tc_fence_after();
 #pragma unroll
         for (int j = 0; j < BKV / 8; j++)
-          umma_tf32(tm_o, desc_kmajor(p_s + (j / 4) * (BQ * 128) + (j % 4) * 32), smem_desc(v_s + j * 1024, BKV * 128, 512, 1),
-                    idesc_o, j > 0 ? 1u : 0u);
+          umma_tf32(tm_o, desc_kmajor(p_s + (j / 4) * (ROWS * 128) + (j % 4) * 32), smem_desc(v_s + j * 1024, BKV * 128, 512, 1), idesc_o,
+                    j > 0 ? 1u : 0u);
         umma_commit(o_full);
-        ok = mbar_wait(o_full, par);         // V and P tiles have been read
-        if (!ok) { atomicExch(flag, 15); break; }
-        if (i + 1 < nkb) load_v(kb_lo + i + 1);
+        if (i + 1 < nkb) {
+          w.wait(((i + 1) & 1) ? s_full1 : s_full0, ((i + 1) >> 1) & 1, 13);   // K tile read: fetch the one after
+          if (i + 2 < nkb) load_k(i + 2);
+        }
+        w.wait(o_full, i & 1, 15);             // V and P tiles read
+        if (i + 1 < nkb) load_v(i + 1);
       }
     }
   } else {
-    // ---- softmax + output: thread = one query row; warp w owns TMEM lanes [32w, 32w+32) ----
-    const int r = warp * 32 + lane;
+    const int qd = warp & 3, half = warp >> 2;
+    const int r = qd * 32 + lane;
     const int tq = q0 + r;
     const bool valid = tq < T;
+    const int lo = (window > 0) ? tq - window + 1 : 0;
     float m = NEG, l = 0.f;
-    float o[HD];
+    float o[HH];
 #pragma unroll
-    for (int d = 0; d < HD; d++) o[d] = 0.f;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    bool ok = true;
+    for (int d = 0; d < HH; d++) o[d] = 0.f;
+    const uint32_t lane_base = (uint32_t)(qd * 32) << 16;
     for (int i = 0; i < nkb; i++) {
-      const uint32_t par = i & 1;
-      const int k0 = (kb_lo + i) * BKV;
-      if (ok) ok = mbar_wait(s_full, par);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) { if (lane == 0) atomicExch(flag, 16); break; }
+      const int k0 = (kb_lo + i) * BKV + half * 32;
+      w.wait((i & 1) ? s_full1 : s_full0, (i >> 1) & 1, 16);
       tc_fence_after();
-      float s[BKV];
-      tmem_ld32(tm_s + lane_base, s);
-      tmem_ld32(tm_s + lane_base + 32, s + 32);
-      const int lo = (window > 0) ? tq - window + 1 : 0;
+      float s[32];
+      tmem_ld<32>(tmem + (i & 1) * BKV + half * 32 + lane_base, s);
+      // a block strictly below the diagonal and inside the window needs no per-element test
+      const bool interior = (k0 + 31 <= q0) && (q0 + ROWS - 1 < T) && (window == 0 || k0 >= q0 + ROWS - window);
       float mx = NEG;
+      if (interior) {
 #pragma unroll
-      for (int c = 0; c < BKV; c++) {
-        const int kg = k0 + c;
-        const bool keep = valid && kg <= tq && kg >= lo;
-        s[c] = keep ? s[c] * scale2 : NEG;
-        mx = fmaxf(mx, s[c]);
+        for (int c = 0; c < 32; c++) { s[c] *= scale2; mx = fmaxf(mx, s[c]); }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 32; c++) {
+          const int kg = k0 + c;
+          s[c] = (valid && kg <= tq && kg >= lo) ? s[c] * scale2 : NEG;
+          mx = fmaxf(mx, s[c]);
+        }
       }
+      float* xp = xch + (i & 1) * (2 * ROWS);
+      xp[half * ROWS + r] = mx;
+      pair_sync(1 + qd);
+      mx = fmaxf(mx, xp[(half ^ 1) * ROWS + r]);
       const float mn = fmaxf(m, mx);
-      const float alpha = exp2f(m - mn);
+      const float alpha = ex2(m - mn);
       float sum = 0.f;
 #pragma unroll
-      for (int c = 0; c < BKV; c++) {
-        const float p = (s[c] > -1.0e38f) ? exp2f(s[c] - mn) : 0.f;
+      for (int c = 0; c < 32; c++) {
+        const float p = (s[c] > -1.0e38f) ? ex2(s[c] - mn) : 0.f;
         s[c] = p;
         sum += p;
       }
       l = l * alpha + sum;
       m = mn;
-      // P as the K-major A operand: atom = 32 keys, row pitch 128 B, 16-byte chunks XOR (row mod 8)
-      {
-        uint8_t* prow = base_ptr + S::P_OFF + r * 128;
-#pragma unroll
-        for (int c4 = 0; c4 < BKV / 4; c4++) {
-          const int atom = c4 / 8, chunk = (c4 % 8) ^ (r & 7);
-          *reinterpret_cast<float4*>(prow + atom * (BQ * 128) + chunk * 16) = make_float4(s[4 * c4], s[4 * c4 + 1], s[4 * c4 + 2], s[4 * c4 + 3]);
-        }
-      }
+      store_row_kmajor<32>(base_ptr + S::P_OFF, r, half * 32, s);
       fence_async_smem();
       tc_fence_before();
       mbar_arrive(p_full);
-      if (ok) ok = mbar_wait(o_full, par);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) { if (lane == 0) atomicExch(flag, 17); break; }
+      w.wait(o_full, i & 1, 17);
       tc_fence_after();
+      float t[HH];
+      tmem_ld<HH>(tm_o + half * HH + lane_base, t);
 #pragma unroll
-      for (int c = 0; c < HD / 32; c++) {
-        float t[32];
-        tmem_ld32(tm_o + lane_base + c * 32, t);
-#pragma unroll
-        for (int d = 0; d < 32; d++) o[c * 32 + d] = o[c * 32 + d] * alpha + t[d];
-      }
+      for (int d = 0; d < HH; d++) o[d] = o[d] * alpha + t[d];
       tc_fence_before();
     }
-    if (ok && valid) {
+    // total row sum = the two halves' sums (same running max on both sides)
+    float* xp = xch;   // every exchange slot was last read before the pair's final sync of the loop
+    pair_sync(1 + qd);
+    xp[half * ROWS + r] = l;
+    pair_sync(1 + qd);
+    l += xp[(half ^ 1) * ROWS + r];
+    if (!w.dead && valid) {
       const float inv = TRUNC_COMP / l;   // the P.V product carries the truncation bias of both operands
-      float* dst = out + (size_t)(row0 + tq) * Hq * HD + (size_t)h * HD;
+      float* dst = out + (size_t)(row0 + tq) * Hq * HD + (size_t)h * HD + half * HH;
 #pragma unroll
-      for (int d = 0; d < HD; d += 4) *reinterpret_cast<float4*>(dst + d) = make_float4(o[d] * inv, o[d + 1] * inv, o[d + 2] * inv, o[d + 3] * inv);
-      lse[(size_t)h * rows + row0 + tq] = m + log2f(l);
+      for (int d = 0; d < HH; d += 4) *reinterpret_cast<float4*>(dst + d) = make_float4(o[d] * inv, o[d + 1] * inv, o[d + 2] * inv, o[d + 3] * inv);
+      if (half == 0) lse[(size_t)h * rows + row0 + tq] = m + log2f(l);
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == MATH_WARPS) {
     tc_fence_after();
     tmem_dealloc(tmem, S::TMEM_COLS);
   }
 }
 
-template <int HD>
-gt_status launch_fwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, const float* q, const float* k, const float* v,
-                     float* out, float* lse, int* flag) {
-  CUtensorMap mq, mk, mv;
-  if (!make_map_2d(&mq, q, (uint64_t)Hq * HD, rows, (uint64_t)Hq * HD, BQ, true) ||
-      !make_map_2d(&mk, k, (uint64_t)Hkv * HD, rows, (uint64_t)Hkv * HD, BKV, true) ||
-      !make_map_2d(&mv, v, (uint64_t)Hkv * HD, rows, (uint64_t)Hkv * HD, BKV, false))
-    return gt_fail(ctx, GT_ERR_CUDA, "attention: tensor map encoding failed");
-  auto kern = attn_fwd_tc_kernel<HD>;
-  static bool attr_set[64] = {};
-  if (!attr_set[ctx->device]) {
-    GT_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<HD>::TOTAL));
-    attr_set[ctx->device] = true;
-  }
-  // the S product's truncation bias is folded into the score scale
-  const float scale2 = 1.4426950408889634f / sqrtf((float)HD) * TRUNC_COMP;
-  dim3 grid(Hq * (rows / T), gt_cdiv(T, BQ), 1);
-  kern<<<grid, 160, FwdSmem<HD>::TOTAL, ctx->stream>>>(mq, mk, mv, out, lse, rows, T, Hq, Hkv, window, scale2, flag);
-  GT_LAUNCHED(ctx, "attn_fwd_tc_kernel");
-  return GT_OK;
-}
-
 // ---------------------------------------------------------------------------------------------
-// Backward. D[h,row] = sum_d dO*O first (one warp per (row, head)), then two kernels, as in the reference
-// (srcAttnBwdDq, srcAttnBwdDkv): each recomputes S and dP on the tensor cores, forms p and dS in registers
-// and feeds them back as the A operand of the gradient products, whose accumulators stay in TMEM for the
-// whole loop. Nothing is reduced with atomics: one CTA owns its 128 query rows (dQ) or its 128 key rows
+// Backward. Ds[h,row] = scale * sum_d dO*O first (one warp per (row, head)), then two kernels, as in the
+// reference (srcAttnBwdDq, srcAttnBwdDkv): each recomputes S and dP on the tensor cores, forms p and dS in
+// registers and feeds them back as the A operand of the gradient products, whose accumulators stay in TMEM for
+// the whole loop. Nothing is reduced with atomics: one CTA owns its 128 query rows (dQ) or its 128 key rows
 // (dK, dV, summing its GQA group inside the loop), so results are deterministic.
 // ---------------------------------------------------------------------------------------------
-__global__ void attn_bwd_d_tc_kernel(int rows, int Hq, int hd, const float* __restrict__ go, const float* __restrict__ o,
-                                     float* __restrict__ D) {
+__global__ void attn_bwd_d_tc_kernel(int rows, int Hq, int hd, float scale, const float* __restrict__ go,
+                                     const float* __restrict__ o, float* __restrict__ D) {
   const int lane = threadIdx.x & 31;
   const long w = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (w >= (long)rows * Hq) return;
@@ -246,91 +287,73 @@ __global__ void attn_bwd_d_tc_kernel(int rows, int Hq, int hd, const float* __re
   for (int d = lane; d < hd; d += 32) acc = fmaf(go[b + d], o[b + d], acc);
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-  if (lane == 0) D[(size_t)h * rows + row] = acc;
-}
-
-// write NC f32 values as row r of a K-major operand tile (atoms of 32 columns, 128 rows each, 128-byte swizzle)
-template <int NC>
-__device__ __forceinline__ void store_row_kmajor(uint8_t* tile, int r, const float* v) {
-#pragma unroll
-  for (int c4 = 0; c4 < NC / 4; c4++) {
-    const int atom = c4 / 8, chunk = (c4 % 8) ^ (r & 7);
-    *reinterpret_cast<float4*>(tile + atom * (128 * 128) + r * 128 + chunk * 16) = make_float4(v[4 * c4], v[4 * c4 + 1], v[4 * c4 + 2], v[4 * c4 + 3]);
-  }
-}
-
-template <int N>
-__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, float* v) {
-#pragma unroll
-  for (int c = 0; c < N / 32; c++) tmem_ld32(taddr + c * 32, v + c * 32);
+  if (lane == 0) D[(size_t)h * rows + row] = acc * scale;
 }
 
 // ---- dK, dV: CTA = 128 keys of one kv head; loop over the group's query heads and over blocks of NQ queries ----
+// Transposed products so that keys are the rows: S^T = K.Q^T and dP^T = V.dO^T (M=128 keys, N=NQ queries); then
+// dV += P^T.dO and dK += dS^T.Q with P^T, dS^T written to shared memory as K-major A operands (K = queries) and
+// dO, Q read a second time as [queries, hd] operands (hd contiguous).
 template <int HD, int NQ>
 struct DkvSmem {
-  static constexpr int KV_BYTES = 128 * HD * 4;          // K, V tiles (K-major A operands)
-  static constexpr int QT_BYTES = NQ * HD * 4;           // one copy of a Q or dO tile
-  static constexpr int PT_BYTES = 128 * NQ * 4;          // P^T, dS^T (K-major A operands, K = queries)
-  static constexpr int K_OFF = 0, V_OFF = KV_BYTES, QK_OFF = 2 * KV_BYTES, DOK_OFF = QK_OFF + QT_BYTES,
-                       QM_OFF = DOK_OFF + QT_BYTES, DOM_OFF = QM_OFF + QT_BYTES, P_OFF = DOM_OFF + QT_BYTES,
-                       DS_OFF = P_OFF + PT_BYTES, BAR_OFF = DS_OFF + PT_BYTES;
+  static constexpr int KV_BYTES = ROWS * HD * 4, QT_BYTES = NQ * HD * 4, PT_BYTES = ROWS * NQ * 4;
+  static constexpr int K_OFF = 0, V_OFF = KV_BYTES, QK_OFF = 2 * KV_BYTES, GK_OFF = QK_OFF + QT_BYTES, QM_OFF = GK_OFF + QT_BYTES,
+                       GM_OFF = QM_OFF + QT_BYTES, P_OFF = GM_OFF + QT_BYTES, DS_OFF = P_OFF + PT_BYTES, BAR_OFF = DS_OFF + PT_BYTES;
   static constexpr int TOTAL = BAR_OFF + 128 + 1024;
-  static constexpr int COLS = 2 * NQ + 2 * HD;
+  static constexpr int COLS = 4 * NQ + 2 * HD;
   static constexpr uint32_t TMEM_COLS = COLS <= 128 ? 128 : (COLS <= 256 ? 256 : 512);
 };
 
 template <int HD, int NQ>
-__global__ void __launch_bounds__(160, 1)
+__global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
                        const __grid_constant__ CUtensorMap mapQk, const __grid_constant__ CUtensorMap mapQm,
                        const __grid_constant__ CUtensorMap mapGk, const __grid_constant__ CUtensorMap mapGm,
-                       const float* __restrict__ lse, const float* __restrict__ Dv, float* gk, int accum_k, float* gv, int accum_v,
-                       int rows, int T, int Hq, int Hkv, int window, float scale2, float scale, int* __restrict__ flag) {
+                       const float* __restrict__ lse, const float* __restrict__ Ds, float* gk, int accum_k, float* gv, int accum_v,
+                       int rows, int T, int Hq, int Hkv, int window, float scale2, float dp_scale, int* __restrict__ flag) {
   extern __shared__ uint8_t smem_raw[];
   using S = DkvSmem<HD, NQ>;
-  constexpr int ATOMS = HD / 32;
+  constexpr int ATOMS = HD / 32, NH = NQ / 2, HH = HD / 2;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t k_s = base + S::K_OFF, v_s = base + S::V_OFF, qk_s = base + S::QK_OFF, gk_s = base + S::DOK_OFF,
-                 qm_s = base + S::QM_OFF, gm_s = base + S::DOM_OFF, p_s = base + S::P_OFF, ds_s = base + S::DS_OFF;
+  const uint32_t k_s = base + S::K_OFF, v_s = base + S::V_OFF, qk_s = base + S::QK_OFF, gk_s = base + S::GK_OFF,
+                 qm_s = base + S::QM_OFF, gm_s = base + S::GM_OFF, p_s = base + S::P_OFF, ds_s = base + S::DS_OFF;
   const uint32_t bars = base + S::BAR_OFF;
-  const uint32_t kv_full = bars, qk_full = bars + 8, qm_full = bars + 16, s_full = bars + 24, p_full = bars + 32, acc_done = bars + 40;
+  const uint32_t kv_full = bars, qk_full = bars + 8, qm_full = bars + 16, s_full0 = bars + 24, s_full1 = bars + 32, p_full = bars + 40,
+                 acc_done = bars + 48;
   const uint32_t tmem_slot = bars + 64;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + S::BAR_OFF + 64);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int k0 = blockIdx.y * 128;            // early keys are read by the most queries: heaviest first
+  const int k0 = blockIdx.y * ROWS;           // early keys are read by the most queries: heaviest first
   const int kvh = blockIdx.x % Hkv, seq = blockIdx.x / Hkv;
   const int group = Hq / Hkv;
   const int row0 = seq * T;
-  const int k_last = min(k0 + 127, T - 1);
+  const int k_last = min(k0 + ROWS - 1, T - 1);
   const int q_max = (window > 0) ? min(T - 1, k_last + window - 1) : T - 1;
   const int qb_lo = k0 / NQ, qb_hi = q_max / NQ;
   const int nqb = qb_hi - qb_lo + 1;
   const int iters = nqb * group;
 
   if (threadIdx.x == 0) {
-    mbar_init(kv_full, 1); mbar_init(qk_full, 1); mbar_init(qm_full, 1); mbar_init(s_full, 1); mbar_init(p_full, 128); mbar_init(acc_done, 1);
+    mbar_init(kv_full, 1); mbar_init(qk_full, 1); mbar_init(qm_full, 1); mbar_init(s_full0, 1); mbar_init(s_full1, 1);
+    mbar_init(p_full, MATH_WARPS * 32); mbar_init(acc_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 4) tmem_alloc(tmem_slot, S::TMEM_COLS);
+  if (warp == MATH_WARPS) tmem_alloc(tmem_slot, S::TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot_ptr;
-  const uint32_t tm_s = tmem, tm_dp = tmem + NQ, tm_dv = tmem + 2 * NQ, tm_dk = tmem + 2 * NQ + HD;
+  // columns: [S^T | dP^T] x 2 buffers, then dV, dK
+  const uint32_t tm_dv = tmem + 4 * NQ, tm_dk = tmem + 4 * NQ + HD;
+  Waiter w{false, flag};
 
-  if (warp == 4) {
+  if (warp == MATH_WARPS) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = idesc_tf32(false, false, 128, NQ);   // S^T = K.Q^T and dP^T = V.dO^T
-      constexpr uint32_t idesc_g = idesc_tf32(false, true, 128, HD);    // dV += P^T.dO, dK += dS^T.Q
-      bool ok = true;
-      mbar_expect_tx(kv_full, 2 * S::KV_BYTES);
-      for (int a = 0; a < ATOMS; a++) {
-        tma_load_2d(k_s + a * (128 * 128), &mapK, kvh * HD + 32 * a, row0 + k0, kv_full);
-        tma_load_2d(v_s + a * (128 * 128), &mapV, kvh * HD + 32 * a, row0 + k0, kv_full);
-      }
-      auto load_k = [&](int it) {   // K-major copies of Q and dO for iteration it
+      constexpr uint32_t idesc_s = idesc_tf32(false, false, ROWS, NQ);
+      constexpr uint32_t idesc_g = idesc_tf32(false, true, ROWS, HD);
+      auto load_k = [&](int it) {   // K-major copies of Q and dO
         const int h = kvh * group + it / nqb, qr = row0 + (qb_lo + it % nqb) * NQ;
         mbar_expect_tx(qk_full, 2 * S::QT_BYTES);
         for (int a = 0; a < ATOMS; a++) {
@@ -338,7 +361,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
           tma_load_2d(gk_s + a * (NQ * 128), &mapGk, h * HD + 32 * a, qr, qk_full);
         }
       };
-      auto load_m = [&](int it) {   // [queries, hd] copies (hd contiguous) for the gradient products
+      auto load_m = [&](int it) {   // [queries, hd] copies for the gradient products
         const int h = kvh * group + it / nqb, qr = row0 + (qb_lo + it % nqb) * NQ;
         mbar_expect_tx(qm_full, 2 * S::QT_BYTES);
         for (int a = 0; a < ATOMS; a++) {
@@ -346,111 +369,136 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
           tma_load_2d(gm_s + a * (NQ * 128), &mapGm, h * HD + 32 * a, qr, qm_full);
         }
       };
-      load_k(0);
-      load_m(0);
-      ok = mbar_wait(kv_full, 0);
-      if (!ok) atomicExch(flag, 21);
-      for (int i = 0; i < iters && ok; i++) {
-        const uint32_t par = i & 1;
-        ok = mbar_wait(qk_full, par);
-        if (!ok) { atomicExch(flag, 22); break; }
-        tc_fence_after();
+      auto mma_s = [&](int i) {
+        const uint32_t tm_s = tmem + (i & 1) * 2 * NQ, tm_dp = tm_s + NQ;
 #pragma unroll
         for (int a = 0; a < ATOMS; a++)
 #pragma unroll
           for (int j = 0; j < 4; j++) {
             const uint32_t acc = (a > 0 || j > 0) ? 1u : 0u;
-            umma_tf32(tm_s, desc_kmajor(k_s + a * (128 * 128) + j * 32), desc_kmajor(qk_s + a * (NQ * 128) + j * 32), idesc_s, acc);
-            umma_tf32(tm_dp, desc_kmajor(v_s + a * (128 * 128) + j * 32), desc_kmajor(gk_s + a * (NQ * 128) + j * 32), idesc_s, acc);
+            umma_tf32(tm_s, desc_kmajor(k_s + a * (ROWS * 128) + j * 32), desc_kmajor(qk_s + a * (NQ * 128) + j * 32), idesc_s, acc);
+            umma_tf32(tm_dp, desc_kmajor(v_s + a * (ROWS * 128) + j * 32), desc_kmajor(gk_s + a * (NQ * 128) + j * 32), idesc_s, acc);
           }
-        umma_commit(s_full);
-        ok = mbar_wait(s_full, par);
-        if (!ok) { atomicExch(flag, 23); break; }
-        if (i + 1 < iters) load_k(i + 1);
-        ok = mbar_wait(qm_full, par) && mbar_wait(p_full, par);
-        if (!ok) { atomicExch(flag, 24); break; }
+        umma_commit((i & 1) ? s_full1 : s_full0);
+      };
+      mbar_expect_tx(kv_full, 2 * S::KV_BYTES);
+      for (int a = 0; a < ATOMS; a++) {
+        tma_load_2d(k_s + a * (ROWS * 128), &mapK, kvh * HD + 32 * a, row0 + k0, kv_full);
+        tma_load_2d(v_s + a * (ROWS * 128), &mapV, kvh * HD + 32 * a, row0 + k0, kv_full);
+      }
+      load_k(0);
+      load_m(0);
+      w.wait(kv_full, 0, 21);
+      w.wait(qk_full, 0, 22);
+      tc_fence_after();
+      mma_s(0);
+      w.wait(s_full0, 0, 23);
+      if (iters > 1) load_k(1);
+      for (int i = 0; i < iters; i++) {
+        if (i + 1 < iters) {
+          w.wait(qk_full, (i + 1) & 1, 22);
+          tc_fence_after();
+          mma_s(i + 1);
+        }
+        w.wait(qm_full, i & 1, 24);
+        w.wait(p_full, i & 1, 24);
         tc_fence_after();
 #pragma unroll
         for (int j = 0; j < NQ / 8; j++) {
           const uint32_t acc = (i > 0 || j > 0) ? 1u : 0u;
-          const uint32_t aoff = (j / 4) * (128 * 128) + (j % 4) * 32;
+          const uint32_t aoff = (j / 4) * (ROWS * 128) + (j % 4) * 32;
           umma_tf32(tm_dv, desc_kmajor(p_s + aoff), smem_desc(gm_s + j * 1024, NQ * 128, 512, 1), idesc_g, acc);
           umma_tf32(tm_dk, desc_kmajor(ds_s + aoff), smem_desc(qm_s + j * 1024, NQ * 128, 512, 1), idesc_g, acc);
         }
         umma_commit(acc_done);
-        ok = mbar_wait(acc_done, par);
-        if (!ok) { atomicExch(flag, 25); break; }
+        if (i + 1 < iters) {
+          w.wait(((i + 1) & 1) ? s_full1 : s_full0, ((i + 1) >> 1) & 1, 23);
+          if (i + 2 < iters) load_k(i + 2);
+        }
+        w.wait(acc_done, i & 1, 25);
         if (i + 1 < iters) load_m(i + 1);
       }
     }
   } else {
-    const int r = warp * 32 + lane;          // key row inside the tile
+    const int qd = warp & 3, half = warp >> 2;
+    const int r = qd * 32 + lane;            // key row inside the tile
     const int kg = k0 + r;                   // key position in the sequence
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    bool ok = true;
+    const uint32_t lane_base = (uint32_t)(qd * 32) << 16;
     for (int i = 0; i < iters; i++) {
-      const uint32_t par = i & 1;
       const int h = kvh * group + i / nqb;
-      const int qpos0 = (qb_lo + i % nqb) * NQ;
-      if (ok) ok = mbar_wait(s_full, par);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) { if (lane == 0) atomicExch(flag, 26); break; }
+      const int qpos0 = (qb_lo + i % nqb) * NQ + half * NH;      // first query of this thread's columns
+      w.wait((i & 1) ? s_full1 : s_full0, (i >> 1) & 1, 26);
       tc_fence_after();
-      float s[NQ], dp[NQ];
-      tmem_ld_cols<NQ>(tm_s + lane_base, s);
-      tmem_ld_cols<NQ>(tm_dp + lane_base, dp);
-      const float* lrow = lse + (size_t)h * rows + row0 + qpos0;
-      const float* drow = Dv + (size_t)h * rows + row0 + qpos0;
+      float s[NH], dp[NH];
+      const uint32_t tm_s = tmem + (i & 1) * 2 * NQ + half * NH + lane_base;
+      tmem_ld<NH>(tm_s, s);
+      tmem_ld<NH>(tm_s + NQ, dp);
+      const float4* l4 = reinterpret_cast<const float4*>(lse + (size_t)h * rows + row0 + qpos0);
+      const float4* d4 = reinterpret_cast<const float4*>(Ds + (size_t)h * rows + row0 + qpos0);
+      // every (key, query) pair of the tile kept: keys at or before the first query, queries inside the sequence
+      // and, with a window, the last query still within reach of the first key
+      const bool interior = (k0 + ROWS - 1 <= qpos0) && (qpos0 + NH - 1 < T) && (window == 0 || k0 >= qpos0 + NH - window) &&
+                            (((size_t)h * rows + row0) % 4 == 0);   // and the 16-byte loads of LSE / Ds are aligned
+      if (interior) {
 #pragma unroll
-      for (int c = 0; c < NQ; c++) {
-        const int tq = qpos0 + c;
-        const bool keep = tq < T && kg <= tq && (window == 0 || kg >= tq - window + 1);   // kg <= tq < T
-        float p = 0.f, d = 0.f;
-        if (keep) {
-          p = exp2f(s[c] * scale2 - __ldg(lrow + c));
-          d = p * (dp[c] * TRUNC_COMP - __ldg(drow + c)) * scale;
+        for (int c4 = 0; c4 < NH / 4; c4++) {
+          const float4 L = __ldg(l4 + c4), Dv = __ldg(d4 + c4);
+          const float Ls[4] = {L.x, L.y, L.z, L.w}, Dd[4] = {Dv.x, Dv.y, Dv.z, Dv.w};
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            const int c = c4 * 4 + e;
+            const float p = ex2(fmaf(s[c], scale2, -Ls[e]));
+            s[c] = p;
+            dp[c] = p * fmaf(dp[c], dp_scale, -Dd[e]);
+          }
         }
-        s[c] = p;
-        dp[c] = d;
+      } else {
+        const float* lrow = lse + (size_t)h * rows + row0 + qpos0;
+        const float* drow = Ds + (size_t)h * rows + row0 + qpos0;
+#pragma unroll
+        for (int c = 0; c < NH; c++) {
+          const int tq = qpos0 + c;
+          const bool keep = tq < T && kg <= tq && (window == 0 || kg >= tq - window + 1);
+          float p = 0.f, d = 0.f;
+          if (keep) {
+            p = ex2(fmaf(s[c], scale2, -__ldg(lrow + c)));
+            d = p * fmaf(dp[c], dp_scale, -__ldg(drow + c));
+          }
+          s[c] = p;
+          dp[c] = d;
+        }
       }
-      if (i > 0) {                            // the previous iteration's gradient products still read P^T / dS^T
-        if (ok) ok = mbar_wait(acc_done, (i - 1) & 1);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) { if (lane == 0) atomicExch(flag, 27); break; }
-      }
-      store_row_kmajor<NQ>(base_ptr + S::P_OFF, r, s);
-      store_row_kmajor<NQ>(base_ptr + S::DS_OFF, r, dp);
+      if (i > 0) w.wait(acc_done, (i - 1) & 1, 27);   // the previous gradient products still read P^T / dS^T
+      store_row_kmajor<NH>(base_ptr + S::P_OFF, r, half * NH, s);
+      store_row_kmajor<NH>(base_ptr + S::DS_OFF, r, half * NH, dp);
       fence_async_smem();
       tc_fence_before();
       mbar_arrive(p_full);
     }
-    if (ok && iters > 0) {
-      ok = mbar_wait(acc_done, (iters - 1) & 1);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok && lane == 0) atomicExch(flag, 28);
-    }
+    if (iters > 0) w.wait(acc_done, (iters - 1) & 1, 28);
     tc_fence_after();
-    if (ok) {   // warp-uniform: the TMEM loads are warp-wide instructions, only the stores are per-row
-      const bool st = kg < T;
-      const size_t off = (size_t)(row0 + (st ? kg : 0)) * Hkv * HD + (size_t)kvh * HD;
-#pragma unroll 1
-      for (int c = 0; c < HD / 32; c++) {
-        float t[32];
-        if (gv) {
-          tmem_ld32(tm_dv + lane_base + c * 32, t);
-          float* dst = gv + off + c * 32;
+    {   // warp-uniform: the TMEM loads are warp-wide instructions, only the stores are per-row
+      const bool st = !w.dead && kg < T;
+      const size_t off = (size_t)(row0 + (kg < T ? kg : 0)) * Hkv * HD + (size_t)kvh * HD + half * HH;
+      float t[HH];
+      if (gv) {
+        tmem_ld<HH>(tm_dv + half * HH + lane_base, t);
+        float* dst = gv + off;
+        if (st) {
 #pragma unroll
-          for (int d = 0; d < 32 && st; d += 4) {
+          for (int d = 0; d < HH; d += 4) {
             float4 o = accum_v ? *reinterpret_cast<float4*>(dst + d) : make_float4(0, 0, 0, 0);
             o.x += t[d] * TRUNC_COMP; o.y += t[d + 1] * TRUNC_COMP; o.z += t[d + 2] * TRUNC_COMP; o.w += t[d + 3] * TRUNC_COMP;
             *reinterpret_cast<float4*>(dst + d) = o;
           }
         }
-        if (gk) {
-          tmem_ld32(tm_dk + lane_base + c * 32, t);
-          float* dst = gk + off + c * 32;
+      }
+      if (gk) {
+        tmem_ld<HH>(tm_dk + half * HH + lane_base, t);
+        float* dst = gk + off;
+        if (st) {
 #pragma unroll
-          for (int d = 0; d < 32 && st; d += 4) {
+          for (int d = 0; d < HH; d += 4) {
             float4 o = accum_k ? *reinterpret_cast<float4*>(dst + d) : make_float4(0, 0, 0, 0);
             o.x += t[d] * TRUNC_COMP; o.y += t[d + 1] * TRUNC_COMP; o.z += t[d + 2] * TRUNC_COMP; o.w += t[d + 3] * TRUNC_COMP;
             *reinterpret_cast<float4*>(dst + d) = o;
@@ -461,75 +509,72 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == MATH_WARPS) {
     tc_fence_after();
     tmem_dealloc(tmem, S::TMEM_COLS);
   }
 }
 
 // ---- dQ: CTA = 128 queries of one head; loop over blocks of NK keys ----
+// S = Q.K^T and dP = dO.V^T (M=128 queries, N=NK keys); dS written as a K-major A operand (K = keys);
+// dQ += dS.K with K read a second time as a [keys, hd] operand.
 template <int HD, int NK>
 struct DqSmem {
-  static constexpr int Q_BYTES = 128 * HD * 4;           // Q, dO tiles (K-major A operands)
-  static constexpr int KT_BYTES = NK * HD * 4;           // one copy of a K or V tile
-  static constexpr int DS_BYTES = 128 * NK * 4;
-  static constexpr int Q_OFF = 0, DO_OFF = Q_BYTES, KK_OFF = 2 * Q_BYTES, VK_OFF = KK_OFF + KT_BYTES, KM_OFF = VK_OFF + KT_BYTES,
+  static constexpr int Q_BYTES = ROWS * HD * 4, KT_BYTES = NK * HD * 4, DS_BYTES = ROWS * NK * 4;
+  static constexpr int Q_OFF = 0, G_OFF = Q_BYTES, KK_OFF = 2 * Q_BYTES, VK_OFF = KK_OFF + KT_BYTES, KM_OFF = VK_OFF + KT_BYTES,
                        DS_OFF = KM_OFF + KT_BYTES, BAR_OFF = DS_OFF + DS_BYTES;
   static constexpr int TOTAL = BAR_OFF + 128 + 1024;
-  static constexpr int COLS = 2 * NK + HD;
+  static constexpr int COLS = 4 * NK + HD;
   static constexpr uint32_t TMEM_COLS = COLS <= 128 ? 128 : (COLS <= 256 ? 256 : 512);
 };
 
 template <int HD, int NK>
-__global__ void __launch_bounds__(160, 1)
+__global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapG,
                       const __grid_constant__ CUtensorMap mapKk, const __grid_constant__ CUtensorMap mapVk,
-                      const __grid_constant__ CUtensorMap mapKm, const float* __restrict__ lse, const float* __restrict__ Dv,
-                      float* gq, int accum_q, int rows, int T, int Hq, int Hkv, int window, float scale2, float scale,
+                      const __grid_constant__ CUtensorMap mapKm, const float* __restrict__ lse, const float* __restrict__ Ds,
+                      float* gq, int accum_q, int rows, int T, int Hq, int Hkv, int window, float scale2, float dp_scale,
                       int* __restrict__ flag) {
   extern __shared__ uint8_t smem_raw[];
   using S = DqSmem<HD, NK>;
-  constexpr int ATOMS = HD / 32;
+  constexpr int ATOMS = HD / 32, NH = NK / 2, HH = HD / 2;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t q_s = base + S::Q_OFF, g_s = base + S::DO_OFF, kk_s = base + S::KK_OFF, vk_s = base + S::VK_OFF,
-                 km_s = base + S::KM_OFF, ds_s = base + S::DS_OFF;
+  const uint32_t q_s = base + S::Q_OFF, g_s = base + S::G_OFF, kk_s = base + S::KK_OFF, vk_s = base + S::VK_OFF, km_s = base + S::KM_OFF,
+                 ds_s = base + S::DS_OFF;
   const uint32_t bars = base + S::BAR_OFF;
-  const uint32_t q_full = bars, kk_full = bars + 8, km_full = bars + 16, s_full = bars + 24, p_full = bars + 32, acc_done = bars + 40;
+  const uint32_t q_full = bars, kk_full = bars + 8, km_full = bars + 16, s_full0 = bars + 24, s_full1 = bars + 32, p_full = bars + 40,
+                 acc_done = bars + 48;
   const uint32_t tmem_slot = bars + 64;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + S::BAR_OFF + 64);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * 128;   // late queries read the most keys: heaviest first
+  const int q0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * ROWS;   // late queries read the most keys: heaviest first
   const int h = blockIdx.x % Hq, seq = blockIdx.x / Hq;
   const int kvh = h / (Hq / Hkv);
   const int row0 = seq * T;
-  const int q_last = min(q0 + 127, T - 1);
+  const int q_last = min(q0 + ROWS - 1, T - 1);
   const int kb_lo = (window > 0 && q0 - window + 1 > 0) ? (q0 - window + 1) / NK : 0;
   const int kb_hi = q_last / NK;
   const int iters = kb_hi - kb_lo + 1;
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1); mbar_init(kk_full, 1); mbar_init(km_full, 1); mbar_init(s_full, 1); mbar_init(p_full, 128); mbar_init(acc_done, 1);
+    mbar_init(q_full, 1); mbar_init(kk_full, 1); mbar_init(km_full, 1); mbar_init(s_full0, 1); mbar_init(s_full1, 1);
+    mbar_init(p_full, MATH_WARPS * 32); mbar_init(acc_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 4) tmem_alloc(tmem_slot, S::TMEM_COLS);
+  if (warp == MATH_WARPS) tmem_alloc(tmem_slot, S::TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot_ptr;
-  const uint32_t tm_s = tmem, tm_dp = tmem + NK, tm_dq = tmem + 2 * NK;
+  const uint32_t tm_dq = tmem + 4 * NK;
+  Waiter w{false, flag};
 
-  if (warp == 4) {
+  if (warp == MATH_WARPS) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = idesc_tf32(false, false, 128, NK);   // S = Q.K^T, dP = dO.V^T
-      constexpr uint32_t idesc_g = idesc_tf32(false, true, 128, HD);    // dQ += dS.K
-      bool ok = true;
-      mbar_expect_tx(q_full, 2 * S::Q_BYTES);
-      for (int a = 0; a < ATOMS; a++) {
-        tma_load_2d(q_s + a * (128 * 128), &mapQ, h * HD + 32 * a, row0 + q0, q_full);
-        tma_load_2d(g_s + a * (128 * 128), &mapG, h * HD + 32 * a, row0 + q0, q_full);
-      }
+      constexpr uint32_t idesc_s = idesc_tf32(false, false, ROWS, NK);
+      constexpr uint32_t idesc_g = idesc_tf32(false, true, ROWS, HD);
       auto load_k = [&](int it) {
         const int kr = row0 + (kb_lo + it) * NK;
         mbar_expect_tx(kk_full, 2 * S::KT_BYTES);
@@ -543,95 +588,105 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         mbar_expect_tx(km_full, S::KT_BYTES);
         for (int a = 0; a < ATOMS; a++) tma_load_2d(km_s + a * (NK * 128), &mapKm, kvh * HD + 32 * a, kr, km_full);
       };
-      load_k(0);
-      load_m(0);
-      ok = mbar_wait(q_full, 0);
-      if (!ok) atomicExch(flag, 31);
-      for (int i = 0; i < iters && ok; i++) {
-        const uint32_t par = i & 1;
-        ok = mbar_wait(kk_full, par);
-        if (!ok) { atomicExch(flag, 32); break; }
-        tc_fence_after();
+      auto mma_s = [&](int i) {
+        const uint32_t tm_s = tmem + (i & 1) * 2 * NK, tm_dp = tm_s + NK;
 #pragma unroll
         for (int a = 0; a < ATOMS; a++)
 #pragma unroll
           for (int j = 0; j < 4; j++) {
             const uint32_t acc = (a > 0 || j > 0) ? 1u : 0u;
-            umma_tf32(tm_s, desc_kmajor(q_s + a * (128 * 128) + j * 32), desc_kmajor(kk_s + a * (NK * 128) + j * 32), idesc_s, acc);
-            umma_tf32(tm_dp, desc_kmajor(g_s + a * (128 * 128) + j * 32), desc_kmajor(vk_s + a * (NK * 128) + j * 32), idesc_s, acc);
+            umma_tf32(tm_s, desc_kmajor(q_s + a * (ROWS * 128) + j * 32), desc_kmajor(kk_s + a * (NK * 128) + j * 32), idesc_s, acc);
+            umma_tf32(tm_dp, desc_kmajor(g_s + a * (ROWS * 128) + j * 32), desc_kmajor(vk_s + a * (NK * 128) + j * 32), idesc_s, acc);
           }
-        umma_commit(s_full);
-        ok = mbar_wait(s_full, par);
-        if (!ok) { atomicExch(flag, 33); break; }
-        if (i + 1 < iters) load_k(i + 1);
-        ok = mbar_wait(km_full, par) && mbar_wait(p_full, par);
-        if (!ok) { atomicExch(flag, 34); break; }
+        umma_commit((i & 1) ? s_full1 : s_full0);
+      };
+      mbar_expect_tx(q_full, 2 * S::Q_BYTES);
+      for (int a = 0; a < ATOMS; a++) {
+        tma_load_2d(q_s + a * (ROWS * 128), &mapQ, h * HD + 32 * a, row0 + q0, q_full);
+        tma_load_2d(g_s + a * (ROWS * 128), &mapG, h * HD + 32 * a, row0 + q0, q_full);
+      }
+      load_k(0);
+      load_m(0);
+      w.wait(q_full, 0, 31);
+      w.wait(kk_full, 0, 32);
+      tc_fence_after();
+      mma_s(0);
+      w.wait(s_full0, 0, 33);
+      if (iters > 1) load_k(1);
+      for (int i = 0; i < iters; i++) {
+        if (i + 1 < iters) {
+          w.wait(kk_full, (i + 1) & 1, 32);
+          tc_fence_after();
+          mma_s(i + 1);
+        }
+        w.wait(km_full, i & 1, 34);
+        w.wait(p_full, i & 1, 34);
         tc_fence_after();
 #pragma unroll
         for (int j = 0; j < NK / 8; j++)
-          umma_tf32(tm_dq, desc_kmajor(ds_s + (j / 4) * (128 * 128) + (j % 4) * 32), smem_desc(km_s + j * 1024, NK * 128, 512, 1), idesc_g,
+          umma_tf32(tm_dq, desc_kmajor(ds_s + (j / 4) * (ROWS * 128) + (j % 4) * 32), smem_desc(km_s + j * 1024, NK * 128, 512, 1), idesc_g,
                     (i > 0 || j > 0) ? 1u : 0u);
         umma_commit(acc_done);
-        ok = mbar_wait(acc_done, par);
-        if (!ok) { atomicExch(flag, 35); break; }
+        if (i + 1 < iters) {
+          w.wait(((i + 1) & 1) ? s_full1 : s_full0, ((i + 1) >> 1) & 1, 33);
+          if (i + 2 < iters) load_k(i + 2);
+        }
+        w.wait(acc_done, i & 1, 35);
         if (i + 1 < iters) load_m(i + 1);
       }
     }
   } else {
-    const int r = warp * 32 + lane;
+    const int qd = warp & 3, half = warp >> 2;
+    const int r = qd * 32 + lane;
     const int tq = q0 + r;
     const bool valid = tq < T;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_base = (uint32_t)(qd * 32) << 16;
     const float L = valid ? lse[(size_t)h * rows + row0 + tq] : 0.f;
-    const float Dr = valid ? Dv[(size_t)h * rows + row0 + tq] : 0.f;
+    const float Dr = valid ? Ds[(size_t)h * rows + row0 + tq] : 0.f;
     const int lo = (window > 0) ? tq - window + 1 : 0;
-    bool ok = true;
     for (int i = 0; i < iters; i++) {
-      const uint32_t par = i & 1;
-      const int kpos0 = (kb_lo + i) * NK;
-      if (ok) ok = mbar_wait(s_full, par);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) { if (lane == 0) atomicExch(flag, 36); break; }
+      const int kpos0 = (kb_lo + i) * NK + half * NH;
+      w.wait((i & 1) ? s_full1 : s_full0, (i >> 1) & 1, 36);
       tc_fence_after();
-      float s[NK], dp[NK];
-      tmem_ld_cols<NK>(tm_s + lane_base, s);
-      tmem_ld_cols<NK>(tm_dp + lane_base, dp);
+      float s[NH], dp[NH];
+      const uint32_t tm_s = tmem + (i & 1) * 2 * NK + half * NH + lane_base;
+      tmem_ld<NH>(tm_s, s);
+      tmem_ld<NH>(tm_s + NK, dp);
+      const bool interior = (kpos0 + NH - 1 <= q0) && (q0 + ROWS - 1 < T) && (window == 0 || kpos0 >= q0 + ROWS - window);
+      if (interior) {
 #pragma unroll
-      for (int c = 0; c < NK; c++) {
-        const int kg = kpos0 + c;
-        const bool keep = valid && kg <= tq && kg >= lo;
-        float d = 0.f;
-        if (keep) {
-          const float p = exp2f(s[c] * scale2 - L);
-          d = p * (dp[c] * TRUNC_COMP - Dr) * scale;
+        for (int c = 0; c < NH; c++) {
+          const float p = ex2(fmaf(s[c], scale2, -L));
+          s[c] = p * fmaf(dp[c], dp_scale, -Dr);
         }
-        s[c] = d;
+      } else {
+#pragma unroll
+        for (int c = 0; c < NH; c++) {
+          const int kg = kpos0 + c;
+          const bool keep = valid && kg <= tq && kg >= lo;
+          float d = 0.f;
+          if (keep) {
+            const float p = ex2(fmaf(s[c], scale2, -L));
+            d = p * fmaf(dp[c], dp_scale, -Dr);
+          }
+          s[c] = d;
+        }
       }
-      if (i > 0) {
-        if (ok) ok = mbar_wait(acc_done, (i - 1) & 1);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) { if (lane == 0) atomicExch(flag, 37); break; }
-      }
-      store_row_kmajor<NK>(base_ptr + S::DS_OFF, r, s);
+      if (i > 0) w.wait(acc_done, (i - 1) & 1, 37);
+      store_row_kmajor<NH>(base_ptr + S::DS_OFF, r, half * NH, s);
       fence_async_smem();
       tc_fence_before();
       mbar_arrive(p_full);
     }
-    if (ok && iters > 0) {
-      ok = mbar_wait(acc_done, (iters - 1) & 1);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok && lane == 0) atomicExch(flag, 38);
-    }
+    if (iters > 0) w.wait(acc_done, (iters - 1) & 1, 38);
     tc_fence_after();
-    if (ok) {   // warp-uniform: the TMEM loads are warp-wide instructions, only the stores are per-row
-      float* dst0 = gq + (size_t)(row0 + (valid ? tq : 0)) * Hq * HD + (size_t)h * HD;
-#pragma unroll 1
-      for (int c = 0; c < HD / 32; c++) {
-        float t[32];
-        tmem_ld32(tm_dq + lane_base + c * 32, t);
-        float* dst = dst0 + c * 32;
+    {   // warp-uniform TMEM load, per-row store
+      float t[HH];
+      tmem_ld<HH>(tm_dq + half * HH + lane_base, t);
+      if (!w.dead && valid) {
+        float* dst = gq + (size_t)(row0 + tq) * Hq * HD + (size_t)h * HD + half * HH;
 #pragma unroll
-        for (int d = 0; d < 32 && valid; d += 4) {
+        for (int d = 0; d < HH; d += 4) {
           float4 o = accum_q ? *reinterpret_cast<float4*>(dst + d) : make_float4(0, 0, 0, 0);
           o.x += t[d] * TRUNC_COMP; o.y += t[d + 1] * TRUNC_COMP; o.z += t[d + 2] * TRUNC_COMP; o.w += t[d + 3] * TRUNC_COMP;
           *reinterpret_cast<float4*>(dst + d) = o;
@@ -641,10 +696,42 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == MATH_WARPS) {
     tc_fence_after();
     tmem_dealloc(tmem, S::TMEM_COLS);
   }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+template <typename K>
+gt_status set_smem(gt_ctx* ctx, K kern, int bytes, bool* done) {
+  if (!done[ctx->device]) {
+    GT_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    done[ctx->device] = true;
+  }
+  return GT_OK;
+}
+
+template <int HD>
+gt_status launch_fwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, const float* q, const float* k, const float* v,
+                     float* out, float* lse, int* flag) {
+  CUtensorMap mq, mk, mv;
+  const uint64_t qw = (uint64_t)Hq * HD, kw = (uint64_t)Hkv * HD;
+  if (!make_map_2d(&mq, q, qw, rows, qw, ROWS, true) || !make_map_2d(&mk, k, kw, rows, kw, BKV, true) ||
+      !make_map_2d(&mv, v, kw, rows, kw, BKV, false))
+    return gt_fail(ctx, GT_ERR_CUDA, "attention: tensor map encoding failed");
+  auto kern = attn_fwd_tc_kernel<HD>;
+  static bool done[64] = {};
+  gt_status st = set_smem(ctx, kern, FwdSmem<HD>::TOTAL, done);
+  if (st) return st;
+  // the S product's truncation bias is folded into the score scale
+  const float scale2 = 1.4426950408889634f / sqrtf((float)HD) * TRUNC_COMP;
+  dim3 grid(Hq * (rows / T), gt_cdiv(T, ROWS), 1);
+  kern<<<grid, THREADS, FwdSmem<HD>::TOTAL, ctx->stream>>>(mq, mk, mv, out, lse, rows, T, Hq, Hkv, window, scale2, flag);
+  GT_LAUNCHED(ctx, "attn_fwd_tc_kernel");
+  return GT_OK;
 }
 
 template <int HD, int NQ, int NK>
@@ -654,56 +741,54 @@ gt_status launch_bwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, 
   float* D = nullptr;
   gt_status st = gt_scratch(ctx, sizeof(float) * (size_t)rows * Hq, &D);
   if (st) return st;
-  attn_bwd_d_tc_kernel<<<gt_cdiv((long)rows * Hq * 32, 256), 256, 0, ctx->stream>>>(rows, Hq, HD, go, out, D);
-  GT_LAUNCHED(ctx, "attn_bwd_d_tc_kernel");
   const float scale = 1.f / sqrtf((float)HD);
+  attn_bwd_d_tc_kernel<<<gt_cdiv((long)rows * Hq * 32, 256), 256, 0, ctx->stream>>>(rows, Hq, HD, scale, go, out, D);
+  GT_LAUNCHED(ctx, "attn_bwd_d_tc_kernel");
   const float scale2 = 1.4426950408889634f * scale * TRUNC_COMP;
+  const float dp_scale = scale * TRUNC_COMP;
   const uint64_t qw = (uint64_t)Hq * HD, kw = (uint64_t)Hkv * HD;
   const int nseq = rows / T;
   if (gk || gv) {
     CUtensorMap mK, mV, mQk, mQm, mGk, mGm;
-    if (!make_map_2d(&mK, k, kw, rows, kw, 128, true) || !make_map_2d(&mV, v, kw, rows, kw, 128, true) ||
+    if (!make_map_2d(&mK, k, kw, rows, kw, ROWS, true) || !make_map_2d(&mV, v, kw, rows, kw, ROWS, true) ||
         !make_map_2d(&mQk, q, qw, rows, qw, NQ, true) || !make_map_2d(&mQm, q, qw, rows, qw, NQ, false) ||
         !make_map_2d(&mGk, go, qw, rows, qw, NQ, true) || !make_map_2d(&mGm, go, qw, rows, qw, NQ, false))
       return gt_fail(ctx, GT_ERR_CUDA, "attention backward: tensor map encoding failed");
     auto kern = attn_bwd_dkv_tc_kernel<HD, NQ>;
-    static bool attr_set[64] = {};
-    if (!attr_set[ctx->device]) {
-      GT_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvSmem<HD, NQ>::TOTAL));
-      attr_set[ctx->device] = true;
-    }
-    dim3 grid(Hkv * nseq, gt_cdiv(T, 128), 1);
-    kern<<<grid, 160, DkvSmem<HD, NQ>::TOTAL, ctx->stream>>>(mK, mV, mQk, mQm, mGk, mGm, lse, D, gk, accum_k, gv, accum_v, rows, T, Hq, Hkv,
-                                                            window, scale2, scale, flag);
+    static bool done[64] = {};
+    st = set_smem(ctx, kern, DkvSmem<HD, NQ>::TOTAL, done);
+    if (st) return st;
+    dim3 grid(Hkv * nseq, gt_cdiv(T, ROWS), 1);
+    kern<<<grid, THREADS, DkvSmem<HD, NQ>::TOTAL, ctx->stream>>>(mK, mV, mQk, mQm, mGk, mGm, lse, D, gk, accum_k, gv, accum_v, rows, T, Hq,
+                                                                Hkv, window, scale2, dp_scale, flag);
     GT_LAUNCHED(ctx, "attn_bwd_dkv_tc_kernel");
   }
   if (gq) {
     CUtensorMap mQ, mG, mKk, mVk, mKm;
-    if (!make_map_2d(&mQ, q, qw, rows, qw, 128, true) || !make_map_2d(&mG, go, qw, rows, qw, 128, true) ||
+    if (!make_map_2d(&mQ, q, qw, rows, qw, ROWS, true) || !make_map_2d(&mG, go, qw, rows, qw, ROWS, true) ||
         !make_map_2d(&mKk, k, kw, rows, kw, NK, true) || !make_map_2d(&mVk, v, kw, rows, kw, NK, true) ||
         !make_map_2d(&mKm, k, kw, rows, kw, NK, false))
       return gt_fail(ctx, GT_ERR_CUDA, "attention backward: tensor map encoding failed");
     auto kern = attn_bwd_dq_tc_kernel<HD, NK>;
-    static bool attr_set[64] = {};
-    if (!attr_set[ctx->device]) {
-      GT_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DqSmem<HD, NK>::TOTAL));
-      attr_set[ctx->device] = true;
-    }
-    dim3 grid(Hq * nseq, gt_cdiv(T, 128), 1);
-    kern<<<grid, 160, DqSmem<HD, NK>::TOTAL, ctx->stream>>>(mQ, mG, mKk, mVk, mKm, lse, D, gq, accum_q, rows, T, Hq, Hkv, window, scale2,
-                                                           scale, flag);
+    static bool done[64] = {};
+    st = set_smem(ctx, kern, DqSmem<HD, NK>::TOTAL, done);
+    if (st) return st;
+    dim3 grid(Hq * nseq, gt_cdiv(T, ROWS), 1);
+    kern<<<grid, THREADS, DqSmem<HD, NK>::TOTAL, ctx->stream>>>(mQ, mG, mKk, mVk, mKm, lse, D, gq, accum_q, rows, T, Hq, Hkv, window, scale2,
+                                                               dp_scale, flag);
     GT_LAUNCHED(ctx, "attn_bwd_dq_tc_kernel");
   }
   return GT_OK;
 }
+
+bool tc_shape_ok(int T, int hd) { return (hd == 32 || hd == 64 || hd == 128) && T >= 64; }
 
 }  // namespace
 
 gt_status gt_attention_fwd_tc(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int hd, int window, const float* q, const float* k,
                               const float* v, float* out, float* lse, bool* handled) {
   *handled = false;
-  if (hd != 32 && hd != 64 && hd != 128) return GT_OK;
-  if (T < 64) return GT_OK;   // tiny sequences stay on the f32 kernels
+  if (!tc_shape_ok(T, hd)) return GT_OK;   // other head sizes and tiny sequences stay on the f32 kernels
   if ((((uintptr_t)q) | ((uintptr_t)k) | ((uintptr_t)v) | ((uintptr_t)out)) & 15) return GT_OK;
   int* flag = device_flag(ctx);
   if (!flag) return GT_OK;
@@ -720,8 +805,7 @@ gt_status gt_attention_bwd_tc(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int
                               const float* v, const float* out, const float* lse, const float* go, float* gq, int accum_q, float* gk,
                               int accum_k, float* gv, int accum_v, bool* handled) {
   *handled = false;
-  if (hd != 32 && hd != 64 && hd != 128) return GT_OK;
-  if (T < 64) return GT_OK;
+  if (!tc_shape_ok(T, hd)) return GT_OK;
   if ((((uintptr_t)q) | ((uintptr_t)k) | ((uintptr_t)v) | ((uintptr_t)go) | ((uintptr_t)gq) | ((uintptr_t)gk) | ((uintptr_t)gv)) & 15) return GT_OK;
   int* flag = device_flag(ctx);
   if (!flag) return GT_OK;

@@ -1,6 +1,7 @@
 // Tensor-core matrix product for sm_100a: tcgen05.mma (kind::tf32, f32 operands read straight from
-// shared memory, f32 accumulators in TMEM), operands staged by TMA into 128B-swizzled tiles, a 4-stage
-// mbarrier pipeline, one elected thread issuing TMA, one issuing MMA, four warps draining TMEM.
+// shared memory, f32 accumulators in TMEM), operands staged by TMA into 128B-swizzled tiles, a 5/6-stage
+// mbarrier pipeline, persistent CTAs (one per SM) with two TMEM accumulators: one elected thread issues TMA, one
+// issues MMA, four warps drain the finished accumulator while the next tile is being accumulated.
 // Covers the three layouts of WebGPUBackend.gemm (src/backend/webgpu.ts:1654-1671; srcGemm
 // src/backend/wgsl.ts:87-196): NT (forward y = x.W^T), NN (dX += dY.W), TN (dW += dY^T.X), with ragged
 // edges handled by TMA zero fill and guarded stores, `accum` by a read-modify-write epilogue, and split-K
@@ -22,7 +23,6 @@ namespace {
 constexpr int BM = 128;          // UMMA M (cta_group::1): accumulator row i lives in TMEM lane i
 constexpr int BK = 32;           // f32 elements per stage along K: 128 bytes = one swizzle row
 constexpr int UMMA_K = 8;        // tf32: 32 bytes of K per instruction
-constexpr int STAGES = 4;
 constexpr int THREADS = 192;     // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
 
 template <int BN>
@@ -30,9 +30,14 @@ struct Smem {
   static constexpr int A_BYTES = BM * BK * 4;   // 16 KB
   static constexpr int B_BYTES = BN * BK * 4;
   static constexpr int STAGE = A_BYTES + B_BYTES;
+  static constexpr int STAGES = BN <= 128 ? 6 : 5;
   static constexpr int TOTAL = STAGES * STAGE + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr uint32_t TMEM_COLS = 2 * BN <= 256 ? 256 : 512;   // two accumulators
 };
 
+// Persistent: each CTA walks output tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... (n fastest, then m, then the
+// split-K slice), so CTAs running at the same time share their A row-blocks in L2. The accumulator is double-buffered
+// in TMEM: while the epilogue warps drain tile i, the MMA warp is already accumulating tile i+1.
 // A_K: A is K-major in memory (NT, NN); else MN-major ([K, M], TN). B_K: B is K-major (NT); else [K, N] (NN, TN).
 template <bool A_K, bool B_K, int BN>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -40,128 +45,148 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
                  int M, int N, int K, int accum, int ksplit, int* __restrict__ flag) {
   extern __shared__ uint8_t smem_raw[];
   using S = Smem<BN>;
-  constexpr uint32_t TMEM_COLS = BN <= 128 ? 128 : 256;
+  constexpr int STAGES = S::STAGES;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bars = base + STAGES * S::STAGE;          // full[STAGES], empty[STAGES], done, tmem slot
+  const uint32_t bars = base + STAGES * S::STAGE;   // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], tmem slot
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-  const uint32_t done_bar = bars + 8u * (2 * STAGES);
-  const uint32_t tmem_slot = bars + 8u * (2 * STAGES + 1);
+  auto acc_full = [&](int b) { return bars + 8u * (2 * STAGES + b); };
+  auto acc_empty = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
+  const uint32_t tmem_slot = bars + 8u * (2 * STAGES + 4);
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-  // split-K: slice z owns K blocks [kb0, kb1)
+  const int tiles_n = (N + BN - 1) / BN, tiles_m = (M + BM - 1) / BM;
+  const int ntiles = tiles_n * tiles_m * ksplit;
   const int kblocks = (K + BK - 1) / BK;
-  const int per = (kblocks + ksplit - 1) / ksplit;
-  const int kb0 = blockIdx.z * per;
-  const int kb1 = min(kblocks, kb0 + per);
-  const int nk = kb1 - kb0;
+  const int per = (kblocks + ksplit - 1) / ksplit;   // K blocks per split-K slice
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    mbar_init(done_bar, 1);
+    for (int b = 0; b < 2; b++) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 128); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  if (warp == 1) tmem_alloc(tmem_slot, S::TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot_ptr;
-  bool ok = true;
+  bool dead = false;   // set once a bounded wait has expired: later waits are skipped, control flow stays the same
+  auto wait = [&](uint32_t bar, uint32_t parity, int code) {
+    if (dead) return;
+    if (!mbar_wait(bar, parity)) { dead = true; atomicExch(flag, code); }
+  };
 
-  if (nk > 0) {
-    if (warp == 0 && lane == 0) {
+  if (warp == 0) {
+    if (lane == 0) {
       // ---- TMA producer ----
-      for (int i = 0; i < nk && ok; i++) {
-        const int s = i % STAGES;
-        ok = mbar_wait(empty_bar(s), ((i / STAGES) & 1) ^ 1);
-        if (!ok) { atomicExch(flag, 1); break; }
-        const uint32_t a_dst = base + s * S::STAGE, b_dst = a_dst + S::A_BYTES;
-        const int k0 = (kb0 + i) * BK;
-        mbar_expect_tx(full_bar(s), S::STAGE);
-        if (A_K) tma_load_2d(a_dst, &mapA, k0, m0, full_bar(s));
-        else
-          for (int c = 0; c < BM / 32; c++) tma_load_2d(a_dst + c * 4096, &mapA, m0 + 32 * c, k0, full_bar(s));
-        if (B_K) tma_load_2d(b_dst, &mapB, k0, n0, full_bar(s));
-        else
-          for (int c = 0; c < BN / 32; c++) tma_load_2d(b_dst + c * 4096, &mapB, n0 + 32 * c, k0, full_bar(s));
+      uint32_t it = 0;
+      for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+        const int n0 = (t % tiles_n) * BN, m0 = ((t / tiles_n) % tiles_m) * BM, z = t / (tiles_n * tiles_m);
+        const int kb0 = z * per, kb1 = min(kblocks, kb0 + per);
+        for (int kb = kb0; kb < kb1; kb++, it++) {
+          const int s = it % STAGES;
+          wait(empty_bar(s), ((it / STAGES) & 1) ^ 1, 1);
+          const uint32_t a_dst = base + s * S::STAGE, b_dst = a_dst + S::A_BYTES;
+          const int k0 = kb * BK;
+          mbar_expect_tx(full_bar(s), S::STAGE);
+          if (A_K) tma_load_2d(a_dst, &mapA, k0, m0, full_bar(s));
+          else
+            for (int c = 0; c < BM / 32; c++) tma_load_2d(a_dst + c * 4096, &mapA, m0 + 32 * c, k0, full_bar(s));
+          if (B_K) tma_load_2d(b_dst, &mapB, k0, n0, full_bar(s));
+          else
+            for (int c = 0; c < BN / 32; c++) tma_load_2d(b_dst + c * 4096, &mapB, n0 + 32 * c, k0, full_bar(s));
+        }
       }
-    } else if (warp == 1 && lane == 0) {
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
       // ---- MMA issuer ----
       constexpr uint32_t idesc = idesc_tf32(!A_K, !B_K, BM, BN);
-      for (int i = 0; i < nk && ok; i++) {
-        const int s = i % STAGES;
-        ok = mbar_wait(full_bar(s), (i / STAGES) & 1);
-        if (!ok) { atomicExch(flag, 2); break; }
+      uint32_t it = 0, tl = 0;
+      for (int t = blockIdx.x; t < ntiles; t += gridDim.x, tl++) {
+        const int z = t / (tiles_n * tiles_m);
+        const int kb0 = z * per, kb1 = min(kblocks, kb0 + per);
+        const int b = tl & 1;
+        wait(acc_empty(b), ((tl >> 1) & 1) ^ 1, 4);   // the epilogue has drained this accumulator
         tc_fence_after();
-        const uint32_t a_src = base + s * S::STAGE, b_src = a_src + S::A_BYTES;
+        const uint32_t d_tmem = tmem + b * BN;
+        for (int kb = kb0; kb < kb1; kb++, it++) {
+          const int s = it % STAGES;
+          wait(full_bar(s), (it / STAGES) & 1, 2);
+          tc_fence_after();
+          const uint32_t a_src = base + s * S::STAGE, b_src = a_src + S::A_BYTES;
 #pragma unroll
-        for (int j = 0; j < BK / UMMA_K; j++) {
-          const uint64_t ad = A_K ? desc_kmajor(a_src + j * 32) : desc_mnmajor(a_src + j * 1024);
-          const uint64_t bd = B_K ? desc_kmajor(b_src + j * 32) : desc_mnmajor(b_src + j * 1024);
-          umma_tf32(tmem, ad, bd, idesc, (i > 0 || j > 0) ? 1u : 0u);
+          for (int j = 0; j < BK / UMMA_K; j++) {
+            const uint64_t ad = A_K ? desc_kmajor(a_src + j * 32) : desc_mnmajor(a_src + j * 1024);
+            const uint64_t bd = B_K ? desc_kmajor(b_src + j * 32) : desc_mnmajor(b_src + j * 1024);
+            umma_tf32(d_tmem, ad, bd, idesc, (kb > kb0 || j > 0) ? 1u : 0u);
+          }
+          umma_commit(empty_bar(s));   // the stage is free once these MMAs have read it
         }
-        umma_commit(empty_bar(s));   // the stage is free once these MMAs have read it
+        umma_commit(acc_full(b));      // accumulator complete
       }
-      umma_commit(done_bar);         // accumulator complete
     }
-  }
-
-  if (warp >= 2) {
+  } else {
     // ---- epilogue: warp w may touch TMEM lanes [32*(w%4), 32*(w%4)+32) ----
     const int q = warp & 3;
-    const int row = m0 + q * 32 + lane;
-    bool have = nk > 0;
-    if (have) {
-      have = mbar_wait(done_bar, 0);
-      if (!have && lane == 0) atomicExch(flag, 3);
-      have = __all_sync(0xffffffffu, have);
-    }
-    tc_fence_after();
-    if (have) {
-      const bool vec = (N & 3) == 0;
+    const bool vec = (N & 3) == 0;
+    uint32_t tl = 0;
+    for (int t = blockIdx.x; t < ntiles; t += gridDim.x, tl++) {
+      const int n0 = (t % tiles_n) * BN, m0 = ((t / tiles_n) % tiles_m) * BM, z = t / (tiles_n * tiles_m);
+      const int b = tl & 1;
+      const bool have = z * per < kblocks;     // an empty split-K slice issues no MMA and contributes nothing
+      const int row = m0 + q * 32 + lane;
+      if (have) wait(acc_full(b), (tl >> 1) & 1, 3);
+      dead = __any_sync(0xffffffffu, dead);
+      tc_fence_after();
+      if (have) {
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; c++) {
-        const int col0 = n0 + c * 32;
-        if (col0 >= N) break;   // uniform across the warp
-        float v[32];
-        tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
+        for (int c = 0; c < BN / 32; c++) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= N) break;   // uniform across the warp
+          float v[32];
+          tmem_ld32(tmem + b * BN + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
 #pragma unroll
-        for (int j = 0; j < 32; j++) v[j] *= TRUNC_COMP;
-        if (row < M) {
-          float* dst = C + (size_t)row * N + col0;
-          if (vec && col0 + 32 <= N) {
-            if (ksplit > 1) {
+          for (int j = 0; j < 32; j++) v[j] *= TRUNC_COMP;
+          if (row < M && !dead) {
+            float* dst = C + (size_t)row * N + col0;
+            if (vec && col0 + 32 <= N) {
+              if (ksplit > 1) {
 #pragma unroll
-              for (int j = 0; j < 32; j += 4) atomicAdd(reinterpret_cast<float4*>(dst + j), make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));
-            } else if (accum) {
+                for (int j = 0; j < 32; j += 4) atomicAdd(reinterpret_cast<float4*>(dst + j), make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));
+              } else if (accum) {
 #pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                float4 o = *reinterpret_cast<float4*>(dst + j);
-                o.x += v[j]; o.y += v[j + 1]; o.z += v[j + 2]; o.w += v[j + 3];
-                *reinterpret_cast<float4*>(dst + j) = o;
+                for (int j = 0; j < 32; j += 4) {
+                  float4 o = *reinterpret_cast<float4*>(dst + j);
+                  o.x += v[j]; o.y += v[j + 1]; o.z += v[j + 2]; o.w += v[j + 3];
+                  *reinterpret_cast<float4*>(dst + j) = o;
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
               }
             } else {
 #pragma unroll
-              for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-            }
-          } else {
-            for (int j = 0; j < 32; j++) {
-              if (col0 + j >= N) break;
-              if (ksplit > 1) atomicAdd(dst + j, v[j]);
-              else dst[j] = accum ? dst[j] + v[j] : v[j];
+              for (int j = 0; j < 32; j++) {
+                if (col0 + j < N) {
+                  if (ksplit > 1) atomicAdd(dst + j, v[j]);
+                  else dst[j] = accum ? dst[j] + v[j] : v[j];
+                }
+              }
             }
           }
         }
       }
+      tc_fence_before();
+      mbar_arrive(acc_empty(b));
     }
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem, TMEM_COLS);
+    tmem_dealloc(tmem, S::TMEM_COLS);
   }
 }
 
@@ -178,7 +203,8 @@ gt_status launch(gt_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, floa
     GT_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<BN>::TOTAL));
     attr_set[ctx->device] = true;
   }
-  dim3 grid(gt_cdiv(N, BN), gt_cdiv(M, BM), ksplit);
+  const long ntiles = (long)gt_cdiv(N, BN) * gt_cdiv(M, BM) * ksplit;
+  dim3 grid((unsigned)min((long)ctx->sm_count, ntiles), 1, 1);
   kern<<<grid, THREADS, Smem<BN>::TOTAL, ctx->stream>>>(ma, mb, c, M, N, K, accum, ksplit, g_flag[ctx->device]);
   GT_LAUNCHED(ctx, "gemm_tf32_kernel");
   return GT_OK;
