@@ -347,6 +347,34 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_profile(args):
+    """One eager step at the benchmark shape with the backend's per-label profiler open: GPU time per entry point
+    (and per product shape), each call bracketed by events and synchronised. Shares, not throughput."""
+    from gguf_trainer_b200.arch import buildModel, smolLM2_135M
+    from gguf_trainer_b200.backend import requireGPU
+    from gguf_trainer_b200.optim import AdamWGpu
+    from gguf_trainer_b200.train import CudaStep
+    cfg = smolLM2_135M()
+    B, T = args.batch, args.seq
+    gpu = requireGPU("the profile", precision=args.precision)
+    m = buildModel(cfg, 1234)
+    for p in m.params():
+        gpu.keepGradOnDevice(p)
+    opt = AdamWGpu(gpu, m.params(), lr=1e-3, beta1=0.9, beta2=0.95, weightDecay=0.1, clip=1.0)
+    ids = zipf_tokens(B * T + 1, cfg.vocabSize, 1.1, 99)
+    step = CudaStep(m, gpu, B, T, capture=False)
+    for _ in range(2):
+        step.run(ids[:-1], ids[1:]); opt.recordStep(); gpu.sync([])
+    gpu.startProfile()
+    step.run(ids[:-1], ids[1:]); opt.recordStep()
+    tot = gpu.stopProfile()
+    gpu.sync([])
+    total = sum(v["ms"] for v in tot.values())
+    print(f"# one step, {B} x {T} tokens, precision {args.precision}: {total:.2f} ms summed over {sum(v['count'] for v in tot.values())} calls")
+    for k, v in sorted(tot.items(), key=lambda kv: -kv[1]["ms"]):
+        print(f"{v['ms']:9.3f} ms {100 * v['ms'] / total:5.1f}%  n={v['count']:4d}  avg {1e3 * v['ms'] / v['count']:8.1f} us  {k}")
+
+
 def run_micro(args):
     """One op of the step at the benchmark shape, launched `--steps` times between two events: prints its
     time and achieved algorithmic rate. Meant for `ncu` captures of a single kernel and for the per-kernel
@@ -415,11 +443,14 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=256)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--profile", action="store_true", help="per-entry-point GPU time of one eager step")
     ap.add_argument("--micro", default="", help="time one op of the step instead: attention | gemm")
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--window", type=int, default=0)
     args = ap.parse_args()
-    if args.micro:
+    if args.profile:
+        run_profile(args)
+    elif args.micro:
         run_micro(args)
     elif args.impl == "reference":
         run_reference(args)

@@ -147,6 +147,8 @@ class CudaBackend:
         self._stateBufs: Dict[int, int] = {}
         self._readback = 0
         self._seedBuf = 0
+        self._pendingAct = {}   # id(tensor) -> (tensor, op code, input tensor): activations not launched yet
+        self.fuseGatedUnits = True
         self._finalizer = weakref.finalize(self, _destroy_ctx, self.lib, self.ctx)
 
     # ------------------------------------------------------------------ plumbing
@@ -270,6 +272,8 @@ class CudaBackend:
     def _entryFor(self, t: Tensor) -> _Entry:
         """webgpu.ts:1539-1573: externals (params, test inputs) get persistent buffers on first use."""
         e = self._entries.get(t)
+        if e is None and id(t) in self._pendingAct:
+            e = self._materializeAct(t)
         if e is None:
             nbytes = t.size * 4
             if self._capturing:
@@ -280,6 +284,13 @@ class CudaBackend:
             self._write(e.data, t.data)
         if e.external and id(t) not in self._touched:
             self._touched[id(t)] = t
+        return e
+
+    def _entryOf(self, t: Tensor):
+        """The device entry of a tensor some op produced (launching it first if it is a deferred activation), or None."""
+        e = self._entries.get(t)
+        if e is None and id(t) in self._pendingAct:
+            e = self._materializeAct(t)
         return e
 
     def _makeOut(self, shape, prev) -> tuple:
@@ -338,6 +349,8 @@ class CudaBackend:
         if self._capturing:
             raise _lib.GtError(4, "sync() inside a graph capture")
         self._readback = 0
+        self._flushPendingActs(only=list(reads))
+        self._pendingAct.clear()
         seen = set()
         for t in reads:
             if id(t) in seen:
@@ -403,6 +416,7 @@ class CudaBackend:
             raise RuntimeError(
                 f"endRegion: mark {mark} is past the {len(self._transients)} live transients; "
                 f"a sync() or reclaim ran inside the region")
+        self._flushPendingActs(only=list(keep))
         keepBufs = set()
         for t in keep:
             e = self._entries.get(t)
@@ -420,7 +434,7 @@ class CudaBackend:
     def seedGradFrom(self, dst: Tensor, src: Tensor):
         """webgpu.ts:748-761."""
         self._ensureBackwardBegun()
-        ed, es = self._entries.get(dst), self._entries.get(src)
+        ed, es = self._entryOf(dst), self._entryOf(src)
         if ed is None or es is None:
             raise RuntimeError("seedGradFrom: tensor has no GPU buffers")
         if dst.size != src.size:
@@ -431,7 +445,7 @@ class CudaBackend:
     def seedGradFromHost(self, t: Tensor):
         """webgpu.ts:1432-1437."""
         self._ensureBackwardBegun()
-        e = self._entries.get(t)
+        e = self._entryOf(t)
         if e is None:
             raise RuntimeError("seedGradFromHost: tensor has no GPU buffers")
         self._write(e.grad, t.grad)
@@ -582,13 +596,78 @@ class CudaBackend:
         return self._elementwise("add", a, b, 0.0)
 
     def mul(self, a, b):
+        if a is not b:
+            for act, other in ((a, b), (b, a)):
+                if id(act) in self._pendingAct and id(other) not in self._pendingAct:
+                    return self._gatedUnit(act, other)
         return self._elementwise("mul", a, b, 0.0)
 
     def silu(self, x):
-        return self._elementwise("silu", x, None, 0.0)
+        return self._activation("silu", x)
 
     def gelu(self, x):
-        return self._elementwise("gelu", x, None, 0.0)
+        return self._activation("gelu", x)
+
+    # An activation is not launched when it is recorded: if its only use turns out to be a product (the gated FFN
+    # unit silu(gate)*up / gelu(gate)*up), one fused kernel does both and the activated gate is never written. Any
+    # other use (another op, a sync that reads it, the end of a recompute region) launches it then, unchanged.
+    def _activation(self, op: str, x: Tensor) -> Tensor:
+        if not self.fuseGatedUnits:
+            return self._elementwise(op, x, None, 0.0)
+        self._beginForwardOp()
+        self._entryFor(x)
+        t = Tensor.zeros(x.shape)
+        t._prev = [x]
+        self._pendingAct[id(t)] = (t, _EW[op], x)
+
+        def _bw():
+            e = self._entries.get(t)
+            if e is None or not e.gradLive:
+                return          # consumed only by fused products, which sent their gradient straight to x
+            self._ensureBackwardBegun()
+            ex = self._entries[x]
+            gx, ax = self._gradTarget(x, ex)
+            self._check(self.lib.gt_ew_bwd(self.ctx, _EW[op], x.size, ex.data, 0, 0.0, e.grad, gx, ax, 0, 0))
+
+        t._backward = _bw
+        return t
+
+    def _materializeAct(self, t: Tensor) -> _Entry:
+        _t, code, x = self._pendingAct.pop(id(t))
+        ex = self._entries[x]
+        nbytes = t.size * 4
+        e = _Entry(self._acquireRecycled(nbytes), self._acquireRecycled(nbytes), nbytes, False, t.size)
+        self._entries[t] = e
+        self._check(self.lib.gt_ew_fwd(self.ctx, code, t.size, ex.data, 0, 0.0, e.data))
+        return e
+
+    def _flushPendingActs(self, only=None):
+        for key in list(self._pendingAct.keys()):
+            t = self._pendingAct[key][0]
+            if only is None or any(t is o for o in only):
+                self._materializeAct(t)
+
+    def _gatedUnit(self, act: Tensor, u: Tensor) -> Tensor:
+        _t, code, x = self._pendingAct[id(act)]
+        self._beginForwardOp()
+        ex, eu = self._entries[x], self._entryFor(u)
+        out, eo = self._makeOut(act.shape, [act, u])
+        n = act.size
+        self._check(self.lib.gt_glu_fwd(self.ctx, code, n, ex.data, eu.data, eo.data))
+
+        def _bw():
+            self._ensureBackwardBegun()
+            go = self._gradSource(eo)
+            gx, ax = self._gradTarget(x, ex)
+            gu, au = self._gradTarget(u, eu)
+            if gx and gx == gu:      # act(x) * x: one buffer takes both terms, in two passes
+                self._check(self.lib.gt_glu_bwd(self.ctx, code, n, ex.data, eu.data, go, gx, ax, 0, 0))
+                self._check(self.lib.gt_glu_bwd(self.ctx, code, n, ex.data, eu.data, go, 0, 0, gu, 1))
+            else:
+                self._check(self.lib.gt_glu_bwd(self.ctx, code, n, ex.data, eu.data, go, gx, ax, gu, au))
+
+        out._backward = _bw
+        return out
 
     def scale(self, x, c):
         return self._elementwise("scale", x, None, float(c))

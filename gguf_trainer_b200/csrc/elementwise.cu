@@ -105,6 +105,47 @@ __global__ void ew_bwd_kernel(size_t n, const float* __restrict__ a, const float
   }
 }
 
+// Gated unit in one pass: out = act(x) * u with act = silu (SwiGLU) or tanh-gelu (GeGLU). The reference issues the
+// activation and the product as two ops (src/arch/llama.ts:209-211, gemma3.ts:208-210); fused, the activated gate never
+// touches HBM: forward 12 B/element instead of 20, backward 20 instead of 32.
+template <int OP>
+__global__ void glu_fwd_kernel(size_t n, const float* __restrict__ x, const float* __restrict__ u, float* __restrict__ out) {
+  size_t n4 = n / 4, stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    float4 a = ((const float4*)x)[i], b = ((const float4*)u)[i], r;
+    r.x = ew_f<OP>(a.x, 0.f, 0.f) * b.x; r.y = ew_f<OP>(a.y, 0.f, 0.f) * b.y;
+    r.z = ew_f<OP>(a.z, 0.f, 0.f) * b.z; r.w = ew_f<OP>(a.w, 0.f, 0.f) * b.w;
+    ((float4*)out)[i] = r;
+  }
+  for (size_t i = n4 * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) out[i] = ew_f<OP>(x[i], 0.f, 0.f) * u[i];
+}
+
+// gx (+)= g * u * act'(x) ; gu (+)= g * act(x)
+template <int OP>
+__global__ void glu_bwd_kernel(size_t n, const float* __restrict__ x, const float* __restrict__ u, const float* __restrict__ g,
+                               float* gx, int acc_x, float* gu, int acc_u) {
+  size_t n4 = n / 4, stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    const float4 a = ((const float4*)x)[i], b = ((const float4*)u)[i], go = ((const float4*)g)[i];
+    if (gx) {
+      float4 o = acc_x ? ((float4*)gx)[i] : make_float4(0, 0, 0, 0);
+      o.x += go.x * b.x * ew_da<OP>(a.x, 0.f, 0.f); o.y += go.y * b.y * ew_da<OP>(a.y, 0.f, 0.f);
+      o.z += go.z * b.z * ew_da<OP>(a.z, 0.f, 0.f); o.w += go.w * b.w * ew_da<OP>(a.w, 0.f, 0.f);
+      ((float4*)gx)[i] = o;
+    }
+    if (gu) {
+      float4 o = acc_u ? ((float4*)gu)[i] : make_float4(0, 0, 0, 0);
+      o.x += go.x * ew_f<OP>(a.x, 0.f, 0.f); o.y += go.y * ew_f<OP>(a.y, 0.f, 0.f);
+      o.z += go.z * ew_f<OP>(a.z, 0.f, 0.f); o.w += go.w * ew_f<OP>(a.w, 0.f, 0.f);
+      ((float4*)gu)[i] = o;
+    }
+  }
+  for (size_t i = n4 * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    if (gx) gx[i] = (acc_x ? gx[i] : 0.f) + g[i] * u[i] * ew_da<OP>(x[i], 0.f, 0.f);
+    if (gu) gu[i] = (acc_u ? gu[i] : 0.f) + g[i] * ew_f<OP>(x[i], 0.f, 0.f);
+  }
+}
+
 inline int ew_grid(gt_ctx* ctx, size_t n) {
   size_t want = (n / 4 + 255) / 256;
   size_t cap = (size_t)ctx->sm_count * 8;
@@ -155,6 +196,34 @@ gt_status gt_ew_bwd(gt_ctx* ctx, int32_t op, uint64_t n, gt_buf a, gt_buf b, flo
     default: return gt_fail(ctx, GT_ERR_ARG, "gt_ew_bwd: unknown op %d", op);
   }
   GT_LAUNCHED(ctx, "ew_bwd_kernel");
+  return GT_OK;
+}
+
+gt_status gt_glu_fwd(gt_ctx* ctx, int32_t op, uint64_t n, gt_buf x, gt_buf u, gt_buf out) {
+  if (n == 0) return GT_OK;
+  const float* px = gt_ptr<const float>(x); const float* pu = gt_ptr<const float>(u); float* po = gt_ptr<float>(out);
+  GT_REQUIRE(ctx, px && pu && po && aligned16(px) && aligned16(pu) && aligned16(po), "gt_glu_fwd: operands must be non-null and 16-byte aligned");
+  GT_REQUIRE(ctx, op == GT_EW_SILU || op == GT_EW_GELU, "gt_glu_fwd: the gate activation must be silu or gelu, got op %d", op);
+  int grid = ew_grid(ctx, n);
+  if (op == GT_EW_SILU) glu_fwd_kernel<GT_EW_SILU><<<grid, 256, 0, ctx->stream>>>(n, px, pu, po);
+  else glu_fwd_kernel<GT_EW_GELU><<<grid, 256, 0, ctx->stream>>>(n, px, pu, po);
+  GT_LAUNCHED(ctx, "glu_fwd_kernel");
+  return GT_OK;
+}
+
+gt_status gt_glu_bwd(gt_ctx* ctx, int32_t op, uint64_t n, gt_buf x, gt_buf u, gt_buf gout, gt_buf gx, int32_t accum_x, gt_buf gu,
+                     int32_t accum_u) {
+  if (n == 0 || (!gx && !gu)) return GT_OK;
+  const float* px = gt_ptr<const float>(x); const float* pu = gt_ptr<const float>(u); const float* pg = gt_ptr<const float>(gout);
+  float* pgx = gt_ptr<float>(gx); float* pgu = gt_ptr<float>(gu);
+  GT_REQUIRE(ctx, px && pu && pg && aligned16(px) && aligned16(pu) && aligned16(pg) && aligned16(pgx) && aligned16(pgu),
+             "gt_glu_bwd: operands must be non-null and 16-byte aligned");
+  GT_REQUIRE(ctx, op == GT_EW_SILU || op == GT_EW_GELU, "gt_glu_bwd: the gate activation must be silu or gelu, got op %d", op);
+  GT_REQUIRE(ctx, !pgx || pgx != pgu, "gt_glu_bwd: the two gradient outputs alias");
+  int grid = ew_grid(ctx, n);
+  if (op == GT_EW_SILU) glu_bwd_kernel<GT_EW_SILU><<<grid, 256, 0, ctx->stream>>>(n, px, pu, pg, pgx, accum_x, pgu, accum_u);
+  else glu_bwd_kernel<GT_EW_GELU><<<grid, 256, 0, ctx->stream>>>(n, px, pu, pg, pgx, accum_x, pgu, accum_u);
+  GT_LAUNCHED(ctx, "glu_bwd_kernel");
   return GT_OK;
 }
 

@@ -94,6 +94,88 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(int rows, int d, const
   }
 }
 
+// 128-bit variant for d % 4 == 0: lane owns float4 columns lane, lane+32, ... (V4 of them). One CTA per SM with 16
+// warps striding over the rows keeps the number of CTAs that finish with global atomics on dw at the SM count.
+template <int V4, int TH>
+__global__ void __launch_bounds__(TH) rmsnorm_bwd_vec_kernel(int rows, int d, const float* __restrict__ x, const float* __restrict__ w,
+                                                              const float* __restrict__ rinv, const float* __restrict__ g, float* gx,
+                                                              int accum_x, float* gw) {
+  extern __shared__ float sdw[];
+  const int lane = threadIdx.x & 31;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const int d4 = d >> 2;
+  if (gw) {
+    for (int j = threadIdx.x; j < d; j += blockDim.x) sdw[j] = 0.f;
+    __syncthreads();
+  }
+  float4 wv[V4], dwv[V4];
+#pragma unroll
+  for (int i = 0; i < V4; i++) {
+    const int j = lane + 32 * i;
+    wv[i] = j < d4 ? reinterpret_cast<const float4*>(w)[j] : make_float4(0, 0, 0, 0);
+    dwv[i] = make_float4(0, 0, 0, 0);
+  }
+  const float invd = 1.f / (float)d;
+  for (int row = warp; row < rows; row += nwarps) {
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)row * d);
+    const float4* gr = reinterpret_cast<const float4*>(g + (size_t)row * d);
+    float4 xv[V4], gv[V4];
+    float S = 0.f;
+#pragma unroll
+    for (int i = 0; i < V4; i++) {
+      const int j = lane + 32 * i;
+      xv[i] = j < d4 ? xr[j] : make_float4(0, 0, 0, 0);
+      gv[i] = j < d4 ? gr[j] : make_float4(0, 0, 0, 0);
+      S = fmaf(gv[i].x * wv[i].x, xv[i].x, S); S = fmaf(gv[i].y * wv[i].y, xv[i].y, S);
+      S = fmaf(gv[i].z * wv[i].z, xv[i].z, S); S = fmaf(gv[i].w * wv[i].w, xv[i].w, S);
+    }
+    S = warp_sum(S);
+    const float r = rinv[row];
+    const float k = r * r * r * S * invd;
+    if (gx) {
+      float4* o = reinterpret_cast<float4*>(gx + (size_t)row * d);
+#pragma unroll
+      for (int i = 0; i < V4; i++) {
+        const int j = lane + 32 * i;
+        if (j < d4) {
+          float4 v;
+          v.x = wv[i].x * r * gv[i].x - xv[i].x * k; v.y = wv[i].y * r * gv[i].y - xv[i].y * k;
+          v.z = wv[i].z * r * gv[i].z - xv[i].z * k; v.w = wv[i].w * r * gv[i].w - xv[i].w * k;
+          if (accum_x) { const float4 p = o[j]; v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w; }
+          o[j] = v;
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < V4; i++) {
+      dwv[i].x = fmaf(gv[i].x * xv[i].x, r, dwv[i].x); dwv[i].y = fmaf(gv[i].y * xv[i].y, r, dwv[i].y);
+      dwv[i].z = fmaf(gv[i].z * xv[i].z, r, dwv[i].z); dwv[i].w = fmaf(gv[i].w * xv[i].w, r, dwv[i].w);
+    }
+  }
+  if (gw) {
+#pragma unroll
+    for (int i = 0; i < V4; i++) {
+      const int j = lane + 32 * i;
+      if (j < d4) {
+        atomicAdd(&sdw[4 * j + 0], dwv[i].x); atomicAdd(&sdw[4 * j + 1], dwv[i].y);
+        atomicAdd(&sdw[4 * j + 2], dwv[i].z); atomicAdd(&sdw[4 * j + 3], dwv[i].w);
+      }
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < d; j += blockDim.x) atomicAdd(&gw[j], sdw[j]);
+  }
+}
+
+template <int V4, int TH = (V4 >= 8 ? 256 : 512)>
+gt_status launch_bwd_vec(gt_ctx* ctx, int rows, int d, const float* x, const float* w, const float* rinv, const float* g, float* gx,
+                         int accum_x, float* gw) {
+  int blocks = min(gt_cdiv(rows, TH / 32), ctx->sm_count * (512 / TH));
+  rmsnorm_bwd_vec_kernel<V4, TH><<<blocks, TH, sizeof(float) * d, ctx->stream>>>(rows, d, x, w, rinv, g, gx, accum_x, gw);
+  GT_LAUNCHED(ctx, "rmsnorm_bwd_vec_kernel");
+  return GT_OK;
+}
+
 template <int NPL>
 gt_status launch_fwd(gt_ctx* ctx, int rows, int d, const float* x, const float* w, float eps, float* y, float* rinv) {
   int blocks = min(gt_cdiv(rows, 8), ctx->sm_count * 8);
@@ -137,6 +219,12 @@ gt_status gt_rmsnorm_bwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf x, gt_buf 
   const float* pr = gt_ptr<const float>(rinv); const float* pg = gt_ptr<const float>(gy);
   float* pgx = gt_ptr<float>(gx); float* pgw = gt_ptr<float>(gw);
   if (pgw && !accum_w) GT_CUDA(ctx, cudaMemsetAsync(pgw, 0, sizeof(float) * d, ctx->stream));
+  if ((d & 3) == 0 && d >= 128 && d <= 1024 && ((((uintptr_t)px) | ((uintptr_t)pw) | ((uintptr_t)pg) | ((uintptr_t)pgx)) & 15) == 0) {
+    if (d <= 128) return launch_bwd_vec<1>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw);
+    if (d <= 256) return launch_bwd_vec<2>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw);
+    if (d <= 640) return launch_bwd_vec<5>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw);
+    return launch_bwd_vec<8>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw);
+  }
   if (d <= 64) return launch_bwd<2>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw);
   if (d <= 128) return launch_bwd<4>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw);
   if (d <= 256) return launch_bwd<8>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw);

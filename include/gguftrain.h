@@ -74,6 +74,11 @@ gt_status gt_gemm(gt_ctx* ctx, int32_t kind, int32_t accum, int32_t M, int32_t N
 gt_status gt_ew_fwd(gt_ctx* ctx, int32_t op, uint64_t n, gt_buf a, gt_buf b, float c, gt_buf out);
 gt_status gt_ew_bwd(gt_ctx* ctx, int32_t op, uint64_t n, gt_buf a, gt_buf b, float c, gt_buf gout,
                     gt_buf ga, int32_t accum_a, gt_buf gb, int32_t accum_b);
+/* Gated unit act(x)*u in one pass, act = GT_EW_SILU or GT_EW_GELU: the reference's silu/gelu followed by mul
+ * (webgpu.ts:905-1078 issues them as two dispatches; src/arch/llama.ts:209-211). gx (+)= g*u*act'(x), gu (+)= g*act(x). */
+gt_status gt_glu_fwd(gt_ctx* ctx, int32_t op, uint64_t n, gt_buf x, gt_buf u, gt_buf out);
+gt_status gt_glu_bwd(gt_ctx* ctx, int32_t op, uint64_t n, gt_buf x, gt_buf u, gt_buf gout,
+                     gt_buf gx, int32_t accum_x, gt_buf gu, int32_t accum_u);
 /* rmsNorm and rmsNormHeads ([rows, d] view; webgpu.ts:1673-1701, wgsl.ts:217-303) */
 gt_status gt_rmsnorm_fwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf x, gt_buf w, float eps, gt_buf y, gt_buf rinv);
 gt_status gt_rmsnorm_bwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf x, gt_buf w, gt_buf rinv, gt_buf gy,

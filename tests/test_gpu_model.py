@@ -261,3 +261,50 @@ def test_muon_trajectory_matches_reference_loop(gpu, oracle):
         assert abs(h["loss"] - want) <= 1e-3 + 1e-3 * abs(want)   # gpu-parity.ts:1141-1142
     for i, p in enumerate(m.params()):
         compare(f"weight[{i}] after {steps} steps", p.data, om.data(i), dict(atol=2e-3, rtol=2e-2), None)
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu"])
+def test_gated_unit_fusion_matches_the_two_op_form(gpu, oracle, act):
+    """silu(g)*u / gelu(g)*u run as one kernel; the result must be what the two reference ops give, including when
+    the activated gate is also used elsewhere and when both factors are the same tensor."""
+    from gpu_harness import rand_tensor
+    rng = oracle.Mulberry32(61)
+    g = rand_tensor(rng, [37, 50], 1.5); u = rand_tensor(rng, [37, 50])
+    f = ag.silu if act == "silu" else ag.gelu
+    up = oracle.Mulberry32(0xBEEF).uniform_pm1((g.size,))
+    act_v, dact, _ = oracle.elementwise(act, g.data, gy=np.ones(g.size, np.float32))
+    # plain gated unit
+    launches = gpu.kernelLaunches()
+    gpu.install()
+    try:
+        out = ag.mul(f(g), u)
+        out.grad[:] = up
+        gpu.seedGradFromHost(out)
+        # run the closures in reverse creation order: product first, then the activation
+        out._backward()
+        out._prev[0]._backward()
+        gpu.sync([out])
+    finally:
+        gpu.uninstall()
+    assert gpu.kernelLaunches() - launches == 2          # one fused forward, one fused backward
+    compare("glu out", out.data, act_v.astype(np.float64) * u.data, FWD)
+    compare("glu d gate", g.grad, up.astype(np.float64) * u.data * dact, BWD)
+    compare("glu d up", u.grad, up.astype(np.float64) * act_v, BWD)
+    # the activated gate has a second consumer: it is materialised and its own backward carries that share
+    g.zeroGrad(); u.zeroGrad()
+    gpu.install()
+    try:
+        a = f(g)
+        out = ag.add(ag.mul(a, u), a)
+        loss_up = up
+        out.grad[:] = loss_up
+        gpu.seedGradFromHost(out)
+        out._backward()                  # add
+        out._prev[0]._backward()         # fused product
+        a._backward()                    # activation (share from the add)
+        gpu.sync([out])
+    finally:
+        gpu.uninstall()
+    compare("shared out", out.data, act_v.astype(np.float64) * u.data + act_v, FWD)
+    compare("shared d gate", g.grad, up.astype(np.float64) * (u.data + 1.0) * dact, BWD)
+    compare("shared d up", u.grad, up.astype(np.float64) * act_v, BWD)
