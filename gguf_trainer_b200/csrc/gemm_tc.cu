@@ -30,8 +30,9 @@ struct Smem {
   static constexpr int A_BYTES = BM * BK * 4;   // 16 KB
   static constexpr int B_BYTES = BN * BK * 4;
   static constexpr int STAGE = A_BYTES + B_BYTES;
-  static constexpr int STAGES = BN <= 128 ? 6 : 5;
-  static constexpr int TOTAL = STAGES * STAGE + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int STAGES = BN <= 128 ? 5 : 4;
+  static constexpr int EPI_BYTES = 4 * 2 * 4096;   // per epilogue warp: two 32x32 f32 staging tiles for the TMA store
+  static constexpr int TOTAL = STAGES * STAGE + EPI_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
   static constexpr uint32_t TMEM_COLS = 2 * BN <= 256 ? 256 : 512;   // two accumulators
 };
 
@@ -41,13 +42,15 @@ struct Smem {
 // A_K: A is K-major in memory (NT, NN); else MN-major ([K, M], TN). B_K: B is K-major (NT); else [K, N] (NN, TN).
 template <bool A_K, bool B_K, int BN>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, float* __restrict__ C,
-                 int M, int N, int K, int accum, int ksplit, int* __restrict__ flag) {
+gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                 const __grid_constant__ CUtensorMap mapC, float* __restrict__ C, int M, int N, int K, int accum, int ksplit,
+                 int use_tma_store, int* __restrict__ flag) {
   extern __shared__ uint8_t smem_raw[];
   using S = Smem<BN>;
   constexpr int STAGES = S::STAGES;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bars = base + STAGES * S::STAGE;   // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], tmem slot
+  const uint32_t epi = base + STAGES * S::STAGE;    // staging tiles of the epilogue warps
+  const uint32_t bars = epi + S::EPI_BYTES;         // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], tmem slot
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
   auto acc_full = [&](int b) { return bars + 8u * (2 * STAGES + b); };
@@ -131,7 +134,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     // ---- epilogue: warp w may touch TMEM lanes [32*(w%4), 32*(w%4)+32) ----
     const int q = warp & 3;
     const bool vec = (N & 3) == 0;
-    uint32_t tl = 0;
+    uint32_t tl = 0, nst = 0;   // nst: TMA stores issued by this warp
     for (int t = blockIdx.x; t < ntiles; t += gridDim.x, tl++) {
       const int n0 = (t % tiles_n) * BN, m0 = ((t / tiles_n) % tiles_m) * BM, z = t / (tiles_n * tiles_m);
       const int b = tl & 1;
@@ -149,7 +152,26 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
           tmem_ld32(tmem + b * BN + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
 #pragma unroll
           for (int j = 0; j < 32; j++) v[j] *= TRUNC_COMP;
-          if (row < M && !dead) {
+          if (use_tma_store) {
+            // Stage the warp's 32x32 block in shared memory (128-byte rows, 16-byte chunks XOR (row mod 8), the layout
+            // the store's tensor map expects) and let TMA write it: whole 128-byte rows, clipped at M and N, as a
+            // plain store or, when accumulating or combining split-K slices, as an f32 reduce-add performed in L2.
+            const uint32_t tile = epi + (uint32_t)(q * 2 + (nst & 1)) * 4096u;
+            if (nst >= 2) tma_wait_read<1>();        // the tile written two blocks ago has been read out
+            __syncwarp();
+            uint8_t* tp = smem_raw + (tile - smem_u32(smem_raw)) + lane * 128;
+#pragma unroll
+            for (int c4 = 0; c4 < 8; c4++)
+              *reinterpret_cast<float4*>(tp + ((c4 ^ (lane & 7)) * 16)) = make_float4(v[4 * c4], v[4 * c4 + 1], v[4 * c4 + 2], v[4 * c4 + 3]);
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0 && !dead && m0 + q * 32 < M) {
+              if (ksplit > 1 || accum) tma_reduce_add_2d(&mapC, tile, col0, m0 + q * 32);
+              else tma_store_2d(&mapC, tile, col0, m0 + q * 32);
+            }
+            if (lane == 0) tma_commit_group();
+            nst++;
+          } else if (row < M && !dead) {
             float* dst = C + (size_t)row * N + col0;
             if (vec && col0 + 32 <= N) {
               if (ksplit > 1) {
@@ -181,6 +203,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
       tc_fence_before();
       mbar_arrive(acc_empty(b));
     }
+    if (lane == 0) tma_wait_all<0>();   // every store of this warp has landed before the CTA's shared memory goes away
   }
   tc_fence_before();
   __syncthreads();
@@ -196,7 +219,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
 int* g_flag[64] = {};
 
 template <bool A_K, bool B_K, int BN>
-gt_status launch(gt_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, float* c, int M, int N, int K, int accum, int ksplit) {
+gt_status launch(gt_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, int tma_store, float* c, int M, int N,
+                 int K, int accum, int ksplit) {
   auto kern = gemm_tf32_kernel<A_K, B_K, BN>;
   static bool attr_set[64] = {};
   if (!attr_set[ctx->device]) {
@@ -205,7 +229,7 @@ gt_status launch(gt_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, floa
   }
   const long ntiles = (long)gt_cdiv(N, BN) * gt_cdiv(M, BM) * ksplit;
   dim3 grid((unsigned)min((long)ctx->sm_count, ntiles), 1, 1);
-  kern<<<grid, THREADS, Smem<BN>::TOTAL, ctx->stream>>>(ma, mb, c, M, N, K, accum, ksplit, g_flag[ctx->device]);
+  kern<<<grid, THREADS, Smem<BN>::TOTAL, ctx->stream>>>(ma, mb, mc, c, M, N, K, accum, ksplit, tma_store, g_flag[ctx->device]);
   GT_LAUNCHED(ctx, "gemm_tf32_kernel");
   return GT_OK;
 }
@@ -286,6 +310,9 @@ gt_status gt_gemm_tc(gt_ctx* ctx, int kind, int accum, int M, int N, int K, cons
   const bool oka = a_k ? make_map_2d(&ma, a, K, M, K, BM, true) : make_map_2d(&ma, a, M, K, M, BK, false);
   const bool okb = b_k ? make_map_2d(&mb, b, K, N, K, bn, true) : make_map_2d(&mb, b, N, K, N, BK, false);
   if (!oka || !okb) return GT_OK;
+  // the output goes through TMA (32x32 blocks of whole 128-byte rows) whenever its row pitch allows a tensor map
+  CUtensorMap mc = ma;
+  const int tma_store = ((N & 3) == 0 && make_map_2d(&mc, c, N, M, N, 32, true)) ? 1 : 0;
   // split K when the output has few tiles and K is deep (dW: K = rows); partial sums meet in L2 with f32 adds
   int ksplit = 1;
   const long tiles = (long)gt_cdiv(N, bn) * gt_cdiv(M, BM);
@@ -297,13 +324,13 @@ gt_status gt_gemm_tc(gt_ctx* ctx, int kind, int accum, int M, int N, int K, cons
   if (ksplit > 1 && !accum) GT_CUDA(ctx, cudaMemsetAsync(c, 0, sizeof(float) * (size_t)M * N, ctx->stream));
   gt_status s;
   if (bn == 192) {
-    if (kind == GT_GEMM_NT) s = launch<true, true, 192>(ctx, ma, mb, c, M, N, K, accum, ksplit);
-    else if (kind == GT_GEMM_NN) s = launch<true, false, 192>(ctx, ma, mb, c, M, N, K, accum, ksplit);
-    else s = launch<false, false, 192>(ctx, ma, mb, c, M, N, K, accum, ksplit);
+    if (kind == GT_GEMM_NT) s = launch<true, true, 192>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit);
+    else if (kind == GT_GEMM_NN) s = launch<true, false, 192>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit);
+    else s = launch<false, false, 192>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit);
   } else {
-    if (kind == GT_GEMM_NT) s = launch<true, true, 128>(ctx, ma, mb, c, M, N, K, accum, ksplit);
-    else if (kind == GT_GEMM_NN) s = launch<true, false, 128>(ctx, ma, mb, c, M, N, K, accum, ksplit);
-    else s = launch<false, false, 128>(ctx, ma, mb, c, M, N, K, accum, ksplit);
+    if (kind == GT_GEMM_NT) s = launch<true, true, 128>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit);
+    else if (kind == GT_GEMM_NN) s = launch<true, false, 128>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit);
+    else s = launch<false, false, 128>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit);
   }
   if (s) return s;
   *handled = true;
