@@ -229,7 +229,7 @@ def run_ours(args):
     groups = model.paramGroups()
     # gradients in one arena, last layers first: the order backward finishes them in
     order = list(reversed(params))
-    arena, arena_elems, _ = gpu.reserveGradArena(order)
+    arena = gpu.reserveGradArena(order)
     for p in params:
         gpu.keepGradOnDevice(p)
     if args.optimizer == "muon":
@@ -260,19 +260,17 @@ def run_ours(args):
     # pinned host staging for the e2e arm
     pin_ids = torch.empty(B * T, dtype=torch.int32).pin_memory()
     pin_tg = torch.empty(B * T, dtype=torch.int32).pin_memory()
-    step = CudaStep(model, gpu, B, T, world=world, capture=not args.no_graph)
+    step = CudaStep(model, gpu, B, T, world=world, capture=not args.no_graph, dp=dp, arena=arena if dp is not None else None)
 
     def one_step(i, resident):
         ids, tg = batch(i)
         if resident and step.graph is not None:
-            gpu._check(gpu.lib.gt_graph_launch(gpu.ctx, step.graph.handle))   # inputs already in HBM
+            step.replay()                       # inputs already in HBM
         else:
             pin_ids.numpy()[:] = ids
             pin_tg.numpy()[:] = tg
             step.run(pin_ids.numpy(), pin_tg.numpy())
-        if dp is not None:
-            dp.allreduce(arena, arena_elems)
-        opt.recordStep()
+        opt.recordStep()                      # the gradient exchange is part of the step (started bucket by bucket in backward)
 
     def barrier():
         gpu.sync([])

@@ -46,9 +46,10 @@ class _Entry:
 class CapturedGraph:
     """One recorded stretch of device work, replayable with new integer inputs."""
 
-    def __init__(self, gpu: "CudaBackend", handle: int, inputs, owned, outputs):
+    def __init__(self, gpu: "CudaBackend", handle: int, inputs, owned, outputs, earlier=()):
         self.gpu = gpu
         self.handle = handle
+        self.handles = list(earlier) + [handle]   # segments in order when the recording was cut (cutCapture)
         self.inputs = inputs      # [(addr, count)] in upload order
         self.owned = owned        # [(addr, size)] transients pinned to this graph
         self.outputs = outputs    # {name: (addr, count)}
@@ -62,11 +63,21 @@ class CapturedGraph:
             if a.size != count:
                 raise ValueError(f"graph input has {a.size} elements, recorded {count}")
             g._check(g.lib.gt_write(g.ctx, addr, a.ctypes.data, a.nbytes))
-        g._check(g.lib.gt_graph_launch(g.ctx, self.handle))
+        self.replay()
+
+    def replay(self, between=None):
+        """Launch the recorded segments in order with the inputs already in place. `between[i]` (if given) is called
+        after segment i has been enqueued: host-issued work that cannot be recorded, e.g. a collective."""
+        g = self.gpu
+        for i, h in enumerate(self.handles):
+            g._check(g.lib.gt_graph_launch(g.ctx, h))
+            if between is not None and i < len(between) and between[i] is not None:
+                between[i]()
 
     def destroy(self):
         g = self.gpu
-        g._check(g.lib.gt_graph_destroy(g.ctx, self.handle))
+        for h in self.handles:
+            g._check(g.lib.gt_graph_destroy(g.ctx, h))
         for addr, _size in self.owned:
             g._check(g.lib.gt_free(g.ctx, addr))
         self.owned = []
@@ -142,6 +153,7 @@ class CudaBackend:
         self._graphSynced = False              # a sync() ran after the current graph was built
         self._capturing = False
         self._captureInputs: List[tuple] = []
+        self._captureSegments: List[int] = []
         self._captureMark = 0
         self._batch = (0, 0)
         self._stateBufs: Dict[int, int] = {}
@@ -507,7 +519,19 @@ class CudaBackend:
         self._check(self.lib.gt_graph_begin(self.ctx))
         self._capturing = True
         self._captureInputs = []
+        self._captureSegments = []
         self._captureMark = len(self._transients)
+
+    def cutCapture(self) -> int:
+        """Close the graph recorded so far and start the next one: the place where the replayer will issue work from
+        the host between two segments. Returns the number of segments closed so far."""
+        if not self._capturing:
+            raise _lib.GtError(4, "cutCapture: not capturing")
+        h = C.c_uint64()
+        self._check(self.lib.gt_graph_end(self.ctx, C.byref(h)))
+        self._captureSegments.append(int(h.value))
+        self._check(self.lib.gt_graph_begin(self.ctx))
+        return len(self._captureSegments)
 
     def endCapture(self, outputs: Optional[Dict[str, Tensor]] = None) -> CapturedGraph:
         h = C.c_uint64()
@@ -521,8 +545,9 @@ class CudaBackend:
         for name, t in (outputs or {}).items():
             e = self._entries[t]
             outs[name] = (e.data, t.size)
-        g = CapturedGraph(self, int(h.value), list(self._captureInputs), owned, outs)
+        g = CapturedGraph(self, int(h.value), list(self._captureInputs), owned, outs, earlier=self._captureSegments)
         self._captureInputs = []
+        self._captureSegments = []
         # externals touched while recording keep their accumulate-or-overwrite state as recorded
         return g
 

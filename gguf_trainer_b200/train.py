@@ -14,7 +14,7 @@ import numpy as np
 
 from . import autograd as ag
 from .autograd import Tensor, backward, crossEntropy, fusedCrossEntropy
-from .backend import CudaBackend
+from .backend import CudaBackend, _as_u32
 from .qk_clip import applyQKClip
 
 
@@ -147,17 +147,65 @@ class CudaStep:
     loss is their mean, so gradients equal `batch` reference micro-batches seeded with 1/batch."""
 
     def __init__(self, model, gpu: CudaBackend, batch: int, seqLen: int, lossChunk: int = 0, world: int = 1,
-                 capture: bool = True):
+                 capture: bool = True, dp: Optional["DataParallel"] = None, arena=None, layersPerBucket: int = 6):
+        """`dp` + `arena` turn on the gradient exchange: `arena` is what `reserveGradArena(list(reversed(params)))`
+        returned, i.e. the parameter gradients in the order backward completes them (last layer first, the tied
+        embedding last). The arena is cut into buckets of `layersPerBucket` layers; each bucket's all-reduce is started
+        on the side stream the moment backward leaves its first layer, so it runs under the rest of backward, and the
+        compute stream only joins it after the last bucket. A captured step is cut into one graph per bucket boundary and
+        the NCCL calls are issued from the host between the segments (they are not recorded into the graphs)."""
         self.model, self.gpu, self.batch, self.seqLen, self.lossChunk = model, gpu, batch, seqLen, lossChunk
         self.world = world
         self.capture = capture
+        self.dp, self.arena, self.layersPerBucket = dp, arena, max(1, layersPerBucket)
         self.graph = None
         self.lossTensor: Optional[Tensor] = None
         self.launchesPerReplay = 0
 
+    def bucketPlan(self):
+        """[(first layer of the bucket, arena offset, element count)] in the order the buckets complete, the last entry
+        reaching the end of the arena (first layers, output norm, embedding)."""
+        base, total, offs = self.arena
+        L = len(self.model.layers)
+        perLayer = len(self.model.params()) - (3 if self.model.output is not None else 2)
+        perLayer //= max(L, 1)
+        # arena order is reversed(params): entry j of the arena list is params[-1 - j]; layer l starts at list index (L-1-l)*perLayer
+        plan = []
+        l_hi = L
+        while l_hi > 0:
+            l_lo = max(0, l_hi - self.layersPerBucket)
+            start = offs[(L - l_hi) * perLayer]
+            end = offs[(L - l_lo) * perLayer] if l_lo > 0 else total
+            plan.append((l_lo, start, end - start))
+            l_hi = l_lo
+        return plan
+
     def _once(self, ids: np.ndarray, targets: np.ndarray, seed: float) -> Tensor:
         loss = sequenceLoss(self.model, ids, targets, self.lossChunk)
-        backward(loss, seed)
+        if self.dp is not None and self.arena is not None:
+            base = self.arena[0]
+            plan = self.bucketPlan()
+            outs = self.model.layerOutputs
+            for l_lo, start, count in plan[:-1]:
+                # backward reaches the closure of layer l_lo's input only after every closure of layers >= l_lo has run
+                t = outs[l_lo - 1]
+                orig = t._backward
+
+                def hooked(orig=orig, start=start, count=count):
+                    if self.gpu._capturing:
+                        self.gpu.cutCapture()         # the replayer starts this bucket's reduction here
+                    else:
+                        self.dp.start(base + start * 4, count)
+                    orig()
+
+                t._backward = hooked
+            backward(loss, seed)
+            _l, start, count = plan[-1]
+            if not self.gpu._capturing:
+                self.dp.start(base + start * 4, count)
+                self.dp.wait()
+        else:
+            backward(loss, seed)
         return loss
 
     def run(self, ids: np.ndarray, targets: np.ndarray) -> None:
@@ -168,6 +216,9 @@ class CudaStep:
         gpu.setBatch(self.batch, self.seqLen)
         try:
             if not self.capture:
+                # eager form of the same step: the previous step's transients go back to the pool and the parameter
+                # gradients restart (sync() re-arms their first-write-overwrites state)
+                gpu.sync([])
                 self.lossTensor = self._once(ids, targets, seed)
                 return
             if self.graph is None:
@@ -180,13 +231,31 @@ class CudaStep:
                 self.graph = gpu.endCapture({"loss": loss})
                 self.launchesPerReplay = gpu.kernelLaunches() - before
                 self.lossTensor = loss
-            self.graph.launch(self.graphInputs(ids, targets))
+            for (addr, count), arr in zip(self.graph.inputs, self.graphInputs(ids, targets)):
+                a = _as_u32(arr)
+                if a.size != count:
+                    raise ValueError(f"step input has {a.size} elements, recorded {count}")
+                gpu._check(gpu.lib.gt_write(gpu.ctx, addr, a.ctypes.data, a.nbytes))
+            self.replay()
         finally:
             gpu.setBatch(0)
             gpu.uninstall()
 
     def graphInputs(self, ids, targets):
         return [ids, targets]
+
+    def replay(self) -> None:
+        """Enqueue the recorded step again on the inputs already on the device (plus the gradient exchange)."""
+        if self.dp is None or self.arena is None:
+            self.graph.replay()
+            return
+        base = self.arena[0]
+        plan = self.bucketPlan()
+        between = [(lambda s=s, c=c: self.dp.start(base + s * 4, c)) for _l, s, c in plan[:-1]]
+        self.graph.replay(between)
+        _l, s, c = plan[-1]
+        self.dp.start(base + s * 4, c)
+        self.dp.wait()
 
     def losses(self) -> np.ndarray:
         """[mean over sequences, per-sequence...] of the last run (blocks)."""

@@ -155,3 +155,26 @@ def test_lora_fold_matches_oracle(oracle):
     finally:
         clearLora(m)
     assert all(p.requiresGrad for p in m.params())
+
+
+def test_bucket_plan_tiles_the_gradient_arena_in_completion_order():
+    from gguf_trainer_b200.train import CudaStep
+    cfg = ModelConfig("qwen3", 23, 8, 5, 2, 1, 4, 16, 1e6, 1e-6)
+    m = buildModel(cfg, 1)
+    order = list(reversed(m.params()))
+    offs, total = [], 0
+    for t in order:
+        offs.append(total)
+        total += (t.size + 63) // 64 * 64
+    step = CudaStep(m, None, 2, 8, dp=object(), arena=(0, total, offs), layersPerBucket=2)
+    plan = step.bucketPlan()
+    assert [p[0] for p in plan] == [3, 1, 0]                 # buckets start at layers 3, 1, 0 (5 layers, 2 per bucket)
+    assert plan[0][1] == 0 and sum(p[2] for p in plan) == total
+    for (_, s0, c0), (_, s1, _c1) in zip(plan, plan[1:]):
+        assert s0 + c0 == s1                                 # contiguous, in the order backward finishes them
+    # the first bucket begins at the last layer's last parameter and ends where layer 2 begins
+    assert order[0] is m.layers[4].down
+    idx_l2_down = next(i for i, t in enumerate(order) if t is m.layers[2].down)
+    assert plan[1][1] == offs[idx_l2_down]
+    # the last bucket reaches the end of the arena: first layer, output norm and the (tied) embedding
+    assert order[-1] is m.tokenEmbd and plan[-1][1] + plan[-1][2] == total
