@@ -112,6 +112,19 @@ gt_status gt_gemm_simt(gt_ctx* ctx, int kind, int accum, int M, int N, int K, co
   return GT_OK;
 }
 
+gt_status gt_gemm_batched(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c, int batch) {
+  if (ctx->precision != GT_PREC_FP32) {
+    bool handled = false;
+    gt_status s = gt_gemm_tc_batched(ctx, kind, accum, M, N, K, a, b, c, batch, &handled);
+    if (s != GT_OK || handled) return s;
+  }
+  for (int i = 0; i < batch; i++) {
+    gt_status s = gt_gemm_simt(ctx, kind, accum, M, N, K, a + (size_t)i * M * K, b + (size_t)i * N * K, c + (size_t)i * M * N);
+    if (s) return s;
+  }
+  return GT_OK;
+}
+
 extern "C" gt_status gt_gemm(gt_ctx* ctx, int32_t kind, int32_t accum, int32_t M, int32_t N, int32_t K, gt_buf a, gt_buf b, gt_buf c) {
   GT_REQUIRE(ctx, M > 0 && N > 0 && K > 0, "gt_gemm: empty product %dx%dx%d", M, N, K);
   GT_REQUIRE(ctx, a && b && c, "gt_gemm: null operand");

@@ -44,7 +44,7 @@ template <bool A_K, bool B_K, int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                  const __grid_constant__ CUtensorMap mapC, float* __restrict__ C, int M, int N, int K, int accum, int ksplit,
-                 int use_tma_store, int* __restrict__ flag) {
+                 int use_tma_store, int batch, int* __restrict__ flag) {
   extern __shared__ uint8_t smem_raw[];
   using S = Smem<BN>;
   constexpr int STAGES = S::STAGES;
@@ -60,7 +60,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_n = (N + BN - 1) / BN, tiles_m = (M + BM - 1) / BM;
-  const int ntiles = tiles_n * tiles_m * ksplit;
+  const int per_mat = tiles_n * tiles_m * ksplit;
+  const int ntiles = per_mat * batch;            // the matrices of a batch are just more tiles
   const int kblocks = (K + BK - 1) / BK;
   const int per = (kblocks + ksplit - 1) / ksplit;   // K blocks per split-K slice
 
@@ -85,7 +86,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
       // ---- TMA producer ----
       uint32_t it = 0;
       for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
-        const int n0 = (t % tiles_n) * BN, m0 = ((t / tiles_n) % tiles_m) * BM, z = t / (tiles_n * tiles_m);
+        const int bi = t / per_mat, tt = t % per_mat;
+        const int n0 = (tt % tiles_n) * BN, m0 = ((tt / tiles_n) % tiles_m) * BM, z = tt / (tiles_n * tiles_m);
         const int kb0 = z * per, kb1 = min(kblocks, kb0 + per);
         for (int kb = kb0; kb < kb1; kb++, it++) {
           const int s = it % STAGES;
@@ -93,12 +95,12 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
           const uint32_t a_dst = base + s * S::STAGE, b_dst = a_dst + S::A_BYTES;
           const int k0 = kb * BK;
           mbar_expect_tx(full_bar(s), S::STAGE);
-          if (A_K) tma_load_2d(a_dst, &mapA, k0, m0, full_bar(s));
+          if (A_K) tma_load_3d(a_dst, &mapA, k0, m0, bi, full_bar(s));
           else
-            for (int c = 0; c < BM / 32; c++) tma_load_2d(a_dst + c * 4096, &mapA, m0 + 32 * c, k0, full_bar(s));
-          if (B_K) tma_load_2d(b_dst, &mapB, k0, n0, full_bar(s));
+            for (int c = 0; c < BM / 32; c++) tma_load_3d(a_dst + c * 4096, &mapA, m0 + 32 * c, k0, bi, full_bar(s));
+          if (B_K) tma_load_3d(b_dst, &mapB, k0, n0, bi, full_bar(s));
           else
-            for (int c = 0; c < BN / 32; c++) tma_load_2d(b_dst + c * 4096, &mapB, n0 + 32 * c, k0, full_bar(s));
+            for (int c = 0; c < BN / 32; c++) tma_load_3d(b_dst + c * 4096, &mapB, n0 + 32 * c, k0, bi, full_bar(s));
         }
       }
     }
@@ -108,7 +110,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
       constexpr uint32_t idesc = idesc_tf32(!A_K, !B_K, BM, BN);
       uint32_t it = 0, tl = 0;
       for (int t = blockIdx.x; t < ntiles; t += gridDim.x, tl++) {
-        const int z = t / (tiles_n * tiles_m);
+        const int z = (t % per_mat) / (tiles_n * tiles_m);
         const int kb0 = z * per, kb1 = min(kblocks, kb0 + per);
         const int b = tl & 1;
         wait(acc_empty(b), ((tl >> 1) & 1) ^ 1, 4);   // the epilogue has drained this accumulator
@@ -136,7 +138,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     const bool vec = (N & 3) == 0;
     uint32_t tl = 0, nst = 0;   // nst: TMA stores issued by this warp
     for (int t = blockIdx.x; t < ntiles; t += gridDim.x, tl++) {
-      const int n0 = (t % tiles_n) * BN, m0 = ((t / tiles_n) % tiles_m) * BM, z = t / (tiles_n * tiles_m);
+      const int bi = t / per_mat, tt = t % per_mat;
+      const int n0 = (tt % tiles_n) * BN, m0 = ((tt / tiles_n) % tiles_m) * BM, z = tt / (tiles_n * tiles_m);
       const int b = tl & 1;
       const bool have = z * per < kblocks;     // an empty split-K slice issues no MMA and contributes nothing
       const int row = m0 + q * 32 + lane;
@@ -166,13 +169,13 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
             fence_async_smem();
             __syncwarp();
             if (lane == 0 && !dead && m0 + q * 32 < M) {
-              if (ksplit > 1 || accum) tma_reduce_add_2d(&mapC, tile, col0, m0 + q * 32);
-              else tma_store_2d(&mapC, tile, col0, m0 + q * 32);
+              if (ksplit > 1 || accum) tma_reduce_add_3d(&mapC, tile, col0, m0 + q * 32, bi);
+              else tma_store_3d(&mapC, tile, col0, m0 + q * 32, bi);
             }
             if (lane == 0) tma_commit_group();
             nst++;
           } else if (row < M && !dead) {
-            float* dst = C + (size_t)row * N + col0;
+            float* dst = C + (size_t)bi * M * N + (size_t)row * N + col0;
             if (vec && col0 + 32 <= N) {
               if (ksplit > 1) {
 #pragma unroll
@@ -220,16 +223,16 @@ int* g_flag[64] = {};
 
 template <bool A_K, bool B_K, int BN>
 gt_status launch(gt_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, int tma_store, float* c, int M, int N,
-                 int K, int accum, int ksplit) {
+                 int K, int accum, int ksplit, int batch) {
   auto kern = gemm_tf32_kernel<A_K, B_K, BN>;
   static bool attr_set[64] = {};
   if (!attr_set[ctx->device]) {
     GT_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<BN>::TOTAL));
     attr_set[ctx->device] = true;
   }
-  const long ntiles = (long)gt_cdiv(N, BN) * gt_cdiv(M, BM) * ksplit;
+  const long ntiles = (long)gt_cdiv(N, BN) * gt_cdiv(M, BM) * ksplit * batch;
   dim3 grid((unsigned)min((long)ctx->sm_count, ntiles), 1, 1);
-  kern<<<grid, THREADS, Smem<BN>::TOTAL, ctx->stream>>>(ma, mb, mc, c, M, N, K, accum, ksplit, tma_store, g_flag[ctx->device]);
+  kern<<<grid, THREADS, Smem<BN>::TOTAL, ctx->stream>>>(ma, mb, mc, c, M, N, K, accum, ksplit, tma_store, batch, g_flag[ctx->device]);
   GT_LAUNCHED(ctx, "gemm_tf32_kernel");
   return GT_OK;
 }
@@ -257,6 +260,18 @@ EncodeTiledFn encode_fn() {
 // kmajor: the tile's rows are K runs (128-byte swizzle); else its rows are MN runs (128-byte swizzle, 32-byte atoms).
 }  // namespace
 
+bool tc::make_map_3d(CUtensorMap* map, const float* ptr, uint64_t inner, uint64_t outer, uint64_t batch, uint64_t row_pitch_elems,
+                     uint64_t batch_stride_elems, uint32_t box_outer, bool kmajor) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return false;
+  cuuint64_t dims[3] = {inner, outer, batch};
+  cuuint64_t strides[2] = {row_pitch_elems * sizeof(float), batch_stride_elems * sizeof(float)};
+  cuuint32_t box[3] = {32, box_outer, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             kmajor ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 bool tc::make_map_2d(CUtensorMap* map, const float* ptr, uint64_t inner, uint64_t outer, uint64_t row_pitch_elems,
                      uint32_t box_outer, bool kmajor) {
   EncodeTiledFn enc = encode_fn();
@@ -268,7 +283,6 @@ bool tc::make_map_2d(CUtensorMap* map, const float* ptr, uint64_t inner, uint64_
   return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
              kmajor ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
-
 
 int* tc::device_flag(gt_ctx* ctx) {
   if (ctx->device < 0 || ctx->device >= 64) return nullptr;
@@ -294,8 +308,11 @@ gt_status gt_gemm_tc_check(gt_ctx* ctx) {
   return GT_OK;
 }
 
-gt_status gt_gemm_tc(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c, bool* handled) {
+// `batch` independent products of the same shape, matrix i of each operand `M*K`, `N*K`, `M*N` elements after matrix i-1.
+gt_status gt_gemm_tc_batched(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c, int batch,
+                             bool* handled) {
   *handled = false;
+  if (batch < 1) return GT_OK;
   // Small or oddly aligned products stay on the f32 kernel: TMA needs 16-byte row pitches and bases.
   const bool a_k = kind != GT_GEMM_TN, b_k = kind == GT_GEMM_NT;
   const int a_inner = a_k ? K : M, b_inner = b_k ? K : N;
@@ -307,32 +324,37 @@ gt_status gt_gemm_tc(gt_ctx* ctx, int kind, int accum, int M, int N, int K, cons
   // tile width: 192 divides the model widths this path is built for (576, 192, 1536, 49152); otherwise 128
   const int bn = (N % 192 == 0 || (N > 128 && (gt_cdiv(N, 192) * 192 - N) < (gt_cdiv(N, 128) * 128 - N))) ? 192 : 128;
   CUtensorMap ma, mb;
-  const bool oka = a_k ? make_map_2d(&ma, a, K, M, K, BM, true) : make_map_2d(&ma, a, M, K, M, BK, false);
-  const bool okb = b_k ? make_map_2d(&mb, b, K, N, K, bn, true) : make_map_2d(&mb, b, N, K, N, BK, false);
+  const uint64_t sa = (uint64_t)M * K, sb = (uint64_t)N * K, sc = (uint64_t)M * N;
+  const bool oka = a_k ? make_map_3d(&ma, a, K, M, batch, K, sa, BM, true) : make_map_3d(&ma, a, M, K, batch, M, sa, BK, false);
+  const bool okb = b_k ? make_map_3d(&mb, b, K, N, batch, K, sb, bn, true) : make_map_3d(&mb, b, N, K, batch, N, sb, BK, false);
   if (!oka || !okb) return GT_OK;
   // the output goes through TMA (32x32 blocks of whole 128-byte rows) whenever its row pitch allows a tensor map
   CUtensorMap mc = ma;
-  const int tma_store = ((N & 3) == 0 && make_map_2d(&mc, c, N, M, N, 32, true)) ? 1 : 0;
+  const int tma_store = ((N & 3) == 0 && make_map_3d(&mc, c, N, M, batch, N, sc, 32, true)) ? 1 : 0;
   // split K when the output has few tiles and K is deep (dW: K = rows); partial sums meet in L2 with f32 adds
   int ksplit = 1;
-  const long tiles = (long)gt_cdiv(N, bn) * gt_cdiv(M, BM);
+  const long tiles = (long)gt_cdiv(N, bn) * gt_cdiv(M, BM) * batch;
   const int kblocks = gt_cdiv(K, BK);
   if (tiles < ctx->sm_count && kblocks >= 16) {
     ksplit = (int)min((long)(ctx->sm_count / tiles), (long)(kblocks / 8));
     if (ksplit < 1) ksplit = 1;
   }
-  if (ksplit > 1 && !accum) GT_CUDA(ctx, cudaMemsetAsync(c, 0, sizeof(float) * (size_t)M * N, ctx->stream));
+  if (ksplit > 1 && !accum) GT_CUDA(ctx, cudaMemsetAsync(c, 0, sizeof(float) * (size_t)M * N * batch, ctx->stream));
   gt_status s;
   if (bn == 192) {
-    if (kind == GT_GEMM_NT) s = launch<true, true, 192>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit);
-    else if (kind == GT_GEMM_NN) s = launch<true, false, 192>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit);
-    else s = launch<false, false, 192>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit);
+    if (kind == GT_GEMM_NT) s = launch<true, true, 192>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
+    else if (kind == GT_GEMM_NN) s = launch<true, false, 192>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
+    else s = launch<false, false, 192>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
   } else {
-    if (kind == GT_GEMM_NT) s = launch<true, true, 128>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit);
-    else if (kind == GT_GEMM_NN) s = launch<true, false, 128>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit);
-    else s = launch<false, false, 128>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit);
+    if (kind == GT_GEMM_NT) s = launch<true, true, 128>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
+    else if (kind == GT_GEMM_NN) s = launch<true, false, 128>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
+    else s = launch<false, false, 128>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
   }
   if (s) return s;
   *handled = true;
   return GT_OK;
+}
+
+gt_status gt_gemm_tc(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c, bool* handled) {
+  return gt_gemm_tc_batched(ctx, kind, accum, M, N, K, a, b, c, 1, handled);
 }

@@ -145,6 +145,65 @@ __global__ void muon_apply_kernel(int m, int n, int flip, float f, const float* 
   }
 }
 
+// ---- the same pieces over a group of same-shape matrices: blockIdx.y = matrix, workspaces are [nb, rows, cols] ----
+__global__ void muon_momentum_batched_kernel(size_t el, float* const* __restrict__ grads, float* const* __restrict__ bufs,
+                                             float* __restrict__ U, float mu, int nesterov) {
+  const int b = blockIdx.y;
+  const float* g = grads[b];
+  float* buf = bufs[b];
+  float* u = U + (size_t)b * el;
+  size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < el; i += stride) {
+    float v = mu * buf[i] + g[i];
+    buf[i] = v;
+    u[i] = nesterov ? g[i] + mu * v : v;
+  }
+}
+__global__ void __launch_bounds__(OT) sumsq_batched_kernel(const float* __restrict__ U, size_t el, int nch, float* __restrict__ partials) {
+  __shared__ float sh[OT / 32];
+  const int b = blockIdx.y;
+  const float* g = U + (size_t)b * el;
+  size_t start = (size_t)blockIdx.x * CHUNK;
+  size_t end = start + CHUNK < el ? start + CHUNK : el;
+  float s = 0.f;
+  for (size_t i = start + threadIdx.x; i < end; i += OT) s = fmaf(g[i], g[i], s);
+  s = block_sum(s, sh);
+  if (threadIdx.x == 0) partials[(size_t)b * nch + blockIdx.x] = s;
+}
+__global__ void frob_inv_batched_kernel(int nch, const float* __restrict__ partials, float* __restrict__ inv) {
+  // one small CTA per matrix, fixed order
+  const int b = blockIdx.x;
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    for (int i = 0; i < nch; i++) t += (double)partials[(size_t)b * nch + i];
+    inv[b] = (float)(1.0 / (sqrt(t) + 1e-7));
+  }
+}
+__global__ void muon_normalize_batched_kernel(int m, int n, int flip, const float* __restrict__ U, const float* __restrict__ inv,
+                                              float* __restrict__ X) {
+  const int b = blockIdx.y;
+  size_t total = (size_t)m * n, stride = (size_t)gridDim.x * blockDim.x;
+  const float s = inv[b];
+  const float* u = U + (size_t)b * total;
+  float* x = X + (size_t)b * total;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    if (!flip) x[i] = u[i] * s;
+    else { size_t a = i / m, c = i % m; x[i] = u[c * n + a] * s; }
+  }
+}
+__global__ void muon_apply_batched_kernel(int m, int n, int flip, float f, const float* __restrict__ X, float* const* __restrict__ datas) {
+  const int b = blockIdx.y;
+  size_t total = (size_t)m * n, stride = (size_t)gridDim.x * blockDim.x;
+  const float* x = X + (size_t)b * total;
+  float* w = datas[b];
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    float o;
+    if (!flip) o = x[i];
+    else { size_t a = i / n, c = i % n; o = x[c * m + a]; }
+    w[i] -= f * o;
+  }
+}
+
 inline int egrid(gt_ctx* ctx, size_t n) {
   size_t want = (n + 255) / 256, cap = (size_t)ctx->sm_count * 8;
   return (int)(want < 1 ? 1 : (want > cap ? cap : want));
@@ -165,7 +224,18 @@ struct GtAdamW {
   float* d_scale = nullptr;
 };
 
+// Matrices of one shape are orthogonalised together: one launch of each elementwise piece and one batched matrix
+// product per Newton-Schulz step for the whole group (the reference records a separate dispatch chain per matrix,
+// src/backend/muon-gpu.ts:385-411).
+struct MuonGroup {
+  int rows = 0, cols = 0, nb = 0;
+  std::vector<int> idx;
+  float *U = nullptr, *X = nullptr, *BX = nullptr, *A = nullptr, *AA = nullptr, *partials = nullptr, *inv = nullptr;
+  float** d_ptrs = nullptr;   // [3][nb]: grad, momentum, data
+};
+
 struct GtMuon {
+  std::vector<MuonGroup> groups;
   int n = 0;
   std::vector<float*> data, grad, buf;
   std::vector<int> rows, cols;
@@ -223,6 +293,7 @@ void gt_optim_destroy(gt_ctx* ctx) {
   for (GtMuon* m : ctx->muons) {
     if (!m) continue;
     for (float* p : m->buf) cudaFree(p);
+    for (auto& g : m->groups) { cudaFree(g.U); cudaFree(g.X); cudaFree(g.BX); cudaFree(g.A); cudaFree(g.AA); cudaFree(g.partials); cudaFree(g.inv); cudaFree(g.d_ptrs); }
     cudaFree(m->U); cudaFree(m->X); cudaFree(m->BX); cudaFree(m->A); cudaFree(m->AA); cudaFree(m->partials); cudaFree(m->inv);
     delete m;
   }
@@ -349,16 +420,33 @@ gt_status gt_muon_create(gt_ctx* ctx, int32_t n, const gt_buf* data, const gt_bu
     int r = rows[i] < cols[i] ? rows[i] : cols[i];
     if (r > m->maxr) m->maxr = r;
   }
-  if (n > 0) {
-    size_t e = sizeof(float) * m->maxel, rr = sizeof(float) * (size_t)m->maxr * m->maxr;
-    gt_status s = dev_alloc(ctx, (void**)&m->U, e, false);
-    if (!s) s = dev_alloc(ctx, (void**)&m->X, e, false);
-    if (!s) s = dev_alloc(ctx, (void**)&m->BX, e, false);
-    if (!s) s = dev_alloc(ctx, (void**)&m->A, rr, false);
-    if (!s) s = dev_alloc(ctx, (void**)&m->AA, rr, false);
-    if (!s) s = dev_alloc(ctx, (void**)&m->partials, sizeof(float) * (m->maxel / CHUNK + 2), false);
-    if (!s) s = dev_alloc(ctx, (void**)&m->inv, 256, true);
+  // group by shape, in first-seen order
+  for (int i = 0; i < n; i++) {
+    MuonGroup* g = nullptr;
+    for (auto& gg : m->groups) if (gg.rows == m->rows[i] && gg.cols == m->cols[i]) { g = &gg; break; }
+    if (!g) { m->groups.emplace_back(); g = &m->groups.back(); g->rows = m->rows[i]; g->cols = m->cols[i]; }
+    g->idx.push_back(i);
+  }
+  for (auto& g : m->groups) {
+    g.nb = (int)g.idx.size();
+    const size_t el = (size_t)g.rows * g.cols;
+    const int r = g.rows < g.cols ? g.rows : g.cols;
+    const int nch = gt_cdiv((long)el, CHUNK);
+    gt_status s = dev_alloc(ctx, (void**)&g.U, sizeof(float) * el * g.nb, false);
+    if (!s) s = dev_alloc(ctx, (void**)&g.X, sizeof(float) * el * g.nb, false);
+    if (!s) s = dev_alloc(ctx, (void**)&g.BX, sizeof(float) * el * g.nb, false);
+    if (!s) s = dev_alloc(ctx, (void**)&g.A, sizeof(float) * (size_t)r * r * g.nb, false);
+    if (!s) s = dev_alloc(ctx, (void**)&g.AA, sizeof(float) * (size_t)r * r * g.nb, false);
+    if (!s) s = dev_alloc(ctx, (void**)&g.partials, sizeof(float) * (size_t)nch * g.nb, false);
+    if (!s) s = dev_alloc(ctx, (void**)&g.inv, sizeof(float) * g.nb, true);
+    if (!s) s = dev_alloc(ctx, (void**)&g.d_ptrs, sizeof(float*) * 3 * g.nb, false);
     if (s) { delete m; return s; }
+    std::vector<float*> ptrs;
+    for (int i : g.idx) ptrs.push_back(m->grad[i]);
+    for (int i : g.idx) ptrs.push_back(m->buf[i]);
+    for (int i : g.idx) ptrs.push_back(m->data[i]);
+    GT_CUDA(ctx, cudaMemcpyAsync(g.d_ptrs, ptrs.data(), sizeof(float*) * ptrs.size(), cudaMemcpyHostToDevice, ctx->stream));
+    GT_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   }
   ctx->muons.push_back(m);
   *out_handle = ctx->muons.size();
@@ -380,22 +468,38 @@ gt_status gt_muon_set_lr(gt_ctx* ctx, uint64_t h, float lr) {
 gt_status gt_muon_step(gt_ctx* ctx, uint64_t h) {
   GtMuon* m = muon_of(ctx, h);
   GT_REQUIRE(ctx, m, "gt_muon_step: bad handle");
-  for (int i = 0; i < m->n; i++) {
-    const int rows = m->rows[i], cols = m->cols[i];
+  for (auto& g : m->groups) {
+    const int rows = g.rows, cols = g.cols, nb = g.nb;
     const size_t el = (size_t)rows * cols;
     const int flip = rows > cols;
     const int r = flip ? cols : rows, c = flip ? rows : cols;
-    muon_momentum_kernel<<<egrid(ctx, el), 256, 0, ctx->stream>>>(el, m->grad[i], m->buf[i], m->U, m->mu, m->nesterov);
-    GT_LAUNCHED(ctx, "muon_momentum_kernel");
-    gt_status s = frob_inv(ctx, m->U, el, m->partials, m->inv);
-    if (s) return s;
-    muon_normalize_kernel<<<egrid(ctx, el), 256, 0, ctx->stream>>>(rows, cols, flip, m->U, m->inv, m->X);
-    GT_LAUNCHED(ctx, "muon_normalize_kernel");
-    s = ns_iterations(ctx, r, c, m->ns, m->X, m->A, m->AA, m->BX);
-    if (s) return s;
-    float f = m->lr * sqrtf(fmaxf(1.f, (float)rows / (float)cols));
-    muon_apply_kernel<<<egrid(ctx, el), 256, 0, ctx->stream>>>(rows, cols, flip, f, m->X, m->data[i]);
-    GT_LAUNCHED(ctx, "muon_apply_kernel");
+    const int nch = gt_cdiv((long)el, CHUNK);
+    const dim3 eg((unsigned)max(1, min(egrid(ctx, el), (ctx->sm_count * 8 + nb - 1) / nb)), (unsigned)nb);
+    float** P = g.d_ptrs;
+    muon_momentum_batched_kernel<<<eg, 256, 0, ctx->stream>>>(el, P, P + nb, g.U, m->mu, m->nesterov);
+    GT_LAUNCHED(ctx, "muon_momentum_batched_kernel");
+    sumsq_batched_kernel<<<dim3(nch, nb), OT, 0, ctx->stream>>>(g.U, el, nch, g.partials);
+    GT_LAUNCHED(ctx, "sumsq_batched_kernel");
+    frob_inv_batched_kernel<<<nb, 32, 0, ctx->stream>>>(nch, g.partials, g.inv);
+    GT_LAUNCHED(ctx, "frob_inv_batched_kernel");
+    muon_normalize_batched_kernel<<<eg, 256, 0, ctx->stream>>>(rows, cols, flip, g.U, g.inv, g.X);
+    GT_LAUNCHED(ctx, "muon_normalize_batched_kernel");
+    for (int it = 0; it < m->ns; it++) {   // A = X.X^T ; AA = A.A ; B = b*A + c*AA ; X = a*X + B.X   (muon.ts:143-155)
+      gt_status st = gt_gemm_batched(ctx, GT_GEMM_NT, 0, r, r, c, g.X, g.X, g.A, nb);
+      if (st) return st;
+      st = gt_gemm_batched(ctx, GT_GEMM_NN, 0, r, r, r, g.A, g.A, g.AA, nb);
+      if (st) return st;
+      const size_t rr = (size_t)r * r * nb;
+      axpby_kernel<<<egrid(ctx, rr), 256, 0, ctx->stream>>>(rr, -4.7750f, g.A, 2.0315f, g.AA, g.AA);
+      GT_LAUNCHED(ctx, "axpby_kernel");
+      st = gt_gemm_batched(ctx, GT_GEMM_NN, 0, r, c, r, g.AA, g.X, g.BX, nb);
+      if (st) return st;
+      axpby_kernel<<<egrid(ctx, el * nb), 256, 0, ctx->stream>>>(el * nb, 3.4445f, g.X, 1.f, g.BX, g.X);
+      GT_LAUNCHED(ctx, "axpby_kernel");
+    }
+    const float f = m->lr * sqrtf(fmaxf(1.f, (float)rows / (float)cols));
+    muon_apply_batched_kernel<<<eg, 256, 0, ctx->stream>>>(rows, cols, flip, f, g.X, P + 2 * nb);
+    GT_LAUNCHED(ctx, "muon_apply_batched_kernel");
   }
   return GT_OK;
 }

@@ -101,6 +101,17 @@ __host__ __device__ constexpr uint32_t idesc_tf32(bool a_mn, bool b_mn, int m, i
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// 3-D forms (x = innermost element, y = row, z = matrix of a batch)
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, uint32_t src, int x, int y, int z) {
+  asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y), "r"(z) : "memory");
+}
 // TMA tile store / f32 reduce-add of a shared-memory tile into global memory (bulk-group completion)
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
@@ -129,6 +140,9 @@ constexpr float TRUNC_COMP = 1.000704f;
 // the tensor give 0. kmajor tiles use the 128-byte swizzle in 16-byte units; MN-major tiles the 32-byte-unit variant.
 bool make_map_2d(CUtensorMap* map, const float* ptr, uint64_t inner, uint64_t outer, uint64_t row_pitch_elems,
                  uint32_t box_outer, bool kmajor);
+// The same for `batch` matrices `batch_stride_elems` apart (box [1, box_outer, 32]).
+bool make_map_3d(CUtensorMap* map, const float* ptr, uint64_t inner, uint64_t outer, uint64_t batch, uint64_t row_pitch_elems,
+                 uint64_t batch_stride_elems, uint32_t box_outer, bool kmajor);
 
 // Device word the kernels set when a bounded wait expires (checked and cleared by gt_sync). Null while a graph is
 // being captured and the word does not exist yet.

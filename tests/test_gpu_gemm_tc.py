@@ -96,3 +96,26 @@ def test_config1_step_in_tf32_mode(gpu, oracle):
     for i, p in enumerate(m.params()):
         r = rel_l2(p.grad, om.grad(i))
         assert r <= REL_L2_TC, f"grad[{i}] {p.shape}: relative L2 {r:.3e}"
+
+
+def test_muon_batched_groups_in_tf32_mode(gpu, oracle):
+    """Three 192x576 and two 576x192 matrices: each shape is orthogonalised as one batch on the tensor cores."""
+    from gguf_trainer_b200.autograd import Tensor
+    from gguf_trainer_b200.optim import MuonGpu
+    rng = oracle.Mulberry32(0x4D4D)
+    shapes = [(192, 576), (576, 192), (192, 576), (576, 192), (192, 576)]
+    ps = [Tensor(rng.randn(s, 0.05), list(s), True) for s in shapes]
+    ws = [p.data.copy().reshape(s) for p, s in zip(ps, shapes)]
+    bufs = [np.zeros(s, np.float32) for s in shapes]
+    opt = MuonGpu(gpu, ps, [], lr=0.05, momentum=0.95, nesterov=True, nsSteps=5, aux={"lr": 1e-3})
+    for _ in range(2):
+        gs = [rng.randn(s, 0.3) for s in shapes]
+        for p, g in zip(ps, gs):
+            gpu.writeStateBuffer(gpu.buffersFor(p)["grad"], g)
+        opt.recordStep()
+        for w, g, b in zip(ws, gs, bufs):
+            oracle.muon_step_array(w, g, b, 0.05, 0.95, True, 5)
+    gpu.sync(ps)
+    for i, (p, w) in enumerate(zip(ps, ws)):
+        r = rel_l2(p.data, w)
+        assert r <= REL_L2_TC, f"matrix {i} {shapes[i]}: relative L2 {r:.3e}"
