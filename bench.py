@@ -216,17 +216,28 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
-    from gguf_trainer_b200.arch import buildModel, smolLM2_135M
+    from gguf_trainer_b200 import autograd as ag
+    from gguf_trainer_b200.arch import buildModel, gemma3_95M, qwen3_0_6B, smolLM2_135M
     from gguf_trainer_b200.backend import requireGPU
     from gguf_trainer_b200.optim import AdamWGpu, MuonGpu
     from gguf_trainer_b200.train import CudaStep, DataParallel
 
-    cfg = smolLM2_135M()
+    # The headline workload is the SmolLM2-135M shape; the other two configurations of the parity list can be timed too.
+    cfg = {"smollm2": smolLM2_135M, "gemma3": gemma3_95M, "qwen3-lora": qwen3_0_6B}[args.config]()
     B, T = args.batch, args.seq
     gpu = requireGPU("the benchmark", device=local, precision=args.precision)
     model = buildModel(cfg, 1234)       # same seed on every rank: replicated weights
-    params = model.params()
-    groups = model.paramGroups()
+    loss_chunk = args.loss_chunk
+    mask = None
+    if args.config == "qwen3-lora":      # frozen base, rank-16 adapters on the 7 projections, 50 % prompt mask, recompute
+        from gguf_trainer_b200.lora import applyLora
+        from gguf_trainer_b200.rng import Mulberry32 as _M
+        lora = applyLora(model, 16, 32.0, _M(4321))
+        ag.setCheckpointing(True)
+    if args.recompute:
+        ag.setCheckpointing(True)
+    params = [p for p in model.params() if p.requiresGrad] if args.config != "qwen3-lora" else lora.groups["aux"]
+    groups = model.paramGroups() if args.config != "qwen3-lora" else lora.groups
     # gradients in one arena, last layers first: the order backward finishes them in
     order = list(reversed(params))
     arena = gpu.reserveGradArena(order)
@@ -251,16 +262,23 @@ def run_ours(args):
     maxStart = len(stream) - T - 1
     starts = np.floor(rng.draws(need) * maxStart).astype(np.int64)
 
+    if args.config == "qwen3-lora":
+        mask = (Mulberry32(5).draws(len(stream)) < 0.5)
+
     def batch(step):
         s = starts[step * B * world + rank * B: step * B * world + (rank + 1) * B]
         ids = np.concatenate([stream[a:a + T] for a in s])
         tg = np.concatenate([stream[a + 1:a + 1 + T] for a in s])
+        if mask is not None:
+            keep = np.concatenate([mask[a + 1:a + 1 + T] for a in s])
+            tg = np.where(keep, tg, -1)
         return ids, tg
 
     # pinned host staging for the e2e arm
     pin_ids = torch.empty(B * T, dtype=torch.int32).pin_memory()
     pin_tg = torch.empty(B * T, dtype=torch.int32).pin_memory()
-    step = CudaStep(model, gpu, B, T, world=world, capture=not args.no_graph, dp=dp, arena=arena if dp is not None else None)
+    step = CudaStep(model, gpu, B, T, lossChunk=loss_chunk, world=world, capture=not args.no_graph, dp=dp,
+                    arena=arena if dp is not None else None)
 
     def one_step(i, resident):
         ids, tg = batch(i)
@@ -315,12 +333,16 @@ def run_ours(args):
         pk = peaks()
         flops, gms, ncalls = backward_gemm_roofline(gpu, B * T)
         achieved = flops / (gms / 1e3) / 1e12
+        metric = METRIC if (args.config == "smollm2" and B == 8 and T == 2048) else f"train tokens/s, {args.config} shape seq{T} b{B}"
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "metric": metric, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_res / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": {"tf32": "tf32 products, f32 accumulate and storage", "fp32": "f32", "bf16": "bf16 products, f32 accumulate"}[args.precision],
             "data": "synthetic",
-            "config": {"workload": f"SmolLM2-135M shape llama (h576 L30 9/3 heads hd64 ffn1536 V49152, tied), full step fwd+bwd+{args.optimizer}, "
+            "config": {"workload": {"smollm2": "SmolLM2-135M shape llama (h576 L30 9/3 heads hd64 ffn1536 V49152, tied)",
+                                    "gemma3": "gemma3 ~95M shape (h640 L12 4/1 heads hd256 ffn2048 V32768, window 512 on 5 of 6 layers)",
+                                    "qwen3-lora": "Qwen3-0.6B shape LoRA r16 (h1024 L28 16/8 heads hd128 ffn3072 V151936), frozen base, 50% loss mask, recompute"}[args.config]
+                                   + f", full step fwd+bwd+{args.optimizer}, "
                                    f"seq {T} x batch {B} per GPU, Zipf(1.1) ids, N(0,0.02) f32 weights",
                        "precision": args.precision, "graph_replay": not args.no_graph,
                        "l2": "per-step working set (activations > 20 GB) exceeds L2; no flush needed",
@@ -441,6 +463,9 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=256)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--config", default="smollm2", choices=["smollm2", "gemma3", "qwen3-lora"])
+    ap.add_argument("--loss-chunk", type=int, default=0)
+    ap.add_argument("--recompute", action="store_true")
     ap.add_argument("--profile", action="store_true", help="per-entry-point GPU time of one eager step")
     ap.add_argument("--micro", default="", help="time one op of the step instead: attention | gemm")
     ap.add_argument("--micro-batch", type=int, default=8)
