@@ -8,8 +8,10 @@
 // accumulation are f32.
 //
 // All three kernels share one shape. A CTA owns 128 rows of the output (queries for forward and dQ, keys for
-// dK/dV) and walks the other axis in blocks. One warp issues TMA and MMA; eight warps do the element math, two
-// per TMEM lane quadrant, each taking half of a block's columns, one output row per thread (no shuffles). The
+// dK/dV) and walks the other axis in blocks. In the backward kernels one thread issues the TMA copies and one
+// thread of another warp the MMAs, each waiting only on what its own instructions need (with a single issuing
+// thread the waits and issue latencies of the two roles added up to more than the tensor time of a block);
+// descriptors are formed by one add per operand. Eight warps do the element math, two per TMEM lane quadrant, each taking half of a block's columns, one output row per thread (no shuffles). The
 // score products of block i+1 are issued before the element math of block i is waited for (their TMEM
 // accumulators are double-buffered), so the tensor pipe and the CUDA cores overlap; operand tiles of the next
 // block are fetched as soon as the products that read the current ones have completed.
@@ -25,7 +27,11 @@ namespace {
 constexpr float NEG = -3.0e38f;
 constexpr int ROWS = 128;          // output rows per CTA = TMEM lanes
 constexpr int MATH_WARPS = 8;
-constexpr int THREADS = (MATH_WARPS + 1) * 32;
+constexpr int MMA_WARP = MATH_WARPS, TMA_WARP = MATH_WARPS + 1;   // one thread of each issues the products / the copies
+constexpr int THREADS = (MATH_WARPS + 2) * 32;
+// The forward kernel runs two CTAs per SM and hides its copy latency that way: one control warp issues both the
+// copies and the products (with a tenth warp it was a fifth slower).
+constexpr int FWD_THREADS = (MATH_WARPS + 1) * 32;
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -40,6 +46,26 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
                : "r"(taddr) : "memory");
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                 "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(taddr) : "memory");
+}
+// issue only: several loads can then share one tmem_wait_ld()
+template <int N>
+__device__ __forceinline__ void tmem_ld_issue(uint32_t taddr, float* v) {
+  static_assert(N == 16 || N % 32 == 0, "column count");
+  if constexpr (N == 16) tmem_ld16_issue(taddr, v);
+  else {
+#pragma unroll
+    for (int c = 0; c < N / 32; c++) tmem_ld32_issue(taddr + c * 32, v + c * 32);
+  }
+}
+// A descriptor of the same tile `bytes` further on (the start-address field counts 16-byte units and cannot
+// carry: shared memory is smaller than the field's range).
+__device__ __forceinline__ uint64_t desc_off(uint64_t d, uint32_t bytes) { return d + (uint64_t)(bytes >> 4); }
 template <int N>
 __device__ __forceinline__ void tmem_ld(uint32_t taddr, float* v) {
   static_assert(N == 16 || N % 32 == 0, "column count");
@@ -92,7 +118,7 @@ struct FwdSmem {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(THREADS, HD <= 64 ? 2 : 1)
+__global__ void __launch_bounds__(FWD_THREADS, HD <= 64 ? 2 : 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                    const __grid_constant__ CUtensorMap mapV, float* __restrict__ out, float* __restrict__ lse, int rows, int T,
                    int Hq, int Hkv, int window, float scale2, int* __restrict__ flag) {
@@ -126,38 +152,41 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     mbar_init(p_full, MATH_WARPS * 32); mbar_init(o_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == MATH_WARPS) tmem_alloc(tmem_slot, S::TMEM_COLS);
+  if (warp == MMA_WARP) tmem_alloc(tmem_slot, S::TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot_ptr;
   const uint32_t tm_o = tmem + 2 * BKV;
   Waiter w{false, flag};
+  auto s_bar = [&](int it) { return (it & 1) ? s_full1 : s_full0; };
+  auto s_par = [&](int it) { return (uint32_t)((it >> 1) & 1); };
 
-  if (warp == MATH_WARPS) {
+  auto load_k = [&](int i) {
+    mbar_expect_tx(k_full, S::K_BYTES);
+    tma_load_3d(k_s, &mapK, 0, row0 + (kb_lo + i) * BKV, kvh * ATOMS, k_full);
+  };
+  auto load_v = [&](int i) {
+    mbar_expect_tx(v_full, S::V_BYTES);
+    tma_load_3d(v_s, &mapV, 0, row0 + (kb_lo + i) * BKV, kvh * ATOMS, v_full);
+  };
+  if (warp == MMA_WARP) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = idesc_tf32(false, false, ROWS, BKV);   // S = Q.K^T, both K-major
       constexpr uint32_t idesc_o = idesc_tf32(false, true, ROWS, HD);     // O = P.V, V is [keys, hd]
-      auto load_k = [&](int i) {
-        mbar_expect_tx(k_full, S::K_BYTES);
-        for (int a = 0; a < ATOMS; a++) tma_load_2d(k_s + a * (BKV * 128), &mapK, kvh * HD + 32 * a, row0 + (kb_lo + i) * BKV, k_full);
-      };
-      auto load_v = [&](int i) {
-        mbar_expect_tx(v_full, S::V_BYTES);
-        for (int a = 0; a < ATOMS; a++) tma_load_2d(v_s + a * (BKV * 128), &mapV, kvh * HD + 32 * a, row0 + (kb_lo + i) * BKV, v_full);
-      };
+      const uint64_t d_q = desc_kmajor(q_s), d_k = desc_kmajor(k_s), d_p = desc_kmajor(p_s), d_v = smem_desc(v_s, BKV * 128, 512, 1);
       auto mma_s = [&](int i) {
         const uint32_t tm_s = tmem + (i & 1) * BKV;
 #pragma unroll
         for (int a = 0; a < ATOMS; a++)
 #pragma unroll
           for (int j = 0; j < 4; j++)
-            umma_tf32(tm_s, desc_kmajor(q_s + a * (ROWS * 128) + j * 32), desc_kmajor(k_s + a * (BKV * 128) + j * 32), idesc_s,
+            umma_tf32(tm_s, desc_off(d_q, a * (ROWS * 128) + j * 32), desc_off(d_k, a * (BKV * 128) + j * 32), idesc_s,
                       (a > 0 || j > 0) ? 1u : 0u);
-        umma_commit((i & 1) ? s_full1 : s_full0);
+        umma_commit(s_bar(i));
       };
       mbar_expect_tx(q_full, S::Q_BYTES);
-      for (int a = 0; a < ATOMS; a++) tma_load_2d(q_s + a * (ROWS * 128), &mapQ, h * HD + 32 * a, row0 + q0, q_full);
+      tma_load_3d(q_s, &mapQ, 0, row0 + q0, h * ATOMS, q_full);
       load_k(0);
       load_v(0);
       w.wait(q_full, 0, 11);
@@ -177,18 +206,17 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         tc_fence_after();
 #pragma unroll
         for (int j = 0; j < BKV / 8; j++)
-          umma_tf32(tm_o, desc_kmajor(p_s + (j / 4) * (ROWS * 128) + (j % 4) * 32), smem_desc(v_s + j * 1024, BKV * 128, 512, 1), idesc_o,
-                    j > 0 ? 1u : 0u);
+          umma_tf32(tm_o, desc_off(d_p, (j / 4) * (ROWS * 128) + (j % 4) * 32), desc_off(d_v, j * 1024), idesc_o, j > 0 ? 1u : 0u);
         umma_commit(o_full);
-        if (i + 1 < nkb) {
-          w.wait(((i + 1) & 1) ? s_full1 : s_full0, ((i + 1) >> 1) & 1, 13);   // K tile read: fetch the one after
-          if (i + 2 < nkb) load_k(i + 2);
+        if (i + 2 < nkb) {                     // K tile read: fetch the one after
+          w.wait(s_bar(i + 1), s_par(i + 1), 13);
+          load_k(i + 2);
         }
         w.wait(o_full, i & 1, 15);             // V and P tiles read
         if (i + 1 < nkb) load_v(i + 1);
       }
     }
-  } else {
+  } else if (warp < MATH_WARPS) {
     const int qd = warp & 3, half = warp >> 2;
     const int r = qd * 32 + lane;
     const int tq = q0 + r;
@@ -201,7 +229,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     const uint32_t lane_base = (uint32_t)(qd * 32) << 16;
     for (int i = 0; i < nkb; i++) {
       const int k0 = (kb_lo + i) * BKV + half * 32;
-      w.wait((i & 1) ? s_full1 : s_full0, (i >> 1) & 1, 16);
+      w.wait(s_bar(i), s_par(i), 16);
       tc_fence_after();
       float s[32];
       tmem_ld<32>(tmem + (i & 1) * BKV + half * 32 + lane_base, s);
@@ -262,7 +290,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == MATH_WARPS) {
+  if (warp == MMA_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem, S::TMEM_COLS);
   }
@@ -293,18 +321,21 @@ __global__ void attn_bwd_d_tc_kernel(int rows, int Hq, int hd, float scale, cons
 // ---- dK, dV: CTA = 128 keys of one kv head; loop over the group's query heads and over blocks of NQ queries ----
 // Transposed products so that keys are the rows: S^T = K.Q^T and dP^T = V.dO^T (M=128 keys, N=NQ queries); then
 // dV += P^T.dO and dK += dS^T.Q with P^T, dS^T written to shared memory as K-major A operands (K = queries) and
-// dO, Q read a second time as [queries, hd] operands (hd contiguous).
-template <int HD, int NQ>
+// dO, Q read a second time as [queries, hd] operands (hd contiguous). KBUF = 2 keeps two blocks of the K-major
+// Q / dO copies in flight (their fetch is the longest latency of the loop) where shared memory has the room.
+template <int HD, int NQ, int KBUF>
 struct DkvSmem {
   static constexpr int KV_BYTES = ROWS * HD * 4, QT_BYTES = NQ * HD * 4, PT_BYTES = ROWS * NQ * 4;
-  static constexpr int K_OFF = 0, V_OFF = KV_BYTES, QK_OFF = 2 * KV_BYTES, GK_OFF = QK_OFF + QT_BYTES, QM_OFF = GK_OFF + QT_BYTES,
-                       GM_OFF = QM_OFF + QT_BYTES, P_OFF = GM_OFF + QT_BYTES, DS_OFF = P_OFF + PT_BYTES, BAR_OFF = DS_OFF + PT_BYTES;
+  static constexpr int K_OFF = 0, V_OFF = KV_BYTES, QK_OFF = 2 * KV_BYTES, GK_OFF = QK_OFF + KBUF * QT_BYTES,
+                       QM_OFF = GK_OFF + KBUF * QT_BYTES, GM_OFF = QM_OFF + QT_BYTES, P_OFF = GM_OFF + QT_BYTES,
+                       DS_OFF = P_OFF + PT_BYTES, BAR_OFF = DS_OFF + PT_BYTES;
   static constexpr int TOTAL = BAR_OFF + 128 + 1024;
   static constexpr int COLS = 4 * NQ + 2 * HD;
   static constexpr uint32_t TMEM_COLS = COLS <= 128 ? 128 : (COLS <= 256 ? 256 : 512);
+  static_assert(TOTAL <= 232448, "shared memory");
 };
 
-template <int HD, int NQ>
+template <int HD, int NQ, int KBUF>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
                        const __grid_constant__ CUtensorMap mapQk, const __grid_constant__ CUtensorMap mapQm,
@@ -312,15 +343,15 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
                        const float* __restrict__ lse, const float* __restrict__ Ds, float* gk, int accum_k, float* gv, int accum_v,
                        int rows, int T, int Hq, int Hkv, int window, float scale2, float dp_scale, int* __restrict__ flag) {
   extern __shared__ uint8_t smem_raw[];
-  using S = DkvSmem<HD, NQ>;
+  using S = DkvSmem<HD, NQ, KBUF>;
   constexpr int ATOMS = HD / 32, NH = NQ / 2, HH = HD / 2;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t k_s = base + S::K_OFF, v_s = base + S::V_OFF, qk_s = base + S::QK_OFF, gk_s = base + S::GK_OFF,
                  qm_s = base + S::QM_OFF, gm_s = base + S::GM_OFF, p_s = base + S::P_OFF, ds_s = base + S::DS_OFF;
   const uint32_t bars = base + S::BAR_OFF;
-  const uint32_t kv_full = bars, qk_full = bars + 8, qm_full = bars + 16, s_full0 = bars + 24, s_full1 = bars + 32, p_full = bars + 40,
-                 acc_done = bars + 48;
+  const uint32_t kv_full = bars, qk_full0 = bars + 8, qk_full1 = bars + 16, qm_full = bars + 24, s_full0 = bars + 32,
+                 s_full1 = bars + 40, p_full = bars + 48, acc_done = bars + 56;
   const uint32_t tmem_slot = bars + 64;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + S::BAR_OFF + 64);
 
@@ -336,11 +367,11 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
   const int iters = nqb * group;
 
   if (threadIdx.x == 0) {
-    mbar_init(kv_full, 1); mbar_init(qk_full, 1); mbar_init(qm_full, 1); mbar_init(s_full0, 1); mbar_init(s_full1, 1);
-    mbar_init(p_full, MATH_WARPS * 32); mbar_init(acc_done, 1);
+    mbar_init(kv_full, 1); mbar_init(qk_full0, 1); mbar_init(qk_full1, 1); mbar_init(qm_full, 1); mbar_init(s_full0, 1);
+    mbar_init(s_full1, 1); mbar_init(p_full, MATH_WARPS * 32); mbar_init(acc_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == MATH_WARPS) tmem_alloc(tmem_slot, S::TMEM_COLS);
+  if (warp == MMA_WARP) tmem_alloc(tmem_slot, S::TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -348,75 +379,103 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
   // columns: [S^T | dP^T] x 2 buffers, then dV, dK
   const uint32_t tm_dv = tmem + 4 * NQ, tm_dk = tmem + 4 * NQ + HD;
   Waiter w{false, flag};
+  // barrier and parity of the K-major copies of block `it`, and of its score products
+  auto qk_bar = [&](int it) { return (KBUF == 2 && (it & 1)) ? qk_full1 : qk_full0; };
+  auto qk_par = [&](int it) { return (uint32_t)((KBUF == 2 ? it >> 1 : it) & 1); };
+  auto s_bar = [&](int it) { return (it & 1) ? s_full1 : s_full0; };
+  auto s_par = [&](int it) { return (uint32_t)((it >> 1) & 1); };
+#ifdef GT_ATTN_TRACE
+  const bool tr = blockIdx.x == 0 && blockIdx.y == 0 && lane == 0;
+  long long tprev = clock64();
+#define TRACE(slot) if (tr && i >= 8 && i < 40) { long long tn = clock64(); flag[64 + (i - 8) * 32 + slot] = (int)(tn - tprev); tprev = tn; }
+#else
+#define TRACE(slot)
+#endif
 
-  if (warp == MATH_WARPS) {
+  if (warp == TMA_WARP) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = idesc_tf32(false, false, ROWS, NQ);
-      constexpr uint32_t idesc_g = idesc_tf32(false, true, ROWS, HD);
       auto load_k = [&](int it) {   // K-major copies of Q and dO
         const int h = kvh * group + it / nqb, qr = row0 + (qb_lo + it % nqb) * NQ;
-        mbar_expect_tx(qk_full, 2 * S::QT_BYTES);
-        for (int a = 0; a < ATOMS; a++) {
-          tma_load_2d(qk_s + a * (NQ * 128), &mapQk, h * HD + 32 * a, qr, qk_full);
-          tma_load_2d(gk_s + a * (NQ * 128), &mapGk, h * HD + 32 * a, qr, qk_full);
-        }
+        const uint32_t bar = qk_bar(it), off = (KBUF == 2 && (it & 1)) ? S::QT_BYTES : 0;
+        mbar_expect_tx(bar, 2 * S::QT_BYTES);
+        tma_load_3d(qk_s + off, &mapQk, 0, qr, h * ATOMS, bar);
+        tma_load_3d(gk_s + off, &mapGk, 0, qr, h * ATOMS, bar);
       };
       auto load_m = [&](int it) {   // [queries, hd] copies for the gradient products
         const int h = kvh * group + it / nqb, qr = row0 + (qb_lo + it % nqb) * NQ;
         mbar_expect_tx(qm_full, 2 * S::QT_BYTES);
-        for (int a = 0; a < ATOMS; a++) {
-          tma_load_2d(qm_s + a * (NQ * 128), &mapQm, h * HD + 32 * a, qr, qm_full);
-          tma_load_2d(gm_s + a * (NQ * 128), &mapGm, h * HD + 32 * a, qr, qm_full);
-        }
+        tma_load_3d(qm_s, &mapQm, 0, qr, h * ATOMS, qm_full);
+        tma_load_3d(gm_s, &mapGm, 0, qr, h * ATOMS, qm_full);
       };
-      auto mma_s = [&](int i) {
-        const uint32_t tm_s = tmem + (i & 1) * 2 * NQ, tm_dp = tm_s + NQ;
+      mbar_expect_tx(kv_full, 2 * S::KV_BYTES);
+      tma_load_3d(k_s, &mapK, 0, row0 + k0, kvh * ATOMS, kv_full);
+      tma_load_3d(v_s, &mapV, 0, row0 + k0, kvh * ATOMS, kv_full);
+      load_k(0);
+      load_m(0);
+      if (KBUF == 2 && iters > 1) load_k(1);
+      // waits in the order the products complete: scores of block 0, then scores of block i+1 before the
+      // gradient products of block i. Once the scores of a block are done its K-major copies may be replaced.
+      w.wait(s_full0, 0, 23);
+      if (KBUF < iters) load_k(KBUF);
+      for (int i = 0; i < iters; i++) {
+        if (i + 1 + KBUF < iters) {
+          w.wait(s_bar(i + 1), s_par(i + 1), 23);
+          TRACE(16)
+          load_k(i + 1 + KBUF);
+          TRACE(17)
+        }
+        w.wait(acc_done, i & 1, 25);              // the gradient products have read the [queries, hd] copies
+        TRACE(18)
+        if (i + 1 < iters) load_m(i + 1);
+        TRACE(19)
+      }
+    }
+  } else if (warp == MMA_WARP) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = idesc_tf32(false, false, ROWS, NQ);
+      constexpr uint32_t idesc_g = idesc_tf32(false, true, ROWS, HD);
+      const uint64_t d_k = desc_kmajor(k_s), d_v = desc_kmajor(v_s), d_qk = desc_kmajor(qk_s), d_gk = desc_kmajor(gk_s),
+                     d_p = desc_kmajor(p_s), d_ds = desc_kmajor(ds_s), d_gm = smem_desc(gm_s, NQ * 128, 512, 1),
+                     d_qm = smem_desc(qm_s, NQ * 128, 512, 1);
+      auto mma_s = [&](int it) {
+        const uint32_t tm_s = tmem + (it & 1) * 2 * NQ, tm_dp = tm_s + NQ;
+        const uint32_t boff = (KBUF == 2 && (it & 1)) ? S::QT_BYTES : 0;
 #pragma unroll
         for (int a = 0; a < ATOMS; a++)
 #pragma unroll
           for (int j = 0; j < 4; j++) {
             const uint32_t acc = (a > 0 || j > 0) ? 1u : 0u;
-            umma_tf32(tm_s, desc_kmajor(k_s + a * (ROWS * 128) + j * 32), desc_kmajor(qk_s + a * (NQ * 128) + j * 32), idesc_s, acc);
-            umma_tf32(tm_dp, desc_kmajor(v_s + a * (ROWS * 128) + j * 32), desc_kmajor(gk_s + a * (NQ * 128) + j * 32), idesc_s, acc);
+            umma_tf32(tm_s, desc_off(d_k, a * (ROWS * 128) + j * 32), desc_off(d_qk, boff + a * (NQ * 128) + j * 32), idesc_s, acc);
+            umma_tf32(tm_dp, desc_off(d_v, a * (ROWS * 128) + j * 32), desc_off(d_gk, boff + a * (NQ * 128) + j * 32), idesc_s, acc);
           }
-        umma_commit((i & 1) ? s_full1 : s_full0);
+        umma_commit(s_bar(it));
       };
-      mbar_expect_tx(kv_full, 2 * S::KV_BYTES);
-      for (int a = 0; a < ATOMS; a++) {
-        tma_load_2d(k_s + a * (ROWS * 128), &mapK, kvh * HD + 32 * a, row0 + k0, kv_full);
-        tma_load_2d(v_s + a * (ROWS * 128), &mapV, kvh * HD + 32 * a, row0 + k0, kv_full);
-      }
-      load_k(0);
-      load_m(0);
       w.wait(kv_full, 0, 21);
-      w.wait(qk_full, 0, 22);
+      w.wait(qk_full0, 0, 22);
       tc_fence_after();
       mma_s(0);
-      w.wait(s_full0, 0, 23);
-      if (iters > 1) load_k(1);
       for (int i = 0; i < iters; i++) {
-        if (i + 1 < iters) {
-          w.wait(qk_full, (i + 1) & 1, 22);
+        if (i + 1 < iters) {                      // next block's scores, under this block's element math
+          w.wait(qk_bar(i + 1), qk_par(i + 1), 22);
+          TRACE(0)
           tc_fence_after();
           mma_s(i + 1);
+          TRACE(1)
         }
         w.wait(qm_full, i & 1, 24);
+        TRACE(2)
         w.wait(p_full, i & 1, 24);
+        TRACE(3)
         tc_fence_after();
 #pragma unroll
         for (int j = 0; j < NQ / 8; j++) {
           const uint32_t acc = (i > 0 || j > 0) ? 1u : 0u;
           const uint32_t aoff = (j / 4) * (ROWS * 128) + (j % 4) * 32;
-          umma_tf32(tm_dv, desc_kmajor(p_s + aoff), smem_desc(gm_s + j * 1024, NQ * 128, 512, 1), idesc_g, acc);
-          umma_tf32(tm_dk, desc_kmajor(ds_s + aoff), smem_desc(qm_s + j * 1024, NQ * 128, 512, 1), idesc_g, acc);
+          umma_tf32(tm_dv, desc_off(d_p, aoff), desc_off(d_gm, j * 1024), idesc_g, acc);
+          umma_tf32(tm_dk, desc_off(d_ds, aoff), desc_off(d_qm, j * 1024), idesc_g, acc);
         }
         umma_commit(acc_done);
-        if (i + 1 < iters) {
-          w.wait(((i + 1) & 1) ? s_full1 : s_full0, ((i + 1) >> 1) & 1, 23);
-          if (i + 2 < iters) load_k(i + 2);
-        }
-        w.wait(acc_done, i & 1, 25);
-        if (i + 1 < iters) load_m(i + 1);
+        TRACE(4)
       }
     }
   } else {
@@ -424,26 +483,40 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
     const int r = qd * 32 + lane;            // key row inside the tile
     const int kg = k0 + r;                   // key position in the sequence
     const uint32_t lane_base = (uint32_t)(qd * 32) << 16;
+#ifdef GT_ATTN_TRACE
+    const bool trm = tr && warp == 0;
+#define TRACEM(slot) if (trm && i >= 8 && i < 40) { long long tn = clock64(); flag[64 + (i - 8) * 32 + slot] = (int)(tn - tprev); tprev = tn; }
+#else
+#define TRACEM(slot)
+#endif
     for (int i = 0; i < iters; i++) {
+      TRACEM(8)
       const int h = kvh * group + i / nqb;
       const int qpos0 = (qb_lo + i % nqb) * NQ + half * NH;      // first query of this thread's columns
-      w.wait((i & 1) ? s_full1 : s_full0, (i >> 1) & 1, 26);
-      tc_fence_after();
-      float s[NH], dp[NH];
-      const uint32_t tm_s = tmem + (i & 1) * 2 * NQ + half * NH + lane_base;
-      tmem_ld<NH>(tm_s, s);
-      tmem_ld<NH>(tm_s + NQ, dp);
       const float4* l4 = reinterpret_cast<const float4*>(lse + (size_t)h * rows + row0 + qpos0);
       const float4* d4 = reinterpret_cast<const float4*>(Ds + (size_t)h * rows + row0 + qpos0);
       // every (key, query) pair of the tile kept: keys at or before the first query, queries inside the sequence
       // and, with a window, the last query still within reach of the first key
       const bool interior = (k0 + ROWS - 1 <= qpos0) && (qpos0 + NH - 1 < T) && (window == 0 || k0 >= qpos0 + NH - window) &&
                             (((size_t)h * rows + row0) % 4 == 0);   // and the 16-byte loads of LSE / Ds are aligned
+      float4 Lv[NH / 4], Dv[NH / 4];
+      if (interior) {                            // fetched under the wait for the products
+#pragma unroll
+        for (int c4 = 0; c4 < NH / 4; c4++) { Lv[c4] = __ldg(l4 + c4); Dv[c4] = __ldg(d4 + c4); }
+      }
+      w.wait(s_bar(i), s_par(i), 26);
+      TRACEM(9)
+      tc_fence_after();
+      float s[NH], dp[NH];
+      const uint32_t tm_s = tmem + (i & 1) * 2 * NQ + half * NH + lane_base;
+      tmem_ld_issue<NH>(tm_s, s);
+      tmem_ld_issue<NH>(tm_s + NQ, dp);
+      tmem_wait_ld();
+      TRACEM(10)
       if (interior) {
 #pragma unroll
         for (int c4 = 0; c4 < NH / 4; c4++) {
-          const float4 L = __ldg(l4 + c4), Dv = __ldg(d4 + c4);
-          const float Ls[4] = {L.x, L.y, L.z, L.w}, Dd[4] = {Dv.x, Dv.y, Dv.z, Dv.w};
+          const float Ls[4] = {Lv[c4].x, Lv[c4].y, Lv[c4].z, Lv[c4].w}, Dd[4] = {Dv[c4].x, Dv[c4].y, Dv[c4].z, Dv[c4].w};
 #pragma unroll
           for (int e = 0; e < 4; e++) {
             const int c = c4 * 4 + e;
@@ -468,13 +541,17 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
           dp[c] = d;
         }
       }
+      TRACEM(11)
       if (i > 0) w.wait(acc_done, (i - 1) & 1, 27);   // the previous gradient products still read P^T / dS^T
+      TRACEM(12)
       store_row_kmajor<NH>(base_ptr + S::P_OFF, r, half * NH, s);
       store_row_kmajor<NH>(base_ptr + S::DS_OFF, r, half * NH, dp);
       fence_async_smem();
       tc_fence_before();
       mbar_arrive(p_full);
+      TRACEM(13)
     }
+#undef TRACEM
     if (iters > 0) w.wait(acc_done, (iters - 1) & 1, 28);
     tc_fence_after();
     {   // warp-uniform: the TMEM loads are warp-wide instructions, only the stores are per-row
@@ -507,9 +584,10 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
       }
     }
   }
+#undef TRACE
   tc_fence_before();
   __syncthreads();
-  if (warp == MATH_WARPS) {
+  if (warp == MMA_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem, S::TMEM_COLS);
   }
@@ -517,18 +595,19 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
 
 // ---- dQ: CTA = 128 queries of one head; loop over blocks of NK keys ----
 // S = Q.K^T and dP = dO.V^T (M=128 queries, N=NK keys); dS written as a K-major A operand (K = keys);
-// dQ += dS.K with K read a second time as a [keys, hd] operand.
-template <int HD, int NK>
+// dQ += dS.K with K read a second time as a [keys, hd] operand. KBUF as in the dK/dV kernel.
+template <int HD, int NK, int KBUF>
 struct DqSmem {
   static constexpr int Q_BYTES = ROWS * HD * 4, KT_BYTES = NK * HD * 4, DS_BYTES = ROWS * NK * 4;
-  static constexpr int Q_OFF = 0, G_OFF = Q_BYTES, KK_OFF = 2 * Q_BYTES, VK_OFF = KK_OFF + KT_BYTES, KM_OFF = VK_OFF + KT_BYTES,
-                       DS_OFF = KM_OFF + KT_BYTES, BAR_OFF = DS_OFF + DS_BYTES;
+  static constexpr int Q_OFF = 0, G_OFF = Q_BYTES, KK_OFF = 2 * Q_BYTES, VK_OFF = KK_OFF + KBUF * KT_BYTES,
+                       KM_OFF = VK_OFF + KBUF * KT_BYTES, DS_OFF = KM_OFF + KT_BYTES, BAR_OFF = DS_OFF + DS_BYTES;
   static constexpr int TOTAL = BAR_OFF + 128 + 1024;
   static constexpr int COLS = 4 * NK + HD;
   static constexpr uint32_t TMEM_COLS = COLS <= 128 ? 128 : (COLS <= 256 ? 256 : 512);
+  static_assert(TOTAL <= 232448, "shared memory");
 };
 
-template <int HD, int NK>
+template <int HD, int NK, int KBUF>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapG,
                       const __grid_constant__ CUtensorMap mapKk, const __grid_constant__ CUtensorMap mapVk,
@@ -536,15 +615,15 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                       float* gq, int accum_q, int rows, int T, int Hq, int Hkv, int window, float scale2, float dp_scale,
                       int* __restrict__ flag) {
   extern __shared__ uint8_t smem_raw[];
-  using S = DqSmem<HD, NK>;
+  using S = DqSmem<HD, NK, KBUF>;
   constexpr int ATOMS = HD / 32, NH = NK / 2, HH = HD / 2;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t q_s = base + S::Q_OFF, g_s = base + S::G_OFF, kk_s = base + S::KK_OFF, vk_s = base + S::VK_OFF, km_s = base + S::KM_OFF,
                  ds_s = base + S::DS_OFF;
   const uint32_t bars = base + S::BAR_OFF;
-  const uint32_t q_full = bars, kk_full = bars + 8, km_full = bars + 16, s_full0 = bars + 24, s_full1 = bars + 32, p_full = bars + 40,
-                 acc_done = bars + 48;
+  const uint32_t q_full = bars, kk_full0 = bars + 8, kk_full1 = bars + 16, km_full = bars + 24, s_full0 = bars + 32,
+                 s_full1 = bars + 40, p_full = bars + 48, acc_done = bars + 56;
   const uint32_t tmem_slot = bars + 64;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + S::BAR_OFF + 64);
 
@@ -559,63 +638,79 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   const int iters = kb_hi - kb_lo + 1;
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1); mbar_init(kk_full, 1); mbar_init(km_full, 1); mbar_init(s_full0, 1); mbar_init(s_full1, 1);
-    mbar_init(p_full, MATH_WARPS * 32); mbar_init(acc_done, 1);
+    mbar_init(q_full, 1); mbar_init(kk_full0, 1); mbar_init(kk_full1, 1); mbar_init(km_full, 1); mbar_init(s_full0, 1);
+    mbar_init(s_full1, 1); mbar_init(p_full, MATH_WARPS * 32); mbar_init(acc_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == MATH_WARPS) tmem_alloc(tmem_slot, S::TMEM_COLS);
+  if (warp == MMA_WARP) tmem_alloc(tmem_slot, S::TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot_ptr;
   const uint32_t tm_dq = tmem + 4 * NK;
   Waiter w{false, flag};
+  auto kk_bar = [&](int it) { return (KBUF == 2 && (it & 1)) ? kk_full1 : kk_full0; };
+  auto kk_par = [&](int it) { return (uint32_t)((KBUF == 2 ? it >> 1 : it) & 1); };
+  auto s_bar = [&](int it) { return (it & 1) ? s_full1 : s_full0; };
+  auto s_par = [&](int it) { return (uint32_t)((it >> 1) & 1); };
 
-  if (warp == MATH_WARPS) {
+  if (warp == TMA_WARP) {
+    if (lane == 0) {
+      auto load_k = [&](int it) {   // K-major copies of K and V
+        const int kr = row0 + (kb_lo + it) * NK;
+        const uint32_t bar = kk_bar(it), off = (KBUF == 2 && (it & 1)) ? S::KT_BYTES : 0;
+        mbar_expect_tx(bar, 2 * S::KT_BYTES);
+        tma_load_3d(kk_s + off, &mapKk, 0, kr, kvh * ATOMS, bar);
+        tma_load_3d(vk_s + off, &mapVk, 0, kr, kvh * ATOMS, bar);
+      };
+      auto load_m = [&](int it) {   // [keys, hd] copy of K for the gradient product
+        const int kr = row0 + (kb_lo + it) * NK;
+        mbar_expect_tx(km_full, S::KT_BYTES);
+        tma_load_3d(km_s, &mapKm, 0, kr, kvh * ATOMS, km_full);
+      };
+      mbar_expect_tx(q_full, 2 * S::Q_BYTES);
+      tma_load_3d(q_s, &mapQ, 0, row0 + q0, h * ATOMS, q_full);
+      tma_load_3d(g_s, &mapG, 0, row0 + q0, h * ATOMS, q_full);
+      load_k(0);
+      load_m(0);
+      if (KBUF == 2 && iters > 1) load_k(1);
+      w.wait(s_full0, 0, 33);                     // same order of waits as in the dK/dV kernel
+      if (KBUF < iters) load_k(KBUF);
+      for (int i = 0; i < iters; i++) {
+        if (i + 1 + KBUF < iters) {
+          w.wait(s_bar(i + 1), s_par(i + 1), 33);
+          load_k(i + 1 + KBUF);
+        }
+        w.wait(acc_done, i & 1, 35);
+        if (i + 1 < iters) load_m(i + 1);
+      }
+    }
+  } else if (warp == MMA_WARP) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = idesc_tf32(false, false, ROWS, NK);
       constexpr uint32_t idesc_g = idesc_tf32(false, true, ROWS, HD);
-      auto load_k = [&](int it) {
-        const int kr = row0 + (kb_lo + it) * NK;
-        mbar_expect_tx(kk_full, 2 * S::KT_BYTES);
-        for (int a = 0; a < ATOMS; a++) {
-          tma_load_2d(kk_s + a * (NK * 128), &mapKk, kvh * HD + 32 * a, kr, kk_full);
-          tma_load_2d(vk_s + a * (NK * 128), &mapVk, kvh * HD + 32 * a, kr, kk_full);
-        }
-      };
-      auto load_m = [&](int it) {
-        const int kr = row0 + (kb_lo + it) * NK;
-        mbar_expect_tx(km_full, S::KT_BYTES);
-        for (int a = 0; a < ATOMS; a++) tma_load_2d(km_s + a * (NK * 128), &mapKm, kvh * HD + 32 * a, kr, km_full);
-      };
-      auto mma_s = [&](int i) {
-        const uint32_t tm_s = tmem + (i & 1) * 2 * NK, tm_dp = tm_s + NK;
+      const uint64_t d_q = desc_kmajor(q_s), d_g = desc_kmajor(g_s), d_kk = desc_kmajor(kk_s), d_vk = desc_kmajor(vk_s),
+                     d_ds = desc_kmajor(ds_s), d_km = smem_desc(km_s, NK * 128, 512, 1);
+      auto mma_s = [&](int it) {
+        const uint32_t tm_s = tmem + (it & 1) * 2 * NK, tm_dp = tm_s + NK;
+        const uint32_t boff = (KBUF == 2 && (it & 1)) ? S::KT_BYTES : 0;
 #pragma unroll
         for (int a = 0; a < ATOMS; a++)
 #pragma unroll
           for (int j = 0; j < 4; j++) {
             const uint32_t acc = (a > 0 || j > 0) ? 1u : 0u;
-            umma_tf32(tm_s, desc_kmajor(q_s + a * (ROWS * 128) + j * 32), desc_kmajor(kk_s + a * (NK * 128) + j * 32), idesc_s, acc);
-            umma_tf32(tm_dp, desc_kmajor(g_s + a * (ROWS * 128) + j * 32), desc_kmajor(vk_s + a * (NK * 128) + j * 32), idesc_s, acc);
+            umma_tf32(tm_s, desc_off(d_q, a * (ROWS * 128) + j * 32), desc_off(d_kk, boff + a * (NK * 128) + j * 32), idesc_s, acc);
+            umma_tf32(tm_dp, desc_off(d_g, a * (ROWS * 128) + j * 32), desc_off(d_vk, boff + a * (NK * 128) + j * 32), idesc_s, acc);
           }
-        umma_commit((i & 1) ? s_full1 : s_full0);
+        umma_commit(s_bar(it));
       };
-      mbar_expect_tx(q_full, 2 * S::Q_BYTES);
-      for (int a = 0; a < ATOMS; a++) {
-        tma_load_2d(q_s + a * (ROWS * 128), &mapQ, h * HD + 32 * a, row0 + q0, q_full);
-        tma_load_2d(g_s + a * (ROWS * 128), &mapG, h * HD + 32 * a, row0 + q0, q_full);
-      }
-      load_k(0);
-      load_m(0);
       w.wait(q_full, 0, 31);
-      w.wait(kk_full, 0, 32);
+      w.wait(kk_full0, 0, 32);
       tc_fence_after();
       mma_s(0);
-      w.wait(s_full0, 0, 33);
-      if (iters > 1) load_k(1);
       for (int i = 0; i < iters; i++) {
         if (i + 1 < iters) {
-          w.wait(kk_full, (i + 1) & 1, 32);
+          w.wait(kk_bar(i + 1), kk_par(i + 1), 32);
           tc_fence_after();
           mma_s(i + 1);
         }
@@ -624,15 +719,9 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         tc_fence_after();
 #pragma unroll
         for (int j = 0; j < NK / 8; j++)
-          umma_tf32(tm_dq, desc_kmajor(ds_s + (j / 4) * (ROWS * 128) + (j % 4) * 32), smem_desc(km_s + j * 1024, NK * 128, 512, 1), idesc_g,
+          umma_tf32(tm_dq, desc_off(d_ds, (j / 4) * (ROWS * 128) + (j % 4) * 32), desc_off(d_km, j * 1024), idesc_g,
                     (i > 0 || j > 0) ? 1u : 0u);
         umma_commit(acc_done);
-        if (i + 1 < iters) {
-          w.wait(((i + 1) & 1) ? s_full1 : s_full0, ((i + 1) >> 1) & 1, 33);
-          if (i + 2 < iters) load_k(i + 2);
-        }
-        w.wait(acc_done, i & 1, 35);
-        if (i + 1 < iters) load_m(i + 1);
       }
     }
   } else {
@@ -646,12 +735,13 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     const int lo = (window > 0) ? tq - window + 1 : 0;
     for (int i = 0; i < iters; i++) {
       const int kpos0 = (kb_lo + i) * NK + half * NH;
-      w.wait((i & 1) ? s_full1 : s_full0, (i >> 1) & 1, 36);
+      w.wait(s_bar(i), s_par(i), 36);
       tc_fence_after();
       float s[NH], dp[NH];
       const uint32_t tm_s = tmem + (i & 1) * 2 * NK + half * NH + lane_base;
-      tmem_ld<NH>(tm_s, s);
-      tmem_ld<NH>(tm_s + NK, dp);
+      tmem_ld_issue<NH>(tm_s, s);
+      tmem_ld_issue<NH>(tm_s + NK, dp);
+      tmem_wait_ld();
       const bool interior = (kpos0 + NH - 1 <= q0) && (q0 + ROWS - 1 < T) && (window == 0 || kpos0 >= q0 + ROWS - window);
       if (interior) {
 #pragma unroll
@@ -696,7 +786,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == MATH_WARPS) {
+  if (warp == MMA_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem, S::TMEM_COLS);
   }
@@ -719,8 +809,8 @@ gt_status launch_fwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, 
                      float* out, float* lse, int* flag) {
   CUtensorMap mq, mk, mv;
   const uint64_t qw = (uint64_t)Hq * HD, kw = (uint64_t)Hkv * HD;
-  if (!make_map_2d(&mq, q, qw, rows, qw, ROWS, true) || !make_map_2d(&mk, k, kw, rows, kw, BKV, true) ||
-      !make_map_2d(&mv, v, kw, rows, kw, BKV, false))
+  if (!make_map_atoms(&mq, q, qw, rows, qw, ROWS, HD / 32, true) || !make_map_atoms(&mk, k, kw, rows, kw, BKV, HD / 32, true) ||
+      !make_map_atoms(&mv, v, kw, rows, kw, BKV, HD / 32, false))
     return gt_fail(ctx, GT_ERR_CUDA, "attention: tensor map encoding failed");
   auto kern = attn_fwd_tc_kernel<HD>;
   static bool done[64] = {};
@@ -729,12 +819,12 @@ gt_status launch_fwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, 
   // the S product's truncation bias is folded into the score scale
   const float scale2 = 1.4426950408889634f / sqrtf((float)HD) * TRUNC_COMP;
   dim3 grid(Hq * (rows / T), gt_cdiv(T, ROWS), 1);
-  kern<<<grid, THREADS, FwdSmem<HD>::TOTAL, ctx->stream>>>(mq, mk, mv, out, lse, rows, T, Hq, Hkv, window, scale2, flag);
+  kern<<<grid, FWD_THREADS, FwdSmem<HD>::TOTAL, ctx->stream>>>(mq, mk, mv, out, lse, rows, T, Hq, Hkv, window, scale2, flag);
   GT_LAUNCHED(ctx, "attn_fwd_tc_kernel");
   return GT_OK;
 }
 
-template <int HD, int NQ, int NK>
+template <int HD, int NQ, int NK, int DKV_KBUF, int DQ_KBUF>
 gt_status launch_bwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, const float* q, const float* k, const float* v,
                      const float* out, const float* lse, const float* go, float* gq, int accum_q, float* gk, int accum_k, float* gv,
                      int accum_v, int* flag) {
@@ -750,31 +840,32 @@ gt_status launch_bwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, 
   const int nseq = rows / T;
   if (gk || gv) {
     CUtensorMap mK, mV, mQk, mQm, mGk, mGm;
-    if (!make_map_2d(&mK, k, kw, rows, kw, ROWS, true) || !make_map_2d(&mV, v, kw, rows, kw, ROWS, true) ||
-        !make_map_2d(&mQk, q, qw, rows, qw, NQ, true) || !make_map_2d(&mQm, q, qw, rows, qw, NQ, false) ||
-        !make_map_2d(&mGk, go, qw, rows, qw, NQ, true) || !make_map_2d(&mGm, go, qw, rows, qw, NQ, false))
+    if (!make_map_atoms(&mK, k, kw, rows, kw, ROWS, HD / 32, true) || !make_map_atoms(&mV, v, kw, rows, kw, ROWS, HD / 32, true) ||
+        !make_map_atoms(&mQk, q, qw, rows, qw, NQ, HD / 32, true) || !make_map_atoms(&mQm, q, qw, rows, qw, NQ, HD / 32, false) ||
+        !make_map_atoms(&mGk, go, qw, rows, qw, NQ, HD / 32, true) || !make_map_atoms(&mGm, go, qw, rows, qw, NQ, HD / 32, false))
       return gt_fail(ctx, GT_ERR_CUDA, "attention backward: tensor map encoding failed");
-    auto kern = attn_bwd_dkv_tc_kernel<HD, NQ>;
+    constexpr int KBUF = DKV_KBUF;
+    auto kern = attn_bwd_dkv_tc_kernel<HD, NQ, KBUF>;
     static bool done[64] = {};
-    st = set_smem(ctx, kern, DkvSmem<HD, NQ>::TOTAL, done);
+    st = set_smem(ctx, kern, DkvSmem<HD, NQ, KBUF>::TOTAL, done);
     if (st) return st;
     dim3 grid(Hkv * nseq, gt_cdiv(T, ROWS), 1);
-    kern<<<grid, THREADS, DkvSmem<HD, NQ>::TOTAL, ctx->stream>>>(mK, mV, mQk, mQm, mGk, mGm, lse, D, gk, accum_k, gv, accum_v, rows, T, Hq,
+    kern<<<grid, THREADS, DkvSmem<HD, NQ, KBUF>::TOTAL, ctx->stream>>>(mK, mV, mQk, mQm, mGk, mGm, lse, D, gk, accum_k, gv, accum_v, rows, T, Hq,
                                                                 Hkv, window, scale2, dp_scale, flag);
     GT_LAUNCHED(ctx, "attn_bwd_dkv_tc_kernel");
   }
   if (gq) {
     CUtensorMap mQ, mG, mKk, mVk, mKm;
-    if (!make_map_2d(&mQ, q, qw, rows, qw, ROWS, true) || !make_map_2d(&mG, go, qw, rows, qw, ROWS, true) ||
-        !make_map_2d(&mKk, k, kw, rows, kw, NK, true) || !make_map_2d(&mVk, v, kw, rows, kw, NK, true) ||
-        !make_map_2d(&mKm, k, kw, rows, kw, NK, false))
+    if (!make_map_atoms(&mQ, q, qw, rows, qw, ROWS, HD / 32, true) || !make_map_atoms(&mG, go, qw, rows, qw, ROWS, HD / 32, true) ||
+        !make_map_atoms(&mKk, k, kw, rows, kw, NK, HD / 32, true) || !make_map_atoms(&mVk, v, kw, rows, kw, NK, HD / 32, true) ||
+        !make_map_atoms(&mKm, k, kw, rows, kw, NK, HD / 32, false))
       return gt_fail(ctx, GT_ERR_CUDA, "attention backward: tensor map encoding failed");
-    auto kern = attn_bwd_dq_tc_kernel<HD, NK>;
+    auto kern = attn_bwd_dq_tc_kernel<HD, NK, DQ_KBUF>;
     static bool done[64] = {};
-    st = set_smem(ctx, kern, DqSmem<HD, NK>::TOTAL, done);
+    st = set_smem(ctx, kern, DqSmem<HD, NK, DQ_KBUF>::TOTAL, done);
     if (st) return st;
     dim3 grid(Hq * nseq, gt_cdiv(T, ROWS), 1);
-    kern<<<grid, THREADS, DqSmem<HD, NK>::TOTAL, ctx->stream>>>(mQ, mG, mKk, mVk, mKm, lse, D, gq, accum_q, rows, T, Hq, Hkv, window, scale2,
+    kern<<<grid, THREADS, DqSmem<HD, NK, DQ_KBUF>::TOTAL, ctx->stream>>>(mQ, mG, mKk, mVk, mKm, lse, D, gq, accum_q, rows, T, Hq, Hkv, window, scale2,
                                                                dp_scale, flag);
     GT_LAUNCHED(ctx, "attn_bwd_dq_tc_kernel");
   }
@@ -810,9 +901,9 @@ gt_status gt_attention_bwd_tc(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int
   int* flag = device_flag(ctx);
   if (!flag) return GT_OK;
   gt_status s;
-  if (hd == 32) s = launch_bwd<32, 64, 64>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
-  else if (hd == 64) s = launch_bwd<64, 64, 64>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
-  else s = launch_bwd<128, 32, 32>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
+  if (hd == 32) s = launch_bwd<32, 64, 64, 2, 2>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
+  else if (hd == 64) s = launch_bwd<64, 64, 64, 2, 2>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
+  else s = launch_bwd<128, 32, 32, 1, 2>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
   if (s) return s;
   *handled = true;
   return GT_OK;

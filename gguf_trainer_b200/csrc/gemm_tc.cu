@@ -272,6 +272,18 @@ bool tc::make_map_3d(CUtensorMap* map, const float* ptr, uint64_t inner, uint64_
              kmajor ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+bool tc::make_map_atoms(CUtensorMap* map, const float* ptr, uint64_t inner, uint64_t outer, uint64_t row_pitch_elems,
+                        uint32_t box_outer, uint32_t atoms, bool kmajor) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc || inner % 32 != 0) return false;
+  cuuint64_t dims[3] = {32, outer, inner / 32};
+  cuuint64_t strides[2] = {row_pitch_elems * sizeof(float), 32 * sizeof(float)};
+  cuuint32_t box[3] = {32, box_outer, atoms};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             kmajor ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 bool tc::make_map_2d(CUtensorMap* map, const float* ptr, uint64_t inner, uint64_t outer, uint64_t row_pitch_elems,
                      uint32_t box_outer, bool kmajor) {
   EncodeTiledFn enc = encode_fn();
@@ -288,8 +300,8 @@ int* tc::device_flag(gt_ctx* ctx) {
   if (ctx->device < 0 || ctx->device >= 64) return nullptr;
   if (!g_flag[ctx->device]) {
     if (ctx->capturing) return nullptr;
-    if (cudaMalloc(&g_flag[ctx->device], 256) != cudaSuccess) { cudaGetLastError(); return nullptr; }
-    cudaMemsetAsync(g_flag[ctx->device], 0, 256, ctx->stream);
+    if (cudaMalloc(&g_flag[ctx->device], 65536) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    cudaMemsetAsync(g_flag[ctx->device], 0, 65536, ctx->stream);
   }
   return g_flag[ctx->device];
 }
@@ -358,3 +370,13 @@ gt_status gt_gemm_tc_batched(gt_ctx* ctx, int kind, int accum, int M, int N, int
 gt_status gt_gemm_tc(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c, bool* handled) {
   return gt_gemm_tc_batched(ctx, kind, accum, M, N, K, a, b, c, 1, handled);
 }
+
+#ifdef GT_ATTN_TRACE
+// Development aid (compiled out by default): copies the trace words a traced kernel left behind the device flag.
+extern "C" int gtx_debug_trace(gt_ctx* ctx, int* out, int n) {
+  int* f = g_flag[ctx->device];
+  if (!f) return -1;
+  cudaStreamSynchronize(ctx->stream);
+  return (int)cudaMemcpy(out, f + 64, sizeof(int) * n, cudaMemcpyDeviceToHost);
+}
+#endif

@@ -58,7 +58,8 @@ __device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint6
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+// issue only: the registers are valid after tmem_wait_ld()
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, float* v) {
   uint32_t* r = reinterpret_cast<uint32_t*>(v);
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
@@ -68,7 +69,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
         "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
         "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr) : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  tmem_ld32_issue(taddr, v);
+  tmem_wait_ld();
 }
 
 // Shared-memory matrix descriptor. Bits: [0,14) start>>4, [16,30) leading byte offset>>4, [32,46) stride byte
@@ -143,6 +148,11 @@ bool make_map_2d(CUtensorMap* map, const float* ptr, uint64_t inner, uint64_t ou
 // The same for `batch` matrices `batch_stride_elems` apart (box [1, box_outer, 32]).
 bool make_map_3d(CUtensorMap* map, const float* ptr, uint64_t inner, uint64_t outer, uint64_t batch, uint64_t row_pitch_elems,
                  uint64_t batch_stride_elems, uint32_t box_outer, bool kmajor);
+
+// The 2-D tensor seen as [inner/32 atoms][outer][32]: one copy of box [atoms, box_outer, 32] at (0, row, column/32)
+// lands `atoms` swizzled tiles of box_outer rows x 128 B one after the other (inner must be a multiple of 32).
+bool make_map_atoms(CUtensorMap* map, const float* ptr, uint64_t inner, uint64_t outer, uint64_t row_pitch_elems, uint32_t box_outer,
+                    uint32_t atoms, bool kmajor);
 
 // Device word the kernels set when a bounded wait expires (checked and cleared by gt_sync). Null while a graph is
 // being captured and the word does not exist yet.
