@@ -63,6 +63,23 @@ __device__ __forceinline__ void tmem_ld_issue(uint32_t taddr, float* v) {
     for (int c = 0; c < N / 32; c++) tmem_ld32_issue(taddr + c * 32, v + c * 32);
   }
 }
+__device__ __forceinline__ void tmem_st16_issue(uint32_t taddr, const float* v) {
+  const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+                 "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+               : "memory");
+}
+// registers to N columns of this warp's lanes; complete after tmem_wait_st()
+template <int N>
+__device__ __forceinline__ void tmem_st_issue(uint32_t taddr, const float* v) {
+  static_assert(N == 16 || N % 32 == 0, "column count");
+  if constexpr (N == 16) tmem_st16_issue(taddr, v);
+  else {
+#pragma unroll
+    for (int c = 0; c < N / 32; c++) tmem_st32_issue(taddr + c * 32, v + c * 32);
+  }
+}
 // A descriptor of the same tile `bytes` further on (the start-address field counts 16-byte units and cannot
 // carry: shared memory is smaller than the field's range).
 __device__ __forceinline__ uint64_t desc_off(uint64_t d, uint32_t bytes) { return d + (uint64_t)(bytes >> 4); }
@@ -232,7 +249,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       w.wait(s_bar(i), s_par(i), 16);
       tc_fence_after();
       float s[32];
-      tmem_ld<32>(tmem + (i & 1) * BKV + half * 32 + lane_base, s);
+      const uint32_t tm_s = tmem + (i & 1) * BKV + half * 32 + lane_base;
+      tmem_ld<32>(tm_s, s);
       // a block strictly below the diagonal and inside the window needs no per-element test
       const bool interior = (k0 + 31 <= q0) && (q0 + ROWS - 1 < T) && (window == 0 || k0 >= q0 + ROWS - window);
       float mx = NEG;
@@ -262,6 +280,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       }
       l = l * alpha + sum;
       m = mn;
+      // (P passed through tensor memory instead, as in the backward kernels, measured a tenth slower here)
       store_row_kmajor<32>(base_ptr + S::P_OFF, r, half * 32, s);
       fence_async_smem();
       tc_fence_before();
@@ -323,19 +342,18 @@ __global__ void attn_bwd_d_tc_kernel(int rows, int Hq, int hd, float scale, cons
 // dV += P^T.dO and dK += dS^T.Q with P^T, dS^T written to shared memory as K-major A operands (K = queries) and
 // dO, Q read a second time as [queries, hd] operands (hd contiguous). KBUF = 2 keeps two blocks of the K-major
 // Q / dO copies in flight (their fetch is the longest latency of the loop) where shared memory has the room.
-template <int HD, int NQ, int KBUF>
+template <int HD, int NQ, int KBUF, int MBUF>
 struct DkvSmem {
-  static constexpr int KV_BYTES = ROWS * HD * 4, QT_BYTES = NQ * HD * 4, PT_BYTES = ROWS * NQ * 4;
+  static constexpr int KV_BYTES = ROWS * HD * 4, QT_BYTES = NQ * HD * 4;
   static constexpr int K_OFF = 0, V_OFF = KV_BYTES, QK_OFF = 2 * KV_BYTES, GK_OFF = QK_OFF + KBUF * QT_BYTES,
-                       QM_OFF = GK_OFF + KBUF * QT_BYTES, GM_OFF = QM_OFF + QT_BYTES, P_OFF = GM_OFF + QT_BYTES,
-                       DS_OFF = P_OFF + PT_BYTES, BAR_OFF = DS_OFF + PT_BYTES;
+                       QM_OFF = GK_OFF + KBUF * QT_BYTES, GM_OFF = QM_OFF + MBUF * QT_BYTES, BAR_OFF = GM_OFF + MBUF * QT_BYTES;
   static constexpr int TOTAL = BAR_OFF + 128 + 1024;
   static constexpr int COLS = 4 * NQ + 2 * HD;
   static constexpr uint32_t TMEM_COLS = COLS <= 128 ? 128 : (COLS <= 256 ? 256 : 512);
   static_assert(TOTAL <= 232448, "shared memory");
 };
 
-template <int HD, int NQ, int KBUF>
+template <int HD, int NQ, int KBUF, int MBUF>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
                        const __grid_constant__ CUtensorMap mapQk, const __grid_constant__ CUtensorMap mapQm,
@@ -343,15 +361,15 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
                        const float* __restrict__ lse, const float* __restrict__ Ds, float* gk, int accum_k, float* gv, int accum_v,
                        int rows, int T, int Hq, int Hkv, int window, float scale2, float dp_scale, int* __restrict__ flag) {
   extern __shared__ uint8_t smem_raw[];
-  using S = DkvSmem<HD, NQ, KBUF>;
+  using S = DkvSmem<HD, NQ, KBUF, MBUF>;
   constexpr int ATOMS = HD / 32, NH = NQ / 2, HH = HD / 2;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t k_s = base + S::K_OFF, v_s = base + S::V_OFF, qk_s = base + S::QK_OFF, gk_s = base + S::GK_OFF,
-                 qm_s = base + S::QM_OFF, gm_s = base + S::GM_OFF, p_s = base + S::P_OFF, ds_s = base + S::DS_OFF;
+                 qm_s = base + S::QM_OFF, gm_s = base + S::GM_OFF;
   const uint32_t bars = base + S::BAR_OFF;
-  const uint32_t kv_full = bars, qk_full0 = bars + 8, qk_full1 = bars + 16, qm_full = bars + 24, s_full0 = bars + 32,
-                 s_full1 = bars + 40, p_full = bars + 48, acc_done = bars + 56;
+  const uint32_t kv_full = bars, qk_full0 = bars + 8, qk_full1 = bars + 16, qm_full0 = bars + 24, s_full0 = bars + 32,
+                 s_full1 = bars + 40, p_full = bars + 48, acc_done = bars + 56, all_done = bars + 72, qm_full1 = bars + 80;
   const uint32_t tmem_slot = bars + 64;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + S::BAR_OFF + 64);
 
@@ -367,8 +385,9 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
   const int iters = nqb * group;
 
   if (threadIdx.x == 0) {
-    mbar_init(kv_full, 1); mbar_init(qk_full0, 1); mbar_init(qk_full1, 1); mbar_init(qm_full, 1); mbar_init(s_full0, 1);
-    mbar_init(s_full1, 1); mbar_init(p_full, MATH_WARPS * 32); mbar_init(acc_done, 1);
+    mbar_init(kv_full, 1); mbar_init(qk_full0, 1); mbar_init(qk_full1, 1); mbar_init(qm_full0, 1); mbar_init(qm_full1, 1);
+    mbar_init(s_full0, 1);
+    mbar_init(s_full1, 1); mbar_init(p_full, MATH_WARPS * 32); mbar_init(acc_done, 1); mbar_init(all_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == MMA_WARP) tmem_alloc(tmem_slot, S::TMEM_COLS);
@@ -382,6 +401,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
   // barrier and parity of the K-major copies of block `it`, and of its score products
   auto qk_bar = [&](int it) { return (KBUF == 2 && (it & 1)) ? qk_full1 : qk_full0; };
   auto qk_par = [&](int it) { return (uint32_t)((KBUF == 2 ? it >> 1 : it) & 1); };
+  auto qm_bar = [&](int it) { return (MBUF == 2 && (it & 1)) ? qm_full1 : qm_full0; };
+  auto qm_par = [&](int it) { return (uint32_t)((MBUF == 2 ? it >> 1 : it) & 1); };
   auto s_bar = [&](int it) { return (it & 1) ? s_full1 : s_full0; };
   auto s_par = [&](int it) { return (uint32_t)((it >> 1) & 1); };
 #ifdef GT_ATTN_TRACE
@@ -403,9 +424,10 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
       };
       auto load_m = [&](int it) {   // [queries, hd] copies for the gradient products
         const int h = kvh * group + it / nqb, qr = row0 + (qb_lo + it % nqb) * NQ;
-        mbar_expect_tx(qm_full, 2 * S::QT_BYTES);
-        tma_load_3d(qm_s, &mapQm, 0, qr, h * ATOMS, qm_full);
-        tma_load_3d(gm_s, &mapGm, 0, qr, h * ATOMS, qm_full);
+        const uint32_t bar = qm_bar(it), off = (MBUF == 2 && (it & 1)) ? S::QT_BYTES : 0;
+        mbar_expect_tx(bar, 2 * S::QT_BYTES);
+        tma_load_3d(qm_s + off, &mapQm, 0, qr, h * ATOMS, bar);
+        tma_load_3d(gm_s + off, &mapGm, 0, qr, h * ATOMS, bar);
       };
       mbar_expect_tx(kv_full, 2 * S::KV_BYTES);
       tma_load_3d(k_s, &mapK, 0, row0 + k0, kvh * ATOMS, kv_full);
@@ -413,6 +435,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
       load_k(0);
       load_m(0);
       if (KBUF == 2 && iters > 1) load_k(1);
+      if (MBUF == 2 && iters > 1) load_m(1);
       // waits in the order the products complete: scores of block 0, then scores of block i+1 before the
       // gradient products of block i. Once the scores of a block are done its K-major copies may be replaced.
       w.wait(s_full0, 0, 23);
@@ -426,7 +449,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
         }
         w.wait(acc_done, i & 1, 25);              // the gradient products have read the [queries, hd] copies
         TRACE(18)
-        if (i + 1 < iters) load_m(i + 1);
+        if (i + MBUF < iters) load_m(i + MBUF);
         TRACE(19)
       }
     }
@@ -435,19 +458,23 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
       constexpr uint32_t idesc_s = idesc_tf32(false, false, ROWS, NQ);
       constexpr uint32_t idesc_g = idesc_tf32(false, true, ROWS, HD);
       const uint64_t d_k = desc_kmajor(k_s), d_v = desc_kmajor(v_s), d_qk = desc_kmajor(qk_s), d_gk = desc_kmajor(gk_s),
-                     d_p = desc_kmajor(p_s), d_ds = desc_kmajor(ds_s), d_gm = smem_desc(gm_s, NQ * 128, 512, 1),
-                     d_qm = smem_desc(qm_s, NQ * 128, 512, 1);
+                     d_gm = smem_desc(gm_s, NQ * 128, 512, 1), d_qm = smem_desc(qm_s, NQ * 128, 512, 1);
       auto mma_s = [&](int it) {
         const uint32_t tm_s = tmem + (it & 1) * 2 * NQ, tm_dp = tm_s + NQ;
         const uint32_t boff = (KBUF == 2 && (it & 1)) ? S::QT_BYTES : 0;
+        // one accumulator at a time: consecutive MMAs into the same TMEM columns pipeline, alternating ones do not
 #pragma unroll
         for (int a = 0; a < ATOMS; a++)
 #pragma unroll
-          for (int j = 0; j < 4; j++) {
-            const uint32_t acc = (a > 0 || j > 0) ? 1u : 0u;
-            umma_tf32(tm_s, desc_off(d_k, a * (ROWS * 128) + j * 32), desc_off(d_qk, boff + a * (NQ * 128) + j * 32), idesc_s, acc);
-            umma_tf32(tm_dp, desc_off(d_v, a * (ROWS * 128) + j * 32), desc_off(d_gk, boff + a * (NQ * 128) + j * 32), idesc_s, acc);
-          }
+          for (int j = 0; j < 4; j++)
+            umma_tf32(tm_s, desc_off(d_k, a * (ROWS * 128) + j * 32), desc_off(d_qk, boff + a * (NQ * 128) + j * 32), idesc_s,
+                      (a > 0 || j > 0) ? 1u : 0u);
+#pragma unroll
+        for (int a = 0; a < ATOMS; a++)
+#pragma unroll
+          for (int j = 0; j < 4; j++)
+            umma_tf32(tm_dp, desc_off(d_v, a * (ROWS * 128) + j * 32), desc_off(d_gk, boff + a * (NQ * 128) + j * 32), idesc_s,
+                      (a > 0 || j > 0) ? 1u : 0u);
         umma_commit(s_bar(it));
       };
       w.wait(kv_full, 0, 21);
@@ -462,26 +489,28 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
           mma_s(i + 1);
           TRACE(1)
         }
-        w.wait(qm_full, i & 1, 24);
+        w.wait(qm_bar(i), qm_par(i), 24);
         TRACE(2)
         w.wait(p_full, i & 1, 24);
         TRACE(3)
         tc_fence_after();
+        const uint32_t tm_p = tmem + (i & 1) * 2 * NQ;   // P^T and dS^T where the math warps wrote them: over S^T, dP^T
+        const uint32_t moff = (MBUF == 2 && (i & 1)) ? S::QT_BYTES : 0;
 #pragma unroll
-        for (int j = 0; j < NQ / 8; j++) {
-          const uint32_t acc = (i > 0 || j > 0) ? 1u : 0u;
-          const uint32_t aoff = (j / 4) * (ROWS * 128) + (j % 4) * 32;
-          umma_tf32(tm_dv, desc_off(d_p, aoff), desc_off(d_gm, j * 1024), idesc_g, acc);
-          umma_tf32(tm_dk, desc_off(d_ds, aoff), desc_off(d_qm, j * 1024), idesc_g, acc);
-        }
+        for (int j = 0; j < NQ / 8; j++) umma_tf32_ts(tm_dv, tm_p + j * 8, desc_off(d_gm, moff + j * 1024), idesc_g, (i > 0 || j > 0) ? 1u : 0u);
+#pragma unroll
+        for (int j = 0; j < NQ / 8; j++)
+          umma_tf32_ts(tm_dk, tm_p + NQ + j * 8, desc_off(d_qm, moff + j * 1024), idesc_g, (i > 0 || j > 0) ? 1u : 0u);
         umma_commit(acc_done);
         TRACE(4)
       }
+      // The math warps do not follow acc_done phase by phase (only the copying thread does), so the end of the
+      // accumulation has a barrier of its own, used once.
+      umma_commit(all_done);
     }
   } else {
     const int qd = warp & 3, half = warp >> 2;
-    const int r = qd * 32 + lane;            // key row inside the tile
-    const int kg = k0 + r;                   // key position in the sequence
+    const int kg = k0 + qd * 32 + lane;      // key position in the sequence: one row of the tile per thread
     const uint32_t lane_base = (uint32_t)(qd * 32) << 16;
 #ifdef GT_ATTN_TRACE
     const bool trm = tr && warp == 0;
@@ -542,17 +571,17 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
         }
       }
       TRACEM(11)
-      if (i > 0) w.wait(acc_done, (i - 1) & 1, 27);   // the previous gradient products still read P^T / dS^T
-      TRACEM(12)
-      store_row_kmajor<NH>(base_ptr + S::P_OFF, r, half * NH, s);
-      store_row_kmajor<NH>(base_ptr + S::DS_OFF, r, half * NH, dp);
-      fence_async_smem();
+      // In place: these columns were last read by the gradient products of block i-2, which the tensor pipe
+      // finished before it wrote the scores of block i there.
+      tmem_st_issue<NH>(tm_s, s);
+      tmem_st_issue<NH>(tm_s + NQ, dp);
+      tmem_wait_st();
       tc_fence_before();
       mbar_arrive(p_full);
       TRACEM(13)
     }
 #undef TRACEM
-    if (iters > 0) w.wait(acc_done, (iters - 1) & 1, 28);
+    w.wait(all_done, 0, 28);
     tc_fence_after();
     {   // warp-uniform: the TMEM loads are warp-wide instructions, only the stores are per-row
       const bool st = !w.dead && kg < T;
@@ -598,9 +627,9 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
 // dQ += dS.K with K read a second time as a [keys, hd] operand. KBUF as in the dK/dV kernel.
 template <int HD, int NK, int KBUF>
 struct DqSmem {
-  static constexpr int Q_BYTES = ROWS * HD * 4, KT_BYTES = NK * HD * 4, DS_BYTES = ROWS * NK * 4;
+  static constexpr int Q_BYTES = ROWS * HD * 4, KT_BYTES = NK * HD * 4;
   static constexpr int Q_OFF = 0, G_OFF = Q_BYTES, KK_OFF = 2 * Q_BYTES, VK_OFF = KK_OFF + KBUF * KT_BYTES,
-                       KM_OFF = VK_OFF + KBUF * KT_BYTES, DS_OFF = KM_OFF + KT_BYTES, BAR_OFF = DS_OFF + DS_BYTES;
+                       KM_OFF = VK_OFF + KBUF * KT_BYTES, BAR_OFF = KM_OFF + KT_BYTES;
   static constexpr int TOTAL = BAR_OFF + 128 + 1024;
   static constexpr int COLS = 4 * NK + HD;
   static constexpr uint32_t TMEM_COLS = COLS <= 128 ? 128 : (COLS <= 256 ? 256 : 512);
@@ -619,11 +648,10 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   constexpr int ATOMS = HD / 32, NH = NK / 2, HH = HD / 2;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t q_s = base + S::Q_OFF, g_s = base + S::G_OFF, kk_s = base + S::KK_OFF, vk_s = base + S::VK_OFF, km_s = base + S::KM_OFF,
-                 ds_s = base + S::DS_OFF;
+  const uint32_t q_s = base + S::Q_OFF, g_s = base + S::G_OFF, kk_s = base + S::KK_OFF, vk_s = base + S::VK_OFF, km_s = base + S::KM_OFF;
   const uint32_t bars = base + S::BAR_OFF;
   const uint32_t q_full = bars, kk_full0 = bars + 8, kk_full1 = bars + 16, km_full = bars + 24, s_full0 = bars + 32,
-                 s_full1 = bars + 40, p_full = bars + 48, acc_done = bars + 56;
+                 s_full1 = bars + 40, p_full = bars + 48, acc_done = bars + 56, all_done = bars + 72;
   const uint32_t tmem_slot = bars + 64;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + S::BAR_OFF + 64);
 
@@ -639,7 +667,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1); mbar_init(kk_full0, 1); mbar_init(kk_full1, 1); mbar_init(km_full, 1); mbar_init(s_full0, 1);
-    mbar_init(s_full1, 1); mbar_init(p_full, MATH_WARPS * 32); mbar_init(acc_done, 1);
+    mbar_init(s_full1, 1); mbar_init(p_full, MATH_WARPS * 32); mbar_init(acc_done, 1); mbar_init(all_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == MMA_WARP) tmem_alloc(tmem_slot, S::TMEM_COLS);
@@ -690,18 +718,22 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       constexpr uint32_t idesc_s = idesc_tf32(false, false, ROWS, NK);
       constexpr uint32_t idesc_g = idesc_tf32(false, true, ROWS, HD);
       const uint64_t d_q = desc_kmajor(q_s), d_g = desc_kmajor(g_s), d_kk = desc_kmajor(kk_s), d_vk = desc_kmajor(vk_s),
-                     d_ds = desc_kmajor(ds_s), d_km = smem_desc(km_s, NK * 128, 512, 1);
+                     d_km = smem_desc(km_s, NK * 128, 512, 1);
       auto mma_s = [&](int it) {
         const uint32_t tm_s = tmem + (it & 1) * 2 * NK, tm_dp = tm_s + NK;
         const uint32_t boff = (KBUF == 2 && (it & 1)) ? S::KT_BYTES : 0;
 #pragma unroll
         for (int a = 0; a < ATOMS; a++)
 #pragma unroll
-          for (int j = 0; j < 4; j++) {
-            const uint32_t acc = (a > 0 || j > 0) ? 1u : 0u;
-            umma_tf32(tm_s, desc_off(d_q, a * (ROWS * 128) + j * 32), desc_off(d_kk, boff + a * (NK * 128) + j * 32), idesc_s, acc);
-            umma_tf32(tm_dp, desc_off(d_g, a * (ROWS * 128) + j * 32), desc_off(d_vk, boff + a * (NK * 128) + j * 32), idesc_s, acc);
-          }
+          for (int j = 0; j < 4; j++)
+            umma_tf32(tm_s, desc_off(d_q, a * (ROWS * 128) + j * 32), desc_off(d_kk, boff + a * (NK * 128) + j * 32), idesc_s,
+                      (a > 0 || j > 0) ? 1u : 0u);
+#pragma unroll
+        for (int a = 0; a < ATOMS; a++)
+#pragma unroll
+          for (int j = 0; j < 4; j++)
+            umma_tf32(tm_dp, desc_off(d_g, a * (ROWS * 128) + j * 32), desc_off(d_vk, boff + a * (NK * 128) + j * 32), idesc_s,
+                      (a > 0 || j > 0) ? 1u : 0u);
         umma_commit(s_bar(it));
       };
       w.wait(q_full, 0, 31);
@@ -718,11 +750,11 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         w.wait(p_full, i & 1, 34);
         tc_fence_after();
 #pragma unroll
-        for (int j = 0; j < NK / 8; j++)
-          umma_tf32(tm_dq, desc_off(d_ds, (j / 4) * (ROWS * 128) + (j % 4) * 32), desc_off(d_km, j * 1024), idesc_g,
-                    (i > 0 || j > 0) ? 1u : 0u);
+        for (int j = 0; j < NK / 8; j++)   // dS is read where the math warps wrote it: over S, in tensor memory
+          umma_tf32_ts(tm_dq, tmem + (i & 1) * 2 * NK + j * 8, desc_off(d_km, j * 1024), idesc_g, (i > 0 || j > 0) ? 1u : 0u);
         umma_commit(acc_done);
       }
+      umma_commit(all_done);   // the end of the accumulation, for the math warps (they do not follow acc_done)
     }
   } else {
     const int qd = warp & 3, half = warp >> 2;
@@ -762,13 +794,12 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           s[c] = d;
         }
       }
-      if (i > 0) w.wait(acc_done, (i - 1) & 1, 37);
-      store_row_kmajor<NH>(base_ptr + S::DS_OFF, r, half * NH, s);
-      fence_async_smem();
+      tmem_st_issue<NH>(tm_s, s);               // dS takes the place of S
+      tmem_wait_st();
       tc_fence_before();
       mbar_arrive(p_full);
     }
-    if (iters > 0) w.wait(acc_done, (iters - 1) & 1, 38);
+    w.wait(all_done, 0, 38);
     tc_fence_after();
     {   // warp-uniform TMEM load, per-row store
       float t[HH];
@@ -824,7 +855,7 @@ gt_status launch_fwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, 
   return GT_OK;
 }
 
-template <int HD, int NQ, int NK, int DKV_KBUF, int DQ_KBUF>
+template <int HD, int NQ, int NK, int DKV_KBUF, int DKV_MBUF, int DQ_KBUF>
 gt_status launch_bwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, const float* q, const float* k, const float* v,
                      const float* out, const float* lse, const float* go, float* gq, int accum_q, float* gk, int accum_k, float* gv,
                      int accum_v, int* flag) {
@@ -844,13 +875,13 @@ gt_status launch_bwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, 
         !make_map_atoms(&mQk, q, qw, rows, qw, NQ, HD / 32, true) || !make_map_atoms(&mQm, q, qw, rows, qw, NQ, HD / 32, false) ||
         !make_map_atoms(&mGk, go, qw, rows, qw, NQ, HD / 32, true) || !make_map_atoms(&mGm, go, qw, rows, qw, NQ, HD / 32, false))
       return gt_fail(ctx, GT_ERR_CUDA, "attention backward: tensor map encoding failed");
-    constexpr int KBUF = DKV_KBUF;
-    auto kern = attn_bwd_dkv_tc_kernel<HD, NQ, KBUF>;
+    constexpr int KBUF = DKV_KBUF, MBUF = DKV_MBUF;
+    auto kern = attn_bwd_dkv_tc_kernel<HD, NQ, KBUF, MBUF>;
     static bool done[64] = {};
-    st = set_smem(ctx, kern, DkvSmem<HD, NQ, KBUF>::TOTAL, done);
+    st = set_smem(ctx, kern, DkvSmem<HD, NQ, KBUF, MBUF>::TOTAL, done);
     if (st) return st;
     dim3 grid(Hkv * nseq, gt_cdiv(T, ROWS), 1);
-    kern<<<grid, THREADS, DkvSmem<HD, NQ, KBUF>::TOTAL, ctx->stream>>>(mK, mV, mQk, mQm, mGk, mGm, lse, D, gk, accum_k, gv, accum_v, rows, T, Hq,
+    kern<<<grid, THREADS, DkvSmem<HD, NQ, KBUF, MBUF>::TOTAL, ctx->stream>>>(mK, mV, mQk, mQm, mGk, mGm, lse, D, gk, accum_k, gv, accum_v, rows, T, Hq,
                                                                 Hkv, window, scale2, dp_scale, flag);
     GT_LAUNCHED(ctx, "attn_bwd_dkv_tc_kernel");
   }
@@ -901,9 +932,9 @@ gt_status gt_attention_bwd_tc(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int
   int* flag = device_flag(ctx);
   if (!flag) return GT_OK;
   gt_status s;
-  if (hd == 32) s = launch_bwd<32, 64, 64, 2, 2>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
-  else if (hd == 64) s = launch_bwd<64, 64, 64, 2, 2>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
-  else s = launch_bwd<128, 32, 32, 1, 2>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
+  if (hd == 32) s = launch_bwd<32, 64, 64, 2, 2, 2>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
+  else if (hd == 64) s = launch_bwd<64, 64, 64, 2, 2, 2>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
+  else s = launch_bwd<128, 32, 32, 2, 1, 2>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
   if (s) return s;
   *handled = true;
   return GT_OK;
