@@ -369,7 +369,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
                  qm_s = base + S::QM_OFF, gm_s = base + S::GM_OFF;
   const uint32_t bars = base + S::BAR_OFF;
   const uint32_t kv_full = bars, qk_full0 = bars + 8, qk_full1 = bars + 16, qm_full0 = bars + 24, s_full0 = bars + 32,
-                 s_full1 = bars + 40, p_full = bars + 48, acc_done = bars + 56, all_done = bars + 72, qm_full1 = bars + 80;
+                 s_full1 = bars + 40, p_full0 = bars + 48, acc_done0 = bars + 56, all_done = bars + 72, qm_full1 = bars + 80,
+                 p_full1 = bars + 88, acc_done1 = bars + 96;
   const uint32_t tmem_slot = bars + 64;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + S::BAR_OFF + 64);
 
@@ -387,7 +388,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1); mbar_init(qk_full0, 1); mbar_init(qk_full1, 1); mbar_init(qm_full0, 1); mbar_init(qm_full1, 1);
     mbar_init(s_full0, 1);
-    mbar_init(s_full1, 1); mbar_init(p_full, MATH_WARPS * 32); mbar_init(acc_done, 1); mbar_init(all_done, 1);
+    mbar_init(s_full1, 1); mbar_init(p_full0, MATH_WARPS * 32); mbar_init(p_full1, MATH_WARPS * 32); mbar_init(acc_done0, 1);
+    mbar_init(acc_done1, 1); mbar_init(all_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == MMA_WARP) tmem_alloc(tmem_slot, S::TMEM_COLS);
@@ -401,6 +403,11 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
   // barrier and parity of the K-major copies of block `it`, and of its score products
   auto qk_bar = [&](int it) { return (KBUF == 2 && (it & 1)) ? qk_full1 : qk_full0; };
   auto qk_par = [&](int it) { return (uint32_t)((KBUF == 2 ? it >> 1 : it) & 1); };
+  // p_full and acc_done alternate between two barriers: their waiters are not throttled by anything else in the
+  // loop, and with a single barrier a waiter that fell one phase behind would take the next phase of the same parity
+  // for the one it missed and wait for ever. With two, that needs four phases, which the data dependences rule out.
+  auto p_bar = [&](int it) { return (it & 1) ? p_full1 : p_full0; };
+  auto a_bar = [&](int it) { return (it & 1) ? acc_done1 : acc_done0; };
   auto qm_bar = [&](int it) { return (MBUF == 2 && (it & 1)) ? qm_full1 : qm_full0; };
   auto qm_par = [&](int it) { return (uint32_t)((MBUF == 2 ? it >> 1 : it) & 1); };
   auto s_bar = [&](int it) { return (it & 1) ? s_full1 : s_full0; };
@@ -447,7 +454,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
           load_k(i + 1 + KBUF);
           TRACE(17)
         }
-        w.wait(acc_done, i & 1, 25);              // the gradient products have read the [queries, hd] copies
+        w.wait(a_bar(i), s_par(i), 25);           // the gradient products have read the [queries, hd] copies
         TRACE(18)
         if (i + MBUF < iters) load_m(i + MBUF);
         TRACE(19)
@@ -491,7 +498,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
         }
         w.wait(qm_bar(i), qm_par(i), 24);
         TRACE(2)
-        w.wait(p_full, i & 1, 24);
+        w.wait(p_bar(i), s_par(i), 24);
         TRACE(3)
         tc_fence_after();
         const uint32_t tm_p = tmem + (i & 1) * 2 * NQ;   // P^T and dS^T where the math warps wrote them: over S^T, dP^T
@@ -501,12 +508,13 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
 #pragma unroll
         for (int j = 0; j < NQ / 8; j++)
           umma_tf32_ts(tm_dk, tm_p + NQ + j * 8, desc_off(d_qm, moff + j * 1024), idesc_g, (i > 0 || j > 0) ? 1u : 0u);
-        umma_commit(acc_done);
+        umma_commit(a_bar(i));
         TRACE(4)
       }
-      // The math warps do not follow acc_done phase by phase (only the copying thread does), so the end of the
-      // accumulation has a barrier of its own, used once.
+      // The end of the accumulation has a barrier of its own, used once (the math warps do not follow acc_done).
+      // The issuing thread waits for it too, whatever happened before: no MMA may be in flight when TMEM is freed.
       umma_commit(all_done);
+      mbar_wait(all_done, 0);
     }
   } else {
     const int qd = warp & 3, half = warp >> 2;
@@ -577,7 +585,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
       tmem_st_issue<NH>(tm_s + NQ, dp);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(p_full);
+      mbar_arrive(p_bar(i));
       TRACEM(13)
     }
 #undef TRACEM
@@ -651,7 +659,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   const uint32_t q_s = base + S::Q_OFF, g_s = base + S::G_OFF, kk_s = base + S::KK_OFF, vk_s = base + S::VK_OFF, km_s = base + S::KM_OFF;
   const uint32_t bars = base + S::BAR_OFF;
   const uint32_t q_full = bars, kk_full0 = bars + 8, kk_full1 = bars + 16, km_full = bars + 24, s_full0 = bars + 32,
-                 s_full1 = bars + 40, p_full = bars + 48, acc_done = bars + 56, all_done = bars + 72;
+                 s_full1 = bars + 40, p_full0 = bars + 48, acc_done = bars + 56, all_done = bars + 72, p_full1 = bars + 80;
   const uint32_t tmem_slot = bars + 64;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + S::BAR_OFF + 64);
 
@@ -667,7 +675,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1); mbar_init(kk_full0, 1); mbar_init(kk_full1, 1); mbar_init(km_full, 1); mbar_init(s_full0, 1);
-    mbar_init(s_full1, 1); mbar_init(p_full, MATH_WARPS * 32); mbar_init(acc_done, 1); mbar_init(all_done, 1);
+    mbar_init(s_full1, 1); mbar_init(p_full0, MATH_WARPS * 32); mbar_init(p_full1, MATH_WARPS * 32); mbar_init(acc_done, 1);
+    mbar_init(all_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == MMA_WARP) tmem_alloc(tmem_slot, S::TMEM_COLS);
@@ -677,6 +686,9 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   const uint32_t tmem = *tmem_slot_ptr;
   const uint32_t tm_dq = tmem + 4 * NK;
   Waiter w{false, flag};
+  // two alternating p_full barriers, as in the dK/dV kernel: the math warps may finish block i+1 before the issuing
+  // thread has looked at block i's barrier (it may be waiting for the [keys, hd] copy)
+  auto p_bar = [&](int it) { return (it & 1) ? p_full1 : p_full0; };
   auto kk_bar = [&](int it) { return (KBUF == 2 && (it & 1)) ? kk_full1 : kk_full0; };
   auto kk_par = [&](int it) { return (uint32_t)((KBUF == 2 ? it >> 1 : it) & 1); };
   auto s_bar = [&](int it) { return (it & 1) ? s_full1 : s_full0; };
@@ -747,7 +759,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           mma_s(i + 1);
         }
         w.wait(km_full, i & 1, 34);
-        w.wait(p_full, i & 1, 34);
+        w.wait(p_bar(i), s_par(i), 34);
         tc_fence_after();
 #pragma unroll
         for (int j = 0; j < NK / 8; j++)   // dS is read where the math warps wrote it: over S, in tensor memory
@@ -755,6 +767,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         umma_commit(acc_done);
       }
       umma_commit(all_done);   // the end of the accumulation, for the math warps (they do not follow acc_done)
+      mbar_wait(all_done, 0);  // and for this thread, whatever happened before: no MMA in flight when TMEM is freed
     }
   } else {
     const int qd = warp & 3, half = warp >> 2;
@@ -797,7 +810,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       tmem_st_issue<NH>(tm_s, s);               // dS takes the place of S
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(p_full);
+      mbar_arrive(p_bar(i));
     }
     w.wait(all_done, 0, 38);
     tc_fence_after();

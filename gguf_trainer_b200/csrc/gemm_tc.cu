@@ -20,34 +20,43 @@ using namespace tc;
 
 namespace {
 
-constexpr int BM = 128;          // UMMA M (cta_group::1): accumulator row i lives in TMEM lane i
+constexpr int BM1 = 128;         // UMMA M (cta_group::1): accumulator row i lives in TMEM lane i
 constexpr int BK = 32;           // f32 elements per stage along K: 128 bytes = one swizzle row
 constexpr int UMMA_K = 8;        // tf32: 32 bytes of K per instruction
-constexpr int THREADS = 192;     // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
 
-template <int BN>
+// Tile shapes. MT = 1: 128 x BN output tile, two TMEM accumulators, so the epilogue of a tile runs under the
+// main loop of the next. MT = 2: 256 x BN, two 128-row halves that share every B tile and fill the tensor memory
+// (no second buffer: the epilogue is exposed). With 4-byte operands the main loop is bound by shared-memory
+// bandwidth, not by the tensor pipe: every stage is written once by TMA and read by the MMAs once per 128-row
+// half, at 128 B/clk. A 256-row tile moves fewer bytes per flop (the B tile is fetched once for both halves), which
+// pays when the tile count still fills the SMs evenly; the host picks per product.
+template <int BN, int MT>
 struct Smem {
-  static constexpr int A_BYTES = BM * BK * 4;   // 16 KB
+  static constexpr int BM = BM1 * MT;
+  static constexpr int A_BYTES = BM * BK * 4;   // 16 / 32 KB
   static constexpr int B_BYTES = BN * BK * 4;
   static constexpr int STAGE = A_BYTES + B_BYTES;
-  static constexpr int STAGES = BN <= 128 ? 5 : 4;
-  static constexpr int EPI_BYTES = 4 * 2 * 4096;   // per epilogue warp: two 32x32 f32 staging tiles for the TMA store
+  static constexpr int STAGES = MT == 2 ? 3 : (BN <= 128 ? 5 : 4);
+  static constexpr int EPI_WARPS = 4 * MT;
+  static constexpr int EPI_TILES = MT == 2 ? 1 : 2;   // 32x32 f32 staging tiles per epilogue warp for the TMA store
+  static constexpr int EPI_BYTES = EPI_WARPS * EPI_TILES * 4096;
   static constexpr int TOTAL = STAGES * STAGE + EPI_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
-  static constexpr uint32_t TMEM_COLS = 2 * BN <= 256 ? 256 : 512;   // two accumulators
+  static constexpr uint32_t TMEM_COLS = 2 * BN <= 256 ? 256 : 512;   // two accumulators (MT = 1) or two halves (MT = 2)
+  static constexpr int THREADS = 64 + 32 * EPI_WARPS;   // warp 0: TMA, warp 1: MMA + TMEM owner, then the epilogue warps
+  static_assert(TOTAL <= 232448, "shared memory");
 };
 
 // Persistent: each CTA walks output tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... (n fastest, then m, then the
-// split-K slice), so CTAs running at the same time share their A row-blocks in L2. The accumulator is double-buffered
-// in TMEM: while the epilogue warps drain tile i, the MMA warp is already accumulating tile i+1.
+// split-K slice), so CTAs running at the same time share their A row-blocks in L2.
 // A_K: A is K-major in memory (NT, NN); else MN-major ([K, M], TN). B_K: B is K-major (NT); else [K, N] (NN, TN).
-template <bool A_K, bool B_K, int BN>
-__global__ void __launch_bounds__(THREADS, 1)
+template <bool A_K, bool B_K, int BN, int MT>
+__global__ void __launch_bounds__(Smem<BN, MT>::THREADS, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                  const __grid_constant__ CUtensorMap mapC, float* __restrict__ C, int M, int N, int K, int accum, int ksplit,
                  int use_tma_store, int batch, int* __restrict__ flag) {
   extern __shared__ uint8_t smem_raw[];
-  using S = Smem<BN>;
-  constexpr int STAGES = S::STAGES;
+  using S = Smem<BN, MT>;
+  constexpr int STAGES = S::STAGES, BM = S::BM;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t epi = base + STAGES * S::STAGE;    // staging tiles of the epilogue warps
   const uint32_t bars = epi + S::EPI_BYTES;         // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], tmem slot
@@ -64,6 +73,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
   const int ntiles = per_mat * batch;            // the matrices of a batch are just more tiles
   const int kblocks = (K + BK - 1) / BK;
   const int per = (kblocks + ksplit - 1) / ksplit;   // K blocks per split-K slice
+  // TMEM slot of a 128-row accumulator and the parity of its hand-over barriers: with MT = 1 the tiles alternate
+  // between two slots, with MT = 2 slot h holds half h of every tile.
+  auto slot_of = [&](uint32_t tl, int h) { return MT == 2 ? h : (int)(tl & 1); };
+  auto par_of = [&](uint32_t tl) { return MT == 2 ? (tl & 1) : ((tl >> 1) & 1); };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -107,43 +120,69 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
   } else if (warp == 1) {
     if (lane == 0) {
       // ---- MMA issuer ----
-      constexpr uint32_t idesc = idesc_tf32(!A_K, !B_K, BM, BN);
+      constexpr uint32_t idesc = idesc_tf32(!A_K, !B_K, BM1, BN);
+      const uint64_t a_desc0 = A_K ? desc_kmajor(base) : desc_mnmajor(base);
+      const uint64_t b_desc0 = B_K ? desc_kmajor(base + S::A_BYTES) : desc_mnmajor(base + S::A_BYTES);
+      constexpr uint32_t A_STEP = A_K ? 32 : 1024, B_STEP = B_K ? 32 : 1024;   // bytes per K = 8 step
       uint32_t it = 0, tl = 0;
+#ifdef GT_ATTN_TRACE
+      const long long tr_c0 = clock64();
+      const uint64_t tr_t0 = gtimer();
+      long long tr_wait = 0;
+#endif
       for (int t = blockIdx.x; t < ntiles; t += gridDim.x, tl++) {
         const int z = (t % per_mat) / (tiles_n * tiles_m);
         const int kb0 = z * per, kb1 = min(kblocks, kb0 + per);
-        const int b = tl & 1;
-        wait(acc_empty(b), ((tl >> 1) & 1) ^ 1, 4);   // the epilogue has drained this accumulator
+        const uint32_t par = par_of(tl) ^ 1;
+        wait(acc_empty(slot_of(tl, 0)), par, 4);   // the epilogue has drained this accumulator
+        if (MT == 2 && kb0 >= kb1) wait(acc_empty(1), par, 4);
         tc_fence_after();
-        const uint32_t d_tmem = tmem + b * BN;
         for (int kb = kb0; kb < kb1; kb++, it++) {
           const int s = it % STAGES;
+#ifdef GT_ATTN_TRACE
+          const long long tr_w0 = clock64();
+#endif
           wait(full_bar(s), (it / STAGES) & 1, 2);
+#ifdef GT_ATTN_TRACE
+          tr_wait += clock64() - tr_w0;
+#endif
           tc_fence_after();
-          const uint32_t a_src = base + s * S::STAGE, b_src = a_src + S::A_BYTES;
+          const uint32_t soff = (uint32_t)(s * S::STAGE) >> 4;
 #pragma unroll
-          for (int j = 0; j < BK / UMMA_K; j++) {
-            const uint64_t ad = A_K ? desc_kmajor(a_src + j * 32) : desc_mnmajor(a_src + j * 1024);
-            const uint64_t bd = B_K ? desc_kmajor(b_src + j * 32) : desc_mnmajor(b_src + j * 1024);
-            umma_tf32(d_tmem, ad, bd, idesc, (kb > kb0 || j > 0) ? 1u : 0u);
+          for (int h = 0; h < MT; h++) {
+            if (h == 1 && kb == kb0) {             // the second half's accumulator is drained a little later
+              wait(acc_empty(1), par, 4);
+              tc_fence_after();
+            }
+            const uint32_t d_tmem = tmem + slot_of(tl, h) * BN;
+#pragma unroll
+            for (int j = 0; j < BK / UMMA_K; j++)
+              umma_tf32(d_tmem, a_desc0 + soff + ((h * 16384 + j * A_STEP) >> 4), b_desc0 + soff + ((j * B_STEP) >> 4), idesc,
+                        (kb > kb0 || j > 0) ? 1u : 0u);
+            if (kb == kb1 - 1) umma_commit(acc_full(slot_of(tl, h)));   // this accumulator is complete
           }
           umma_commit(empty_bar(s));   // the stage is free once these MMAs have read it
         }
-        umma_commit(acc_full(b));      // accumulator complete
       }
+#ifdef GT_ATTN_TRACE
+      if (blockIdx.x == 0) {   // cycles, nanoseconds, K blocks, tiles and cycles spent waiting for operands
+        flag[64] = (int)(clock64() - tr_c0); flag[65] = (int)(gtimer() - tr_t0); flag[66] = (int)it; flag[67] = (int)tl;
+        flag[68] = (int)tr_wait;
+      }
+#endif
     }
   } else {
     // ---- epilogue: warp w may touch TMEM lanes [32*(w%4), 32*(w%4)+32) ----
-    const int q = warp & 3;
+    const int q = warp & 3, ew = warp - 2, half = ew >> 2;
     const bool vec = (N & 3) == 0;
     uint32_t tl = 0, nst = 0;   // nst: TMA stores issued by this warp
     for (int t = blockIdx.x; t < ntiles; t += gridDim.x, tl++) {
       const int bi = t / per_mat, tt = t % per_mat;
-      const int n0 = (tt % tiles_n) * BN, m0 = ((tt / tiles_n) % tiles_m) * BM, z = tt / (tiles_n * tiles_m);
-      const int b = tl & 1;
+      const int n0 = (tt % tiles_n) * BN, m0 = ((tt / tiles_n) % tiles_m) * BM + half * BM1, z = tt / (tiles_n * tiles_m);
+      const int b = slot_of(tl, half);
       const bool have = z * per < kblocks;     // an empty split-K slice issues no MMA and contributes nothing
       const int row = m0 + q * 32 + lane;
-      if (have) wait(acc_full(b), (tl >> 1) & 1, 3);
+      if (have) wait(acc_full(b), par_of(tl), 3);
       dead = __any_sync(0xffffffffu, dead);
       tc_fence_after();
       if (have) {
@@ -159,8 +198,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
             // Stage the warp's 32x32 block in shared memory (128-byte rows, 16-byte chunks XOR (row mod 8), the layout
             // the store's tensor map expects) and let TMA write it: whole 128-byte rows, clipped at M and N, as a
             // plain store or, when accumulating or combining split-K slices, as an f32 reduce-add performed in L2.
-            const uint32_t tile = epi + (uint32_t)(q * 2 + (nst & 1)) * 4096u;
-            if (nst >= 2) tma_wait_read<1>();        // the tile written two blocks ago has been read out
+            const uint32_t tile = epi + (uint32_t)(ew * S::EPI_TILES + (nst % S::EPI_TILES)) * 4096u;
+            if (nst >= S::EPI_TILES) tma_wait_read<S::EPI_TILES - 1>();   // the tile's previous contents have been read out
             __syncwarp();
             uint8_t* tp = smem_raw + (tile - smem_u32(smem_raw)) + lane * 128;
 #pragma unroll
@@ -221,20 +260,29 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
 // ---------------------------------------------------------------------------------------------
 int* g_flag[64] = {};
 
-template <bool A_K, bool B_K, int BN>
+template <bool A_K, bool B_K, int BN, int MT>
 gt_status launch(gt_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, int tma_store, float* c, int M, int N,
                  int K, int accum, int ksplit, int batch) {
-  auto kern = gemm_tf32_kernel<A_K, B_K, BN>;
+  auto kern = gemm_tf32_kernel<A_K, B_K, BN, MT>;
+  using S = Smem<BN, MT>;
   static bool attr_set[64] = {};
   if (!attr_set[ctx->device]) {
-    GT_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<BN>::TOTAL));
+    GT_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
     attr_set[ctx->device] = true;
   }
-  const long ntiles = (long)gt_cdiv(N, BN) * gt_cdiv(M, BM) * ksplit * batch;
+  const long ntiles = (long)gt_cdiv(N, BN) * gt_cdiv(M, S::BM) * ksplit * batch;
   dim3 grid((unsigned)min((long)ctx->sm_count, ntiles), 1, 1);
-  kern<<<grid, THREADS, Smem<BN>::TOTAL, ctx->stream>>>(ma, mb, mc, c, M, N, K, accum, ksplit, tma_store, batch, g_flag[ctx->device]);
+  kern<<<grid, S::THREADS, S::TOTAL, ctx->stream>>>(ma, mb, mc, c, M, N, K, accum, ksplit, tma_store, batch, g_flag[ctx->device]);
   GT_LAUNCHED(ctx, "gemm_tf32_kernel");
   return GT_OK;
+}
+
+template <int BN, int MT>
+gt_status launch_kind(gt_ctx* ctx, int kind, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, int tma_store, float* c,
+                      int M, int N, int K, int accum, int ksplit, int batch) {
+  if (kind == GT_GEMM_NT) return launch<true, true, BN, MT>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
+  if (kind == GT_GEMM_NN) return launch<true, false, BN, MT>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
+  return launch<false, false, BN, MT>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
 }
 
 }  // namespace
@@ -333,35 +381,54 @@ gt_status gt_gemm_tc_batched(gt_ctx* ctx, int kind, int accum, int M, int N, int
   if ((((uintptr_t)a) | ((uintptr_t)b) | ((uintptr_t)c)) & 15) return GT_OK;
   if (ctx->device < 0 || ctx->device >= 64) return GT_OK;
   if (!device_flag(ctx)) return GT_OK;
-  // tile width: 192 divides the model widths this path is built for (576, 192, 1536, 49152); otherwise 128
-  const int bn = (N % 192 == 0 || (N > 128 && (gt_cdiv(N, 192) * 192 - N) < (gt_cdiv(N, 128) * 128 - N))) ? 192 : 128;
+  // Tile shape and split-K factor: the cheapest of the four shapes under a small cost model (cycles of the CTA with
+  // the most work: waves x (K blocks x cycles per K block + epilogue)), calibrated on in-kernel cycle counts.
+  const int kblocks = gt_cdiv(K, BK);
+  struct Cfg { int mt, bn; };
+  static const Cfg cfgs[4] = {{1, 192}, {1, 128}, {2, 256}, {2, 192}};
+  static const char* force = getenv("GT_GEMM_TILE");   // "mt,bn": development override
+  int best = 0, ksplit = 1;
+  double best_cost = 1e30;
+  for (int i = 0; i < 4; i++) {
+    const int mt = cfgs[i].mt, bn = cfgs[i].bn, bm = BM1 * mt;
+    if (force) {
+      int fm = 0, fb = 0;
+      if (sscanf(force, "%d,%d", &fm, &fb) == 2 && (fm != mt || fb != bn)) continue;
+    }
+    const long tiles = (long)gt_cdiv(N, bn) * gt_cdiv(M, bm) * batch;
+    // split K when the output has few tiles and K is deep (dW: K = rows); partial sums meet in L2 with f32 adds
+    int ks = 1;
+    if (tiles < ctx->sm_count && kblocks >= 16) {
+      ks = (int)min((long)(ctx->sm_count / tiles), (long)(kblocks / 8));
+      if (ks < 1) ks = 1;
+    }
+    const long units = tiles * ks;
+    const long waves = gt_cdiv(units, (long)ctx->sm_count);
+    const double kb_unit = (double)gt_cdiv(kblocks, ks);
+    // One K block costs the slower of its MMAs (N/2 cycles each) and its shared-memory traffic at 128 B/clk: the stage
+    // is written once by TMA and read once per 128-row half by the MMAs (measured: 0.9 of that bound). The epilogue
+    // of a 256-row tile is exposed, that of a 128-row tile mostly hidden.
+    const double tensor = mt * 4.0 * (bn / 2);
+    const double smem = 0.92 * ((bm * 128.0 + bn * 128.0) + mt * (BM1 * 128.0 + bn * 128.0)) / 128.0;
+    const double epilogue = mt == 2 ? 14.0 * bn + 900.0 : 1500.0;
+    const double cost = waves * (kb_unit * (tensor > smem ? tensor : smem) + epilogue);
+    if (cost < best_cost) { best_cost = cost; best = i; ksplit = ks; }
+  }
+  const int mt = cfgs[best].mt, bn = cfgs[best].bn, bm = BM1 * mt;
   CUtensorMap ma, mb;
   const uint64_t sa = (uint64_t)M * K, sb = (uint64_t)N * K, sc = (uint64_t)M * N;
-  const bool oka = a_k ? make_map_3d(&ma, a, K, M, batch, K, sa, BM, true) : make_map_3d(&ma, a, M, K, batch, M, sa, BK, false);
+  const bool oka = a_k ? make_map_3d(&ma, a, K, M, batch, K, sa, bm, true) : make_map_3d(&ma, a, M, K, batch, M, sa, BK, false);
   const bool okb = b_k ? make_map_3d(&mb, b, K, N, batch, K, sb, bn, true) : make_map_3d(&mb, b, N, K, batch, N, sb, BK, false);
   if (!oka || !okb) return GT_OK;
   // the output goes through TMA (32x32 blocks of whole 128-byte rows) whenever its row pitch allows a tensor map
   CUtensorMap mc = ma;
   const int tma_store = ((N & 3) == 0 && make_map_3d(&mc, c, N, M, batch, N, sc, 32, true)) ? 1 : 0;
-  // split K when the output has few tiles and K is deep (dW: K = rows); partial sums meet in L2 with f32 adds
-  int ksplit = 1;
-  const long tiles = (long)gt_cdiv(N, bn) * gt_cdiv(M, BM) * batch;
-  const int kblocks = gt_cdiv(K, BK);
-  if (tiles < ctx->sm_count && kblocks >= 16) {
-    ksplit = (int)min((long)(ctx->sm_count / tiles), (long)(kblocks / 8));
-    if (ksplit < 1) ksplit = 1;
-  }
   if (ksplit > 1 && !accum) GT_CUDA(ctx, cudaMemsetAsync(c, 0, sizeof(float) * (size_t)M * N * batch, ctx->stream));
   gt_status s;
-  if (bn == 192) {
-    if (kind == GT_GEMM_NT) s = launch<true, true, 192>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
-    else if (kind == GT_GEMM_NN) s = launch<true, false, 192>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
-    else s = launch<false, false, 192>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
-  } else {
-    if (kind == GT_GEMM_NT) s = launch<true, true, 128>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
-    else if (kind == GT_GEMM_NN) s = launch<true, false, 128>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
-    else s = launch<false, false, 128>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
-  }
+  if (mt == 1 && bn == 192) s = launch_kind<192, 1>(ctx, kind, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
+  else if (mt == 1) s = launch_kind<128, 1>(ctx, kind, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
+  else if (bn == 256) s = launch_kind<256, 2>(ctx, kind, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
+  else s = launch_kind<192, 2>(ctx, kind, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
   if (s) return s;
   *handled = true;
   return GT_OK;
