@@ -256,6 +256,191 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
 }
 
 // ---------------------------------------------------------------------------------------------
+// The same product on CTA pairs (cta_group::2): a cluster of two CTAs on neighbouring SMs owns a 256 x BN output
+// tile. Each CTA stages its 128 rows of A and HALF of the B tile (the pair's tensor cores read both halves), so a
+// K block costs each SM 16 KB + BN/2 x 128 B of shared-memory writes and as many reads, against 16 KB + BN x 128 B
+// for a CTA working alone: with 4-byte operands that traffic, not the tensor pipe, bounds the main loop. Each
+// CTA holds its 128 rows of the accumulator, twice (the epilogue of a tile runs under the next tile's main loop).
+// Roles per CTA as above; the MMAs are issued by the even CTA only. Barriers: the TMA copies of both CTAs count
+// their bytes on the even CTA's `full`; `empty` and `acc_full` receive the MMA completions in both CTAs (multicast
+// commit); the epilogue threads of both CTAs arrive on the even CTA's `acc_empty`.
+// ---------------------------------------------------------------------------------------------
+template <int BN>
+struct SmemPair {
+  static constexpr int BH = BN / 2;                 // rows of the B tile staged by each CTA
+  static constexpr int A_BYTES = BM1 * BK * 4;      // 16 KB
+  static constexpr int B_BYTES = BH * BK * 4;
+  static constexpr int STAGE = A_BYTES + B_BYTES;
+  static constexpr int EPI_BYTES = 4 * 2 * 4096;
+  static constexpr int STAGES = (232448 - EPI_BYTES - 1024 - 256) / STAGE;   // 6 for BN = 256 and 192
+  static constexpr int TOTAL = STAGES * STAGE + EPI_BYTES + 1024 + 256;
+  static constexpr uint32_t TMEM_COLS = 2 * BN <= 256 ? 256 : 512;
+  static constexpr int THREADS = 192;
+  static_assert(BH % 32 == 0 && STAGES >= 3 && 8 * (2 * STAGES + 5) <= 256, "tile");
+};
+
+template <bool A_K, bool B_K, int BN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SmemPair<BN>::THREADS, 1)
+gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                      const __grid_constant__ CUtensorMap mapC, float* __restrict__ C, int M, int N, int K, int accum, int ksplit,
+                      int use_tma_store, int batch, int* __restrict__ flag) {
+  extern __shared__ uint8_t smem_raw[];
+  using S = SmemPair<BN>;
+  constexpr int STAGES = S::STAGES, BM = 2 * BM1;
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t epi = base + STAGES * S::STAGE;
+  const uint32_t bars = epi + S::EPI_BYTES;         // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], tmem slot
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto acc_full = [&](int b) { return bars + 8u * (2 * STAGES + b); };
+  auto acc_empty = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
+  const uint32_t tmem_slot = bars + 8u * (2 * STAGES + 4);
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = (int)cluster_ctarank();          // 0: issues the MMAs; both stage operands and drain their rows
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+  const int tiles_n = (N + BN - 1) / BN, tiles_m = (M + BM - 1) / BM;
+  const int per_mat = tiles_n * tiles_m * ksplit;
+  const int ntiles = per_mat * batch;
+  const int kblocks = (K + BK - 1) / BK;
+  const int per = (kblocks + ksplit - 1) / ksplit;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; b++) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 256); }   // 128 epilogue threads per CTA
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc_pair(tmem_slot, S::TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();            // the peer's barriers exist before anything is signalled to them
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot_ptr;
+  bool dead = false;
+  auto wait = [&](uint32_t bar, uint32_t parity, int code) {
+    if (dead) return;
+    if (!mbar_wait(bar, parity)) { dead = true; atomicExch(flag, code); }
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---- TMA producer (both CTAs) ----
+      uint32_t it = 0;
+      for (int t = pair; t < ntiles; t += npairs) {
+        const int bi = t / per_mat, tt = t % per_mat;
+        const int n0 = (tt % tiles_n) * BN + rank * S::BH, m0 = ((tt / tiles_n) % tiles_m) * BM + rank * BM1, z = tt / (tiles_n * tiles_m);
+        const int kb0 = z * per, kb1 = min(kblocks, kb0 + per);
+        for (int kb = kb0; kb < kb1; kb++, it++) {
+          const int s = it % STAGES;
+          wait(empty_bar(s), ((it / STAGES) & 1) ^ 1, 1);
+          const uint32_t a_dst = base + s * S::STAGE, b_dst = a_dst + S::A_BYTES;
+          const int k0 = kb * BK;
+          if (rank == 0) mbar_expect_tx(full_bar(s), 2 * S::STAGE);   // both CTAs' stages
+          if (A_K) tma_load_3d_pair(a_dst, &mapA, k0, m0, bi, full_bar(s));
+          else
+            for (int c = 0; c < BM1 / 32; c++) tma_load_3d_pair(a_dst + c * 4096, &mapA, m0 + 32 * c, k0, bi, full_bar(s));
+          if (B_K) tma_load_3d_pair(b_dst, &mapB, k0, n0, bi, full_bar(s));
+          else
+            for (int c = 0; c < S::BH / 32; c++) tma_load_3d_pair(b_dst + c * 4096, &mapB, n0 + 32 * c, k0, bi, full_bar(s));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      // ---- MMA issuer (even CTA) ----
+      constexpr uint32_t idesc = idesc_tf32(!A_K, !B_K, BM, BN);
+      const uint64_t a_desc0 = A_K ? desc_kmajor(base) : desc_mnmajor(base);
+      const uint64_t b_desc0 = B_K ? desc_kmajor(base + S::A_BYTES) : desc_mnmajor(base + S::A_BYTES);
+      constexpr uint32_t A_STEP = A_K ? 32 : 1024, B_STEP = B_K ? 32 : 1024;
+      uint32_t it = 0, tl = 0;
+      for (int t = pair; t < ntiles; t += npairs, tl++) {
+        const int z = (t % per_mat) / (tiles_n * tiles_m);
+        const int kb0 = z * per, kb1 = min(kblocks, kb0 + per);
+        const int b = tl & 1;
+        wait(acc_empty(b), ((tl >> 1) & 1) ^ 1, 4);   // both CTAs have drained this accumulator
+        tc_fence_after();
+        const uint32_t d_tmem = tmem + b * BN;
+        for (int kb = kb0; kb < kb1; kb++, it++) {
+          const int s = it % STAGES;
+          wait(full_bar(s), (it / STAGES) & 1, 2);
+          tc_fence_after();
+          const uint32_t soff = (uint32_t)(s * S::STAGE) >> 4;
+#pragma unroll
+          for (int j = 0; j < BK / UMMA_K; j++)
+            umma_tf32_pair(d_tmem, a_desc0 + soff + ((j * A_STEP) >> 4), b_desc0 + soff + ((j * B_STEP) >> 4), idesc,
+                           (kb > kb0 || j > 0) ? 1u : 0u);
+          umma_commit_pair(empty_bar(s), 3);   // the stage is free in both CTAs once these MMAs have read it
+        }
+        if (kb1 > kb0) umma_commit_pair(acc_full(b), 3);
+      }
+    }
+  } else {
+    // ---- epilogue (both CTAs): this CTA's 128 rows ----
+    const int q = warp & 3;
+    const bool vec = (N & 3) == 0;
+    uint32_t tl = 0, nst = 0;
+    for (int t = pair; t < ntiles; t += npairs, tl++) {
+      const int bi = t / per_mat, tt = t % per_mat;
+      const int n0 = (tt % tiles_n) * BN, m0 = ((tt / tiles_n) % tiles_m) * BM + rank * BM1, z = tt / (tiles_n * tiles_m);
+      const int b = tl & 1;
+      const bool have = z * per < kblocks;
+      const int row = m0 + q * 32 + lane;
+      if (have) wait(acc_full(b), (tl >> 1) & 1, 3);
+      dead = __any_sync(0xffffffffu, dead);
+      tc_fence_after();
+      if (have) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; c++) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= N) break;
+          float v[32];
+          tmem_ld32(tmem + b * BN + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
+#pragma unroll
+          for (int j = 0; j < 32; j++) v[j] *= TRUNC_COMP;
+          if (use_tma_store) {
+            const uint32_t tile = epi + (uint32_t)(q * 2 + (nst & 1)) * 4096u;
+            if (nst >= 2) tma_wait_read<1>();
+            __syncwarp();
+            uint8_t* tp = smem_raw + (tile - smem_u32(smem_raw)) + lane * 128;
+#pragma unroll
+            for (int c4 = 0; c4 < 8; c4++)
+              *reinterpret_cast<float4*>(tp + ((c4 ^ (lane & 7)) * 16)) = make_float4(v[4 * c4], v[4 * c4 + 1], v[4 * c4 + 2], v[4 * c4 + 3]);
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0 && !dead && m0 + q * 32 < M) {
+              if (ksplit > 1 || accum) tma_reduce_add_3d(&mapC, tile, col0, m0 + q * 32, bi);
+              else tma_store_3d(&mapC, tile, col0, m0 + q * 32, bi);
+            }
+            if (lane == 0) tma_commit_group();
+            nst++;
+          } else if (row < M && !dead) {
+            float* dst = C + (size_t)bi * M * N + (size_t)row * N + col0;
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+              if (col0 + j < N) {
+                if (ksplit > 1) atomicAdd(dst + j, v[j]);
+                else dst[j] = accum ? dst[j] + v[j] : v[j];
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive_leader(acc_empty(b));
+    }
+    if (lane == 0) tma_wait_all<0>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();            // neither CTA leaves (or frees tensor memory) while the other may still signal it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem, S::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
 int* g_flag[64] = {};
@@ -275,6 +460,54 @@ gt_status launch(gt_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, cons
   kern<<<grid, S::THREADS, S::TOTAL, ctx->stream>>>(ma, mb, mc, c, M, N, K, accum, ksplit, tma_store, batch, g_flag[ctx->device]);
   GT_LAUNCHED(ctx, "gemm_tf32_kernel");
   return GT_OK;
+}
+
+template <bool A_K, bool B_K, int BN>
+gt_status launch_pair(gt_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, int tma_store, float* c, int M, int N,
+                      int K, int accum, int ksplit, int batch, int npairs) {
+  auto kern = gemm_tf32_pair_kernel<A_K, B_K, BN>;
+  using S = SmemPair<BN>;
+  static bool attr_set[64] = {};
+  if (!attr_set[ctx->device]) {
+    GT_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+    attr_set[ctx->device] = true;
+  }
+  const long ntiles = (long)gt_cdiv(N, BN) * gt_cdiv(M, 2 * BM1) * ksplit * batch;
+  dim3 grid(2u * (unsigned)min((long)npairs, ntiles), 1, 1);
+  kern<<<grid, S::THREADS, S::TOTAL, ctx->stream>>>(ma, mb, mc, c, M, N, K, accum, ksplit, tma_store, batch, g_flag[ctx->device]);
+  GT_LAUNCHED(ctx, "gemm_tf32_pair_kernel");
+  return GT_OK;
+}
+
+template <int BN>
+gt_status launch_pair_kind(gt_ctx* ctx, int kind, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, int tma_store,
+                           float* c, int M, int N, int K, int accum, int ksplit, int batch, int npairs) {
+  if (kind == GT_GEMM_NT) return launch_pair<true, true, BN>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch, npairs);
+  if (kind == GT_GEMM_NN) return launch_pair<true, false, BN>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch, npairs);
+  return launch_pair<false, false, BN>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch, npairs);
+}
+
+// CTA pairs that can be resident at once (two neighbouring SMs each); 0 when the device cannot run the pair kernel.
+int pair_capacity(gt_ctx* ctx) {
+  static int cap[64];
+  static bool known[64] = {};
+  if (!known[ctx->device]) {
+    auto kern = gemm_tf32_pair_kernel<true, true, 192>;
+    int n = 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2u * (unsigned)ctx->sm_count, 1, 1);
+    cfg.blockDim = dim3(SmemPair<192>::THREADS, 1, 1);
+    cfg.dynamicSmemBytes = SmemPair<192>::TOTAL;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemPair<192>::TOTAL) != cudaSuccess ||
+        cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+      cudaGetLastError();
+      n = 0;
+    }
+    cap[ctx->device] = n;
+    known[ctx->device] = true;
+    if (getenv("GT_GEMM_TILE")) fprintf(stderr, "[gguftrain] resident CTA pairs: %d\n", n);
+  }
+  return cap[ctx->device];
 }
 
 template <int BN, int MT>
@@ -384,48 +617,59 @@ gt_status gt_gemm_tc_batched(gt_ctx* ctx, int kind, int accum, int M, int N, int
   // Tile shape and split-K factor: the cheapest of the four shapes under a small cost model (cycles of the CTA with
   // the most work: waves x (K blocks x cycles per K block + epilogue)), calibrated on in-kernel cycle counts.
   const int kblocks = gt_cdiv(K, BK);
-  struct Cfg { int mt, bn; };
-  static const Cfg cfgs[4] = {{1, 192}, {1, 128}, {2, 256}, {2, 192}};
+  struct Cfg { int mt, bn; };   // mt 1, 2: 128 / 256 rows on one CTA; mt 3: 256 rows on a CTA pair
+  static const Cfg cfgs[6] = {{1, 192}, {1, 128}, {2, 256}, {2, 192}, {3, 192}, {3, 256}};
   static const char* force = getenv("GT_GEMM_TILE");   // "mt,bn": development override
+  const int npairs = pair_capacity(ctx);
   int best = 0, ksplit = 1;
   double best_cost = 1e30;
-  for (int i = 0; i < 4; i++) {
-    const int mt = cfgs[i].mt, bn = cfgs[i].bn, bm = BM1 * mt;
+  for (int i = 0; i < 6; i++) {
+    const int mt = cfgs[i].mt, bn = cfgs[i].bn, bm = mt == 1 ? BM1 : 2 * BM1;
+    if (mt == 3 && npairs < 8) continue;
     if (force) {
       int fm = 0, fb = 0;
       if (sscanf(force, "%d,%d", &fm, &fb) == 2 && (fm != mt || fb != bn)) continue;
     }
+    const long workers = mt == 3 ? npairs : ctx->sm_count;
     const long tiles = (long)gt_cdiv(N, bn) * gt_cdiv(M, bm) * batch;
     // split K when the output has few tiles and K is deep (dW: K = rows); partial sums meet in L2 with f32 adds
     int ks = 1;
-    if (tiles < ctx->sm_count && kblocks >= 16) {
-      ks = (int)min((long)(ctx->sm_count / tiles), (long)(kblocks / 8));
+    if (tiles < workers && kblocks >= 16) {
+      ks = (int)min((long)(workers / tiles), (long)(kblocks / 8));
       if (ks < 1) ks = 1;
     }
     const long units = tiles * ks;
-    const long waves = gt_cdiv(units, (long)ctx->sm_count);
+    const long waves = gt_cdiv(units, workers);
     const double kb_unit = (double)gt_cdiv(kblocks, ks);
     // One K block costs the slower of its MMAs (N/2 cycles each) and its shared-memory traffic at 128 B/clk: the stage
     // is written once by TMA and read once per 128-row half by the MMAs (measured: 0.9 of that bound). The epilogue
     // of a 256-row tile is exposed, that of a 128-row tile mostly hidden.
-    const double tensor = mt * 4.0 * (bn / 2);
-    const double smem = 0.92 * ((bm * 128.0 + bn * 128.0) + mt * (BM1 * 128.0 + bn * 128.0)) / 128.0;
+    // A CTA of a pair stages 128 rows of A and half of the B tile but still serves both halves of B to the pair's
+    // tensor cores: measured 640 (BN 192) and 720 (BN 256) cycles per K block, little better per flop than one CTA
+    // with a 256-row tile; what the pair adds is the second accumulator (hidden epilogue) and a deeper pipeline.
+    const double tensor = (mt == 2 ? 2 : 1) * 4.0 * (bn / 2);
+    const double smem = mt == 3 ? (bn == 192 ? 640.0 : 720.0)
+                                : 0.92 * ((bm * 128.0 + bn * 128.0) + mt * (BM1 * 128.0 + bn * 128.0)) / 128.0;
     const double epilogue = mt == 2 ? 14.0 * bn + 900.0 : 1500.0;
     const double cost = waves * (kb_unit * (tensor > smem ? tensor : smem) + epilogue);
     if (cost < best_cost) { best_cost = cost; best = i; ksplit = ks; }
   }
-  const int mt = cfgs[best].mt, bn = cfgs[best].bn, bm = BM1 * mt;
+  if (best_cost >= 1e30) return GT_OK;
+  const int mt = cfgs[best].mt, bn = cfgs[best].bn;
+  const int a_box = mt == 2 ? 2 * BM1 : BM1, b_box = mt == 3 ? bn / 2 : bn;   // rows one TMA copy brings
   CUtensorMap ma, mb;
   const uint64_t sa = (uint64_t)M * K, sb = (uint64_t)N * K, sc = (uint64_t)M * N;
-  const bool oka = a_k ? make_map_3d(&ma, a, K, M, batch, K, sa, bm, true) : make_map_3d(&ma, a, M, K, batch, M, sa, BK, false);
-  const bool okb = b_k ? make_map_3d(&mb, b, K, N, batch, K, sb, bn, true) : make_map_3d(&mb, b, N, K, batch, N, sb, BK, false);
+  const bool oka = a_k ? make_map_3d(&ma, a, K, M, batch, K, sa, a_box, true) : make_map_3d(&ma, a, M, K, batch, M, sa, BK, false);
+  const bool okb = b_k ? make_map_3d(&mb, b, K, N, batch, K, sb, b_box, true) : make_map_3d(&mb, b, N, K, batch, N, sb, BK, false);
   if (!oka || !okb) return GT_OK;
   // the output goes through TMA (32x32 blocks of whole 128-byte rows) whenever its row pitch allows a tensor map
   CUtensorMap mc = ma;
   const int tma_store = ((N & 3) == 0 && make_map_3d(&mc, c, N, M, batch, N, sc, 32, true)) ? 1 : 0;
   if (ksplit > 1 && !accum) GT_CUDA(ctx, cudaMemsetAsync(c, 0, sizeof(float) * (size_t)M * N * batch, ctx->stream));
   gt_status s;
-  if (mt == 1 && bn == 192) s = launch_kind<192, 1>(ctx, kind, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
+  if (mt == 3 && bn == 192) s = launch_pair_kind<192>(ctx, kind, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch, npairs);
+  else if (mt == 3) s = launch_pair_kind<256>(ctx, kind, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch, npairs);
+  else if (mt == 1 && bn == 192) s = launch_kind<192, 1>(ctx, kind, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
   else if (mt == 1) s = launch_kind<128, 1>(ctx, kind, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
   else if (bn == 256) s = launch_kind<256, 2>(ctx, kind, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
   else s = launch_kind<192, 2>(ctx, kind, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
