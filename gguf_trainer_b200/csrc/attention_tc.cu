@@ -322,19 +322,27 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
 // the whole loop. Nothing is reduced with atomics: one CTA owns its 128 query rows (dQ) or its 128 key rows
 // (dK, dV, summing its GQA group inside the loop), so results are deterministic.
 // ---------------------------------------------------------------------------------------------
-__global__ void attn_bwd_d_tc_kernel(int rows, int Hq, int hd, float scale, const float* __restrict__ go,
-                                     const float* __restrict__ o, float* __restrict__ D) {
-  const int lane = threadIdx.x & 31;
-  const long w = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  if (w >= (long)rows * Hq) return;
-  const int h = (int)(w % Hq);
-  const long row = w / Hq;
-  const size_t b = (size_t)row * Hq * hd + (size_t)h * hd;
+// HD / 4 lanes per (row, head), one 16-byte load of dO and of O each: the kernel streams both tensors once.
+template <int HD>
+__global__ void attn_bwd_d_tc_kernel(long nitems, float scale, const float* __restrict__ go, const float* __restrict__ o,
+                                     float* __restrict__ D, int rows, int Hq) {
+  constexpr int L = HD / 4;                   // lanes per item: 8, 16 or 32
+  const long gid = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long item = gid / L;                  // row * Hq + h
+  const int sub = (int)(gid % L);
   float acc = 0.f;
-  for (int d = lane; d < hd; d += 32) acc = fmaf(go[b + d], o[b + d], acc);
+  if (item < nitems) {
+    const float4 g = __ldg(reinterpret_cast<const float4*>(go + item * HD) + sub);
+    const float4 v = __ldg(reinterpret_cast<const float4*>(o + item * HD) + sub);
+    acc = g.x * v.x + g.y * v.y + g.z * v.z + g.w * v.w;
+  }
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-  if (lane == 0) D[(size_t)h * rows + row] = acc * scale;
+  for (int off = L / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (item < nitems && sub == 0) {
+    const long row = item / Hq;
+    const int h = (int)(item % Hq);
+    D[(size_t)h * rows + row] = acc * scale;
+  }
 }
 
 // ---- dK, dV: CTA = 128 keys of one kv head; loop over the group's query heads and over blocks of NQ queries ----
@@ -876,7 +884,8 @@ gt_status launch_bwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, 
   gt_status st = gt_scratch(ctx, sizeof(float) * (size_t)rows * Hq, &D);
   if (st) return st;
   const float scale = 1.f / sqrtf((float)HD);
-  attn_bwd_d_tc_kernel<<<gt_cdiv((long)rows * Hq * 32, 256), 256, 0, ctx->stream>>>(rows, Hq, HD, scale, go, out, D);
+  const long nitems = (long)rows * Hq;
+  attn_bwd_d_tc_kernel<HD><<<(unsigned)gt_cdiv(nitems * (HD / 4), 256l), 256, 0, ctx->stream>>>(nitems, scale, go, out, D, rows, Hq);
   GT_LAUNCHED(ctx, "attn_bwd_d_tc_kernel");
   const float scale2 = 1.4426950408889634f * scale * TRUNC_COMP;
   const float dp_scale = scale * TRUNC_COMP;
@@ -941,7 +950,8 @@ gt_status gt_attention_bwd_tc(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int
                               int accum_k, float* gv, int accum_v, bool* handled) {
   *handled = false;
   if (!tc_shape_ok(T, hd)) return GT_OK;
-  if ((((uintptr_t)q) | ((uintptr_t)k) | ((uintptr_t)v) | ((uintptr_t)go) | ((uintptr_t)gq) | ((uintptr_t)gk) | ((uintptr_t)gv)) & 15) return GT_OK;
+  if ((((uintptr_t)q) | ((uintptr_t)k) | ((uintptr_t)v) | ((uintptr_t)out) | ((uintptr_t)go) | ((uintptr_t)gq) | ((uintptr_t)gk) | ((uintptr_t)gv)) & 15)
+    return GT_OK;
   int* flag = device_flag(ctx);
   if (!flag) return GT_OK;
   gt_status s;

@@ -38,6 +38,40 @@ __global__ void rope_kernel(long npairs, int H, int hd, int period, const float2
   }
 }
 
+// Four pairs per thread (hd a multiple of 8, 16-byte aligned operands, fewer than 2^31 pairs): two 16-byte loads of
+// the row, two of the table, two 16-byte stores, 32-bit index arithmetic.
+template <bool BWD>
+__global__ void rope_vec_kernel(unsigned nvec, int H, int hd, int period, const float2* __restrict__ tab,
+                                const float* __restrict__ in, float* out, int accum) {
+  const unsigned half = hd >> 1, hv = half >> 2;
+  const unsigned stride = gridDim.x * blockDim.x;
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    const unsigned j = (i % hv) * 4, rh = i / hv;   // first pair of the four, row*H + h
+    const unsigned t = (rh / (unsigned)H) % (unsigned)period;
+    const float4* tp = reinterpret_cast<const float4*>(tab + (size_t)t * half + j);
+    const float4 c01 = __ldg(tp), c23 = __ldg(tp + 1);   // (cos, sin) of pairs j..j+3
+    const size_t b = (size_t)rh * hd + j;
+    const float4 a0 = *reinterpret_cast<const float4*>(in + b), a1 = *reinterpret_cast<const float4*>(in + b + half);
+    float4 o0, o1;
+    if (!BWD) {
+      o0 = make_float4(a0.x * c01.x - a1.x * c01.y, a0.y * c01.z - a1.y * c01.w, a0.z * c23.x - a1.z * c23.y, a0.w * c23.z - a1.w * c23.w);
+      o1 = make_float4(a0.x * c01.y + a1.x * c01.x, a0.y * c01.w + a1.y * c01.z, a0.z * c23.y + a1.z * c23.x, a0.w * c23.w + a1.w * c23.z);
+    } else {
+      o0 = make_float4(c01.x * a0.x + c01.y * a1.x, c01.z * a0.y + c01.w * a1.y, c23.x * a0.z + c23.y * a1.z, c23.z * a0.w + c23.w * a1.w);
+      o1 = make_float4(-c01.y * a0.x + c01.x * a1.x, -c01.w * a0.y + c01.z * a1.y, -c23.y * a0.z + c23.x * a1.z, -c23.w * a0.w + c23.z * a1.w);
+    }
+    float4* p0 = reinterpret_cast<float4*>(out + b);
+    float4* p1 = reinterpret_cast<float4*>(out + b + half);
+    if (accum) {
+      const float4 q0 = *p0, q1 = *p1;
+      o0 = make_float4(q0.x + o0.x, q0.y + o0.y, q0.z + o0.z, q0.w + o0.w);
+      o1 = make_float4(q1.x + o1.x, q1.y + o1.y, q1.z + o1.z, q1.w + o1.w);
+    }
+    *p0 = o0;
+    *p1 = o1;
+  }
+}
+
 __global__ void embedding_fwd_kernel(long n, int d, const float* __restrict__ w, const uint32_t* __restrict__ ids,
                                      float* __restrict__ out) {
   long stride = (long)gridDim.x * blockDim.x;
@@ -87,6 +121,13 @@ gt_status rope_run(gt_ctx* ctx, int rows, int H, int hd, double base, int pos_of
   gt_status s = rope_table(ctx, period, hd, base, pos_offset, &tab);
   if (s) return s;
   long npairs = (long)rows * H * (hd / 2);
+  if (hd % 8 == 0 && npairs < (1l << 31) && ((((uintptr_t)in) | ((uintptr_t)out)) & 15) == 0) {
+    const long nvec = npairs / 4;
+    int grid = (int)min((long)ctx->sm_count * 8, (nvec + 255) / 256);
+    rope_vec_kernel<BWD><<<grid, 256, 0, ctx->stream>>>((unsigned)nvec, H, hd, period, tab, in, out, accum);
+    GT_LAUNCHED(ctx, "rope_vec_kernel");
+    return GT_OK;
+  }
   int grid = (int)min((long)ctx->sm_count * 16, (npairs + 255) / 256);
   rope_kernel<BWD><<<grid, 256, 0, ctx->stream>>>(npairs, H, hd, period, tab, in, out, accum);
   GT_LAUNCHED(ctx, "rope_kernel");

@@ -121,7 +121,7 @@ def test_embedding_is_bit_exact_gather_and_scatter_adds_duplicates(gpu, oracle):
 
 
 @pytest.mark.parametrize("T,H,hd,base,off", [(7, 2, 8, 10_000.0, 0), (130, 9, 64, 100_000.0, 0),
-                                            (33, 4, 256, 1_000_000.0, 5), (2048, 1, 32, 10_000.0, 0)])
+                                            (33, 4, 256, 1_000_000.0, 5), (2048, 1, 32, 10_000.0, 0), (5, 3, 12, 10_000.0, 2)])
 def test_rope(gpu, oracle, T, H, hd, base, off):
     rng = oracle.Mulberry32(41)
     x = rand_tensor(rng, [T, H * hd])
