@@ -619,7 +619,7 @@ gt_status gt_gemm_tc_batched(gt_ctx* ctx, int kind, int accum, int M, int N, int
   const int kblocks = gt_cdiv(K, BK);
   struct Cfg { int mt, bn; };   // mt 1, 2: 128 / 256 rows on one CTA; mt 3: 256 rows on a CTA pair
   static const Cfg cfgs[6] = {{1, 192}, {1, 128}, {2, 256}, {2, 192}, {3, 192}, {3, 256}};
-  static const char* force = getenv("GT_GEMM_TILE");   // "mt,bn": development override
+  const char* force = getenv("GT_GEMM_TILE");   // "mt,bn": forces one tile shape (read per call so tests can switch it)
   const int npairs = pair_capacity(ctx);
   int best = 0, ksplit = 1;
   double best_cost = 1e30;

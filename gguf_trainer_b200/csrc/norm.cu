@@ -120,8 +120,16 @@ __global__ void __launch_bounds__(TH) rmsnorm_bwd_vec_kernel(int rows, int d, co
   for (int row = warp; row < rows; row += nwarps) {
     const float4* xr = reinterpret_cast<const float4*>(x + (size_t)row * d);
     const float4* gr = reinterpret_cast<const float4*>(g + (size_t)row * d);
-    float4 xv[V4], gv[V4];
+    float4 xv[V4], gv[V4], pv[V4];
     float S = 0.f;
+    if (gx && accum_x) {   // the old dx values are fetched with the row, not after the reduction (one round trip, not two)
+      const float4* orow = reinterpret_cast<const float4*>(gx + (size_t)row * d);
+#pragma unroll
+      for (int i = 0; i < V4; i++) {
+        const int j = lane + 32 * i;
+        pv[i] = j < d4 ? orow[j] : make_float4(0, 0, 0, 0);
+      }
+    }
 #pragma unroll
     for (int i = 0; i < V4; i++) {
       const int j = lane + 32 * i;
@@ -142,7 +150,7 @@ __global__ void __launch_bounds__(TH) rmsnorm_bwd_vec_kernel(int rows, int d, co
           float4 v;
           v.x = wv[i].x * r * gv[i].x - xv[i].x * k; v.y = wv[i].y * r * gv[i].y - xv[i].y * k;
           v.z = wv[i].z * r * gv[i].z - xv[i].z * k; v.w = wv[i].w * r * gv[i].w - xv[i].w * k;
-          if (accum_x) { const float4 p = o[j]; v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w; }
+          if (accum_x) { v.x += pv[i].x; v.y += pv[i].y; v.z += pv[i].z; v.w += pv[i].w; }
           o[j] = v;
         }
       }

@@ -54,6 +54,32 @@ def test_gemm_tf32(gpu, oracle, kind, M, N, K):
         gpu._check(gpu.lib.gt_free(gpu.ctx, b))
 
 
+TILES = ["1,192", "1,128", "2,256", "2,192", "3,192", "3,256"]   # rows per CTA x columns; 3 = a CTA pair (cta_group::2)
+
+
+@pytest.mark.parametrize("tile", TILES)
+@pytest.mark.parametrize("kind,M,N,K,accum", [("NT", 1000, 1536, 576, 0), ("NN", 2048, 576, 1536, 1), ("TN", 576, 1536, 4096, 0),
+                                              ("TN", 300, 200, 2048, 1), ("NT", 513, 49, 96, 0)])
+def test_gemm_every_tile_shape(gpu, oracle, monkeypatch, tile, kind, M, N, K, accum):
+    """Each tile shape of the dispatcher forced in turn (the cost model would otherwise pick one per product):
+    ragged edges, accumulate, split-K, all layouts."""
+    monkeypatch.setenv("GT_GEMM_TILE", tile)
+    rng = oracle.Mulberry32(M + 11 * N + 5 * K)
+    A, B, C0 = rng.randn((M, K), 0.5), rng.randn((N, K), 0.5), rng.randn((M, N), 0.5)
+    want = A.astype(np.float64) @ B.astype(np.float64).T + (C0.astype(np.float64) if accum else 0.0)
+    a_store = A if kind != "TN" else np.ascontiguousarray(A.T)
+    b_store = B if kind == "NT" else np.ascontiguousarray(B.T)
+    da, db, dc = _dev(gpu, a_store), _dev(gpu, b_store), _dev(gpu, C0)
+    gpu._gemm(kind, accum, M, N, K, da, db, dc)
+    got = gpu.readStateBuffer(dc, M * N).reshape(M, N)
+    gpu.sync([])
+    r = rel_l2(got, want)
+    assert np.isfinite(got).all() and r <= REL_L2_TC, f"tile {tile} {kind} {M}x{N}x{K}: relative L2 {r:.3e}"
+    assert r > 1e-6, "the strict-f32 kernel answered: the forced tile shape was not used"
+    for b in (da, db, dc):
+        gpu._check(gpu.lib.gt_free(gpu.ctx, b))
+
+
 def test_tf32_products_differ_from_strict_f32(gpu, oracle):
     """Guards against the tensor-core path silently falling through to the f32 kernel."""
     rng = oracle.Mulberry32(5)
