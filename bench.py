@@ -355,7 +355,7 @@ def run_ours(args):
                          "frac": achieved / pk["tflops_sustained"],
                          # dram__bytes_read.sum + dram__bytes_write.sum of these 14 launches at rows 16384 from one ncu capture
                          # (profiles/gemm_tf32_rows16384.md), per launch; only meaningful at the default shape
-                         "traffic": (1098.7e6 / 14) if (args.config == "smollm2" and B * T == 16384) else None,
+                         "traffic": (1095.7e6 / 14) if (args.config == "smollm2" and B * T == 16384) else None,
                          "kernel": f"backward matrix products of one layer (dX and dW for 7 projections, {ncalls} launches, rows {B * T})",
                          "peak_source": f"{pk['src']} bf16 sustained (tf32 runs at half the bf16 rate; no separate tf32 peak is measured)"},
         }

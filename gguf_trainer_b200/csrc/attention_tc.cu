@@ -11,7 +11,10 @@
 // dK/dV) and walks the other axis in blocks. In the backward kernels one thread issues the TMA copies and one
 // thread of another warp the MMAs, each waiting only on what its own instructions need (with a single issuing
 // thread the waits and issue latencies of the two roles added up to more than the tensor time of a block);
-// descriptors are formed by one add per operand. Eight warps do the element math, two per TMEM lane quadrant, each taking half of a block's columns, one output row per thread (no shuffles). The
+// descriptors are formed by one add per operand. Eight warps do the element math, two per TMEM lane quadrant, each
+// taking half of a block's columns, one output row per thread (no shuffles). In forward P goes to the second
+// product through a shared-memory tile; in backward P^T / dS^T are written back over S^T / dP^T in tensor memory
+// and read from there as the A operand of the gradient products. The
 // score products of block i+1 are issued before the element math of block i is waited for (their TMEM
 // accumulators are double-buffered), so the tensor pipe and the CUDA cores overlap; operand tiles of the next
 // block are fetched as soon as the products that read the current ones have completed.
