@@ -433,19 +433,24 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
 
   if (warp == TMA_WARP) {
     if (lane == 0) {
-      auto load_k = [&](int it) {   // K-major copies of Q and dO
-        const int h = kvh * group + it / nqb, qr = row0 + (qb_lo + it % nqb) * NQ;
+      // Both copies are requested block after block, so (head, query block) of the next request is kept by counting:
+      // a division by the run-time block count costs this single thread more than the copy instructions themselves.
+      int k_h = kvh * group, k_qb = 0, m_h = kvh * group, m_qb = 0;
+      auto load_k = [&](int it) {   // K-major copies of Q and dO, block `it` (called with it = 0, 1, 2, ...)
+        const int qr = row0 + (qb_lo + k_qb) * NQ;
         const uint32_t bar = qk_bar(it), off = (KBUF == 2 && (it & 1)) ? S::QT_BYTES : 0;
         mbar_expect_tx(bar, 2 * S::QT_BYTES);
-        tma_load_3d(qk_s + off, &mapQk, 0, qr, h * ATOMS, bar);
-        tma_load_3d(gk_s + off, &mapGk, 0, qr, h * ATOMS, bar);
+        tma_load_3d(qk_s + off, &mapQk, 0, qr, k_h * ATOMS, bar);
+        tma_load_3d(gk_s + off, &mapGk, 0, qr, k_h * ATOMS, bar);
+        if (++k_qb == nqb) { k_qb = 0; k_h++; }
       };
-      auto load_m = [&](int it) {   // [queries, hd] copies for the gradient products
-        const int h = kvh * group + it / nqb, qr = row0 + (qb_lo + it % nqb) * NQ;
+      auto load_m = [&](int it) {   // [queries, hd] copies for the gradient products, block `it` (same order)
+        const int qr = row0 + (qb_lo + m_qb) * NQ;
         const uint32_t bar = qm_bar(it), off = (MBUF == 2 && (it & 1)) ? S::QT_BYTES : 0;
         mbar_expect_tx(bar, 2 * S::QT_BYTES);
-        tma_load_3d(qm_s + off, &mapQm, 0, qr, h * ATOMS, bar);
-        tma_load_3d(gm_s + off, &mapGm, 0, qr, h * ATOMS, bar);
+        tma_load_3d(qm_s + off, &mapQm, 0, qr, m_h * ATOMS, bar);
+        tma_load_3d(gm_s + off, &mapGm, 0, qr, m_h * ATOMS, bar);
+        if (++m_qb == nqb) { m_qb = 0; m_h++; }
       };
       mbar_expect_tx(kv_full, 2 * S::KV_BYTES);
       tma_load_3d(k_s, &mapK, 0, row0 + k0, kvh * ATOMS, kv_full);
@@ -531,6 +536,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
     const int qd = warp & 3, half = warp >> 2;
     const int kg = k0 + qd * 32 + lane;      // key position in the sequence: one row of the tile per thread
     const uint32_t lane_base = (uint32_t)(qd * 32) << 16;
+    int c_h = kvh * group, c_qb = 0;         // (head, query block) of block i, kept by counting
 #ifdef GT_ATTN_TRACE
     const bool trm = tr && warp == 0;
 #define TRACEM(slot) if (trm && i >= 8 && i < 40) { long long tn = clock64(); flag[64 + (i - 8) * 32 + slot] = (int)(tn - tprev); tprev = tn; }
@@ -539,8 +545,9 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
 #endif
     for (int i = 0; i < iters; i++) {
       TRACEM(8)
-      const int h = kvh * group + i / nqb;
-      const int qpos0 = (qb_lo + i % nqb) * NQ + half * NH;      // first query of this thread's columns
+      const int h = c_h;
+      const int qpos0 = (qb_lo + c_qb) * NQ + half * NH;         // first query of this thread's columns
+      if (++c_qb == nqb) { c_qb = 0; c_h++; }
       const float4* l4 = reinterpret_cast<const float4*>(lse + (size_t)h * rows + row0 + qpos0);
       const float4* d4 = reinterpret_cast<const float4*>(Ds + (size_t)h * rows + row0 + qpos0);
       // every (key, query) pair of the tile kept: keys at or before the first query, queries inside the sequence
