@@ -651,29 +651,36 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
 // ---- dQ: CTA = 128 queries of one head; loop over blocks of NK keys ----
 // S = Q.K^T and dP = dO.V^T (M=128 queries, N=NK keys); dS written as a K-major A operand (K = keys);
 // dQ += dS.K with K read a second time as a [keys, hd] operand. KBUF as in the dK/dV kernel.
-template <int HD, int NK, int KBUF>
+// SB: one [S | dP] pair in tensor memory instead of two and single-buffered copies, small enough for two CTAs per SM:
+// a CTA then runs its products and its element math strictly one after the other, and the second CTA fills the gaps.
+template <int HD, int NK, int KBUF, bool SB>
 struct DqSmem {
   static constexpr int Q_BYTES = ROWS * HD * 4, KT_BYTES = NK * HD * 4;
   static constexpr int Q_OFF = 0, G_OFF = Q_BYTES, KK_OFF = 2 * Q_BYTES, VK_OFF = KK_OFF + KBUF * KT_BYTES,
                        KM_OFF = VK_OFF + KBUF * KT_BYTES, BAR_OFF = KM_OFF + KT_BYTES;
-  static constexpr int TOTAL = BAR_OFF + 128 + 1024;
-  static constexpr int COLS = 4 * NK + HD;
+  static constexpr int SLACK = SB ? 896 : 1024;   // for rounding the base up to 1024 B (two CTAs must fit 228 KB together)
+  static constexpr int TOTAL = BAR_OFF + 128 + SLACK;
+  static constexpr int COLS = (SB ? 2 : 4) * NK + HD;
   static constexpr uint32_t TMEM_COLS = COLS <= 128 ? 128 : (COLS <= 256 ? 256 : 512);
   static_assert(TOTAL <= 232448, "shared memory");
 };
 
-template <int HD, int NK, int KBUF>
-__global__ void __launch_bounds__(THREADS, 1)
+template <int HD, int NK, int KBUF, bool SB>
+__global__ void __launch_bounds__(THREADS, SB ? 2 : 1)
 attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapG,
                       const __grid_constant__ CUtensorMap mapKk, const __grid_constant__ CUtensorMap mapVk,
                       const __grid_constant__ CUtensorMap mapKm, const float* __restrict__ lse, const float* __restrict__ Ds,
                       float* gq, int accum_q, int rows, int T, int Hq, int Hkv, int window, float scale2, float dp_scale,
                       int* __restrict__ flag) {
   extern __shared__ uint8_t smem_raw[];
-  using S = DqSmem<HD, NK, KBUF>;
+  using S = DqSmem<HD, NK, KBUF, SB>;
   constexpr int ATOMS = HD / 32, NH = NK / 2, HH = HD / 2;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  if (base - smem_u32(smem_raw) > (uint32_t)S::SLACK) {   // cannot happen while dynamic shared memory starts 128-byte aligned
+    if (threadIdx.x == 0) atomicExch(flag, 39);
+    return;
+  }
   const uint32_t q_s = base + S::Q_OFF, g_s = base + S::G_OFF, kk_s = base + S::KK_OFF, vk_s = base + S::VK_OFF, km_s = base + S::KM_OFF;
   const uint32_t bars = base + S::BAR_OFF;
   const uint32_t q_full = bars, kk_full0 = bars + 8, kk_full1 = bars + 16, km_full = bars + 24, s_full0 = bars + 32,
@@ -702,7 +709,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot_ptr;
-  const uint32_t tm_dq = tmem + 4 * NK;
+  const uint32_t tm_dq = tmem + (SB ? 2 : 4) * NK;
+  auto sbuf = [&](int it) { return SB ? 0u : (uint32_t)((it & 1) * 2 * NK); };   // TMEM columns of block it's [S | dP]
   Waiter w{false, flag};
   // two alternating p_full barriers, as in the dK/dV kernel: the math warps may finish block i+1 before the issuing
   // thread has looked at block i's barrier (it may be waiting for the [keys, hd] copy)
@@ -750,7 +758,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       const uint64_t d_q = desc_kmajor(q_s), d_g = desc_kmajor(g_s), d_kk = desc_kmajor(kk_s), d_vk = desc_kmajor(vk_s),
                      d_km = smem_desc(km_s, NK * 128, 512, 1);
       auto mma_s = [&](int it) {
-        const uint32_t tm_s = tmem + (it & 1) * 2 * NK, tm_dp = tm_s + NK;
+        const uint32_t tm_s = tmem + sbuf(it), tm_dp = tm_s + NK;
         const uint32_t boff = (KBUF == 2 && (it & 1)) ? S::KT_BYTES : 0;
 #pragma unroll
         for (int a = 0; a < ATOMS; a++)
@@ -771,7 +779,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       tc_fence_after();
       mma_s(0);
       for (int i = 0; i < iters; i++) {
-        if (i + 1 < iters) {
+        if (!SB && i + 1 < iters) {               // next block's scores, under this block's element math
           w.wait(kk_bar(i + 1), kk_par(i + 1), 32);
           tc_fence_after();
           mma_s(i + 1);
@@ -781,8 +789,13 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         tc_fence_after();
 #pragma unroll
         for (int j = 0; j < NK / 8; j++)   // dS is read where the math warps wrote it: over S, in tensor memory
-          umma_tf32_ts(tm_dq, tmem + (i & 1) * 2 * NK + j * 8, desc_off(d_km, j * 1024), idesc_g, (i > 0 || j > 0) ? 1u : 0u);
+          umma_tf32_ts(tm_dq, tmem + sbuf(i) + j * 8, desc_off(d_km, j * 1024), idesc_g, (i > 0 || j > 0) ? 1u : 0u);
         umma_commit(acc_done);
+        if (SB && i + 1 < iters) {                // one score buffer: the next scores follow the product that read dS
+          w.wait(kk_bar(i + 1), kk_par(i + 1), 32);
+          tc_fence_after();
+          mma_s(i + 1);
+        }
       }
       umma_commit(all_done);   // the end of the accumulation, for the math warps (they do not follow acc_done)
       mbar_wait(all_done, 0);  // and for this thread, whatever happened before: no MMA in flight when TMEM is freed
@@ -801,7 +814,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       w.wait(s_bar(i), s_par(i), 36);
       tc_fence_after();
       float s[NH], dp[NH];
-      const uint32_t tm_s = tmem + (i & 1) * 2 * NK + half * NH + lane_base;
+      const uint32_t tm_s = tmem + sbuf(i) + half * NH + lane_base;
       tmem_ld_issue<NH>(tm_s, s);
       tmem_ld_issue<NH>(tm_s + NK, dp);
       tmem_wait_ld();
@@ -886,7 +899,7 @@ gt_status launch_fwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, 
   return GT_OK;
 }
 
-template <int HD, int NQ, int NK, int DKV_KBUF, int DKV_MBUF, int DQ_KBUF>
+template <int HD, int NQ, int NK, int DKV_KBUF, int DKV_MBUF, int DQ_KBUF, bool DQ_SB>
 gt_status launch_bwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, const float* q, const float* k, const float* v,
                      const float* out, const float* lse, const float* go, float* gq, int accum_q, float* gk, int accum_k, float* gv,
                      int accum_v, int* flag) {
@@ -923,12 +936,12 @@ gt_status launch_bwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, 
         !make_map_atoms(&mKk, k, kw, rows, kw, NK, HD / 32, true) || !make_map_atoms(&mVk, v, kw, rows, kw, NK, HD / 32, true) ||
         !make_map_atoms(&mKm, k, kw, rows, kw, NK, HD / 32, false))
       return gt_fail(ctx, GT_ERR_CUDA, "attention backward: tensor map encoding failed");
-    auto kern = attn_bwd_dq_tc_kernel<HD, NK, DQ_KBUF>;
+    auto kern = attn_bwd_dq_tc_kernel<HD, NK, DQ_KBUF, DQ_SB>;
     static bool done[64] = {};
-    st = set_smem(ctx, kern, DqSmem<HD, NK, DQ_KBUF>::TOTAL, done);
+    st = set_smem(ctx, kern, DqSmem<HD, NK, DQ_KBUF, DQ_SB>::TOTAL, done);
     if (st) return st;
     dim3 grid(Hq * nseq, gt_cdiv(T, ROWS), 1);
-    kern<<<grid, THREADS, DqSmem<HD, NK, DQ_KBUF>::TOTAL, ctx->stream>>>(mQ, mG, mKk, mVk, mKm, lse, D, gq, accum_q, rows, T, Hq, Hkv, window, scale2,
+    kern<<<grid, THREADS, DqSmem<HD, NK, DQ_KBUF, DQ_SB>::TOTAL, ctx->stream>>>(mQ, mG, mKk, mVk, mKm, lse, D, gq, accum_q, rows, T, Hq, Hkv, window, scale2,
                                                                dp_scale, flag);
     GT_LAUNCHED(ctx, "attn_bwd_dq_tc_kernel");
   }
@@ -965,9 +978,9 @@ gt_status gt_attention_bwd_tc(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int
   int* flag = device_flag(ctx);
   if (!flag) return GT_OK;
   gt_status s;
-  if (hd == 32) s = launch_bwd<32, 64, 64, 2, 2, 2>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
-  else if (hd == 64) s = launch_bwd<64, 64, 64, 2, 2, 2>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
-  else s = launch_bwd<128, 32, 32, 2, 1, 2>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
+  if (hd == 32) s = launch_bwd<32, 64, 64, 2, 2, 1, true>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
+  else if (hd == 64) s = launch_bwd<64, 64, 64, 2, 2, 1, true>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
+  else s = launch_bwd<128, 32, 32, 2, 1, 2, false>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
   if (s) return s;
   *handled = true;
   return GT_OK;
