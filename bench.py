@@ -407,6 +407,9 @@ def run_micro(args):
     B, T = args.micro_batch, args.seq
     rows = B * T
     h, q, kv, f, V, Hq, Hkv, hd = 576, 576, 192, 1536, 49152, 9, 3, 64
+    if args.heads:                                   # attention at another head layout, e.g. 4,1,256 (gemma3)
+        Hq, Hkv, hd = (int(x) for x in args.heads.split(","))
+        q, kv = Hq * hd, Hkv * hd
     rng = np.random.default_rng(0)
 
     def buf(n, fill=True):
@@ -473,6 +476,7 @@ def main():
     ap.add_argument("--micro", default="", help="time one op of the step instead: attention | gemm")
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--window", type=int, default=0)
+    ap.add_argument("--heads", default="", help="--micro attention: Hq,Hkv,hd instead of 9,3,64")
     args = ap.parse_args()
     if args.profile:
         run_profile(args)

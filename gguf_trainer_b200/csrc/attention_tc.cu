@@ -105,6 +105,47 @@ struct Waiter {
     if (dead) return;
     if (!mbar_wait(bar, parity)) { dead = true; atomicExch(flag, code); }
   }
+  __device__ __forceinline__ void wait_cluster(uint32_t bar, uint32_t parity, int code) {
+    if (dead) return;
+    if (!mbar_wait_cluster(bar, parity)) { dead = true; atomicExch(flag, code); }
+  }
+};
+
+// Head dimension 256 runs as pairs of CTAs (a cluster of two): each holds one 128-wide half of the head, so its
+// tiles are those of a 128-wide head, computes the score products over its half and adds the other CTA's partial
+// sums; from there on both hold the same scores and each forms its half of the outputs. Math thread t of one CTA
+// and math thread t of the other own the same elements. A CTA has one exchange buffer, written by its peer:
+// `full` counts the peer's 256 writers of a block, `free` (on the writer's side) the 256 readers of the block before.
+constexpr int PAIR_XCHG_BYTES = 32 * MATH_WARPS * 32 * 4;   // 32 values per math thread
+struct PairSum {
+  uint32_t buf_peer, full_local, full_peer, free_local, free_peer;
+  const float4* buf_local;
+  __device__ __forceinline__ void init(uint32_t buf_s, const void* buf_ptr, uint32_t full, uint32_t free_, uint32_t peer) {
+    buf_local = reinterpret_cast<const float4*>(buf_ptr);
+    buf_peer = cluster_addr_of(buf_s, peer);
+    full_local = full; free_local = free_;
+    full_peer = cluster_addr_of(full, peer); free_peer = cluster_addr_of(free_, peer);
+  }
+  // a[0..NA) and b[0..NB) += the peer's values of block i (blocks are exchanged in order, i = 0, 1, 2, ...)
+  template <int NA, int NB>
+  __device__ __forceinline__ void add(Waiter& w, int i, int t, float* a, float* b, int code) {
+    static_assert(NA % 4 == 0 && NB % 4 == 0 && NA + NB <= 32, "exchange size");
+    if (i > 0) w.wait_cluster(free_local, (uint32_t)((i - 1) & 1), code);   // the peer has read block i-1
+#pragma unroll
+    for (int j = 0; j < (NA + NB) / 4; j++) {
+      const float* v = j < NA / 4 ? a + 4 * j : b + 4 * (j - NA / 4);
+      st_cluster_f32x4(buf_peer + (uint32_t)(j * (MATH_WARPS * 32) + t) * 16u, v[0], v[1], v[2], v[3]);
+    }
+    mbar_arrive_cluster(full_peer);
+    w.wait_cluster(full_local, (uint32_t)(i & 1), code);
+#pragma unroll
+    for (int j = 0; j < (NA + NB) / 4; j++) {
+      float* v = j < NA / 4 ? a + 4 * j : b + 4 * (j - NA / 4);
+      const float4 x = buf_local[j * (MATH_WARPS * 32) + t];
+      v[0] += x.x; v[1] += x.y; v[2] += x.z; v[3] += x.w;
+    }
+    mbar_arrive_cluster(free_peer);
+  }
 };
 
 // Write NC consecutive f32 values, starting at column c0 (a multiple of 4), as row r of a K-major operand tile:
@@ -127,31 +168,33 @@ __device__ __forceinline__ void store_row_kmajor(uint8_t* tile, int r, int c0, c
 // ---------------------------------------------------------------------------------------------
 constexpr int BKV = 64;
 
-template <int HD>
+template <int HD, int SPLIT>
 struct FwdSmem {
   static constexpr int Q_BYTES = ROWS * HD * 4, K_BYTES = BKV * HD * 4, V_BYTES = BKV * HD * 4, P_BYTES = ROWS * BKV * 4;
   static constexpr int Q_OFF = 0, K_OFF = Q_BYTES, V_OFF = K_OFF + K_BYTES, P_OFF = V_OFF + V_BYTES, X_OFF = P_OFF + P_BYTES;
   static constexpr int X_BYTES = 2 * 2 * ROWS * 4;   // partial row maxima [parity][half][row]
-  static constexpr int BAR_OFF = X_OFF + X_BYTES;
+  static constexpr int XC_OFF = X_OFF + X_BYTES, XC_BYTES = SPLIT == 2 ? PAIR_XCHG_BYTES : 0;   // the peer's partial scores
+  static constexpr int BAR_OFF = XC_OFF + XC_BYTES;
   static constexpr int TOTAL = BAR_OFF + 128 + 1024;
   static constexpr uint32_t TMEM_COLS = (2 * BKV + HD) <= 256 ? 256 : 512;
+  static_assert(TOTAL <= 232448, "shared memory");
 };
 
-template <int HD>
+template <int HD, int SPLIT>   // HD: columns of the head held by one CTA; the head is HD * SPLIT wide
 __global__ void __launch_bounds__(FWD_THREADS, HD <= 64 ? 2 : 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                    const __grid_constant__ CUtensorMap mapV, float* __restrict__ out, float* __restrict__ lse, int rows, int T,
                    int Hq, int Hkv, int window, float scale2, int* __restrict__ flag) {
   extern __shared__ uint8_t smem_raw[];
-  using S = FwdSmem<HD>;
-  constexpr int ATOMS = HD / 32, HH = HD / 2;
+  using S = FwdSmem<HD, SPLIT>;
+  constexpr int ATOMS = HD / 32, HH = HD / 2, HDF = HD * SPLIT;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t q_s = base + S::Q_OFF, k_s = base + S::K_OFF, v_s = base + S::V_OFF, p_s = base + S::P_OFF;
   float* xch = reinterpret_cast<float*>(base_ptr + S::X_OFF);
   const uint32_t bars = base + S::BAR_OFF;
   const uint32_t q_full = bars, k_full = bars + 8, v_full = bars + 16, s_full0 = bars + 24, s_full1 = bars + 32, p_full = bars + 40,
-                 o_full = bars + 48;
+                 o_full = bars + 48, x_full = bars + 72, x_free = bars + 80;
   const uint32_t tmem_slot = bars + 64;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + S::BAR_OFF + 64);
 
@@ -159,7 +202,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
   // Causal work grows with the query position: the heaviest tiles are launched first, and all (head, sequence)
   // pairs of one tile index are adjacent, so the tail of the grid is made of the lightest tiles.
   const int q0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * ROWS;
-  const int h = blockIdx.x % Hq, seq = blockIdx.x / Hq;
+  const int crank = SPLIT == 2 ? (int)(blockIdx.x & 1) : 0, bx = blockIdx.x / SPLIT;   // which half of the head; tile
+  const int h = bx % Hq, seq = bx / Hq;
   const int kvh = h / (Hq / Hkv);
   const int row0 = seq * T;
   const int q_last = min(q0 + ROWS - 1, T - 1);
@@ -170,25 +214,28 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1); mbar_init(k_full, 1); mbar_init(v_full, 1); mbar_init(s_full0, 1); mbar_init(s_full1, 1);
     mbar_init(p_full, MATH_WARPS * 32); mbar_init(o_full, 1);
+    mbar_init(x_full, MATH_WARPS * 32); mbar_init(x_free, MATH_WARPS * 32);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == MMA_WARP) tmem_alloc(tmem_slot, S::TMEM_COLS);
   tc_fence_before();
-  __syncthreads();
+  if (SPLIT == 2) cluster_sync_all(); else __syncthreads();   // the peer's barriers exist before anything arrives there
   tc_fence_after();
   const uint32_t tmem = *tmem_slot_ptr;
   const uint32_t tm_o = tmem + 2 * BKV;
   Waiter w{false, flag};
+  PairSum xs;
+  if (SPLIT == 2) xs.init(base + S::XC_OFF, base_ptr + S::XC_OFF, x_full, x_free, (uint32_t)(crank ^ 1));
   auto s_bar = [&](int it) { return (it & 1) ? s_full1 : s_full0; };
   auto s_par = [&](int it) { return (uint32_t)((it >> 1) & 1); };
 
   auto load_k = [&](int i) {
     mbar_expect_tx(k_full, S::K_BYTES);
-    tma_load_3d(k_s, &mapK, 0, row0 + (kb_lo + i) * BKV, kvh * ATOMS, k_full);
+    tma_load_3d(k_s, &mapK, 0, row0 + (kb_lo + i) * BKV, (kvh * SPLIT + crank) * ATOMS, k_full);
   };
   auto load_v = [&](int i) {
     mbar_expect_tx(v_full, S::V_BYTES);
-    tma_load_3d(v_s, &mapV, 0, row0 + (kb_lo + i) * BKV, kvh * ATOMS, v_full);
+    tma_load_3d(v_s, &mapV, 0, row0 + (kb_lo + i) * BKV, (kvh * SPLIT + crank) * ATOMS, v_full);
   };
   if (warp == MMA_WARP) {
     if (lane == 0) {
@@ -206,7 +253,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         umma_commit(s_bar(i));
       };
       mbar_expect_tx(q_full, S::Q_BYTES);
-      tma_load_3d(q_s, &mapQ, 0, row0 + q0, h * ATOMS, q_full);
+      tma_load_3d(q_s, &mapQ, 0, row0 + q0, (h * SPLIT + crank) * ATOMS, q_full);
       load_k(0);
       load_v(0);
       w.wait(q_full, 0, 11);
@@ -254,6 +301,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       float s[32];
       const uint32_t tm_s = tmem + (i & 1) * BKV + half * 32 + lane_base;
       tmem_ld<32>(tm_s, s);
+      if constexpr (SPLIT == 2) xs.add<32, 0>(w, i, (int)threadIdx.x, s, s, 18);   // + the other half of the head
       // a block strictly below the diagonal and inside the window needs no per-element test
       const bool interior = (k0 + 31 <= q0) && (q0 + ROWS - 1 < T) && (window == 0 || k0 >= q0 + ROWS - window);
       float mx = NEG;
@@ -304,14 +352,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     l += xp[(half ^ 1) * ROWS + r];
     if (!w.dead && valid) {
       const float inv = TRUNC_COMP / l;   // the P.V product carries the truncation bias of both operands
-      float* dst = out + (size_t)(row0 + tq) * Hq * HD + (size_t)h * HD + half * HH;
+      float* dst = out + (size_t)(row0 + tq) * Hq * HDF + (size_t)h * HDF + crank * HD + half * HH;
 #pragma unroll
       for (int d = 0; d < HH; d += 4) *reinterpret_cast<float4*>(dst + d) = make_float4(o[d] * inv, o[d + 1] * inv, o[d + 2] * inv, o[d + 3] * inv);
-      if (half == 0) lse[(size_t)h * rows + row0 + tq] = m + log2f(l);
+      if (half == 0 && crank == 0) lse[(size_t)h * rows + row0 + tq] = m + log2f(l);
     }
   }
   tc_fence_before();
-  __syncthreads();
+  if (SPLIT == 2) cluster_sync_all(); else __syncthreads();   // neither CTA of a pair leaves while the other may still write to it
   if (warp == MMA_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem, S::TMEM_COLS);
@@ -329,15 +377,19 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
 template <int HD>
 __global__ void attn_bwd_d_tc_kernel(long nitems, float scale, const float* __restrict__ go, const float* __restrict__ o,
                                      float* __restrict__ D, int rows, int Hq) {
-  constexpr int L = HD / 4;                   // lanes per item: 8, 16 or 32
+  constexpr int L = HD / 4 < 32 ? HD / 4 : 32;   // lanes per item: 8, 16 or 32
+  constexpr int PER = HD / 4 / L;                // 16-byte loads per lane and tensor (2 at HD 256)
   const long gid = (long)blockIdx.x * blockDim.x + threadIdx.x;
   const long item = gid / L;                  // row * Hq + h
   const int sub = (int)(gid % L);
   float acc = 0.f;
   if (item < nitems) {
-    const float4 g = __ldg(reinterpret_cast<const float4*>(go + item * HD) + sub);
-    const float4 v = __ldg(reinterpret_cast<const float4*>(o + item * HD) + sub);
-    acc = g.x * v.x + g.y * v.y + g.z * v.z + g.w * v.w;
+#pragma unroll
+    for (int e = 0; e < PER; e++) {
+      const float4 g = __ldg(reinterpret_cast<const float4*>(go + item * HD) + sub + e * L);
+      const float4 v = __ldg(reinterpret_cast<const float4*>(o + item * HD) + sub + e * L);
+      acc += g.x * v.x + g.y * v.y + g.z * v.z + g.w * v.w;
+    }
   }
 #pragma unroll
   for (int off = L / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
@@ -353,18 +405,20 @@ __global__ void attn_bwd_d_tc_kernel(long nitems, float scale, const float* __re
 // dV += P^T.dO and dK += dS^T.Q with P^T, dS^T written to shared memory as K-major A operands (K = queries) and
 // dO, Q read a second time as [queries, hd] operands (hd contiguous). KBUF = 2 keeps two blocks of the K-major
 // Q / dO copies in flight (their fetch is the longest latency of the loop) where shared memory has the room.
-template <int HD, int NQ, int KBUF, int MBUF>
+template <int HD, int NQ, int KBUF, int MBUF, int SPLIT>
 struct DkvSmem {
   static constexpr int KV_BYTES = ROWS * HD * 4, QT_BYTES = NQ * HD * 4;
   static constexpr int K_OFF = 0, V_OFF = KV_BYTES, QK_OFF = 2 * KV_BYTES, GK_OFF = QK_OFF + KBUF * QT_BYTES,
-                       QM_OFF = GK_OFF + KBUF * QT_BYTES, GM_OFF = QM_OFF + MBUF * QT_BYTES, BAR_OFF = GM_OFF + MBUF * QT_BYTES;
+                       QM_OFF = GK_OFF + KBUF * QT_BYTES, GM_OFF = QM_OFF + MBUF * QT_BYTES, XC_OFF = GM_OFF + MBUF * QT_BYTES,
+                       BAR_OFF = XC_OFF + (SPLIT == 2 ? PAIR_XCHG_BYTES : 0);
   static constexpr int TOTAL = BAR_OFF + 128 + 1024;
   static constexpr int COLS = 4 * NQ + 2 * HD;
+  static_assert(SPLIT == 1 || NQ <= 32, "a pair exchanges at most 32 values per thread");
   static constexpr uint32_t TMEM_COLS = COLS <= 128 ? 128 : (COLS <= 256 ? 256 : 512);
   static_assert(TOTAL <= 232448, "shared memory");
 };
 
-template <int HD, int NQ, int KBUF, int MBUF>
+template <int HD, int NQ, int KBUF, int MBUF, int SPLIT>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
                        const __grid_constant__ CUtensorMap mapQk, const __grid_constant__ CUtensorMap mapQm,
@@ -372,8 +426,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
                        const float* __restrict__ lse, const float* __restrict__ Ds, float* gk, int accum_k, float* gv, int accum_v,
                        int rows, int T, int Hq, int Hkv, int window, float scale2, float dp_scale, int* __restrict__ flag) {
   extern __shared__ uint8_t smem_raw[];
-  using S = DkvSmem<HD, NQ, KBUF, MBUF>;
-  constexpr int ATOMS = HD / 32, NH = NQ / 2, HH = HD / 2;
+  using S = DkvSmem<HD, NQ, KBUF, MBUF, SPLIT>;
+  constexpr int ATOMS = HD / 32, NH = NQ / 2, HH = HD / 2, HDF = HD * SPLIT;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t k_s = base + S::K_OFF, v_s = base + S::V_OFF, qk_s = base + S::QK_OFF, gk_s = base + S::GK_OFF,
@@ -381,13 +435,14 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
   const uint32_t bars = base + S::BAR_OFF;
   const uint32_t kv_full = bars, qk_full0 = bars + 8, qk_full1 = bars + 16, qm_full0 = bars + 24, s_full0 = bars + 32,
                  s_full1 = bars + 40, p_full0 = bars + 48, acc_done0 = bars + 56, all_done = bars + 72, qm_full1 = bars + 80,
-                 p_full1 = bars + 88, acc_done1 = bars + 96;
+                 p_full1 = bars + 88, acc_done1 = bars + 96, x_full = bars + 104, x_free = bars + 112;
   const uint32_t tmem_slot = bars + 64;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + S::BAR_OFF + 64);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int k0 = blockIdx.y * ROWS;           // early keys are read by the most queries: heaviest first
-  const int kvh = blockIdx.x % Hkv, seq = blockIdx.x / Hkv;
+  const int crank = SPLIT == 2 ? (int)(blockIdx.x & 1) : 0, bx = blockIdx.x / SPLIT;   // which half of the head; tile
+  const int kvh = bx % Hkv, seq = bx / Hkv;
   const int group = Hq / Hkv;
   const int row0 = seq * T;
   const int k_last = min(k0 + ROWS - 1, T - 1);
@@ -401,16 +456,19 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
     mbar_init(s_full0, 1);
     mbar_init(s_full1, 1); mbar_init(p_full0, MATH_WARPS * 32); mbar_init(p_full1, MATH_WARPS * 32); mbar_init(acc_done0, 1);
     mbar_init(acc_done1, 1); mbar_init(all_done, 1);
+    mbar_init(x_full, MATH_WARPS * 32); mbar_init(x_free, MATH_WARPS * 32);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == MMA_WARP) tmem_alloc(tmem_slot, S::TMEM_COLS);
   tc_fence_before();
-  __syncthreads();
+  if (SPLIT == 2) cluster_sync_all(); else __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot_ptr;
   // columns: [S^T | dP^T] x 2 buffers, then dV, dK
   const uint32_t tm_dv = tmem + 4 * NQ, tm_dk = tmem + 4 * NQ + HD;
   Waiter w{false, flag};
+  PairSum xs;
+  if (SPLIT == 2) xs.init(base + S::XC_OFF, base_ptr + S::XC_OFF, x_full, x_free, (uint32_t)(crank ^ 1));
   // barrier and parity of the K-major copies of block `it`, and of its score products
   auto qk_bar = [&](int it) { return (KBUF == 2 && (it & 1)) ? qk_full1 : qk_full0; };
   auto qk_par = [&](int it) { return (uint32_t)((KBUF == 2 ? it >> 1 : it) & 1); };
@@ -440,21 +498,21 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
         const int qr = row0 + (qb_lo + k_qb) * NQ;
         const uint32_t bar = qk_bar(it), off = (KBUF == 2 && (it & 1)) ? S::QT_BYTES : 0;
         mbar_expect_tx(bar, 2 * S::QT_BYTES);
-        tma_load_3d(qk_s + off, &mapQk, 0, qr, k_h * ATOMS, bar);
-        tma_load_3d(gk_s + off, &mapGk, 0, qr, k_h * ATOMS, bar);
+        tma_load_3d(qk_s + off, &mapQk, 0, qr, (k_h * SPLIT + crank) * ATOMS, bar);
+        tma_load_3d(gk_s + off, &mapGk, 0, qr, (k_h * SPLIT + crank) * ATOMS, bar);
         if (++k_qb == nqb) { k_qb = 0; k_h++; }
       };
       auto load_m = [&](int it) {   // [queries, hd] copies for the gradient products, block `it` (same order)
         const int qr = row0 + (qb_lo + m_qb) * NQ;
         const uint32_t bar = qm_bar(it), off = (MBUF == 2 && (it & 1)) ? S::QT_BYTES : 0;
         mbar_expect_tx(bar, 2 * S::QT_BYTES);
-        tma_load_3d(qm_s + off, &mapQm, 0, qr, m_h * ATOMS, bar);
-        tma_load_3d(gm_s + off, &mapGm, 0, qr, m_h * ATOMS, bar);
+        tma_load_3d(qm_s + off, &mapQm, 0, qr, (m_h * SPLIT + crank) * ATOMS, bar);
+        tma_load_3d(gm_s + off, &mapGm, 0, qr, (m_h * SPLIT + crank) * ATOMS, bar);
         if (++m_qb == nqb) { m_qb = 0; m_h++; }
       };
       mbar_expect_tx(kv_full, 2 * S::KV_BYTES);
-      tma_load_3d(k_s, &mapK, 0, row0 + k0, kvh * ATOMS, kv_full);
-      tma_load_3d(v_s, &mapV, 0, row0 + k0, kvh * ATOMS, kv_full);
+      tma_load_3d(k_s, &mapK, 0, row0 + k0, (kvh * SPLIT + crank) * ATOMS, kv_full);
+      tma_load_3d(v_s, &mapV, 0, row0 + k0, (kvh * SPLIT + crank) * ATOMS, kv_full);
       load_k(0);
       load_m(0);
       if (KBUF == 2 && iters > 1) load_k(1);
@@ -567,6 +625,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
       tmem_ld_issue<NH>(tm_s, s);
       tmem_ld_issue<NH>(tm_s + NQ, dp);
       tmem_wait_ld();
+      if constexpr (SPLIT == 2) xs.add<NH, NH>(w, i, (int)threadIdx.x, s, dp, 29);   // + the other half of the head
       TRACEM(10)
       if (interior) {
 #pragma unroll
@@ -611,7 +670,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
     tc_fence_after();
     {   // warp-uniform: the TMEM loads are warp-wide instructions, only the stores are per-row
       const bool st = !w.dead && kg < T;
-      const size_t off = (size_t)(row0 + (kg < T ? kg : 0)) * Hkv * HD + (size_t)kvh * HD + half * HH;
+      const size_t off = (size_t)(row0 + (kg < T ? kg : 0)) * Hkv * HDF + (size_t)kvh * HDF + crank * HD + half * HH;
       float t[HH];
       if (gv) {
         tmem_ld<HH>(tm_dv + half * HH + lane_base, t);
@@ -641,7 +700,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
   }
 #undef TRACE
   tc_fence_before();
-  __syncthreads();
+  if (SPLIT == 2) cluster_sync_all(); else __syncthreads();   // neither CTA of a pair leaves while the other may still write to it
   if (warp == MMA_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem, S::TMEM_COLS);
@@ -653,11 +712,12 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
 // dQ += dS.K with K read a second time as a [keys, hd] operand. KBUF as in the dK/dV kernel.
 // SB: one [S | dP] pair in tensor memory instead of two and single-buffered copies, small enough for two CTAs per SM:
 // a CTA then runs its products and its element math strictly one after the other, and the second CTA fills the gaps.
-template <int HD, int NK, int KBUF, bool SB>
+template <int HD, int NK, int KBUF, bool SB, int SPLIT>
 struct DqSmem {
   static constexpr int Q_BYTES = ROWS * HD * 4, KT_BYTES = NK * HD * 4;
   static constexpr int Q_OFF = 0, G_OFF = Q_BYTES, KK_OFF = 2 * Q_BYTES, VK_OFF = KK_OFF + KBUF * KT_BYTES,
-                       KM_OFF = VK_OFF + KBUF * KT_BYTES, BAR_OFF = KM_OFF + KT_BYTES;
+                       KM_OFF = VK_OFF + KBUF * KT_BYTES, XC_OFF = KM_OFF + KT_BYTES, BAR_OFF = XC_OFF + (SPLIT == 2 ? PAIR_XCHG_BYTES : 0);
+  static_assert(SPLIT == 1 || NK <= 32, "a pair exchanges at most 32 values per thread");
   static constexpr int SLACK = SB ? 896 : 1024;   // for rounding the base up to 1024 B (two CTAs must fit 228 KB together)
   static constexpr int TOTAL = BAR_OFF + 128 + SLACK;
   static constexpr int COLS = (SB ? 2 : 4) * NK + HD;
@@ -665,7 +725,7 @@ struct DqSmem {
   static_assert(TOTAL <= 232448, "shared memory");
 };
 
-template <int HD, int NK, int KBUF, bool SB>
+template <int HD, int NK, int KBUF, bool SB, int SPLIT>
 __global__ void __launch_bounds__(THREADS, SB ? 2 : 1)
 attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapG,
                       const __grid_constant__ CUtensorMap mapKk, const __grid_constant__ CUtensorMap mapVk,
@@ -673,8 +733,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                       float* gq, int accum_q, int rows, int T, int Hq, int Hkv, int window, float scale2, float dp_scale,
                       int* __restrict__ flag) {
   extern __shared__ uint8_t smem_raw[];
-  using S = DqSmem<HD, NK, KBUF, SB>;
-  constexpr int ATOMS = HD / 32, NH = NK / 2, HH = HD / 2;
+  using S = DqSmem<HD, NK, KBUF, SB, SPLIT>;
+  constexpr int ATOMS = HD / 32, NH = NK / 2, HH = HD / 2, HDF = HD * SPLIT;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
   if (base - smem_u32(smem_raw) > (uint32_t)S::SLACK) {   // cannot happen while dynamic shared memory starts 128-byte aligned
@@ -684,13 +744,15 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   const uint32_t q_s = base + S::Q_OFF, g_s = base + S::G_OFF, kk_s = base + S::KK_OFF, vk_s = base + S::VK_OFF, km_s = base + S::KM_OFF;
   const uint32_t bars = base + S::BAR_OFF;
   const uint32_t q_full = bars, kk_full0 = bars + 8, kk_full1 = bars + 16, km_full = bars + 24, s_full0 = bars + 32,
-                 s_full1 = bars + 40, p_full0 = bars + 48, acc_done = bars + 56, all_done = bars + 72, p_full1 = bars + 80;
+                 s_full1 = bars + 40, p_full0 = bars + 48, acc_done = bars + 56, all_done = bars + 72, p_full1 = bars + 80,
+                 x_full = bars + 88, x_free = bars + 96;
   const uint32_t tmem_slot = bars + 64;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + S::BAR_OFF + 64);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * ROWS;   // late queries read the most keys: heaviest first
-  const int h = blockIdx.x % Hq, seq = blockIdx.x / Hq;
+  const int crank = SPLIT == 2 ? (int)(blockIdx.x & 1) : 0, bx = blockIdx.x / SPLIT;   // which half of the head; tile
+  const int h = bx % Hq, seq = bx / Hq;
   const int kvh = h / (Hq / Hkv);
   const int row0 = seq * T;
   const int q_last = min(q0 + ROWS - 1, T - 1);
@@ -702,14 +764,17 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     mbar_init(q_full, 1); mbar_init(kk_full0, 1); mbar_init(kk_full1, 1); mbar_init(km_full, 1); mbar_init(s_full0, 1);
     mbar_init(s_full1, 1); mbar_init(p_full0, MATH_WARPS * 32); mbar_init(p_full1, MATH_WARPS * 32); mbar_init(acc_done, 1);
     mbar_init(all_done, 1);
+    mbar_init(x_full, MATH_WARPS * 32); mbar_init(x_free, MATH_WARPS * 32);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == MMA_WARP) tmem_alloc(tmem_slot, S::TMEM_COLS);
   tc_fence_before();
-  __syncthreads();
+  if (SPLIT == 2) cluster_sync_all(); else __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot_ptr;
   const uint32_t tm_dq = tmem + (SB ? 2 : 4) * NK;
+  PairSum xs;
+  if (SPLIT == 2) xs.init(base + S::XC_OFF, base_ptr + S::XC_OFF, x_full, x_free, (uint32_t)(crank ^ 1));
   auto sbuf = [&](int it) { return SB ? 0u : (uint32_t)((it & 1) * 2 * NK); };   // TMEM columns of block it's [S | dP]
   Waiter w{false, flag};
   // two alternating p_full barriers, as in the dK/dV kernel: the math warps may finish block i+1 before the issuing
@@ -726,17 +791,17 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         const int kr = row0 + (kb_lo + it) * NK;
         const uint32_t bar = kk_bar(it), off = (KBUF == 2 && (it & 1)) ? S::KT_BYTES : 0;
         mbar_expect_tx(bar, 2 * S::KT_BYTES);
-        tma_load_3d(kk_s + off, &mapKk, 0, kr, kvh * ATOMS, bar);
-        tma_load_3d(vk_s + off, &mapVk, 0, kr, kvh * ATOMS, bar);
+        tma_load_3d(kk_s + off, &mapKk, 0, kr, (kvh * SPLIT + crank) * ATOMS, bar);
+        tma_load_3d(vk_s + off, &mapVk, 0, kr, (kvh * SPLIT + crank) * ATOMS, bar);
       };
       auto load_m = [&](int it) {   // [keys, hd] copy of K for the gradient product
         const int kr = row0 + (kb_lo + it) * NK;
         mbar_expect_tx(km_full, S::KT_BYTES);
-        tma_load_3d(km_s, &mapKm, 0, kr, kvh * ATOMS, km_full);
+        tma_load_3d(km_s, &mapKm, 0, kr, (kvh * SPLIT + crank) * ATOMS, km_full);
       };
       mbar_expect_tx(q_full, 2 * S::Q_BYTES);
-      tma_load_3d(q_s, &mapQ, 0, row0 + q0, h * ATOMS, q_full);
-      tma_load_3d(g_s, &mapG, 0, row0 + q0, h * ATOMS, q_full);
+      tma_load_3d(q_s, &mapQ, 0, row0 + q0, (h * SPLIT + crank) * ATOMS, q_full);
+      tma_load_3d(g_s, &mapG, 0, row0 + q0, (h * SPLIT + crank) * ATOMS, q_full);
       load_k(0);
       load_m(0);
       if (KBUF == 2 && iters > 1) load_k(1);
@@ -818,6 +883,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       tmem_ld_issue<NH>(tm_s, s);
       tmem_ld_issue<NH>(tm_s + NK, dp);
       tmem_wait_ld();
+      if constexpr (SPLIT == 2) xs.add<NH, NH>(w, i, (int)threadIdx.x, s, dp, 37);   // + the other half of the head
       const bool interior = (kpos0 + NH - 1 <= q0) && (q0 + ROWS - 1 < T) && (window == 0 || kpos0 >= q0 + ROWS - window);
       if (interior) {
 #pragma unroll
@@ -849,7 +915,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       float t[HH];
       tmem_ld<HH>(tm_dq + half * HH + lane_base, t);
       if (!w.dead && valid) {
-        float* dst = gq + (size_t)(row0 + tq) * Hq * HD + (size_t)h * HD + half * HH;
+        float* dst = gq + (size_t)(row0 + tq) * Hq * HDF + (size_t)h * HDF + crank * HD + half * HH;
 #pragma unroll
         for (int d = 0; d < HH; d += 4) {
           float4 o = accum_q ? *reinterpret_cast<float4*>(dst + d) : make_float4(0, 0, 0, 0);
@@ -860,7 +926,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     }
   }
   tc_fence_before();
-  __syncthreads();
+  if (SPLIT == 2) cluster_sync_all(); else __syncthreads();   // neither CTA of a pair leaves while the other may still write to it
   if (warp == MMA_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem, S::TMEM_COLS);
@@ -879,40 +945,61 @@ gt_status set_smem(gt_ctx* ctx, K kern, int bytes, bool* done) {
   return GT_OK;
 }
 
-template <int HD>
+// <<<grid, threads, smem, stream>>> with the grid's x axis grouped into clusters of `split` CTAs
+template <typename... KA, typename... A>
+cudaError_t launch_split(void (*kern)(KA...), dim3 grid, int threads, int smem, cudaStream_t stream, int split, A... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(threads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = split;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = split > 1 ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KA>(args)...);
+}
+
+template <int HD, int SPLIT>
 gt_status launch_fwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, const float* q, const float* k, const float* v,
                      float* out, float* lse, int* flag) {
   CUtensorMap mq, mk, mv;
-  const uint64_t qw = (uint64_t)Hq * HD, kw = (uint64_t)Hkv * HD;
+  const uint64_t qw = (uint64_t)Hq * HD * SPLIT, kw = (uint64_t)Hkv * HD * SPLIT;
   if (!make_map_atoms(&mq, q, qw, rows, qw, ROWS, HD / 32, true) || !make_map_atoms(&mk, k, kw, rows, kw, BKV, HD / 32, true) ||
       !make_map_atoms(&mv, v, kw, rows, kw, BKV, HD / 32, false))
     return gt_fail(ctx, GT_ERR_CUDA, "attention: tensor map encoding failed");
-  auto kern = attn_fwd_tc_kernel<HD>;
+  auto kern = attn_fwd_tc_kernel<HD, SPLIT>;
+  using SM = FwdSmem<HD, SPLIT>;
   static bool done[64] = {};
-  gt_status st = set_smem(ctx, kern, FwdSmem<HD>::TOTAL, done);
+  gt_status st = set_smem(ctx, kern, SM::TOTAL, done);
   if (st) return st;
   // the S product's truncation bias is folded into the score scale
-  const float scale2 = 1.4426950408889634f / sqrtf((float)HD) * TRUNC_COMP;
-  dim3 grid(Hq * (rows / T), gt_cdiv(T, ROWS), 1);
-  kern<<<grid, FWD_THREADS, FwdSmem<HD>::TOTAL, ctx->stream>>>(mq, mk, mv, out, lse, rows, T, Hq, Hkv, window, scale2, flag);
+  const float scale2 = 1.4426950408889634f / sqrtf((float)(HD * SPLIT)) * TRUNC_COMP;
+  dim3 grid(Hq * (rows / T) * SPLIT, gt_cdiv(T, ROWS), 1);
+  if (SPLIT == 1) kern<<<grid, FWD_THREADS, SM::TOTAL, ctx->stream>>>(mq, mk, mv, out, lse, rows, T, Hq, Hkv, window, scale2, flag);
+  else GT_CUDA(ctx, launch_split(kern, grid, FWD_THREADS, SM::TOTAL, ctx->stream, SPLIT, mq, mk, mv, out, lse, rows, T, Hq, Hkv, window, scale2, flag));
   GT_LAUNCHED(ctx, "attn_fwd_tc_kernel");
   return GT_OK;
 }
 
-template <int HD, int NQ, int NK, int DKV_KBUF, int DKV_MBUF, int DQ_KBUF, bool DQ_SB>
+template <int HD, int NQ, int NK, int DKV_KBUF, int DKV_MBUF, int DQ_KBUF, bool DQ_SB, int SPLIT>
 gt_status launch_bwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, const float* q, const float* k, const float* v,
                      const float* out, const float* lse, const float* go, float* gq, int accum_q, float* gk, int accum_k, float* gv,
                      int accum_v, int* flag) {
   float* D = nullptr;
   gt_status st = gt_scratch(ctx, sizeof(float) * (size_t)rows * Hq, &D);
   if (st) return st;
-  const float scale = 1.f / sqrtf((float)HD);
+  constexpr int HDF = HD * SPLIT;
+  const float scale = 1.f / sqrtf((float)HDF);
   const long nitems = (long)rows * Hq;
-  attn_bwd_d_tc_kernel<HD><<<(unsigned)gt_cdiv(nitems * (HD / 4), 256l), 256, 0, ctx->stream>>>(nitems, scale, go, out, D, rows, Hq);
+  attn_bwd_d_tc_kernel<HDF><<<(unsigned)gt_cdiv(nitems * (HDF / 4 < 32 ? HDF / 4 : 32), 256l), 256, 0, ctx->stream>>>(nitems, scale, go, out, D, rows, Hq);
   GT_LAUNCHED(ctx, "attn_bwd_d_tc_kernel");
   const float scale2 = 1.4426950408889634f * scale * TRUNC_COMP;
   const float dp_scale = scale * TRUNC_COMP;
-  const uint64_t qw = (uint64_t)Hq * HD, kw = (uint64_t)Hkv * HD;
+  const uint64_t qw = (uint64_t)Hq * HDF, kw = (uint64_t)Hkv * HDF;
   const int nseq = rows / T;
   if (gk || gv) {
     CUtensorMap mK, mV, mQk, mQm, mGk, mGm;
@@ -921,13 +1008,18 @@ gt_status launch_bwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, 
         !make_map_atoms(&mGk, go, qw, rows, qw, NQ, HD / 32, true) || !make_map_atoms(&mGm, go, qw, rows, qw, NQ, HD / 32, false))
       return gt_fail(ctx, GT_ERR_CUDA, "attention backward: tensor map encoding failed");
     constexpr int KBUF = DKV_KBUF, MBUF = DKV_MBUF;
-    auto kern = attn_bwd_dkv_tc_kernel<HD, NQ, KBUF, MBUF>;
+    auto kern = attn_bwd_dkv_tc_kernel<HD, NQ, KBUF, MBUF, SPLIT>;
+    using SM = DkvSmem<HD, NQ, KBUF, MBUF, SPLIT>;
     static bool done[64] = {};
-    st = set_smem(ctx, kern, DkvSmem<HD, NQ, KBUF, MBUF>::TOTAL, done);
+    st = set_smem(ctx, kern, SM::TOTAL, done);
     if (st) return st;
-    dim3 grid(Hkv * nseq, gt_cdiv(T, ROWS), 1);
-    kern<<<grid, THREADS, DkvSmem<HD, NQ, KBUF, MBUF>::TOTAL, ctx->stream>>>(mK, mV, mQk, mQm, mGk, mGm, lse, D, gk, accum_k, gv, accum_v, rows, T, Hq,
-                                                                Hkv, window, scale2, dp_scale, flag);
+    dim3 grid(Hkv * nseq * SPLIT, gt_cdiv(T, ROWS), 1);
+    if (SPLIT == 1)
+      kern<<<grid, THREADS, SM::TOTAL, ctx->stream>>>(mK, mV, mQk, mQm, mGk, mGm, lse, D, gk, accum_k, gv, accum_v, rows, T, Hq, Hkv, window, scale2,
+                                                      dp_scale, flag);
+    else
+      GT_CUDA(ctx, launch_split(kern, grid, THREADS, SM::TOTAL, ctx->stream, SPLIT, mK, mV, mQk, mQm, mGk, mGm, lse, D, gk, accum_k, gv, accum_v,
+                                rows, T, Hq, Hkv, window, scale2, dp_scale, flag));
     GT_LAUNCHED(ctx, "attn_bwd_dkv_tc_kernel");
   }
   if (gq) {
@@ -936,19 +1028,23 @@ gt_status launch_bwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, 
         !make_map_atoms(&mKk, k, kw, rows, kw, NK, HD / 32, true) || !make_map_atoms(&mVk, v, kw, rows, kw, NK, HD / 32, true) ||
         !make_map_atoms(&mKm, k, kw, rows, kw, NK, HD / 32, false))
       return gt_fail(ctx, GT_ERR_CUDA, "attention backward: tensor map encoding failed");
-    auto kern = attn_bwd_dq_tc_kernel<HD, NK, DQ_KBUF, DQ_SB>;
+    auto kern = attn_bwd_dq_tc_kernel<HD, NK, DQ_KBUF, DQ_SB, SPLIT>;
+    using SM = DqSmem<HD, NK, DQ_KBUF, DQ_SB, SPLIT>;
     static bool done[64] = {};
-    st = set_smem(ctx, kern, DqSmem<HD, NK, DQ_KBUF, DQ_SB>::TOTAL, done);
+    st = set_smem(ctx, kern, SM::TOTAL, done);
     if (st) return st;
-    dim3 grid(Hq * nseq, gt_cdiv(T, ROWS), 1);
-    kern<<<grid, THREADS, DqSmem<HD, NK, DQ_KBUF, DQ_SB>::TOTAL, ctx->stream>>>(mQ, mG, mKk, mVk, mKm, lse, D, gq, accum_q, rows, T, Hq, Hkv, window, scale2,
-                                                               dp_scale, flag);
+    dim3 grid(Hq * nseq * SPLIT, gt_cdiv(T, ROWS), 1);
+    if (SPLIT == 1)
+      kern<<<grid, THREADS, SM::TOTAL, ctx->stream>>>(mQ, mG, mKk, mVk, mKm, lse, D, gq, accum_q, rows, T, Hq, Hkv, window, scale2, dp_scale, flag);
+    else
+      GT_CUDA(ctx, launch_split(kern, grid, THREADS, SM::TOTAL, ctx->stream, SPLIT, mQ, mG, mKk, mVk, mKm, lse, D, gq, accum_q, rows, T, Hq, Hkv,
+                                window, scale2, dp_scale, flag));
     GT_LAUNCHED(ctx, "attn_bwd_dq_tc_kernel");
   }
   return GT_OK;
 }
 
-bool tc_shape_ok(int T, int hd) { return (hd == 32 || hd == 64 || hd == 128) && T >= 64; }
+bool tc_shape_ok(int T, int hd) { return (hd == 32 || hd == 64 || hd == 128 || hd == 256) && T >= 64; }
 
 }  // namespace
 
@@ -960,9 +1056,10 @@ gt_status gt_attention_fwd_tc(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int
   int* flag = device_flag(ctx);
   if (!flag) return GT_OK;
   gt_status s;
-  if (hd == 32) s = launch_fwd<32>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, flag);
-  else if (hd == 64) s = launch_fwd<64>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, flag);
-  else s = launch_fwd<128>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, flag);
+  if (hd == 32) s = launch_fwd<32, 1>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, flag);
+  else if (hd == 64) s = launch_fwd<64, 1>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, flag);
+  else if (hd == 128) s = launch_fwd<128, 1>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, flag);
+  else s = launch_fwd<128, 2>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, flag);   // 256: pairs of CTAs, half a head each
   if (s) return s;
   *handled = true;
   return GT_OK;
@@ -978,9 +1075,10 @@ gt_status gt_attention_bwd_tc(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int
   int* flag = device_flag(ctx);
   if (!flag) return GT_OK;
   gt_status s;
-  if (hd == 32) s = launch_bwd<32, 64, 64, 2, 2, 1, true>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
-  else if (hd == 64) s = launch_bwd<64, 64, 64, 2, 2, 1, true>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
-  else s = launch_bwd<128, 32, 32, 2, 1, 2, false>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
+  if (hd == 32) s = launch_bwd<32, 64, 64, 2, 2, 1, true, 1>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
+  else if (hd == 64) s = launch_bwd<64, 64, 64, 2, 2, 1, true, 1>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
+  else if (hd == 128) s = launch_bwd<128, 32, 32, 2, 1, 2, false, 1>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
+  else s = launch_bwd<128, 32, 32, 1, 1, 1, false, 2>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
   if (s) return s;
   *handled = true;
   return GT_OK;

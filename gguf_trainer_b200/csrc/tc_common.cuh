@@ -184,6 +184,35 @@ __device__ __forceinline__ void mbar_arrive_leader(uint32_t bar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar & PAIR_LEADER_MASK) : "memory");
 }
 
+// ---- split pairs: the two CTAs of a cluster each hold half of a contraction (half of the head dimension) and add
+// each other's partial sums, passed through the other CTA's shared memory with plain remote stores.
+__device__ __forceinline__ uint32_t cluster_addr_of(uint32_t cta_addr, uint32_t rank) {   // the same offset in CTA `rank`
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(cta_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f32x4(uint32_t cluster_addr, float x, float y, float z, float w) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
+}
+// one arrival on a barrier of any CTA of the cluster; this thread's earlier reads and writes are ordered before it
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity) {   // own barrier, other CTA's writes acquired
+  uint32_t ok;
+  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity) {   // false on timeout
+  if (mbar_try_cluster(bar, parity)) return true;
+  const uint64_t t0 = gtimer();
+  while (!mbar_try_cluster(bar, parity)) {
+    if (gtimer() - t0 > WAIT_NS) return false;
+  }
+  return true;
+}
+
 // make generic-proxy shared-memory writes visible to the async proxy (TMA, tcgen05.mma operand reads)
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 

@@ -1,5 +1,6 @@
-"""Tensor-core (tcgen05, TF32) attention through the op interface against the CPU oracle: head dims 32/64/128,
-GQA groups, sliding windows, ragged sequence lengths, batched sequences. Bound: relative L2 <= 2e-3."""
+"""Tensor-core (tcgen05, TF32) attention through the op interface against the CPU oracle: head dims 32/64/128 and
+256 (the last as pairs of CTAs holding half a head each), GQA groups, sliding windows, ragged sequence lengths,
+batched sequences. Bound: relative L2 <= 2e-3."""
 import numpy as np
 import pytest
 
@@ -19,7 +20,8 @@ def gpu():
 
 
 CASES = [(64, 2, 1, 64, 0), (130, 4, 2, 64, 0), (193, 4, 1, 32, 0), (300, 9, 3, 64, 0), (257, 4, 2, 128, 0),
-         (200, 4, 2, 64, 33), (300, 2, 1, 32, 100), (513, 2, 2, 64, 512), (640, 3, 1, 128, 70)]
+         (200, 4, 2, 64, 33), (300, 2, 1, 32, 100), (513, 2, 2, 64, 512), (640, 3, 1, 128, 70),
+         (64, 1, 1, 256, 0), (257, 4, 1, 256, 0), (300, 4, 2, 256, 100), (640, 2, 1, 256, 512)]
 
 
 @pytest.mark.parametrize("T,Hq,Hkv,hd,window", CASES)
