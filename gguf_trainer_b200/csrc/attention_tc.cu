@@ -1,5 +1,5 @@
 // Flash-style causal attention on the 5th-generation tensor cores (tcgen05, kind::tf32, f32 accumulators in
-// TMEM), for head dimensions 32, 64 and 128: grouped-query heads, optional sliding window, sequences batched
+// TMEM), for head dimensions 32, 64, 128 and (as pairs of CTAs, see PairSum) 256: grouped-query heads, optional sliding window, sequences batched
 // as [nseq*T] rows. Same formulation as the reference's flash kernels (srcAttnFwd/BwdDq/BwdDkv,
 // src/backend/wgsl.ts:657-918): exp2-domain scores, running max with a -3e38 sentinel, LSE[h,row] = m + log2(l)
 // as the only forward side buffer, backward recomputing p = exp2(s*SCALE2 - LSE) and using D = sum_d dO*O.
