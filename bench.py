@@ -373,23 +373,34 @@ def run_ours(args):
 def run_profile(args):
     """One eager step at the benchmark shape with the backend's per-label profiler open: GPU time per entry point
     (and per product shape), each call bracketed by events and synchronised. Shares, not throughput."""
-    from gguf_trainer_b200.arch import buildModel, smolLM2_135M
+    from gguf_trainer_b200 import autograd as ag
+    from gguf_trainer_b200.arch import buildModel, gemma3_95M, qwen3_0_6B, smolLM2_135M
     from gguf_trainer_b200.backend import requireGPU
     from gguf_trainer_b200.optim import AdamWGpu
     from gguf_trainer_b200.train import CudaStep
-    cfg = smolLM2_135M()
+    cfg = {"smollm2": smolLM2_135M, "gemma3": gemma3_95M, "qwen3-lora": qwen3_0_6B}[args.config]()
     B, T = args.batch, args.seq
     gpu = requireGPU("the profile", precision=args.precision)
     m = buildModel(cfg, 1234)
-    for p in m.params():
-        gpu.keepGradOnDevice(p)
-    opt = AdamWGpu(gpu, m.params(), lr=1e-3, beta1=0.9, beta2=0.95, weightDecay=0.1, clip=1.0)
+    params = m.params()
     ids = zipf_tokens(B * T + 1, cfg.vocabSize, 1.1, 99)
-    step = CudaStep(m, gpu, B, T, capture=False)
+    tg = ids[1:]
+    if args.config == "qwen3-lora":      # as in the timed run: frozen base, adapters, half of the targets masked, recompute
+        from gguf_trainer_b200.lora import applyLora
+        from gguf_trainer_b200.rng import Mulberry32
+        params = applyLora(m, 16, 32.0, Mulberry32(4321)).groups["aux"]
+        ag.setCheckpointing(True)
+        tg = np.where(Mulberry32(5).draws(B * T) < 0.5, tg, -1)
+    if args.recompute:
+        ag.setCheckpointing(True)
+    for p in params:
+        gpu.keepGradOnDevice(p)
+    opt = AdamWGpu(gpu, params, lr=1e-3, beta1=0.9, beta2=0.95, weightDecay=0.1, clip=1.0)
+    step = CudaStep(m, gpu, B, T, lossChunk=args.loss_chunk, capture=False)
     for _ in range(2):
-        step.run(ids[:-1], ids[1:]); opt.recordStep(); gpu.sync([])
+        step.run(ids[:-1], tg); opt.recordStep(); gpu.sync([])
     gpu.startProfile()
-    step.run(ids[:-1], ids[1:]); opt.recordStep()
+    step.run(ids[:-1], tg); opt.recordStep()
     tot = gpu.stopProfile()
     gpu.sync([])
     total = sum(v["ms"] for v in tot.values())

@@ -195,6 +195,11 @@ def linear(x: Tensor, w: Tensor) -> Tensor:
     if _lora:
         ad = _lora.get(id(w))
         if ad is not None:
+            be = _need_backend()
+            if getattr(be, "fuseLora", False):       # optional backend extension: the same sum as one recorded op
+                if x.shape[1] != w.shape[1] or x.shape[1] != ad.a.shape[1] or ad.b.shape[1] != ad.a.shape[0]:
+                    raise ValueError(f"linear dim mismatch: x is {x.shape}, w is {w.shape}, adapter A {ad.a.shape}, B {ad.b.shape}")
+                return be.loraLinear(x, w, ad.a, ad.b, ad.scale)
             return add(_linear_raw(x, w), scale(_linear_raw(_linear_raw(x, ad.a), ad.b), ad.scale))
     return _linear_raw(x, w)
 

@@ -161,6 +161,7 @@ class CudaBackend:
         self._seedBuf = 0
         self._pendingAct = {}   # id(tensor) -> (tensor, op code, input tensor): activations not launched yet
         self.fuseGatedUnits = True
+        self.fuseLora = True               # adapter-carrying projections as one op (loraLinear) instead of four
         self._finalizer = weakref.finalize(self, _destroy_ctx, self.lib, self.ctx)
 
     # ------------------------------------------------------------------ plumbing
@@ -585,6 +586,52 @@ class CudaBackend:
             gx, ax = self._gradTarget(x, ex)
             if gx:
                 self._gemm("NN", ax, T, inDim, outDim, go, ew.data, gx)
+            if w.requiresGrad:
+                gw, aw = self._gradTarget(w, ew)
+                if gw:
+                    self._gemm("TN", aw, outDim, inDim, T, go, ex.data, gw)
+
+        out._backward = _bw
+        return out
+
+    def loraLinear(self, x: Tensor, w: Tensor, a: Tensor, b: Tensor, scale: float) -> Tensor:
+        """The adapter-carrying projection of autograd.ts:311-319, y = x·Wᵀ + scale·((x·Aᵀ)·Bᵀ), as one op. Recorded as
+        `add(linear(x,w), scale(linear(linear(x,a),b), scale))` it costs two more passes over [T, out] in forward
+        (scale, add) and two in backward; here the factor is applied to the [T, r] intermediate instead and the
+        low-rank product accumulates into y inside the matrix product, so nothing but matrix products touches
+        [T, out]. (scale·t)·Bᵀ equals scale·(t·Bᵀ) up to rounding, exactly when scale is a power of two, e.g. the
+        usual alpha/r = 2.) Gradients: dx += g·W + (scale·(g·B))·A, dB += gᵀ·(scale·t), dA += (scale·(g·B))ᵀ·x,
+        and dW += gᵀ·x when the base weight is not frozen."""
+        self._beginForwardOp()
+        T, inDim = x.shape
+        outDim, r = w.shape[0], a.shape[0]
+        ex, ew, ea, eb = self._entryFor(x), self._entryFor(w), self._entryFor(a), self._entryFor(b)
+        out, eo = self._makeOut([T, outDim], [x, w, a, b])
+        small = T * r * 4
+        t, ts, dts, dt = (self._acquireRecycled(small) for _ in range(4))
+        sc = _EW["scale"]
+        self._gemm("NT", 0, T, r, inDim, ex.data, ea.data, t)
+        self._check(self.lib.gt_ew_fwd(self.ctx, sc, T * r, t, 0, float(scale), ts))
+        self._gemm("NT", 0, T, outDim, inDim, ex.data, ew.data, eo.data)
+        self._gemm("NT", 1, T, outDim, r, ts, eb.data, eo.data)
+
+        def _bw():
+            self._ensureBackwardBegun()
+            go = self._gradSource(eo)
+            gx, ax = self._gradTarget(x, ex)
+            self._gemm("NN", 0, T, r, outDim, go, eb.data, dts)
+            self._check(self.lib.gt_ew_fwd(self.ctx, sc, T * r, dts, 0, float(scale), dt))
+            if b.requiresGrad:
+                gb, ab = self._gradTarget(b, eb)
+                if gb:
+                    self._gemm("TN", ab, outDim, r, T, go, ts, gb)
+            if a.requiresGrad:
+                ga, aa = self._gradTarget(a, ea)
+                if ga:
+                    self._gemm("TN", aa, r, inDim, T, dt, ex.data, ga)
+            if gx:
+                self._gemm("NN", ax, T, inDim, outDim, go, ew.data, gx)
+                self._gemm("NN", 1, T, inDim, r, dt, ea.data, gx)
             if w.requiresGrad:
                 gw, aw = self._gradTarget(w, ew)
                 if gw:

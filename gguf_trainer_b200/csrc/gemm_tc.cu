@@ -609,7 +609,7 @@ gt_status gt_gemm_tc_batched(gt_ctx* ctx, int kind, int accum, int M, int N, int
   // Small or oddly aligned products stay on the f32 kernel: TMA needs 16-byte row pitches and bases.
   const bool a_k = kind != GT_GEMM_TN, b_k = kind == GT_GEMM_NT;
   const int a_inner = a_k ? K : M, b_inner = b_k ? K : N;
-  if (M < 64 || N < 16 || K < 16) return GT_OK;
+  if (M < 16 || N < 16 || K < 16) return GT_OK;   // (rows of a tile past M or N are zero-filled by TMA and clipped on store)
   if ((a_inner & 3) || (b_inner & 3)) return GT_OK;
   if ((((uintptr_t)a) | ((uintptr_t)b) | ((uintptr_t)c)) & 15) return GT_OK;
   if (ctx->device < 0 || ctx->device >= 64) return GT_OK;

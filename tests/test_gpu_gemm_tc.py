@@ -24,7 +24,8 @@ def _dev(gpu, a):
 
 
 SHAPES = [(128, 128, 32), (128, 192, 64), (256, 192, 576), (300, 200, 100), (2048, 576, 576), (1000, 1536, 576),
-          (576, 1536, 2048), (192, 576, 4096), (2048, 64, 1536), (130, 16, 576), (4096, 576, 16)]
+          (576, 1536, 2048), (192, 576, 4096), (2048, 64, 1536), (130, 16, 576), (4096, 576, 16),
+          (16, 1024, 4096), (16, 200, 300), (24, 64, 2048), (48, 576, 16)]   # rank-16 adapter gradients: M below one tile
 
 
 @pytest.mark.parametrize("kind", ["NT", "NN", "TN"])

@@ -163,14 +163,19 @@ def test_recompute_is_bit_identical(gpu, oracle, arch):
         compare("recompute grad", b, a, BWD, 1e-6)
 
 
-def test_lora_parity_and_frozen_base(gpu, oracle):
-    """tests/gpu-parity.ts:2037-2138: adapters train, the base stays frozen and gets no gradient."""
+@pytest.mark.parametrize("fused,alpha", [(True, 8.0), (False, 8.0), (True, 5.0)])
+def test_lora_parity_and_frozen_base(gpu, oracle, fused, alpha):
+    """tests/gpu-parity.ts:2037-2138: adapters train, the base stays frozen and gets no gradient. Both recordings of
+    the adapter-carrying projection: as one op (with a scale that is, and one that is not, a power of two) and as
+    the reference's four."""
     from gguf_trainer_b200.lora import applyLora, clearLora
     from gguf_trainer_b200.rng import Mulberry32
     cfg = tiny("qwen3")
     om, m = paired(oracle, cfg, 31)
-    n_ad = om.apply_lora(4, 8.0, 4321)
-    h = applyLora(m, 4, 8.0, Mulberry32(4321))
+    n_ad = om.apply_lora(4, alpha, 4321)
+    h = applyLora(m, 4, alpha, Mulberry32(4321))
+    was = gpu.fuseLora
+    gpu.fuseLora = fused
     try:
         assert len(h.groups["aux"]) == n_ad
         base_n = len(m.params())
@@ -200,6 +205,7 @@ def test_lora_parity_and_frozen_base(gpu, oracle):
         for a, p in zip(before, m.params()):
             assert np.abs(a - p.data).max() <= 1e-5
     finally:
+        gpu.fuseLora = was
         clearLora(m)
 
 
