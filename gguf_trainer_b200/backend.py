@@ -571,6 +571,9 @@ class CudaBackend:
     def _gemm(self, kind: str, accum: int, M: int, N: int, K: int, a: int, b: int, c: int):
         self._check(self.lib.gt_gemm(self.ctx, _KIND[kind], accum, M, N, K, a, b, c))
 
+    def _gemm2(self, kind: str, accum: int, M: int, N: int, K: int, a: int, b: int, K2: int, a2: int, b2: int, c: int):
+        self._check(self.lib.gt_gemm2(self.ctx, _KIND[kind], accum, M, N, K, a, b, K2, a2, b2, c))
+
     def linear(self, x: Tensor, w: Tensor) -> Tensor:
         """webgpu.ts:884-903."""
         self._beginForwardOp()
@@ -598,8 +601,8 @@ class CudaBackend:
         """The adapter-carrying projection of autograd.ts:311-319, y = x·Wᵀ + scale·((x·Aᵀ)·Bᵀ), as one op. Recorded as
         `add(linear(x,w), scale(linear(linear(x,a),b), scale))` it costs two more passes over [T, out] in forward
         (scale, add) and two in backward; here the factor is applied to the [T, r] intermediate instead and the
-        low-rank product accumulates into y inside the matrix product, so nothing but matrix products touches
-        [T, out]. (scale·t)·Bᵀ equals scale·(t·Bᵀ) up to rounding, exactly when scale is a power of two, e.g. the
+        low-rank product is r more columns of the wide product's contraction (`gt_gemm2`), so [T, out] is written
+        once and not read back. (scale·t)·Bᵀ equals scale·(t·Bᵀ) up to rounding, exactly when scale is a power of two, e.g. the
         usual alpha/r = 2.) Gradients: dx += g·W + (scale·(g·B))·A, dB += gᵀ·(scale·t), dA += (scale·(g·B))ᵀ·x,
         and dW += gᵀ·x when the base weight is not frozen."""
         self._beginForwardOp()
@@ -612,8 +615,7 @@ class CudaBackend:
         sc = _EW["scale"]
         self._gemm("NT", 0, T, r, inDim, ex.data, ea.data, t)
         self._check(self.lib.gt_ew_fwd(self.ctx, sc, T * r, t, 0, float(scale), ts))
-        self._gemm("NT", 0, T, outDim, inDim, ex.data, ew.data, eo.data)
-        self._gemm("NT", 1, T, outDim, r, ts, eb.data, eo.data)
+        self._gemm2("NT", 0, T, outDim, inDim, ex.data, ew.data, r, ts, eb.data, eo.data)
 
         def _bw():
             self._ensureBackwardBegun()
@@ -630,8 +632,7 @@ class CudaBackend:
                 if ga:
                     self._gemm("TN", aa, r, inDim, T, dt, ex.data, ga)
             if gx:
-                self._gemm("NN", ax, T, inDim, outDim, go, ew.data, gx)
-                self._gemm("NN", 1, T, inDim, r, dt, ea.data, gx)
+                self._gemm2("NN", ax, T, inDim, outDim, go, ew.data, r, dt, ea.data, gx)
             if w.requiresGrad:
                 gw, aw = self._gradTarget(w, ew)
                 if gw:

@@ -85,6 +85,8 @@ gt_status gt_gemm_tc_batched(gt_ctx* ctx, int kind, int accum, int M, int N, int
                              int batch, bool* handled);
 // batch of same-shape products through whichever path gt_gemm would take for one of them
 gt_status gt_gemm_batched(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c, int batch);
+gt_status gt_gemm_tc2(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, int K2, const float* a2,
+                      const float* b2, float* c, bool* handled);
 gt_status gt_gemm_tc_check(gt_ctx* ctx);
 void gt_optim_destroy(gt_ctx* ctx);
 void gt_dp_teardown(gt_ctx* ctx);

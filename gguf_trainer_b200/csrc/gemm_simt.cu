@@ -135,3 +135,20 @@ extern "C" gt_status gt_gemm(gt_ctx* ctx, int32_t kind, int32_t accum, int32_t M
   }
   return gt_gemm_simt(ctx, kind, accum, M, N, K, gt_ptr<const float>(a), gt_ptr<const float>(b), gt_ptr<float>(c));
 }
+
+// c (+)= op(a).op(b) + op(a2).op(b2): one launch on the tensor-core path (the second product's K blocks follow the
+// first's in the main loop), two accumulating products otherwise.
+extern "C" gt_status gt_gemm2(gt_ctx* ctx, int32_t kind, int32_t accum, int32_t M, int32_t N, int32_t K, gt_buf a, gt_buf b, int32_t K2,
+                              gt_buf a2, gt_buf b2, gt_buf c) {
+  GT_REQUIRE(ctx, M > 0 && N > 0 && K > 0 && K2 > 0, "gt_gemm2: empty product %dx%dx(%d+%d)", M, N, K, K2);
+  GT_REQUIRE(ctx, a && b && a2 && b2 && c, "gt_gemm2: null operand");
+  if (ctx->precision != GT_PREC_FP32) {
+    bool handled = false;
+    gt_status s = gt_gemm_tc2(ctx, kind, accum, M, N, K, gt_ptr<const float>(a), gt_ptr<const float>(b), K2, gt_ptr<const float>(a2),
+                              gt_ptr<const float>(b2), gt_ptr<float>(c), &handled);
+    if (s != GT_OK || handled) return s;
+  }
+  gt_status s = gt_gemm(ctx, kind, accum, M, N, K, a, b, c);
+  if (s) return s;
+  return gt_gemm(ctx, kind, 1, M, N, K2, a2, b2, c);
+}

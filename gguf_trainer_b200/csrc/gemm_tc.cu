@@ -52,7 +52,8 @@ struct Smem {
 template <bool A_K, bool B_K, int BN, int MT>
 __global__ void __launch_bounds__(Smem<BN, MT>::THREADS, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-                 const __grid_constant__ CUtensorMap mapC, float* __restrict__ C, int M, int N, int K, int accum, int ksplit,
+                 const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapA2,
+                 const __grid_constant__ CUtensorMap mapB2, float* __restrict__ C, int M, int N, int K, int K2, int accum, int ksplit,
                  int use_tma_store, int batch, int* __restrict__ flag) {
   extern __shared__ uint8_t smem_raw[];
   using S = Smem<BN, MT>;
@@ -71,7 +72,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
   const int tiles_n = (N + BN - 1) / BN, tiles_m = (M + BM - 1) / BM;
   const int per_mat = tiles_n * tiles_m * ksplit;
   const int ntiles = per_mat * batch;            // the matrices of a batch are just more tiles
-  const int kblocks = (K + BK - 1) / BK;
+  // A second product A2.B2 of the same layout (K2 deep, 0 = none) is accumulated into the same tiles: its K blocks
+  // simply follow those of the first in the main loop, read through their own tensor maps.
+  const int kblocks1 = (K + BK - 1) / BK;
+  const int kblocks = kblocks1 + (K2 + BK - 1) / BK;
   const int per = (kblocks + ksplit - 1) / ksplit;   // K blocks per split-K slice
   // TMEM slot of a 128-row accumulator and the parity of its hand-over barriers: with MT = 1 the tiles alternate
   // between two slots, with MT = 2 slot h holds half h of every tile.
@@ -106,14 +110,17 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
           const int s = it % STAGES;
           wait(empty_bar(s), ((it / STAGES) & 1) ^ 1, 1);
           const uint32_t a_dst = base + s * S::STAGE, b_dst = a_dst + S::A_BYTES;
-          const int k0 = kb * BK;
+          const bool second = kb >= kblocks1;
+          const CUtensorMap* pa = second ? &mapA2 : &mapA;
+          const CUtensorMap* pb = second ? &mapB2 : &mapB;
+          const int k0 = (second ? kb - kblocks1 : kb) * BK;
           mbar_expect_tx(full_bar(s), S::STAGE);
-          if (A_K) tma_load_3d(a_dst, &mapA, k0, m0, bi, full_bar(s));
+          if (A_K) tma_load_3d(a_dst, pa, k0, m0, bi, full_bar(s));
           else
-            for (int c = 0; c < BM / 32; c++) tma_load_3d(a_dst + c * 4096, &mapA, m0 + 32 * c, k0, bi, full_bar(s));
-          if (B_K) tma_load_3d(b_dst, &mapB, k0, n0, bi, full_bar(s));
+            for (int c = 0; c < BM / 32; c++) tma_load_3d(a_dst + c * 4096, pa, m0 + 32 * c, k0, bi, full_bar(s));
+          if (B_K) tma_load_3d(b_dst, pb, k0, n0, bi, full_bar(s));
           else
-            for (int c = 0; c < BN / 32; c++) tma_load_3d(b_dst + c * 4096, &mapB, n0 + 32 * c, k0, bi, full_bar(s));
+            for (int c = 0; c < BN / 32; c++) tma_load_3d(b_dst + c * 4096, pb, n0 + 32 * c, k0, bi, full_bar(s));
         }
       }
     }
@@ -446,8 +453,8 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
 int* g_flag[64] = {};
 
 template <bool A_K, bool B_K, int BN, int MT>
-gt_status launch(gt_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, int tma_store, float* c, int M, int N,
-                 int K, int accum, int ksplit, int batch) {
+gt_status launch(gt_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const CUtensorMap& ma2,
+                 const CUtensorMap& mb2, int tma_store, float* c, int M, int N, int K, int K2, int accum, int ksplit, int batch) {
   auto kern = gemm_tf32_kernel<A_K, B_K, BN, MT>;
   using S = Smem<BN, MT>;
   static bool attr_set[64] = {};
@@ -457,7 +464,7 @@ gt_status launch(gt_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, cons
   }
   const long ntiles = (long)gt_cdiv(N, BN) * gt_cdiv(M, S::BM) * ksplit * batch;
   dim3 grid((unsigned)min((long)ctx->sm_count, ntiles), 1, 1);
-  kern<<<grid, S::THREADS, S::TOTAL, ctx->stream>>>(ma, mb, mc, c, M, N, K, accum, ksplit, tma_store, batch, g_flag[ctx->device]);
+  kern<<<grid, S::THREADS, S::TOTAL, ctx->stream>>>(ma, mb, mc, ma2, mb2, c, M, N, K, K2, accum, ksplit, tma_store, batch, g_flag[ctx->device]);
   GT_LAUNCHED(ctx, "gemm_tf32_kernel");
   return GT_OK;
 }
@@ -511,11 +518,11 @@ int pair_capacity(gt_ctx* ctx) {
 }
 
 template <int BN, int MT>
-gt_status launch_kind(gt_ctx* ctx, int kind, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, int tma_store, float* c,
-                      int M, int N, int K, int accum, int ksplit, int batch) {
-  if (kind == GT_GEMM_NT) return launch<true, true, BN, MT>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
-  if (kind == GT_GEMM_NN) return launch<true, false, BN, MT>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
-  return launch<false, false, BN, MT>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
+gt_status launch_kind(gt_ctx* ctx, int kind, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const CUtensorMap& ma2,
+                      const CUtensorMap& mb2, int tma_store, float* c, int M, int N, int K, int K2, int accum, int ksplit, int batch) {
+  if (kind == GT_GEMM_NT) return launch<true, true, BN, MT>(ctx, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch);
+  if (kind == GT_GEMM_NN) return launch<true, false, BN, MT>(ctx, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch);
+  return launch<false, false, BN, MT>(ctx, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch);
 }
 
 }  // namespace
@@ -602,21 +609,26 @@ gt_status gt_gemm_tc_check(gt_ctx* ctx) {
 }
 
 // `batch` independent products of the same shape, matrix i of each operand `M*K`, `N*K`, `M*N` elements after matrix i-1.
-gt_status gt_gemm_tc_batched(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c, int batch,
-                             bool* handled) {
+// With K2 > 0 (batch 1 only): c (+)= op(a).op(b) + op(a2).op(b2), the second product of the same kind and K2 deep.
+static gt_status gemm_tc_dispatch(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, int K2,
+                                  const float* a2, const float* b2, float* c, int batch, bool* handled) {
   *handled = false;
-  if (batch < 1) return GT_OK;
+  if (batch < 1 || (K2 > 0 && batch != 1)) return GT_OK;
   // Small or oddly aligned products stay on the f32 kernel: TMA needs 16-byte row pitches and bases.
   const bool a_k = kind != GT_GEMM_TN, b_k = kind == GT_GEMM_NT;
   const int a_inner = a_k ? K : M, b_inner = b_k ? K : N;
   if (M < 16 || N < 16 || K < 16) return GT_OK;   // (rows of a tile past M or N are zero-filled by TMA and clipped on store)
   if ((a_inner & 3) || (b_inner & 3)) return GT_OK;
   if ((((uintptr_t)a) | ((uintptr_t)b) | ((uintptr_t)c)) & 15) return GT_OK;
+  if (K2 > 0) {
+    const int a2_inner = a_k ? K2 : M, b2_inner = b_k ? K2 : N;
+    if ((a2_inner & 3) || (b2_inner & 3) || ((((uintptr_t)a2) | ((uintptr_t)b2)) & 15)) return GT_OK;
+  }
   if (ctx->device < 0 || ctx->device >= 64) return GT_OK;
   if (!device_flag(ctx)) return GT_OK;
   // Tile shape and split-K factor: the cheapest of the four shapes under a small cost model (cycles of the CTA with
   // the most work: waves x (K blocks x cycles per K block + epilogue)), calibrated on in-kernel cycle counts.
-  const int kblocks = gt_cdiv(K, BK);
+  const int kblocks = gt_cdiv(K, BK) + gt_cdiv(K2, BK);
   struct Cfg { int mt, bn; };   // mt 1, 2: 128 / 256 rows on one CTA; mt 3: 256 rows on a CTA pair
   static const Cfg cfgs[6] = {{1, 192}, {1, 128}, {2, 256}, {2, 192}, {3, 192}, {3, 256}};
   const char* force = getenv("GT_GEMM_TILE");   // "mt,bn": forces one tile shape (read per call so tests can switch it)
@@ -625,7 +637,7 @@ gt_status gt_gemm_tc_batched(gt_ctx* ctx, int kind, int accum, int M, int N, int
   double best_cost = 1e30;
   for (int i = 0; i < 6; i++) {
     const int mt = cfgs[i].mt, bn = cfgs[i].bn, bm = mt == 1 ? BM1 : 2 * BM1;
-    if (mt == 3 && npairs < 8) continue;
+    if (mt == 3 && (npairs < 8 || K2 > 0)) continue;   // (the pair kernel takes one product)
     if (force) {
       int fm = 0, fb = 0;
       if (sscanf(force, "%d,%d", &fm, &fb) == 2 && (fm != mt || fb != bn)) continue;
@@ -662,6 +674,13 @@ gt_status gt_gemm_tc_batched(gt_ctx* ctx, int kind, int accum, int M, int N, int
   const bool oka = a_k ? make_map_3d(&ma, a, K, M, batch, K, sa, a_box, true) : make_map_3d(&ma, a, M, K, batch, M, sa, BK, false);
   const bool okb = b_k ? make_map_3d(&mb, b, K, N, batch, K, sb, b_box, true) : make_map_3d(&mb, b, N, K, batch, N, sb, BK, false);
   if (!oka || !okb) return GT_OK;
+  CUtensorMap ma2 = ma, mb2 = mb;
+  if (K2 > 0) {
+    const uint64_t sa2 = (uint64_t)M * K2, sb2 = (uint64_t)N * K2;
+    const bool oka2 = a_k ? make_map_3d(&ma2, a2, K2, M, 1, K2, sa2, a_box, true) : make_map_3d(&ma2, a2, M, K2, 1, M, sa2, BK, false);
+    const bool okb2 = b_k ? make_map_3d(&mb2, b2, K2, N, 1, K2, sb2, b_box, true) : make_map_3d(&mb2, b2, N, K2, 1, N, sb2, BK, false);
+    if (!oka2 || !okb2) return GT_OK;
+  }
   // the output goes through TMA (32x32 blocks of whole 128-byte rows) whenever its row pitch allows a tensor map
   CUtensorMap mc = ma;
   const int tma_store = ((N & 3) == 0 && make_map_3d(&mc, c, N, M, batch, N, sc, 32, true)) ? 1 : 0;
@@ -669,17 +688,27 @@ gt_status gt_gemm_tc_batched(gt_ctx* ctx, int kind, int accum, int M, int N, int
   gt_status s;
   if (mt == 3 && bn == 192) s = launch_pair_kind<192>(ctx, kind, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch, npairs);
   else if (mt == 3) s = launch_pair_kind<256>(ctx, kind, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch, npairs);
-  else if (mt == 1 && bn == 192) s = launch_kind<192, 1>(ctx, kind, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
-  else if (mt == 1) s = launch_kind<128, 1>(ctx, kind, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
-  else if (bn == 256) s = launch_kind<256, 2>(ctx, kind, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
-  else s = launch_kind<192, 2>(ctx, kind, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch);
+  else if (mt == 1 && bn == 192) s = launch_kind<192, 1>(ctx, kind, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch);
+  else if (mt == 1) s = launch_kind<128, 1>(ctx, kind, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch);
+  else if (bn == 256) s = launch_kind<256, 2>(ctx, kind, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch);
+  else s = launch_kind<192, 2>(ctx, kind, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch);
   if (s) return s;
   *handled = true;
   return GT_OK;
 }
 
+gt_status gt_gemm_tc_batched(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c, int batch,
+                             bool* handled) {
+  return gemm_tc_dispatch(ctx, kind, accum, M, N, K, a, b, 0, nullptr, nullptr, c, batch, handled);
+}
+
 gt_status gt_gemm_tc(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c, bool* handled) {
-  return gt_gemm_tc_batched(ctx, kind, accum, M, N, K, a, b, c, 1, handled);
+  return gemm_tc_dispatch(ctx, kind, accum, M, N, K, a, b, 0, nullptr, nullptr, c, 1, handled);
+}
+
+gt_status gt_gemm_tc2(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, int K2, const float* a2,
+                      const float* b2, float* c, bool* handled) {
+  return gemm_tc_dispatch(ctx, kind, accum, M, N, K, a, b, K2, a2, b2, c, 1, handled);
 }
 
 #ifdef GT_ATTN_TRACE

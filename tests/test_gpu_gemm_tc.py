@@ -55,6 +55,34 @@ def test_gemm_tf32(gpu, oracle, kind, M, N, K):
         gpu._check(gpu.lib.gt_free(gpu.ctx, b))
 
 
+@pytest.mark.parametrize("kind", ["NT", "NN", "TN"])
+@pytest.mark.parametrize("M,N,K,K2", [(2048, 3072, 1024, 16), (300, 200, 100, 16), (1000, 576, 70, 40), (64, 1536, 4096, 8),
+                                      (4096, 192, 576, 576)])
+def test_gemm2_two_products_into_one_tile(gpu, oracle, kind, M, N, K, K2):
+    """gt_gemm2: C (+)= A.B + A2.B2 with the second product's K blocks following the first's in one launch (the
+    projection with a rank-16 adapter and its input gradient), ragged K on both, split-K, accumulate."""
+    rng = oracle.Mulberry32(M + 3 * N + 5 * K + 7 * K2)
+    A, B = rng.randn((M, K), 0.5), rng.randn((N, K), 0.5)
+    A2, B2 = rng.randn((M, K2), 0.5), rng.randn((N, K2), 0.5)
+    C0 = rng.randn((M, N), 0.5)
+    want = A.astype(np.float64) @ B.astype(np.float64).T + A2.astype(np.float64) @ B2.astype(np.float64).T
+    sa = (lambda X: X if kind != "TN" else np.ascontiguousarray(X.T))
+    sb = (lambda X: X if kind == "NT" else np.ascontiguousarray(X.T))
+    bufs = [_dev(gpu, sa(A)), _dev(gpu, sb(B)), _dev(gpu, sa(A2)), _dev(gpu, sb(B2))]
+    for accum in (0, 1):
+        dc = _dev(gpu, C0)
+        gpu._gemm2(kind, accum, M, N, K, bufs[0], bufs[1], K2, bufs[2], bufs[3], dc)
+        got = gpu.readStateBuffer(dc, M * N).reshape(M, N)
+        ref = want + (C0.astype(np.float64) if accum else 0.0)
+        r = rel_l2(got, ref)
+        assert np.isfinite(got).all()
+        assert r <= REL_L2_TC, f"{kind} {M}x{N}x({K}+{K2}) accum={accum}: relative L2 {r:.3e}"
+        gpu._check(gpu.lib.gt_free(gpu.ctx, dc))
+    gpu.sync([])
+    for b in bufs:
+        gpu._check(gpu.lib.gt_free(gpu.ctx, b))
+
+
 TILES = ["1,192", "1,128", "2,256", "2,192", "3,192", "3,256"]   # rows per CTA x columns; 3 = a CTA pair (cta_group::2)
 
 
