@@ -212,6 +212,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
   const int nkb = kb_hi - kb_lo + 1;
 
   if (threadIdx.x == 0) {
+    tma_prefetch_map(&mapQ); tma_prefetch_map(&mapK); tma_prefetch_map(&mapV);
     mbar_init(q_full, 1); mbar_init(k_full, 1); mbar_init(v_full, 1); mbar_init(s_full0, 1); mbar_init(s_full1, 1);
     mbar_init(p_full, MATH_WARPS * 32); mbar_init(o_full, 1);
     mbar_init(x_full, MATH_WARPS * 32); mbar_init(x_free, MATH_WARPS * 32);
@@ -452,6 +453,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
   const int iters = nqb * group;
 
   if (threadIdx.x == 0) {
+    tma_prefetch_map(&mapK); tma_prefetch_map(&mapV); tma_prefetch_map(&mapQk); tma_prefetch_map(&mapGk);
+    tma_prefetch_map(&mapQm); tma_prefetch_map(&mapGm);
     mbar_init(kv_full, 1); mbar_init(qk_full0, 1); mbar_init(qk_full1, 1); mbar_init(qm_full0, 1); mbar_init(qm_full1, 1);
     mbar_init(s_full0, 1);
     mbar_init(s_full1, 1); mbar_init(p_full0, MATH_WARPS * 32); mbar_init(p_full1, MATH_WARPS * 32); mbar_init(acc_done0, 1);
@@ -761,6 +764,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   const int iters = kb_hi - kb_lo + 1;
 
   if (threadIdx.x == 0) {
+    tma_prefetch_map(&mapQ); tma_prefetch_map(&mapG); tma_prefetch_map(&mapKk); tma_prefetch_map(&mapVk); tma_prefetch_map(&mapKm);
     mbar_init(q_full, 1); mbar_init(kk_full0, 1); mbar_init(kk_full1, 1); mbar_init(km_full, 1); mbar_init(s_full0, 1);
     mbar_init(s_full1, 1); mbar_init(p_full0, MATH_WARPS * 32); mbar_init(p_full1, MATH_WARPS * 32); mbar_init(acc_done, 1);
     mbar_init(all_done, 1);

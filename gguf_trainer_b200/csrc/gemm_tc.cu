@@ -83,6 +83,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
   auto par_of = [&](uint32_t tl) { return MT == 2 ? (tl & 1) : ((tl >> 1) & 1); };
 
   if (threadIdx.x == 0) {
+    tma_prefetch_map(&mapA); tma_prefetch_map(&mapB);
+    if (K2 > 0) { tma_prefetch_map(&mapA2); tma_prefetch_map(&mapB2); }
+    if (use_tma_store) tma_prefetch_map(&mapC);
     for (int s = 0; s < STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     for (int b = 0; b < 2; b++) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 128); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");

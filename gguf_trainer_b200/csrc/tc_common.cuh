@@ -125,6 +125,10 @@ __host__ __device__ constexpr uint32_t idesc_tf32(bool a_mn, bool b_mn, int m, i
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// starts the fetch of a tensor map (a kernel parameter) into the descriptor cache before its first copy needs it
+__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
 // 3-D forms (x = innermost element, y = row, z = matrix of a batch)
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"

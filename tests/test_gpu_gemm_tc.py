@@ -83,6 +83,44 @@ def test_gemm2_two_products_into_one_tile(gpu, oracle, kind, M, N, K, K2):
         gpu._check(gpu.lib.gt_free(gpu.ctx, b))
 
 
+@pytest.mark.parametrize("frozen_base", [True, False])
+def test_lora_projection_as_one_op_tf32(gpu, oracle, frozen_base):
+    """`loraLinear` on the tensor-core path (gt_gemm2 forward and input gradient, 16-row adapter gradient) against
+    f64 formulas of y = x.W^T + s.(x.A^T).B^T, with a scale that is not a power of two."""
+    from gpu_harness import rand_tensor, upstream
+    from gguf_trainer_b200 import autograd as ag
+    T, din, dout, r, s = 200, 96, 80, 16, 1.25
+    rng = oracle.Mulberry32(77)
+    x = rand_tensor(rng, [T, din]); w = rand_tensor(rng, [dout, din], 0.3, requires_grad=not frozen_base)
+    la = rand_tensor(rng, [r, din], 0.3); lb = rand_tensor(rng, [dout, r], 0.3)
+    for t in (x, w, la, lb):
+        t.zeroGrad()
+    ag.setLoraAdapters({id(w): ag.LoraAdapter(la, lb, s)})
+    gpu.install()
+    try:
+        y = ag.linear(x, w)
+        g = upstream(oracle, y.size)
+        y.grad[:] = g
+        gpu.seedGradFromHost(y)
+        y._backward()
+        gpu.sync([y])
+    finally:
+        gpu.uninstall()
+        ag.setLoraAdapters({})
+    X, W, A, B = (t.data.astype(np.float64).reshape(t.shape) for t in (x, w, la, lb))
+    G = g.astype(np.float64).reshape(T, dout)
+    t1 = X @ A.T
+    want = {"y": X @ W.T + s * (t1 @ B.T), "dx": G @ W + s * (G @ B) @ A, "dA": s * (G @ B).T @ X, "dB": s * G.T @ t1}
+    got = {"y": y.data, "dx": x.grad, "dA": la.grad, "dB": lb.grad}
+    if not frozen_base:
+        want["dW"], got["dW"] = G.T @ X, w.grad
+    else:
+        assert not w.grad.any()
+    for k in want:
+        e = rel_l2(got[k], want[k])
+        assert e <= REL_L2_TC, f"{k}: relative L2 {e:.3e}"
+
+
 TILES = ["1,192", "1,128", "2,256", "2,192", "3,192", "3,256"]   # rows per CTA x columns; 3 = a CTA pair (cta_group::2)
 
 

@@ -178,3 +178,49 @@ def test_bucket_plan_tiles_the_gradient_arena_in_completion_order():
     assert plan[1][1] == offs[idx_l2_down]
     # the last bucket reaches the end of the arena: first layer, output norm and the (tied) embedding
     assert order[-1] is m.tokenEmbd and plan[-1][1] + plan[-1][2] == total
+
+
+def test_linear_routes_an_adapter_to_one_op_or_to_the_reference_four():
+    """`linear` (autograd.ts:311-319) with an adapter on the weight: a backend that offers `loraLinear` gets that one
+    call; any other backend gets the reference's add(linear(x,w), scale(linear(linear(x,a),b), s))."""
+    from gguf_trainer_b200 import autograd as ag
+    from gguf_trainer_b200.autograd import Tensor
+
+    class Recorder:
+        def __init__(self, fuse):
+            self.calls = []
+            if fuse:
+                self.fuseLora = True
+
+        def _out(self, name, shape):
+            self.calls.append(name)
+            return Tensor.zeros(shape)
+
+        def linear(self, x, w):
+            return self._out("linear", [x.shape[0], w.shape[0]])
+
+        def scale(self, x, c):
+            return self._out(f"scale {c}", x.shape)
+
+        def add(self, a, b):
+            return self._out("add", a.shape)
+
+        def loraLinear(self, x, w, a, b, s):
+            return self._out(f"loraLinear {s}", [x.shape[0], w.shape[0]])
+
+    x, w = Tensor.zeros([5, 8]), Tensor.zeros([6, 8])
+    a, b = Tensor.zeros([2, 8]), Tensor.zeros([6, 2])
+    prev = ag.opsBackend()
+    try:
+        ag.setLoraAdapters({id(w): ag.LoraAdapter(a, b, 1.5)})
+        for fuse, want in ((True, ["loraLinear 1.5"]), (False, ["linear", "linear", "linear", "scale 1.5", "add"])):
+            r = Recorder(fuse)
+            ag.setOpsBackend(r)
+            y = ag.linear(x, w)
+            assert y.shape == [5, 6] and r.calls == want
+            r.calls.clear()
+            ag.linear(x, Tensor.zeros([6, 8]))            # a weight without an adapter: the plain product
+            assert r.calls == ["linear"]
+    finally:
+        ag.setLoraAdapters({})
+        ag.setOpsBackend(prev)
