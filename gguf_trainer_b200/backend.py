@@ -611,18 +611,18 @@ class CudaBackend:
         ex, ew, ea, eb = self._entryFor(x), self._entryFor(w), self._entryFor(a), self._entryFor(b)
         out, eo = self._makeOut([T, outDim], [x, w, a, b])
         small = T * r * 4
-        t, ts, dts, dt = (self._acquireRecycled(small) for _ in range(4))
-        sc = _EW["scale"]
-        self._gemm("NT", 0, T, r, inDim, ex.data, ea.data, t)
-        self._check(self.lib.gt_ew_fwd(self.ctx, sc, T * r, t, 0, float(scale), ts))
+        ts, dt = self._acquireRecycled(small), self._acquireRecycled(small)
+        s = float(scale)
+        kNT, kNN = _KIND["NT"], _KIND["NN"]
+        # ts = scale·(x·Aᵀ): the factor rides on the product's epilogue (gt_gemm_scaled), no pass of its own
+        self._check(self.lib.gt_gemm_scaled(self.ctx, kNT, 0, T, r, inDim, ex.data, ea.data, ts, s))
         self._gemm2("NT", 0, T, outDim, inDim, ex.data, ew.data, r, ts, eb.data, eo.data)
 
         def _bw():
             self._ensureBackwardBegun()
             go = self._gradSource(eo)
             gx, ax = self._gradTarget(x, ex)
-            self._gemm("NN", 0, T, r, outDim, go, eb.data, dts)
-            self._check(self.lib.gt_ew_fwd(self.ctx, sc, T * r, dts, 0, float(scale), dt))
+            self._check(self.lib.gt_gemm_scaled(self.ctx, kNN, 0, T, r, outDim, go, eb.data, dt, s))   # dt = scale·(g·B)
             if b.requiresGrad:
                 gb, ab = self._gradTarget(b, eb)
                 if gb:

@@ -78,8 +78,8 @@ static inline T* gt_ptr(gt_buf b) { return reinterpret_cast<T*>(static_cast<uint
 static inline int gt_cdiv(long a, long b) { return (int)((a + b - 1) / b); }
 
 // internal cross-file entry points
-gt_status gt_gemm_simt(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c);
-gt_status gt_gemm_tc(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c,
+gt_status gt_gemm_simt(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c, float alpha);
+gt_status gt_gemm_tc(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c, float alpha,
                      bool* handled);
 gt_status gt_gemm_tc_batched(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c,
                              int batch, bool* handled);

@@ -12,7 +12,7 @@ constexpr int BM = 128, BN = 128, BK = 16, TM = 8, TN = 8, PAD = 4;
 template <bool A_KCONTIG, bool B_KCONTIG>
 __global__ void __launch_bounds__(256) gemm_f32_kernel(int M, int N, int K, const float* __restrict__ a, long sam, long sak,
                                                        const float* __restrict__ b, long sbn, long sbk,
-                                                       float* __restrict__ c, int accum, int ksplit) {
+                                                       float* __restrict__ c, int accum, int ksplit, float alpha) {
   __shared__ __align__(16) float As[BK][BM + PAD];
   __shared__ __align__(16) float Bs[BK][BN + PAD];
   const int tid = threadIdx.x;
@@ -72,15 +72,16 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(int M, int N, int K, cons
       int gn = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + j - 4);
       if (gn >= N) continue;
       float* dst = c + (long)gm * N + gn;
-      if (ksplit > 1) atomicAdd(dst, acc[i][j]);
-      else *dst = accum ? *dst + acc[i][j] : acc[i][j];
+      const float v = acc[i][j] * alpha;
+      if (ksplit > 1) atomicAdd(dst, v);
+      else *dst = accum ? *dst + v : v;
     }
   }
 }
 
 }  // namespace
 
-gt_status gt_gemm_simt(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c) {
+gt_status gt_gemm_simt(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c, float alpha) {
   dim3 grid(gt_cdiv(N, BN), gt_cdiv(M, BM), 1);
   // Few output tiles and a deep K (the dW product, K = rows): split K across CTAs and reduce with
   // f32 atomics into C. Order of the partial sums then varies run to run at the 1e-7 level.
@@ -97,13 +98,13 @@ gt_status gt_gemm_simt(gt_ctx* ctx, int kind, int accum, int M, int N, int K, co
   grid.z = ksplit;
   switch (kind) {
     case GT_GEMM_NT:
-      gemm_f32_kernel<true, true><<<grid, 256, 0, ctx->stream>>>(M, N, K, a, K, 1, b, K, 1, c, accum, ksplit);
+      gemm_f32_kernel<true, true><<<grid, 256, 0, ctx->stream>>>(M, N, K, a, K, 1, b, K, 1, c, accum, ksplit, alpha);
       break;
     case GT_GEMM_NN:
-      gemm_f32_kernel<true, false><<<grid, 256, 0, ctx->stream>>>(M, N, K, a, K, 1, b, 1, N, c, accum, ksplit);
+      gemm_f32_kernel<true, false><<<grid, 256, 0, ctx->stream>>>(M, N, K, a, K, 1, b, 1, N, c, accum, ksplit, alpha);
       break;
     case GT_GEMM_TN:
-      gemm_f32_kernel<false, false><<<grid, 256, 0, ctx->stream>>>(M, N, K, a, 1, M, b, 1, N, c, accum, ksplit);
+      gemm_f32_kernel<false, false><<<grid, 256, 0, ctx->stream>>>(M, N, K, a, 1, M, b, 1, N, c, accum, ksplit, alpha);
       break;
     default:
       return gt_fail(ctx, GT_ERR_ARG, "gt_gemm: unknown kind %d", kind);
@@ -119,21 +120,27 @@ gt_status gt_gemm_batched(gt_ctx* ctx, int kind, int accum, int M, int N, int K,
     if (s != GT_OK || handled) return s;
   }
   for (int i = 0; i < batch; i++) {
-    gt_status s = gt_gemm_simt(ctx, kind, accum, M, N, K, a + (size_t)i * M * K, b + (size_t)i * N * K, c + (size_t)i * M * N);
+    gt_status s = gt_gemm_simt(ctx, kind, accum, M, N, K, a + (size_t)i * M * K, b + (size_t)i * N * K, c + (size_t)i * M * N, 1.f);
     if (s) return s;
   }
   return GT_OK;
 }
 
-extern "C" gt_status gt_gemm(gt_ctx* ctx, int32_t kind, int32_t accum, int32_t M, int32_t N, int32_t K, gt_buf a, gt_buf b, gt_buf c) {
+// c (+)= alpha * op(a).op(b): the factor is applied to the f32 accumulator when it is written out
+extern "C" gt_status gt_gemm_scaled(gt_ctx* ctx, int32_t kind, int32_t accum, int32_t M, int32_t N, int32_t K, gt_buf a, gt_buf b, gt_buf c,
+                                    float alpha) {
   GT_REQUIRE(ctx, M > 0 && N > 0 && K > 0, "gt_gemm: empty product %dx%dx%d", M, N, K);
   GT_REQUIRE(ctx, a && b && c, "gt_gemm: null operand");
   if (ctx->precision != GT_PREC_FP32) {
     bool handled = false;
-    gt_status s = gt_gemm_tc(ctx, kind, accum, M, N, K, gt_ptr<const float>(a), gt_ptr<const float>(b), gt_ptr<float>(c), &handled);
+    gt_status s = gt_gemm_tc(ctx, kind, accum, M, N, K, gt_ptr<const float>(a), gt_ptr<const float>(b), gt_ptr<float>(c), alpha, &handled);
     if (s != GT_OK || handled) return s;
   }
-  return gt_gemm_simt(ctx, kind, accum, M, N, K, gt_ptr<const float>(a), gt_ptr<const float>(b), gt_ptr<float>(c));
+  return gt_gemm_simt(ctx, kind, accum, M, N, K, gt_ptr<const float>(a), gt_ptr<const float>(b), gt_ptr<float>(c), alpha);
+}
+
+extern "C" gt_status gt_gemm(gt_ctx* ctx, int32_t kind, int32_t accum, int32_t M, int32_t N, int32_t K, gt_buf a, gt_buf b, gt_buf c) {
+  return gt_gemm_scaled(ctx, kind, accum, M, N, K, a, b, c, 1.f);
 }
 
 // c (+)= op(a).op(b) + op(a2).op(b2): one launch on the tensor-core path (the second product's K blocks follow the

@@ -54,7 +54,7 @@ __global__ void __launch_bounds__(Smem<BN, MT>::THREADS, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                  const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapA2,
                  const __grid_constant__ CUtensorMap mapB2, float* __restrict__ C, int M, int N, int K, int K2, int accum, int ksplit,
-                 int use_tma_store, int batch, int* __restrict__ flag) {
+                 int use_tma_store, int batch, float out_scale, int* __restrict__ flag) {
   extern __shared__ uint8_t smem_raw[];
   using S = Smem<BN, MT>;
   constexpr int STAGES = S::STAGES, BM = S::BM;
@@ -203,7 +203,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
           float v[32];
           tmem_ld32(tmem + b * BN + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
 #pragma unroll
-          for (int j = 0; j < 32; j++) v[j] *= TRUNC_COMP;
+          for (int j = 0; j < 32; j++) v[j] *= out_scale;   // the caller's factor times the truncation compensation
           if (use_tma_store) {
             // Stage the warp's 32x32 block in shared memory (128-byte rows, 16-byte chunks XOR (row mod 8), the layout
             // the store's tensor map expects) and let TMA write it: whole 128-byte rows, clipped at M and N, as a
@@ -293,7 +293,7 @@ template <bool A_K, bool B_K, int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SmemPair<BN>::THREADS, 1)
 gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                       const __grid_constant__ CUtensorMap mapC, float* __restrict__ C, int M, int N, int K, int accum, int ksplit,
-                      int use_tma_store, int batch, int* __restrict__ flag) {
+                      int use_tma_store, int batch, float out_scale, int* __restrict__ flag) {
   extern __shared__ uint8_t smem_raw[];
   using S = SmemPair<BN>;
   constexpr int STAGES = S::STAGES, BM = 2 * BM1;
@@ -407,7 +407,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
           float v[32];
           tmem_ld32(tmem + b * BN + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
 #pragma unroll
-          for (int j = 0; j < 32; j++) v[j] *= TRUNC_COMP;
+          for (int j = 0; j < 32; j++) v[j] *= out_scale;   // the caller's factor times the truncation compensation
           if (use_tma_store) {
             const uint32_t tile = epi + (uint32_t)(q * 2 + (nst & 1)) * 4096u;
             if (nst >= 2) tma_wait_read<1>();
@@ -457,7 +457,7 @@ int* g_flag[64] = {};
 
 template <bool A_K, bool B_K, int BN, int MT>
 gt_status launch(gt_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const CUtensorMap& ma2,
-                 const CUtensorMap& mb2, int tma_store, float* c, int M, int N, int K, int K2, int accum, int ksplit, int batch) {
+                 const CUtensorMap& mb2, int tma_store, float* c, int M, int N, int K, int K2, int accum, int ksplit, int batch, float out_scale) {
   auto kern = gemm_tf32_kernel<A_K, B_K, BN, MT>;
   using S = Smem<BN, MT>;
   static bool attr_set[64] = {};
@@ -467,14 +467,14 @@ gt_status launch(gt_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, cons
   }
   const long ntiles = (long)gt_cdiv(N, BN) * gt_cdiv(M, S::BM) * ksplit * batch;
   dim3 grid((unsigned)min((long)ctx->sm_count, ntiles), 1, 1);
-  kern<<<grid, S::THREADS, S::TOTAL, ctx->stream>>>(ma, mb, mc, ma2, mb2, c, M, N, K, K2, accum, ksplit, tma_store, batch, g_flag[ctx->device]);
+  kern<<<grid, S::THREADS, S::TOTAL, ctx->stream>>>(ma, mb, mc, ma2, mb2, c, M, N, K, K2, accum, ksplit, tma_store, batch, out_scale, g_flag[ctx->device]);
   GT_LAUNCHED(ctx, "gemm_tf32_kernel");
   return GT_OK;
 }
 
 template <bool A_K, bool B_K, int BN>
 gt_status launch_pair(gt_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, int tma_store, float* c, int M, int N,
-                      int K, int accum, int ksplit, int batch, int npairs) {
+                      int K, int accum, int ksplit, int batch, int npairs, float out_scale) {
   auto kern = gemm_tf32_pair_kernel<A_K, B_K, BN>;
   using S = SmemPair<BN>;
   static bool attr_set[64] = {};
@@ -484,17 +484,17 @@ gt_status launch_pair(gt_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb,
   }
   const long ntiles = (long)gt_cdiv(N, BN) * gt_cdiv(M, 2 * BM1) * ksplit * batch;
   dim3 grid(2u * (unsigned)min((long)npairs, ntiles), 1, 1);
-  kern<<<grid, S::THREADS, S::TOTAL, ctx->stream>>>(ma, mb, mc, c, M, N, K, accum, ksplit, tma_store, batch, g_flag[ctx->device]);
+  kern<<<grid, S::THREADS, S::TOTAL, ctx->stream>>>(ma, mb, mc, c, M, N, K, accum, ksplit, tma_store, batch, out_scale, g_flag[ctx->device]);
   GT_LAUNCHED(ctx, "gemm_tf32_pair_kernel");
   return GT_OK;
 }
 
 template <int BN>
 gt_status launch_pair_kind(gt_ctx* ctx, int kind, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, int tma_store,
-                           float* c, int M, int N, int K, int accum, int ksplit, int batch, int npairs) {
-  if (kind == GT_GEMM_NT) return launch_pair<true, true, BN>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch, npairs);
-  if (kind == GT_GEMM_NN) return launch_pair<true, false, BN>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch, npairs);
-  return launch_pair<false, false, BN>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch, npairs);
+                           float* c, int M, int N, int K, int accum, int ksplit, int batch, int npairs, float out_scale) {
+  if (kind == GT_GEMM_NT) return launch_pair<true, true, BN>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch, npairs, out_scale);
+  if (kind == GT_GEMM_NN) return launch_pair<true, false, BN>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch, npairs, out_scale);
+  return launch_pair<false, false, BN>(ctx, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch, npairs, out_scale);
 }
 
 // CTA pairs that can be resident at once (two neighbouring SMs each); 0 when the device cannot run the pair kernel.
@@ -522,10 +522,10 @@ int pair_capacity(gt_ctx* ctx) {
 
 template <int BN, int MT>
 gt_status launch_kind(gt_ctx* ctx, int kind, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const CUtensorMap& ma2,
-                      const CUtensorMap& mb2, int tma_store, float* c, int M, int N, int K, int K2, int accum, int ksplit, int batch) {
-  if (kind == GT_GEMM_NT) return launch<true, true, BN, MT>(ctx, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch);
-  if (kind == GT_GEMM_NN) return launch<true, false, BN, MT>(ctx, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch);
-  return launch<false, false, BN, MT>(ctx, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch);
+                      const CUtensorMap& mb2, int tma_store, float* c, int M, int N, int K, int K2, int accum, int ksplit, int batch, float out_scale) {
+  if (kind == GT_GEMM_NT) return launch<true, true, BN, MT>(ctx, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch, out_scale);
+  if (kind == GT_GEMM_NN) return launch<true, false, BN, MT>(ctx, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch, out_scale);
+  return launch<false, false, BN, MT>(ctx, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch, out_scale);
 }
 
 }  // namespace
@@ -614,7 +614,7 @@ gt_status gt_gemm_tc_check(gt_ctx* ctx) {
 // `batch` independent products of the same shape, matrix i of each operand `M*K`, `N*K`, `M*N` elements after matrix i-1.
 // With K2 > 0 (batch 1 only): c (+)= op(a).op(b) + op(a2).op(b2), the second product of the same kind and K2 deep.
 static gt_status gemm_tc_dispatch(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, int K2,
-                                  const float* a2, const float* b2, float* c, int batch, bool* handled) {
+                                  const float* a2, const float* b2, float* c, int batch, float alpha, bool* handled) {
   *handled = false;
   if (batch < 1 || (K2 > 0 && batch != 1)) return GT_OK;
   // Small or oddly aligned products stay on the f32 kernel: TMA needs 16-byte row pitches and bases.
@@ -688,13 +688,14 @@ static gt_status gemm_tc_dispatch(gt_ctx* ctx, int kind, int accum, int M, int N
   CUtensorMap mc = ma;
   const int tma_store = ((N & 3) == 0 && make_map_3d(&mc, c, N, M, batch, N, sc, 32, true)) ? 1 : 0;
   if (ksplit > 1 && !accum) GT_CUDA(ctx, cudaMemsetAsync(c, 0, sizeof(float) * (size_t)M * N * batch, ctx->stream));
+  const float out_scale = alpha * TRUNC_COMP;
   gt_status s;
-  if (mt == 3 && bn == 192) s = launch_pair_kind<192>(ctx, kind, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch, npairs);
-  else if (mt == 3) s = launch_pair_kind<256>(ctx, kind, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch, npairs);
-  else if (mt == 1 && bn == 192) s = launch_kind<192, 1>(ctx, kind, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch);
-  else if (mt == 1) s = launch_kind<128, 1>(ctx, kind, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch);
-  else if (bn == 256) s = launch_kind<256, 2>(ctx, kind, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch);
-  else s = launch_kind<192, 2>(ctx, kind, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch);
+  if (mt == 3 && bn == 192) s = launch_pair_kind<192>(ctx, kind, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch, npairs, out_scale);
+  else if (mt == 3) s = launch_pair_kind<256>(ctx, kind, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch, npairs, out_scale);
+  else if (mt == 1 && bn == 192) s = launch_kind<192, 1>(ctx, kind, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch, out_scale);
+  else if (mt == 1) s = launch_kind<128, 1>(ctx, kind, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch, out_scale);
+  else if (bn == 256) s = launch_kind<256, 2>(ctx, kind, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch, out_scale);
+  else s = launch_kind<192, 2>(ctx, kind, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch, out_scale);
   if (s) return s;
   *handled = true;
   return GT_OK;
@@ -702,16 +703,17 @@ static gt_status gemm_tc_dispatch(gt_ctx* ctx, int kind, int accum, int M, int N
 
 gt_status gt_gemm_tc_batched(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c, int batch,
                              bool* handled) {
-  return gemm_tc_dispatch(ctx, kind, accum, M, N, K, a, b, 0, nullptr, nullptr, c, batch, handled);
+  return gemm_tc_dispatch(ctx, kind, accum, M, N, K, a, b, 0, nullptr, nullptr, c, batch, 1.f, handled);
 }
 
-gt_status gt_gemm_tc(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c, bool* handled) {
-  return gemm_tc_dispatch(ctx, kind, accum, M, N, K, a, b, 0, nullptr, nullptr, c, 1, handled);
+gt_status gt_gemm_tc(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c, float alpha,
+                     bool* handled) {
+  return gemm_tc_dispatch(ctx, kind, accum, M, N, K, a, b, 0, nullptr, nullptr, c, 1, alpha, handled);
 }
 
 gt_status gt_gemm_tc2(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, int K2, const float* a2,
                       const float* b2, float* c, bool* handled) {
-  return gemm_tc_dispatch(ctx, kind, accum, M, N, K, a, b, K2, a2, b2, c, 1, handled);
+  return gemm_tc_dispatch(ctx, kind, accum, M, N, K, a, b, K2, a2, b2, c, 1, 1.f, handled);
 }
 
 #ifdef GT_ATTN_TRACE

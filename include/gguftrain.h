@@ -70,6 +70,10 @@ gt_status gt_stats(gt_ctx* ctx, uint64_t* out4);
 /* C[M,N] (+)= op(A)*op(B): NT A[M,K] B[N,K]; NN A[M,K] B[K,N]; TN A[K,M] B[K,N]
  * (WebGPUBackend.gemm, webgpu.ts:1654-1671; srcGemm wgsl.ts:87-196). */
 gt_status gt_gemm(gt_ctx* ctx, int32_t kind, int32_t accum, int32_t M, int32_t N, int32_t K, gt_buf a, gt_buf b, gt_buf c);
+/* The same with a factor on the product: C (+)= alpha * op(A)*op(B) (the alpha/r of a LoRA adapter, applied where
+ * the [T, r] intermediate is written instead of by a `scale` pass, src/model/autograd.ts:311-319). */
+gt_status gt_gemm_scaled(gt_ctx* ctx, int32_t kind, int32_t accum, int32_t M, int32_t N, int32_t K, gt_buf a, gt_buf b, gt_buf c,
+                         float alpha);
 /* C[M,N] (+)= op(A)*op(B) + op(A2)*op(B2), both products of layout `kind`, the second K2 deep: the projection with a
  * LoRA adapter, x.W^T + (s.x.A^T).B^T, and its input gradient g.W + (s.g.B).A, as one product each
  * (`linear`, src/model/autograd.ts:311-319, records them as separate ops joined by `add`). */

@@ -83,6 +83,27 @@ def test_gemm2_two_products_into_one_tile(gpu, oracle, kind, M, N, K, K2):
         gpu._check(gpu.lib.gt_free(gpu.ctx, b))
 
 
+@pytest.mark.parametrize("kind,M,N,K,accum", [("NT", 2048, 16, 1024, 0), ("NN", 300, 16, 200, 1), ("TN", 576, 1536, 4096, 1),
+                                              ("NT", 513, 200, 96, 0)])
+def test_gemm_scaled(gpu, oracle, kind, M, N, K, accum):
+    """gt_gemm_scaled: C (+)= alpha * A.B with the factor applied in the epilogue (thin adapter products, split-K too)."""
+    alpha = 1.25
+    rng = oracle.Mulberry32(3 * M + N + 9 * K)
+    A, B, C0 = rng.randn((M, K), 0.5), rng.randn((N, K), 0.5), rng.randn((M, N), 0.5)
+    want = alpha * (A.astype(np.float64) @ B.astype(np.float64).T) + (C0.astype(np.float64) if accum else 0.0)
+    a_store = A if kind != "TN" else np.ascontiguousarray(A.T)
+    b_store = B if kind == "NT" else np.ascontiguousarray(B.T)
+    da, db, dc = _dev(gpu, a_store), _dev(gpu, b_store), _dev(gpu, C0)
+    kinds = {"NT": 0, "NN": 1, "TN": 2}
+    gpu._check(gpu.lib.gt_gemm_scaled(gpu.ctx, kinds[kind], accum, M, N, K, da, db, dc, alpha))
+    got = gpu.readStateBuffer(dc, M * N).reshape(M, N)
+    gpu.sync([])
+    r = rel_l2(got, want)
+    assert r <= REL_L2_TC, f"{kind} {M}x{N}x{K}: relative L2 {r:.3e}"
+    for b in (da, db, dc):
+        gpu._check(gpu.lib.gt_free(gpu.ctx, b))
+
+
 @pytest.mark.parametrize("frozen_base", [True, False])
 def test_lora_projection_as_one_op_tf32(gpu, oracle, frozen_base):
     """`loraLinear` on the tensor-core path (gt_gemm2 forward and input gradient, 16-row adapter gradient) against
