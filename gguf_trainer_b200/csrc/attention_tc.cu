@@ -114,8 +114,9 @@ struct Waiter {
 // Head dimension 256 runs as pairs of CTAs (a cluster of two): each holds one 128-wide half of the head, so its
 // tiles are those of a 128-wide head, computes the score products over its half and adds the other CTA's partial
 // sums; from there on both hold the same scores and each forms its half of the outputs. Math thread t of one CTA
-// and math thread t of the other own the same elements. A CTA has one exchange buffer, written by its peer:
-// `full` counts the peer's 256 writers of a block, `free` (on the writer's side) the 256 readers of the block before.
+// and math thread t of the other own the same elements, so a warp exchanges only with the same warp of the other
+// CTA and has its own pair of barriers. A CTA has one exchange buffer, written by its peer: a warp's `full` counts
+// the peer warp's 32 writers of a block, `free` (on the writer's side) the 32 readers of the block before.
 constexpr int PAIR_XCHG_BYTES = 32 * MATH_WARPS * 32 * 4;   // 32 values per math thread
 struct PairSum {
   uint32_t buf_peer, full_local, full_peer, free_local, free_peer;
@@ -175,7 +176,7 @@ struct FwdSmem {
   static constexpr int X_BYTES = 2 * 2 * ROWS * 4;   // partial row maxima [parity][half][row]
   static constexpr int XC_OFF = X_OFF + X_BYTES, XC_BYTES = SPLIT == 2 ? PAIR_XCHG_BYTES : 0;   // the peer's partial scores
   static constexpr int BAR_OFF = XC_OFF + XC_BYTES;
-  static constexpr int TOTAL = BAR_OFF + 128 + 1024;
+  static constexpr int TOTAL = BAR_OFF + (SPLIT == 2 ? 256 : 128) + 1024;   // a pair adds one exchange barrier pair per math warp
   static constexpr uint32_t TMEM_COLS = (2 * BKV + HD) <= 256 ? 256 : 512;
   static_assert(TOTAL <= 232448, "shared memory");
 };
@@ -194,7 +195,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
   float* xch = reinterpret_cast<float*>(base_ptr + S::X_OFF);
   const uint32_t bars = base + S::BAR_OFF;
   const uint32_t q_full = bars, k_full = bars + 8, v_full = bars + 16, s_full0 = bars + 24, s_full1 = bars + 32, p_full = bars + 40,
-                 o_full = bars + 48, x_full = bars + 72, x_free = bars + 80;
+                 o_full = bars + 48, x_full = bars + 128, x_free = bars + 192;
   const uint32_t tmem_slot = bars + 64;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + S::BAR_OFF + 64);
 
@@ -215,7 +216,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     tma_prefetch_map(&mapQ); tma_prefetch_map(&mapK); tma_prefetch_map(&mapV);
     mbar_init(q_full, 1); mbar_init(k_full, 1); mbar_init(v_full, 1); mbar_init(s_full0, 1); mbar_init(s_full1, 1);
     mbar_init(p_full, MATH_WARPS * 32); mbar_init(o_full, 1);
-    mbar_init(x_full, MATH_WARPS * 32); mbar_init(x_free, MATH_WARPS * 32);
+    if (SPLIT == 2)
+      for (int mw = 0; mw < MATH_WARPS; mw++) { mbar_init(x_full + 8 * mw, 32); mbar_init(x_free + 8 * mw, 32); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == MMA_WARP) tmem_alloc(tmem_slot, S::TMEM_COLS);
@@ -226,7 +228,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
   const uint32_t tm_o = tmem + 2 * BKV;
   Waiter w{false, flag};
   PairSum xs;
-  if (SPLIT == 2) xs.init(base + S::XC_OFF, base_ptr + S::XC_OFF, x_full, x_free, (uint32_t)(crank ^ 1));
+  if (SPLIT == 2 && warp < MATH_WARPS) xs.init(base + S::XC_OFF, base_ptr + S::XC_OFF, x_full + 8 * warp, x_free + 8 * warp, (uint32_t)(crank ^ 1));
   auto s_bar = [&](int it) { return (it & 1) ? s_full1 : s_full0; };
   auto s_par = [&](int it) { return (uint32_t)((it >> 1) & 1); };
 
@@ -412,7 +414,7 @@ struct DkvSmem {
   static constexpr int K_OFF = 0, V_OFF = KV_BYTES, QK_OFF = 2 * KV_BYTES, GK_OFF = QK_OFF + KBUF * QT_BYTES,
                        QM_OFF = GK_OFF + KBUF * QT_BYTES, GM_OFF = QM_OFF + MBUF * QT_BYTES, XC_OFF = GM_OFF + MBUF * QT_BYTES,
                        BAR_OFF = XC_OFF + (SPLIT == 2 ? PAIR_XCHG_BYTES : 0);
-  static constexpr int TOTAL = BAR_OFF + 128 + 1024;
+  static constexpr int TOTAL = BAR_OFF + (SPLIT == 2 ? 256 : 128) + 1024;   // a pair adds one exchange barrier pair per math warp
   static constexpr int COLS = 4 * NQ + 2 * HD;
   static_assert(SPLIT == 1 || NQ <= 32, "a pair exchanges at most 32 values per thread");
   static constexpr uint32_t TMEM_COLS = COLS <= 128 ? 128 : (COLS <= 256 ? 256 : 512);
@@ -436,7 +438,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
   const uint32_t bars = base + S::BAR_OFF;
   const uint32_t kv_full = bars, qk_full0 = bars + 8, qk_full1 = bars + 16, qm_full0 = bars + 24, s_full0 = bars + 32,
                  s_full1 = bars + 40, p_full0 = bars + 48, acc_done0 = bars + 56, all_done = bars + 72, qm_full1 = bars + 80,
-                 p_full1 = bars + 88, acc_done1 = bars + 96, x_full = bars + 104, x_free = bars + 112;
+                 p_full1 = bars + 88, acc_done1 = bars + 96, x_full = bars + 128, x_free = bars + 192;
   const uint32_t tmem_slot = bars + 64;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + S::BAR_OFF + 64);
 
@@ -459,7 +461,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
     mbar_init(s_full0, 1);
     mbar_init(s_full1, 1); mbar_init(p_full0, MATH_WARPS * 32); mbar_init(p_full1, MATH_WARPS * 32); mbar_init(acc_done0, 1);
     mbar_init(acc_done1, 1); mbar_init(all_done, 1);
-    mbar_init(x_full, MATH_WARPS * 32); mbar_init(x_free, MATH_WARPS * 32);
+    if (SPLIT == 2)
+      for (int mw = 0; mw < MATH_WARPS; mw++) { mbar_init(x_full + 8 * mw, 32); mbar_init(x_free + 8 * mw, 32); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == MMA_WARP) tmem_alloc(tmem_slot, S::TMEM_COLS);
@@ -471,7 +474,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
   const uint32_t tm_dv = tmem + 4 * NQ, tm_dk = tmem + 4 * NQ + HD;
   Waiter w{false, flag};
   PairSum xs;
-  if (SPLIT == 2) xs.init(base + S::XC_OFF, base_ptr + S::XC_OFF, x_full, x_free, (uint32_t)(crank ^ 1));
+  if (SPLIT == 2 && warp < MATH_WARPS) xs.init(base + S::XC_OFF, base_ptr + S::XC_OFF, x_full + 8 * warp, x_free + 8 * warp, (uint32_t)(crank ^ 1));
   // barrier and parity of the K-major copies of block `it`, and of its score products
   auto qk_bar = [&](int it) { return (KBUF == 2 && (it & 1)) ? qk_full1 : qk_full0; };
   auto qk_par = [&](int it) { return (uint32_t)((KBUF == 2 ? it >> 1 : it) & 1); };
@@ -722,7 +725,7 @@ struct DqSmem {
                        KM_OFF = VK_OFF + KBUF * KT_BYTES, XC_OFF = KM_OFF + KT_BYTES, BAR_OFF = XC_OFF + (SPLIT == 2 ? PAIR_XCHG_BYTES : 0);
   static_assert(SPLIT == 1 || NK <= 32, "a pair exchanges at most 32 values per thread");
   static constexpr int SLACK = SB ? 896 : 1024;   // for rounding the base up to 1024 B (two CTAs must fit 228 KB together)
-  static constexpr int TOTAL = BAR_OFF + 128 + SLACK;
+  static constexpr int TOTAL = BAR_OFF + (SPLIT == 2 ? 256 : 128) + SLACK;
   static constexpr int COLS = (SB ? 2 : 4) * NK + HD;
   static constexpr uint32_t TMEM_COLS = COLS <= 128 ? 128 : (COLS <= 256 ? 256 : 512);
   static_assert(TOTAL <= 232448, "shared memory");
@@ -748,7 +751,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   const uint32_t bars = base + S::BAR_OFF;
   const uint32_t q_full = bars, kk_full0 = bars + 8, kk_full1 = bars + 16, km_full = bars + 24, s_full0 = bars + 32,
                  s_full1 = bars + 40, p_full0 = bars + 48, acc_done = bars + 56, all_done = bars + 72, p_full1 = bars + 80,
-                 x_full = bars + 88, x_free = bars + 96;
+                 x_full = bars + 128, x_free = bars + 192;
   const uint32_t tmem_slot = bars + 64;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + S::BAR_OFF + 64);
 
@@ -768,7 +771,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     mbar_init(q_full, 1); mbar_init(kk_full0, 1); mbar_init(kk_full1, 1); mbar_init(km_full, 1); mbar_init(s_full0, 1);
     mbar_init(s_full1, 1); mbar_init(p_full0, MATH_WARPS * 32); mbar_init(p_full1, MATH_WARPS * 32); mbar_init(acc_done, 1);
     mbar_init(all_done, 1);
-    mbar_init(x_full, MATH_WARPS * 32); mbar_init(x_free, MATH_WARPS * 32);
+    if (SPLIT == 2)
+      for (int mw = 0; mw < MATH_WARPS; mw++) { mbar_init(x_full + 8 * mw, 32); mbar_init(x_free + 8 * mw, 32); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == MMA_WARP) tmem_alloc(tmem_slot, S::TMEM_COLS);
@@ -778,7 +782,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   const uint32_t tmem = *tmem_slot_ptr;
   const uint32_t tm_dq = tmem + (SB ? 2 : 4) * NK;
   PairSum xs;
-  if (SPLIT == 2) xs.init(base + S::XC_OFF, base_ptr + S::XC_OFF, x_full, x_free, (uint32_t)(crank ^ 1));
+  if (SPLIT == 2 && warp < MATH_WARPS) xs.init(base + S::XC_OFF, base_ptr + S::XC_OFF, x_full + 8 * warp, x_free + 8 * warp, (uint32_t)(crank ^ 1));
   auto sbuf = [&](int it) { return SB ? 0u : (uint32_t)((it & 1) * 2 * NK); };   // TMEM columns of block it's [S | dP]
   Waiter w{false, flag};
   // two alternating p_full barriers, as in the dK/dV kernel: the math warps may finish block i+1 before the issuing
