@@ -159,6 +159,57 @@ __global__ void muon_momentum_batched_kernel(size_t el, float* const* __restrict
     u[i] = nesterov ? g[i] + mu * v : v;
   }
 }
+// 16-byte forms of the batched pieces (el % 4 == 0, 16-byte aligned matrices), without the transposition: the
+// Newton-Schulz products are issued in the layout the matrix is stored in (see gt_muon_step).
+__global__ void muon_momentum_batched_v4_kernel(size_t el4, float* const* __restrict__ grads, float* const* __restrict__ bufs,
+                                                float* __restrict__ U, float mu, int nesterov) {
+  const int b = blockIdx.y;
+  const float4* g = reinterpret_cast<const float4*>(grads[b]);
+  float4* buf = reinterpret_cast<float4*>(bufs[b]);
+  float4* u = reinterpret_cast<float4*>(U) + (size_t)b * el4;
+  size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < el4; i += stride) {
+    const float4 gv = g[i];
+    float4 v = buf[i];
+    v.x = mu * v.x + gv.x; v.y = mu * v.y + gv.y; v.z = mu * v.z + gv.z; v.w = mu * v.w + gv.w;
+    buf[i] = v;
+    u[i] = nesterov ? make_float4(gv.x + mu * v.x, gv.y + mu * v.y, gv.z + mu * v.z, gv.w + mu * v.w) : v;
+  }
+}
+// X = U * inv[matrix]
+__global__ void muon_scale_batched_v4_kernel(size_t el4, const float* __restrict__ U, const float* __restrict__ inv, float* __restrict__ X) {
+  const int b = blockIdx.y;
+  const float s = inv[b];
+  const float4* u = reinterpret_cast<const float4*>(U) + (size_t)b * el4;
+  float4* x = reinterpret_cast<float4*>(X) + (size_t)b * el4;
+  size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < el4; i += stride) {
+    const float4 v = u[i];
+    x[i] = make_float4(v.x * s, v.y * s, v.z * s, v.w * s);
+  }
+}
+// W -= f * X
+__global__ void muon_apply_batched_v4_kernel(size_t el4, float f, const float* __restrict__ X, float* const* __restrict__ datas) {
+  const int b = blockIdx.y;
+  const float4* x = reinterpret_cast<const float4*>(X) + (size_t)b * el4;
+  float4* w = reinterpret_cast<float4*>(datas[b]);
+  size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < el4; i += stride) {
+    const float4 o = x[i];
+    float4 v = w[i];
+    v.x -= f * o.x; v.y -= f * o.y; v.z -= f * o.z; v.w -= f * o.w;
+    w[i] = v;
+  }
+}
+// B' = ca*I + cb*A + cc*AA over nb matrices of r x r, written over AA: then a*X + (b*A + c*A.A).X is the one product B'.X
+__global__ void ns_poly_batched_kernel(size_t n, int r, float ca, float cb, const float* __restrict__ A, float cc, float* AA) {
+  size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t rr = (size_t)r * r;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const size_t e = i % rr;
+    AA[i] = cb * A[i] + cc * AA[i] + ((e / r == e % r) ? ca : 0.f);
+  }
+}
 __global__ void __launch_bounds__(OT) sumsq_batched_kernel(const float* __restrict__ U, size_t el, int nch, float* __restrict__ partials) {
   __shared__ float sh[OT / 32];
   const int b = blockIdx.y;
@@ -232,6 +283,7 @@ struct MuonGroup {
   std::vector<int> idx;
   float *U = nullptr, *X = nullptr, *BX = nullptr, *A = nullptr, *AA = nullptr, *partials = nullptr, *inv = nullptr;
   float** d_ptrs = nullptr;   // [3][nb]: grad, momentum, data
+  bool v4 = false;            // every matrix of the group 16-byte aligned and a multiple of 4 elements
 };
 
 struct GtMuon {
@@ -445,6 +497,8 @@ gt_status gt_muon_create(gt_ctx* ctx, int32_t n, const gt_buf* data, const gt_bu
     for (int i : g.idx) ptrs.push_back(m->grad[i]);
     for (int i : g.idx) ptrs.push_back(m->buf[i]);
     for (int i : g.idx) ptrs.push_back(m->data[i]);
+    g.v4 = (el % 4) == 0;
+    for (float* q : ptrs) g.v4 = g.v4 && (((uintptr_t)q) & 15) == 0;
     GT_CUDA(ctx, cudaMemcpyAsync(g.d_ptrs, ptrs.data(), sizeof(float*) * ptrs.size(), cudaMemcpyHostToDevice, ctx->stream));
     GT_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   }
@@ -476,6 +530,40 @@ gt_status gt_muon_step(gt_ctx* ctx, uint64_t h) {
     const int nch = gt_cdiv((long)el, CHUNK);
     const dim3 eg((unsigned)max(1, min(egrid(ctx, el), (ctx->sm_count * 8 + nb - 1) / nb)), (unsigned)nb);
     float** P = g.d_ptrs;
+    const float f = m->lr * sqrtf(fmaxf(1.f, (float)rows / (float)cols));
+    if (g.v4) {
+      // The iteration runs on the matrix as it is stored. The reference transposes a tall matrix first so that
+      // A = X.X^T is the small Gram matrix (muon.ts:120-131); here the same Gram matrix is X^T.X (a TN product) and the
+      // update X.B'^T (an NT product), so no transposed copy is made. And a*X + (b*A + c*A.A).X is formed as ONE
+      // product B'.X with B' = a*I + b*A + c*A.A, into the other of two buffers, instead of a product and a pass.
+      const size_t el4 = el / 4;
+      muon_momentum_batched_v4_kernel<<<eg, 256, 0, ctx->stream>>>(el4, P, P + nb, g.U, m->mu, m->nesterov);
+      GT_LAUNCHED(ctx, "muon_momentum_batched_v4_kernel");
+      sumsq_batched_kernel<<<dim3(nch, nb), OT, 0, ctx->stream>>>(g.U, el, nch, g.partials);
+      GT_LAUNCHED(ctx, "sumsq_batched_kernel");
+      frob_inv_batched_kernel<<<nb, 32, 0, ctx->stream>>>(nch, g.partials, g.inv);
+      GT_LAUNCHED(ctx, "frob_inv_batched_kernel");
+      float *X = g.X, *Y = g.BX;
+      muon_scale_batched_v4_kernel<<<eg, 256, 0, ctx->stream>>>(el4, g.U, g.inv, X);
+      GT_LAUNCHED(ctx, "muon_scale_batched_v4_kernel");
+      for (int it = 0; it < m->ns; it++) {
+        gt_status st = flip ? gt_gemm_batched(ctx, GT_GEMM_TN, 0, r, r, c, X, X, g.A, nb)     // X is [c, r]: A = X^T.X
+                            : gt_gemm_batched(ctx, GT_GEMM_NT, 0, r, r, c, X, X, g.A, nb);    // X is [r, c]: A = X.X^T
+        if (st) return st;
+        st = gt_gemm_batched(ctx, GT_GEMM_NN, 0, r, r, r, g.A, g.A, g.AA, nb);
+        if (st) return st;
+        const size_t rr = (size_t)r * r * nb;
+        ns_poly_batched_kernel<<<egrid(ctx, rr), 256, 0, ctx->stream>>>(rr, r, 3.4445f, -4.7750f, g.A, 2.0315f, g.AA);
+        GT_LAUNCHED(ctx, "ns_poly_batched_kernel");
+        st = flip ? gt_gemm_batched(ctx, GT_GEMM_NT, 0, c, r, r, X, g.AA, Y, nb)               // [c, r] = X.B'^T
+                  : gt_gemm_batched(ctx, GT_GEMM_NN, 0, r, c, r, g.AA, X, Y, nb);              // [r, c] = B'.X
+        if (st) return st;
+        float* t = X; X = Y; Y = t;
+      }
+      muon_apply_batched_v4_kernel<<<eg, 256, 0, ctx->stream>>>(el4, f, X, P + 2 * nb);
+      GT_LAUNCHED(ctx, "muon_apply_batched_v4_kernel");
+      continue;
+    }
     muon_momentum_batched_kernel<<<eg, 256, 0, ctx->stream>>>(el, P, P + nb, g.U, m->mu, m->nesterov);
     GT_LAUNCHED(ctx, "muon_momentum_batched_kernel");
     sumsq_batched_kernel<<<dim3(nch, nb), OT, 0, ctx->stream>>>(g.U, el, nch, g.partials);
@@ -497,7 +585,6 @@ gt_status gt_muon_step(gt_ctx* ctx, uint64_t h) {
       axpby_kernel<<<egrid(ctx, el * nb), 256, 0, ctx->stream>>>(el * nb, 3.4445f, g.X, 1.f, g.BX, g.X);
       GT_LAUNCHED(ctx, "axpby_kernel");
     }
-    const float f = m->lr * sqrtf(fmaxf(1.f, (float)rows / (float)cols));
     muon_apply_batched_kernel<<<eg, 256, 0, ctx->stream>>>(rows, cols, flip, f, g.X, P + 2 * nb);
     GT_LAUNCHED(ctx, "muon_apply_batched_kernel");
   }

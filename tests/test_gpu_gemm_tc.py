@@ -142,6 +142,31 @@ def test_lora_projection_as_one_op_tf32(gpu, oracle, frozen_base):
         assert e <= REL_L2_TC, f"{k}: relative L2 {e:.3e}"
 
 
+def test_muon_step_tf32_batched_shapes(gpu, oracle):
+    """The Muon step on the tensor-core path: same-shape matrices batched, tall ones iterated as stored (Gram matrix
+    X^T.X, update X.B'^T) and wide ones as X.X^T, B'.X; the applied update against the CPU oracle. Five Newton-Schulz
+    iterations compound the products' error, so the bound on the update is 5e-3 relative L2."""
+    from gguf_trainer_b200.autograd import Tensor
+    from gguf_trainer_b200.optim import MuonGpu
+    rng = oracle.Mulberry32(0x4D4E)
+    shapes = [(160, 64), (160, 64), (64, 160), (96, 96)]
+    ps = [Tensor(rng.randn(s, 0.5), list(s), True) for s in shapes]
+    ws = [p.data.copy().reshape(s) for p, s in zip(ps, shapes)]
+    w0 = [w.copy() for w in ws]
+    bufs = [np.zeros(s, np.float32) for s in shapes]
+    opt = MuonGpu(gpu, ps, [], lr=0.05, momentum=0.95, nesterov=True, nsSteps=5, aux={"lr": 1e-3})
+    for _ in range(2):
+        for p, w, b, s in zip(ps, ws, bufs, shapes):
+            g = rng.randn(s, 0.3)
+            gpu.writeStateBuffer(gpu.buffersFor(p)["grad"], g)
+            oracle.muon_step_array(w, g, b, 0.05, 0.95, True, 5)
+        opt.recordStep()
+    gpu.sync(ps)
+    for p, w, z, s in zip(ps, ws, w0, shapes):
+        r = rel_l2(p.data.reshape(s) - z, w - z)
+        assert r <= 5e-3, f"{s}: update relative L2 {r:.3e}"
+
+
 TILES = ["1,192", "1,128", "2,256", "2,192", "3,192", "3,256"]   # rows per CTA x columns; 3 = a CTA pair (cta_group::2)
 
 
