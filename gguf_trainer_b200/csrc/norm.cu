@@ -178,7 +178,10 @@ __global__ void __launch_bounds__(TH) rmsnorm_bwd_vec_kernel(int rows, int d, co
 template <int V4, int TH = (V4 >= 8 ? 256 : 512)>
 gt_status launch_bwd_vec(gt_ctx* ctx, int rows, int d, const float* x, const float* w, const float* rinv, const float* g, float* gx,
                          int accum_x, float* gw) {
-  int blocks = min(gt_cdiv(rows, TH / 32), ctx->sm_count * (512 / TH));
+  // Narrow rows (the per-head norms, d = 128 or 256) keep few bytes in flight per warp: more resident CTAs make up for it.
+  // (Only with many rows: every CTA ends with d atomics on dw, which a short launch would feel.)
+  const int per_sm = (V4 <= 2 && rows >= 65536) ? (V4 == 1 ? 4 : 3) : 512 / TH;
+  int blocks = min(gt_cdiv(rows, TH / 32), ctx->sm_count * per_sm);
   rmsnorm_bwd_vec_kernel<V4, TH><<<blocks, TH, sizeof(float) * d, ctx->stream>>>(rows, d, x, w, rinv, g, gx, accum_x, gw);
   GT_LAUNCHED(ctx, "rmsnorm_bwd_vec_kernel");
   return GT_OK;
