@@ -280,8 +280,8 @@ def run_ours(args):
     step = CudaStep(model, gpu, B, T, lossChunk=loss_chunk, world=world, capture=not args.no_graph, dp=dp,
                     arena=arena if dp is not None else None)
 
-    def one_step(i, resident):
-        ids, tg = batch(i)
+    def one_step(i, resident, prepared=None):
+        ids, tg = prepared if prepared is not None else batch(i)
         if resident and step.graph is not None:
             step.replay()                       # inputs already in HBM
         else:
@@ -300,8 +300,11 @@ def run_ours(args):
         barrier()
         gpu.recordEvent(0)
         loss = None
+        nxt = batch(first)
         for i in range(steps):
-            one_step(first + i, resident)
+            one_step(first + i, resident, nxt)
+            if i + 1 < steps:
+                nxt = batch(first + i + 1)  # the next batch is drawn on the host while this step runs on the device
             if not resident:
                 loss = step.losses()      # device -> host read of the step's result, every step
         gpu.recordEvent(1)
