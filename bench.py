@@ -278,7 +278,7 @@ def run_ours(args):
     pin_ids = torch.empty(B * T, dtype=torch.int32).pin_memory()
     pin_tg = torch.empty(B * T, dtype=torch.int32).pin_memory()
     step = CudaStep(model, gpu, B, T, lossChunk=loss_chunk, world=world, capture=not args.no_graph, dp=dp,
-                    arena=arena if dp is not None else None)
+                    arena=arena if dp is not None else None, layersPerBucket=args.layers_per_bucket)
 
     def one_step(i, resident, prepared=None):
         ids, tg = prepared if prepared is not None else batch(i)
@@ -490,6 +490,7 @@ def main():
     ap.add_argument("--micro", default="", help="time one op of the step instead: attention | gemm")
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--window", type=int, default=0)
+    ap.add_argument("--layers-per-bucket", type=int, default=6, help="data parallel: layers per gradient all-reduce bucket")
     ap.add_argument("--heads", default="", help="--micro attention: Hq,Hkv,hd instead of 9,3,64")
     args = ap.parse_args()
     if args.profile:
