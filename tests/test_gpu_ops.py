@@ -3,7 +3,7 @@ Cases follow the reference's tests/gpu-parity.ts (shapes, seeds, tolerances); st
 import numpy as np
 import pytest
 
-from gpu_harness import BWD, FWD, compare, op_case, rand_tensor, rel_l2
+from gpu_harness import BWD, FWD, REL_L2_FP32, compare, op_case, rand_tensor, rel_l2
 
 pytestmark = pytest.mark.gpu
 
@@ -287,3 +287,44 @@ def test_gemm_is_deterministic_run_to_run(gpu, oracle):
             gpu.uninstall()
         outs.append(y.data.copy())
     assert np.array_equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("kind", ["NT", "NN", "TN"])
+def test_gemm_scaled_and_gemm2_strict_f32(gpu, oracle, kind):
+    """The two extra product entry points in strict-f32 mode: C (+)= alpha*A.B and C (+)= A.B + A2.B2, ragged sizes,
+    against f64 products of the same f32 inputs (relative L2 <= 1e-5); and their argument checks."""
+    from gguf_trainer_b200._lib import GtError
+    M, N, K, K2, alpha = 37, 29, 53, 8, 0.75
+    rng = oracle.Mulberry32(99)
+    A, B = rng.randn((M, K), 0.5), rng.randn((N, K), 0.5)
+    A2, B2 = rng.randn((M, K2), 0.5), rng.randn((N, K2), 0.5)
+    C0 = rng.randn((M, N), 0.5)
+    sa = (lambda X: X if kind != "TN" else np.ascontiguousarray(X.T))
+    sb = (lambda X: X if kind == "NT" else np.ascontiguousarray(X.T))
+    kinds = {"NT": 0, "NN": 1, "TN": 2}
+
+    def dev(a):
+        b = gpu.createStateBuffer(a.nbytes)
+        gpu.writeStateBuffer(b, a)
+        return b
+
+    da, db, da2, db2 = dev(sa(A)), dev(sb(B)), dev(sa(A2)), dev(sb(B2))
+    AB = A.astype(np.float64) @ B.astype(np.float64).T
+    AB2 = A2.astype(np.float64) @ B2.astype(np.float64).T
+    for accum in (0, 1):
+        base = C0.astype(np.float64) if accum else 0.0
+        dc = dev(C0)
+        gpu._check(gpu.lib.gt_gemm_scaled(gpu.ctx, kinds[kind], accum, M, N, K, da, db, dc, alpha))
+        assert rel_l2(gpu.readStateBuffer(dc, M * N).reshape(M, N), alpha * AB + base) <= REL_L2_FP32
+        gpu.writeStateBuffer(dc, C0)
+        gpu._check(gpu.lib.gt_gemm2(gpu.ctx, kinds[kind], accum, M, N, K, da, db, K2, da2, db2, dc))
+        assert rel_l2(gpu.readStateBuffer(dc, M * N).reshape(M, N), AB + AB2 + base) <= REL_L2_FP32
+        gpu._check(gpu.lib.gt_free(gpu.ctx, dc))
+    dc = dev(C0)
+    with pytest.raises(GtError, match="empty product"):
+        gpu._check(gpu.lib.gt_gemm2(gpu.ctx, kinds[kind], 0, M, N, K, da, db, 0, da2, db2, dc))
+    with pytest.raises(GtError, match="null operand"):
+        gpu._check(gpu.lib.gt_gemm2(gpu.ctx, kinds[kind], 0, M, N, K, da, db, K2, 0, db2, dc))
+    gpu.sync([])
+    for b in (da, db, da2, db2, dc):
+        gpu._check(gpu.lib.gt_free(gpu.ctx, b))
