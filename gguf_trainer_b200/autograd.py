@@ -133,6 +133,7 @@ def checkpoint(inputs: List[Tensor], fn: Callable[[], Tensor]) -> Tensor:
     rb = _ops_backend if (_ops_backend is not None and hasattr(_ops_backend, "beginRegion")) else None
     born = _tensors_created
     mark = rb.beginRegion() if rb else 0
+    tok = rb.regionToken() if (rb is not None and hasattr(rb, "regionToken")) else None   # optional backend extension
     out = fn()
     _assert_self_contained(out, inputs, born)
     if rb:
@@ -141,6 +142,8 @@ def checkpoint(inputs: List[Tensor], fn: Callable[[], Tensor]) -> Tensor:
 
     def _bw():
         mark2 = rb.beginRegion() if rb else 0
+        if tok is not None:
+            rb.replayOf(tok)
         replay = fn()
         if rb:
             rb.seedGradFrom(replay, out)

@@ -149,6 +149,12 @@ class CudaBackend:
         self._transients: List[tuple] = []     # (addr, size)
         self._regionFree: List[tuple] = []
         self._regionsOpened = 0
+        # Attention outputs kept across a recompute region (see regionToken / replayOf)
+        self.keepAttentionAcrossRecompute = True
+        self._regionDepth = 0
+        self._curRec: Optional[dict] = None
+        self._regionRecs: Dict[int, dict] = {}
+        self._nextRegionId = 1
         self._backwardBegun = False
         self._graphSynced = False              # a sync() ran after the current graph was built
         self._capturing = False
@@ -396,6 +402,9 @@ class CudaBackend:
         self._touched.clear()
         self._backwardBegun = False
         self._graphSynced = True
+        self._regionRecs.clear()
+        self._curRec = None
+        self._regionDepth = 0
 
     def reclaimStepTransients(self, keep: Sequence[Tensor] = ()):
         """webgpu.ts:612-633: recycle this micro-batch's transients without the readback."""
@@ -418,7 +427,35 @@ class CudaBackend:
     # ------------------------------------------------------------------ regions (RegionBackend)
     def beginRegion(self) -> int:
         self._regionsOpened += 1
+        self._regionDepth += 1
+        if self._regionDepth == 1 and self.keepAttentionAcrossRecompute:
+            self._curRec = {"id": self._nextRegionId, "saved": [], "pos": 0, "replay": False}
+            self._nextRegionId += 1
+        else:
+            if self._curRec is not None:             # a region inside a region: nothing is kept for either
+                self._regionRecs.pop(self._curRec["id"], None)
+            self._curRec = None
         return len(self._transients)
+
+    # Optional extension of RegionBackend, used by `checkpoint` when present. A recompute region runs its forward
+    # twice; the attention inside it is the one op whose second run costs real time (a quarter of a layer's forward)
+    # while its result is, by construction, bit-identical to the first. So the first run's attention outputs (O and
+    # the row statistics) survive the region's end, and the replay, told which region it repeats, takes them instead
+    # of launching the kernel again. Everything else of the region is still freed and recomputed.
+    def regionToken(self) -> Optional[int]:
+        """Identity of the outermost region just opened (None when nothing will be kept for it)."""
+        rec = self._curRec
+        if rec is None or rec["replay"]:
+            return None
+        self._regionRecs[rec["id"]] = rec
+        return rec["id"]
+
+    def replayOf(self, token: Optional[int]):
+        """The region just opened repeats the forward of region `token`."""
+        rec = self._regionRecs.get(token) if token is not None else None
+        if rec is not None and self._regionDepth == 1:
+            rec["replay"], rec["pos"] = True, 0
+            self._curRec = rec
 
     def regionCount(self) -> int:
         return self._regionsOpened
@@ -436,7 +473,23 @@ class CudaBackend:
             if e is not None:
                 keepBufs.add(e.data)
                 keepBufs.add(e.grad)
-        retained = self._transients[:mark]
+        rec = self._curRec if self._regionDepth == 1 else None
+        self._regionDepth = max(0, self._regionDepth - 1)
+        release = set()
+        if rec is not None:
+            self._curRec = None
+            held = {b for item in rec["saved"] for b in item[:2]}
+            if rec["replay"]:
+                release = held                       # the replay and its backward are over: the kept outputs go too
+                self._regionRecs.pop(rec["id"], None)
+            elif rec["id"] in self._regionRecs:
+                keepBufs |= held                     # first run, and `checkpoint` asked for a token: keep them
+        retained = []
+        for tr in self._transients[:mark]:
+            if tr[0] in release:
+                self._regionFree.append(tr)
+            else:
+                retained.append(tr)
         for tr in self._transients[mark:]:
             if tr[0] in keepBufs:
                 retained.append(tr)
@@ -822,9 +875,22 @@ class CudaBackend:
         self._beginForwardOp()
         self._checkT(T, q.shape[0], "attention")
         eq, ek, ev = self._entryFor(q), self._entryFor(k), self._entryFor(v)
-        out, eo = self._makeOut([T, Hq * hd], [q, k, v])
-        lse = self._acquireRecycled(Hq * T * 4)
-        self._check(self.lib.gt_attention_fwd(self.ctx, T, Hq, Hkv, hd, window, eq.data, ek.data, ev.data, eo.data, lse))
+        rec = self._curRec
+        nbytes = T * Hq * hd * 4
+        if rec is not None and rec["replay"] and rec["pos"] < len(rec["saved"]) and rec["saved"][rec["pos"]][2] == nbytes:
+            # replay of a recompute region: the first run's output and row statistics, no launch
+            data, lse, _n = rec["saved"][rec["pos"]]
+            rec["pos"] += 1
+            out = Tensor.zeros([T, Hq * hd])
+            out._prev = [q, k, v]
+            eo = _Entry(data, self._acquireRecycled(nbytes), nbytes, False, out.size)
+            self._entries[out] = eo
+        else:
+            out, eo = self._makeOut([T, Hq * hd], [q, k, v])
+            lse = self._acquireRecycled(Hq * T * 4)
+            self._check(self.lib.gt_attention_fwd(self.ctx, T, Hq, Hkv, hd, window, eq.data, ek.data, ev.data, eo.data, lse))
+            if rec is not None and not rec["replay"]:
+                rec["saved"].append((eo.data, lse, nbytes))
 
         def _bw():
             self._ensureBackwardBegun()

@@ -163,6 +163,40 @@ def test_recompute_is_bit_identical(gpu, oracle, arch):
         compare("recompute grad", b, a, BWD, 1e-6)
 
 
+def test_recompute_keeps_attention_outputs(gpu, oracle):
+    """A recompute region's replay takes the first run's attention output instead of launching the kernel again:
+    one launch fewer per layer, same loss bit for bit and the same gradients as the replay that recomputes everything."""
+    cfg = tiny("qwen3")
+    ids = oracle.Mulberry32(5).randint(12, cfg.vocabSize)
+    tg = oracle.Mulberry32(6).randint(12, cfg.vocabSize)
+    was = gpu.keepAttentionAcrossRecompute
+    outs, launches = [], []
+    try:
+        for keep in (False, True):
+            gpu.keepAttentionAcrossRecompute = keep
+            _, m = paired(oracle, cfg, 78)
+            ag.setCheckpointing(True)
+            before = gpu.kernelLaunches()
+            gpu.install()
+            try:
+                loss = sequenceLoss(m, ids, tg)
+                ag.backward(loss, 1.0)
+                gpu.sync([loss])
+            finally:
+                gpu.uninstall()
+                ag.setCheckpointing(False)
+            launches.append(gpu.kernelLaunches() - before)
+            outs.append((loss.data.copy(), [p.grad.copy() for p in m.params()]))
+    finally:
+        gpu.keepAttentionAcrossRecompute = was
+    saved = launches[0] - launches[1]
+    # (the first of the two runs may also build a RoPE table once)
+    assert len(m.layers) <= saved <= len(m.layers) + 2, f"launches {launches}, layers {len(m.layers)}"
+    assert np.array_equal(outs[0][0], outs[1][0])
+    for a, b in zip(outs[0][1], outs[1][1]):
+        compare("gradient with kept attention outputs", b, a, BWD, 1e-6)   # (f32 atomics in dw: not bit-stable run to run)
+
+
 @pytest.mark.parametrize("fused,alpha", [(True, 8.0), (False, 8.0), (True, 5.0)])
 def test_lora_parity_and_frozen_base(gpu, oracle, fused, alpha):
     """tests/gpu-parity.ts:2037-2138: adapters train, the base stays frozen and gets no gradient. Both recordings of
