@@ -53,8 +53,8 @@ def test_attention_tf32(gpu, oracle, T, Hq, Hkv, hd, window):
         assert e <= REL_L2_TC, f"{name}: relative L2 {e:.3e}"
 
 
-def test_attention_tf32_batched_sequences_do_not_see_each_other(gpu, oracle):
-    B, T, Hq, Hkv, hd = 3, 150, 4, 2, 64
+@pytest.mark.parametrize("B,T,Hq,Hkv,hd", [(3, 150, 4, 2, 64), (2, 150, 2, 1, 256)])
+def test_attention_tf32_batched_sequences_do_not_see_each_other(gpu, oracle, B, T, Hq, Hkv, hd):
     rng = oracle.Mulberry32(9)
     q = rand_tensor(rng, [B * T, Hq * hd]); k = rand_tensor(rng, [B * T, Hkv * hd]); v = rand_tensor(rng, [B * T, Hkv * hd])
     gpu.install()
