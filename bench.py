@@ -340,7 +340,7 @@ def run_ours(args):
         line = {
             "metric": metric, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_res / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": {"tf32": "tf32 products, f32 accumulate and storage", "fp32": "f32", "bf16": "bf16 products, f32 accumulate"}[args.precision],
+            "dtype": {"tf32": "tf32 products, f32 accumulate and storage", "fp32": "f32"}[args.precision],
             "data": "synthetic",
             "config": {"workload": {"smollm2": "SmolLM2-135M shape llama (h576 L30 9/3 heads hd64 ffn1536 V49152, tied)",
                                     "gemma3": "gemma3 ~95M shape (h640 L12 4/1 heads hd256 ffn2048 V32768, window 512 on 5 of 6 layers)",
@@ -476,7 +476,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--precision", default="tf32", choices=["fp32", "tf32", "bf16"])
+    ap.add_argument("--precision", default="tf32", choices=["fp32", "tf32"])
     ap.add_argument("--optimizer", default="adamw", choices=["adamw", "muon"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--seq", type=int, default=2048)

@@ -20,7 +20,7 @@ _TYPES = {
     "const int32_t*": C.POINTER(C.c_int32), "uint64_t": C.c_uint64, "uint64_t*": C.POINTER(C.c_uint64),
     "const uint64_t*": C.POINTER(C.c_uint64), "float": C.c_float, "float*": C.POINTER(C.c_float), "double": C.c_double,
     "const void*": C.c_void_p, "void*": C.c_void_p, "char*": C.c_char_p, "const uint8_t*": C.c_void_p,
-    "uint8_t*": C.c_void_p,
+    "uint8_t*": C.c_void_p, "uint32_t*": C.POINTER(C.c_uint32),
 }
 
 

@@ -327,9 +327,21 @@ def keptTeacherRows(teacherIds, teacherProbs, T: int, k: int, V: int) -> int:
     return kept
 
 
+def _on_device(values, V: int, where: str) -> bool:
+    """Integer inputs produced on the device (the window gather) carry the bound their producer checked once; the
+    per-element validators have nothing on the host to read."""
+    bound = getattr(values, "bound", None)
+    if bound is None or not hasattr(values, "addr"):
+        return False
+    if bound > V:
+        raise ValueError(f"{where}: device-resident ids were checked against a vocabulary of {bound}, this table has {V} rows")
+    return True
+
+
 def embedding(weight: Tensor, ids) -> Tensor:
     assertMatrix(weight, "weight", "embedding")
-    assertIdsInTable(ids, weight.shape[0], "embedding")
+    if not _on_device(ids, weight.shape[0], "embedding"):
+        assertIdsInTable(ids, weight.shape[0], "embedding")
     return _need_backend().embedding(weight, ids)
 
 
@@ -345,7 +357,12 @@ def crossEntropy(logits: Tensor, targets) -> Tensor:
     """autograd.ts:897-952 (validation above the dispatch; `kept` passed down)."""
     assertMatrix(logits, "logits", "crossEntropy")
     T, V = logits.shape
-    kept = keptRowsInVocab(targets, T, V, "crossEntropy")
+    if _on_device(targets, V, "crossEntropy"):
+        if len(targets) != T:
+            raise ValueError(f"crossEntropy: {len(targets)} targets for {T} logit rows.")
+        kept = -1      # counted on the device from the targets themselves
+    else:
+        kept = keptRowsInVocab(targets, T, V, "crossEntropy")
     return _need_backend().crossEntropy(logits, targets, kept)
 
 
@@ -363,7 +380,12 @@ def fusedCrossEntropy(hidden: Tensor, w: Tensor, targets, chunk: int) -> Tensor:
         raise ValueError(
             "fusedCrossEntropy: the readout weight carries a LoRA adapter, which this "
             "path cannot apply. Put the readout in the aux param group, or use --loss-chunk 0.")
-    kept = keptRowsInVocab(targets, T, V, "fusedCrossEntropy")
+    if _on_device(targets, V, "fusedCrossEntropy"):
+        if len(targets) != T:
+            raise ValueError(f"fusedCrossEntropy: {len(targets)} targets for {T} hidden rows.")
+        kept = -1
+    else:
+        kept = keptRowsInVocab(targets, T, V, "fusedCrossEntropy")
     return _need_backend().fusedCrossEntropy(hidden, w, targets, chunk, kept)
 
 

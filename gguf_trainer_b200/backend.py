@@ -28,7 +28,7 @@ from .autograd import Tensor
 
 _EW = {"add": 0, "mul": 1, "silu": 2, "gelu": 3, "scale": 4}
 _KIND = {"NT": 0, "NN": 1, "TN": 2}
-PRECISION = {"fp32": 0, "tf32": 1, "bf16": 2}
+PRECISION = {"fp32": 0, "tf32": 1}   # (the C ABI reserves 2 for BF16 and refuses it: there are no BF16 kernels)
 
 
 class _Entry:
@@ -50,19 +50,28 @@ class CapturedGraph:
         self.gpu = gpu
         self.handle = handle
         self.handles = list(earlier) + [handle]   # segments in order when the recording was cut (cutCapture)
-        self.inputs = inputs      # [(addr, count)] in upload order
+        self.inputs = inputs      # [(addr, count, role, bound)] in upload order
         self.owned = owned        # [(addr, size)] transients pinned to this graph
         self.outputs = outputs    # {name: (addr, count)}
 
-    def launch(self, inputs: Sequence[np.ndarray]):
+    def writeInputs(self, inputs: Sequence[np.ndarray]):
+        """Validate and upload the integer inputs of the next replay. The recorded kernels index the embedding table
+        and the logits with these values and have no bound of their own, so the checks the eager ops run above the
+        dispatch (assertIdsInTable, keptRowsInVocab: src/model/autograd.ts:813-823, 875-894) run here too."""
         if len(inputs) != len(self.inputs):
             raise ValueError(f"graph takes {len(self.inputs)} integer inputs, got {len(inputs)}")
         g = self.gpu
-        for (addr, count), arr in zip(self.inputs, inputs):
-            a = _as_u32(arr)
-            if a.size != count:
-                raise ValueError(f"graph input has {a.size} elements, recorded {count}")
+        staged = []
+        for (addr, count, role, bound), arr in zip(self.inputs, inputs):
+            if np.asarray(arr).size != count:
+                raise ValueError(f"graph input has {np.asarray(arr).size} elements, recorded {count}")
+            _checkIntegerInput(arr, role, bound)
+            staged.append((addr, _as_u32(arr)))
+        for addr, a in staged:
             g._check(g.lib.gt_write(g.ctx, addr, a.ctypes.data, a.nbytes))
+
+    def launch(self, inputs: Sequence[np.ndarray]):
+        self.writeInputs(inputs)
         self.replay()
 
     def replay(self, between=None):
@@ -81,6 +90,25 @@ class CapturedGraph:
         for addr, _size in self.owned:
             g._check(g.lib.gt_free(g.ctx, addr))
         self.owned = []
+
+
+def _checkIntegerInput(values, role: str, bound: int):
+    """The range check of one replayed integer input: `ids` index a table of `bound` rows; `targets` are -1 or a
+    vocabulary row; `teacher` ids are vocabulary rows except for a -1 in a row's first slot (checked per element here
+    as -1 or a row, the eager op checks the slot rule)."""
+    if role is None:
+        return
+    a = np.asarray(values)
+    if a.dtype == np.uint32:
+        a = a.astype(np.int64)
+        a[a == 0xFFFFFFFF] = -1
+    if role == "ids":
+        ag.assertIdsInTable(a, bound, "embedding (replay)")
+    else:
+        bad = np.nonzero((a < -1) | (a >= bound))[0]
+        if bad.size:
+            t = int(bad[0])
+            raise ValueError(f"{role} (replay): value {int(a[t])} at position {t} is not -1 (ignore) or an integer in [0,{bound})")
 
 
 def _as_u32(values) -> np.ndarray:
@@ -157,6 +185,7 @@ class CudaBackend:
         self._nextRegionId = 1
         self._backwardBegun = False
         self._graphSynced = False              # a sync() ran after the current graph was built
+        self._graphOpen = False                # forward ops were recorded since the last sync()
         self._capturing = False
         self._captureInputs: List[tuple] = []
         self._captureSegments: List[int] = []
@@ -211,8 +240,8 @@ class CudaBackend:
         self.ctx = None
 
     def setPrecision(self, precision: str):
-        self.precision = precision
         self._check(self.lib.gt_set_precision(self.ctx, PRECISION[precision]))
+        self.precision = precision
 
     def setBatch(self, batch: int, seq_len: int = 0):
         """Rows passed to the ops are `batch` sequences of `seq_len` rows; 0 restores one sequence per call."""
@@ -269,12 +298,15 @@ class CudaBackend:
         self._check(self.lib.gt_read(self.ctx, addr, out.ctypes.data, out.nbytes))
         self._readback += out.nbytes
 
-    def _uploadU32(self, values) -> int:
+    def _uploadU32(self, values, role: Optional[str] = None, bound: int = 0) -> int:
+        if hasattr(values, "addr") and hasattr(values, "bound"):
+            return int(values.addr)          # already on the device (ingest.DeviceInts): nothing to upload or replay-patch
         a = _as_u32(values)
         if self._capturing:
-            # a replayed graph reads its integer inputs from fixed buffers the launcher rewrites
+            # a replayed graph reads its integer inputs from fixed buffers the launcher rewrites; `role` and `bound`
+            # are what the launcher checks new values against
             addr = self._acquirePersistent(a.nbytes)
-            self._captureInputs.append((addr, a.size))
+            self._captureInputs.append((addr, a.size, role, bound))
             return addr
         addr = self._acquireTransient(a.nbytes)
         self._write(addr, a)
@@ -401,7 +433,9 @@ class CudaBackend:
         self._regionFree = []
         self._touched.clear()
         self._backwardBegun = False
-        self._graphSynced = True
+        if self._graphOpen:                    # (a sync with no graph behind it, e.g. after building an optimizer, arms nothing)
+            self._graphSynced = True
+        self._graphOpen = False
         self._regionRecs.clear()
         self._curRec = None
         self._regionDepth = 0
@@ -520,6 +554,7 @@ class CudaBackend:
     def _beginForwardOp(self):
         self._backwardBegun = False
         self._graphSynced = False
+        self._graphOpen = True
 
     def _ensureBackwardBegun(self):
         """webgpu.ts:1397-1429. A sync() between a graph's forward and its backward recycled the graph's
@@ -554,6 +589,23 @@ class CudaBackend:
         out = np.empty(n, np.float32)
         self._read(buf, out)
         return out
+
+    # ------------------------------------------------------------------ asynchronous reads (checkpoints)
+    def readAsync(self, addr: int, nbytes: int) -> int:
+        """Start copying `nbytes` at `addr`, as of the work enqueued so far, to pinned host memory on a copy stream
+        that runs beside later compute. Returns a ticket for `readFinish`."""
+        t = C.c_uint64()
+        self._check(self.lib.gt_read_async(self.ctx, addr, nbytes, C.byref(t)))
+        return int(t.value)
+
+    def readFence(self):
+        """Later compute waits (on the device) for every read started so far: call before work that overwrites their
+        sources. The optimizers call it at the top of `recordStep`."""
+        self._check(self.lib.gt_read_fence(self.ctx))
+
+    def readFinish(self, ticket: int, out: np.ndarray):
+        assert out.flags["C_CONTIGUOUS"]
+        self._check(self.lib.gt_read_finish(self.ctx, ticket, out.ctypes.data, out.nbytes))
 
     # ------------------------------------------------------------------ graph capture
     def beginCapture(self, seed: float = 1.0, accumulate: bool = True):
@@ -594,7 +646,7 @@ class CudaBackend:
         owned = self._transients[self._captureMark:] + self._regionFree
         self._transients = self._transients[:self._captureMark]
         self._regionFree = []
-        owned = owned + [(a, n * 4) for a, n in self._captureInputs]
+        owned = owned + [(a, n * 4) for a, n, _r, _b in self._captureInputs]
         outs = {}
         for name, t in (outputs or {}).items():
             e = self._entries[t]
@@ -829,7 +881,7 @@ class CudaBackend:
         d = weight.shape[1]
         T = len(ids)
         ew = self._entryFor(weight)
-        idBuf = self._uploadU32(ids)
+        idBuf = self._uploadU32(ids, "ids", weight.shape[0])
         out, eo = self._makeOut([T, d], [weight])
         self._check(self.lib.gt_embedding_fwd(self.ctx, T, d, ew.data, idBuf, eo.data))
 
@@ -934,7 +986,7 @@ class CudaBackend:
         self._beginForwardOp()
         T, V = logits.shape
         el = self._entryFor(logits)
-        tgt = self._uploadU32(targets)
+        tgt = self._uploadU32(targets, "targets", V)
         stats = self._acquireRecycled(T * 16)
         loss, eo, invKept = self._lossOut([logits])
         self._check(self.lib.gt_ce_fwd(self.ctx, T, V, el.data, tgt, stats, eo.data, invKept))
@@ -955,7 +1007,7 @@ class CudaBackend:
         T, H = hidden.shape
         V = w.shape[0]
         eh, ew = self._entryFor(hidden), self._entryFor(w)
-        tgt = self._uploadU32(targets)
+        tgt = self._uploadU32(targets, "targets", V)
         run = self._acquireRecycled(T * 12)
         width = min(chunk, V)
         ch = self._acquireRecycled(T * width * 4)
@@ -990,7 +1042,7 @@ class CudaBackend:
         self._beginForwardOp()
         T, V = logits.shape
         el = self._entryFor(logits)
-        ids = self._uploadU32(teacherIds)
+        ids = self._uploadU32(teacherIds, "teacher", V)
         probs = self._uploadF32(teacherProbs)
         stats = self._acquireRecycled(T * 16)
         loss, eo, invKept = self._lossOut([logits])

@@ -221,33 +221,23 @@ gt_status gt_attention_fwd_simt(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, i
   return GT_OK;
 }
 
+gt_status gt_attention_bwd_simt_scratch(gt_ctx* ctx, float* D, int rows, int T, int Hq, int Hkv, int hd, int window,
+                                        const float* q, const float* k, const float* v, const float* out, const float* lse,
+                                        const float* go, float* gq, int accum_q, float* gk, int accum_k, float* gv,
+                                        int accum_v);
+
 gt_status gt_attention_bwd_simt(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int hd, int window, const float* q,
                                 const float* k, const float* v, const float* out, const float* lse, const float* go,
                                 float* gq, int accum_q, float* gk, int accum_k, float* gv, int accum_v) {
-  const float scale = 1.f / sqrtf((float)hd);
-  const float scale2 = 1.4426950408889634f * scale;
   float* D = nullptr;
   gt_status s = gt_scratch(ctx, sizeof(float) * (size_t)rows * Hq, &D);
   if (s) return s;
-  long warps = (long)rows * Hq;
-  attn_bwd_d_kernel<<<gt_cdiv(warps * 32, 256), 256, 0, ctx->stream>>>(rows, Hq, hd, go, out, D);
-  GT_LAUNCHED(ctx, "attn_bwd_d_kernel");
-  if (gq) {
-    attn_bwd_dq_kernel<<<gt_cdiv(warps, WARPS), WARPS * 32, sizeof(float) * WARPS * 2 * hd, ctx->stream>>>(
-        rows, T, Hq, Hkv, hd, window, scale2, scale, q, k, v, go, lse, D, gq, accum_q);
-    GT_LAUNCHED(ctx, "attn_bwd_dq_kernel");
-  }
-  if (gk || gv) {
-    long kw = (long)rows * Hkv;
-    attn_bwd_dkv_kernel<<<gt_cdiv(kw, WARPS), WARPS * 32, sizeof(float) * WARPS * 2 * hd, ctx->stream>>>(
-        rows, T, Hq, Hkv, hd, window, scale2, scale, q, k, v, go, lse, D, gk, accum_k, gv, accum_v);
-    GT_LAUNCHED(ctx, "attn_bwd_dkv_kernel");
-  }
-  return GT_OK;
+  return gt_attention_bwd_simt_scratch(ctx, D, rows, T, Hq, Hkv, hd, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv,
+                                       accum_v);
 }
 
-// The same backward launches with the row-dot scratch D supplied by the caller instead of taken from the
-// context's growable scratch block (used by the entry point that must not allocate).
+// The backward launches with the row-dot scratch D supplied by the caller: the context's growable scratch block
+// (gt_attention_bwd_simt above) or the fixed array of the entry point that must not allocate.
 gt_status gt_attention_bwd_simt_scratch(gt_ctx* ctx, float* D, int rows, int T, int Hq, int Hkv, int hd, int window,
                                         const float* q, const float* k, const float* v, const float* out, const float* lse,
                                         const float* go, float* gq, int accum_q, float* gk, int accum_k, float* gv,

@@ -487,13 +487,6 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
   auto qm_par = [&](int it) { return (uint32_t)((MBUF == 2 ? it >> 1 : it) & 1); };
   auto s_bar = [&](int it) { return (it & 1) ? s_full1 : s_full0; };
   auto s_par = [&](int it) { return (uint32_t)((it >> 1) & 1); };
-#ifdef GT_ATTN_TRACE
-  const bool tr = blockIdx.x == 0 && blockIdx.y == 0 && lane == 0;
-  long long tprev = clock64();
-#define TRACE(slot) if (tr && i >= 8 && i < 40) { long long tn = clock64(); flag[64 + (i - 8) * 32 + slot] = (int)(tn - tprev); tprev = tn; }
-#else
-#define TRACE(slot)
-#endif
 
   if (warp == TMA_WARP) {
     if (lane == 0) {
@@ -530,14 +523,10 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
       for (int i = 0; i < iters; i++) {
         if (i + 1 + KBUF < iters) {
           w.wait(s_bar(i + 1), s_par(i + 1), 23);
-          TRACE(16)
           load_k(i + 1 + KBUF);
-          TRACE(17)
         }
         w.wait(a_bar(i), s_par(i), 25);           // the gradient products have read the [queries, hd] copies
-        TRACE(18)
         if (i + MBUF < iters) load_m(i + MBUF);
-        TRACE(19)
       }
     }
   } else if (warp == MMA_WARP) {
@@ -571,15 +560,11 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
       for (int i = 0; i < iters; i++) {
         if (i + 1 < iters) {                      // next block's scores, under this block's element math
           w.wait(qk_bar(i + 1), qk_par(i + 1), 22);
-          TRACE(0)
           tc_fence_after();
           mma_s(i + 1);
-          TRACE(1)
         }
         w.wait(qm_bar(i), qm_par(i), 24);
-        TRACE(2)
         w.wait(p_bar(i), s_par(i), 24);
-        TRACE(3)
         tc_fence_after();
         const uint32_t tm_p = tmem + (i & 1) * 2 * NQ;   // P^T and dS^T where the math warps wrote them: over S^T, dP^T
         const uint32_t moff = (MBUF == 2 && (i & 1)) ? S::QT_BYTES : 0;
@@ -589,7 +574,6 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
         for (int j = 0; j < NQ / 8; j++)
           umma_tf32_ts(tm_dk, tm_p + NQ + j * 8, desc_off(d_qm, moff + j * 1024), idesc_g, (i > 0 || j > 0) ? 1u : 0u);
         umma_commit(a_bar(i));
-        TRACE(4)
       }
       // The end of the accumulation has a barrier of its own, used once (the math warps do not follow acc_done).
       // The issuing thread waits for it too, whatever happened before: no MMA may be in flight when TMEM is freed.
@@ -601,14 +585,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
     const int kg = k0 + qd * 32 + lane;      // key position in the sequence: one row of the tile per thread
     const uint32_t lane_base = (uint32_t)(qd * 32) << 16;
     int c_h = kvh * group, c_qb = 0;         // (head, query block) of block i, kept by counting
-#ifdef GT_ATTN_TRACE
-    const bool trm = tr && warp == 0;
-#define TRACEM(slot) if (trm && i >= 8 && i < 40) { long long tn = clock64(); flag[64 + (i - 8) * 32 + slot] = (int)(tn - tprev); tprev = tn; }
-#else
-#define TRACEM(slot)
-#endif
     for (int i = 0; i < iters; i++) {
-      TRACEM(8)
       const int h = c_h;
       const int qpos0 = (qb_lo + c_qb) * NQ + half * NH;         // first query of this thread's columns
       if (++c_qb == nqb) { c_qb = 0; c_h++; }
@@ -624,7 +601,6 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
         for (int c4 = 0; c4 < NH / 4; c4++) { Lv[c4] = __ldg(l4 + c4); Dv[c4] = __ldg(d4 + c4); }
       }
       w.wait(s_bar(i), s_par(i), 26);
-      TRACEM(9)
       tc_fence_after();
       float s[NH], dp[NH];
       const uint32_t tm_s = tmem + (i & 1) * 2 * NQ + half * NH + lane_base;
@@ -632,7 +608,6 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
       tmem_ld_issue<NH>(tm_s + NQ, dp);
       tmem_wait_ld();
       if constexpr (SPLIT == 2) xs.add<NH, NH>(w, i, (int)threadIdx.x, s, dp, 29);   // + the other half of the head
-      TRACEM(10)
       if (interior) {
 #pragma unroll
         for (int c4 = 0; c4 < NH / 4; c4++) {
@@ -661,7 +636,6 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
           dp[c] = d;
         }
       }
-      TRACEM(11)
       // In place: these columns were last read by the gradient products of block i-2, which the tensor pipe
       // finished before it wrote the scores of block i there.
       tmem_st_issue<NH>(tm_s, s);
@@ -669,9 +643,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(p_bar(i));
-      TRACEM(13)
     }
-#undef TRACEM
     w.wait(all_done, 0, 28);
     tc_fence_after();
     {   // warp-uniform: the TMEM loads are warp-wide instructions, only the stores are per-row
@@ -704,7 +676,6 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
       }
     }
   }
-#undef TRACE
   tc_fence_before();
   if (SPLIT == 2) cluster_sync_all(); else __syncthreads();   // neither CTA of a pair leaves while the other may still write to it
   if (warp == MMA_WARP) {

@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "libgguftrain_cuda.so")
 SOURCES = ["ctx.cu", "gemm_simt.cu", "gemm_tc.cu", "elementwise.cu", "norm.cu", "rope_embed.cu", "attention.cu",
-           "attention_simt.cu", "attention_tc.cu", "loss.cu", "optim.cu", "dp.cu", "noalloc.cu"]
+           "attention_simt.cu", "attention_tc.cu", "loss.cu", "optim.cu", "dp.cu", "noalloc.cu", "ingest.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 EXTRA = os.environ.get("GT_NVCC_EXTRA", "").split()
 FLAGS = EXTRA + ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math=false",

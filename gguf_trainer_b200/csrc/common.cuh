@@ -41,6 +41,8 @@ struct gt_ctx {
   // small scratch for reductions (never pooled)
   float* scratch = nullptr;
   uint64_t scratch_bytes = 0;
+  std::vector<float*> retired_scratch;   // outgrown scratch blocks: captured graphs may still name them, freed with the context
+  int* flags = nullptr;   // 256 zero-initialised device words: latched conditions and self-resetting counters (gt_flags)
   // staging
   void* pinned = nullptr;
   uint64_t pinned_bytes = 0, pinned_cursor = 0;
@@ -50,12 +52,25 @@ struct gt_ctx {
   std::vector<cudaGraphExec_t> graphs;
   cudaEvent_t events[64] = {};
   GtDp* dp = nullptr;
+  // asynchronous reads (gt_read_async): a copy stream, and pinned blocks recycled by size
+  cudaStream_t copy_stream = nullptr;
+  cudaEvent_t copy_fork = nullptr, copy_done = nullptr;
+  bool copy_pending = false;
+  struct AsyncRead { void* pinned; uint64_t bytes; cudaEvent_t done; };
+  std::unordered_map<uint64_t, AsyncRead> async_reads;
+  std::multimap<uint64_t, void*> pinned_free;
+  uint64_t next_ticket = 1;
 };
 
 gt_status gt_fail(gt_ctx* ctx, gt_status code, const char* fmt, ...);
 gt_status gt_check_cuda(gt_ctx* ctx, cudaError_t e, const char* what);
 // scratch of at least `bytes` (grows outside graph capture only)
 gt_status gt_scratch(gt_ctx* ctx, uint64_t bytes, float** out);
+// 256 device words that start at zero (allocated on first use, never inside a graph capture: null then).
+// GT_FLAG_WINDOW is raised by the window gather when a window leaves the corpus and is read and cleared by gt_sync;
+// the counters are left at zero by the kernels that use them.
+int* gt_flags(gt_ctx* ctx);
+enum { GT_FLAG_WINDOW = 0, GT_FLAG_TOKEN_MAX = 1, GT_FLAG_NORM_COUNTER = 8 };
 
 #define GT_CUDA(ctx, call)                                              \
   do {                                                                  \

@@ -28,16 +28,26 @@ gt_status gt_check_cuda(gt_ctx* ctx, cudaError_t e, const char* what) {
 gt_status gt_scratch(gt_ctx* ctx, uint64_t bytes, float** out) {
   if (bytes > ctx->scratch_bytes) {
     if (ctx->capturing) return gt_fail(ctx, GT_ERR_STATE, "scratch growth to %llu bytes inside a graph capture; run the step once eagerly first", (unsigned long long)bytes);
-    // the old block may still be read by queued kernels: drain first
-    GT_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    if (ctx->scratch) cudaFree(ctx->scratch);
+    // The old block may still be read by queued kernels, and every graph captured so far has its address recorded
+    // in its kernel nodes: it is retired, not freed, and goes away with the context.
+    if (ctx->scratch) ctx->retired_scratch.push_back(ctx->scratch);
     ctx->scratch = nullptr;
+    ctx->scratch_bytes = 0;
     uint64_t want = bytes < (8u << 20) ? (8u << 20) : bytes;
     GT_CUDA(ctx, cudaMalloc(&ctx->scratch, want));
     ctx->scratch_bytes = want;
   }
   *out = ctx->scratch;
   return GT_OK;
+}
+
+int* gt_flags(gt_ctx* ctx) {
+  if (!ctx->flags) {
+    if (ctx->capturing) return nullptr;
+    if (cudaMalloc(&ctx->flags, 256 * sizeof(int)) != cudaSuccess) { cudaGetLastError(); ctx->flags = nullptr; return nullptr; }
+    cudaMemsetAsync(ctx->flags, 0, 256 * sizeof(int), ctx->stream);
+  }
+  return ctx->flags;
 }
 
 extern "C" {
@@ -77,7 +87,15 @@ gt_status gt_destroy(gt_ctx* ctx) {
   for (auto& kv : ctx->rope_tables) cudaFree(kv.second);
   for (auto ev : ctx->events) if (ev) cudaEventDestroy(ev);
   if (ctx->scratch) cudaFree(ctx->scratch);
+  for (float* p : ctx->retired_scratch) cudaFree(p);
   if (ctx->pinned) cudaFreeHost(ctx->pinned);
+  if (ctx->flags) cudaFree(ctx->flags);
+  if (ctx->copy_stream) cudaStreamSynchronize(ctx->copy_stream);
+  for (auto& kv : ctx->async_reads) { cudaFreeHost(kv.second.pinned); cudaEventDestroy(kv.second.done); }
+  for (auto& kv : ctx->pinned_free) cudaFreeHost(kv.second);
+  if (ctx->copy_fork) cudaEventDestroy(ctx->copy_fork);
+  if (ctx->copy_done) cudaEventDestroy(ctx->copy_done);
+  if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
   cudaStreamDestroy(ctx->stream);
   delete ctx;
   return GT_OK;
@@ -94,6 +112,9 @@ gt_status gt_device_name(gt_ctx* ctx, char* out, int32_t cap) {
 
 gt_status gt_set_precision(gt_ctx* ctx, int32_t mode) {
   GT_REQUIRE(ctx, mode >= GT_PREC_FP32 && mode <= GT_PREC_BF16, "gt_set_precision: unknown mode %d", mode);
+  if (mode == GT_PREC_BF16)
+    return gt_fail(ctx, GT_ERR_UNSUPPORTED, "gt_set_precision: there are no BF16 kernels in this library (a single BF16 product is 1.6e-3 off in "
+                   "relative L2, which leaves no room under the 2e-3 bound of a whole step); use GT_PREC_TF32 or GT_PREC_FP32");
   ctx->precision = mode;
   return GT_OK;
 }
@@ -235,6 +256,79 @@ gt_status gt_sync(gt_ctx* ctx) {
   ctx->readback_bytes = 0;
   gt_status ts = gt_gemm_tc_check(ctx);
   if (ts) return ts;
+  if (ctx->flags) {
+    int h = 0;
+    GT_CUDA(ctx, cudaMemcpyAsync(&h, ctx->flags + GT_FLAG_WINDOW, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    GT_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (h != 0) {
+      cudaMemsetAsync(ctx->flags + GT_FLAG_WINDOW, 0, sizeof(int), ctx->stream);
+      return gt_fail(ctx, GT_ERR_ARG, "gt_gather_windows: a window start past corpus length - T - 1 was given; its rows were ignored");
+    }
+  }
+  return GT_OK;
+}
+
+// ---- asynchronous reads: weights and optimizer state on their way to a checkpoint while the next step runs
+//      (readStateBuffer, src/backend/webgpu.ts:1492-1503, is the blocking form) ----
+static gt_status copy_stream_ready(gt_ctx* ctx) {
+  if (ctx->copy_stream) return GT_OK;
+  if (ctx->capturing) return gt_fail(ctx, GT_ERR_STATE, "gt_read_async inside a graph capture");
+  GT_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
+  GT_CUDA(ctx, cudaEventCreateWithFlags(&ctx->copy_fork, cudaEventDisableTiming));
+  GT_CUDA(ctx, cudaEventCreateWithFlags(&ctx->copy_done, cudaEventDisableTiming));
+  return GT_OK;
+}
+
+gt_status gt_read_async(gt_ctx* ctx, gt_buf src, uint64_t bytes, uint64_t* out_ticket) {
+  GT_REQUIRE(ctx, src && bytes > 0 && out_ticket, "gt_read_async: null argument");
+  if (ctx->capturing) return gt_fail(ctx, GT_ERR_STATE, "gt_read_async inside a graph capture");
+  gt_status s = copy_stream_ready(ctx);
+  if (s) return s;
+  // a pinned block of at least this size, recycled from finished reads when one fits
+  void* pinned = nullptr;
+  uint64_t cap = (bytes + 4095) / 4096 * 4096;
+  auto it = ctx->pinned_free.lower_bound(cap);
+  if (it != ctx->pinned_free.end() && it->first <= 2 * cap) {
+    pinned = it->second;
+    cap = it->first;
+    ctx->pinned_free.erase(it);
+  } else {
+    GT_CUDA(ctx, cudaMallocHost(&pinned, cap));
+  }
+  gt_ctx::AsyncRead r{pinned, cap, nullptr};
+  GT_CUDA(ctx, cudaEventCreateWithFlags(&r.done, cudaEventDisableTiming));
+  // the copy starts once everything enqueued so far on the compute stream has run, and runs beside what follows
+  GT_CUDA(ctx, cudaEventRecord(ctx->copy_fork, ctx->stream));
+  GT_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_stream, ctx->copy_fork, 0));
+  GT_CUDA(ctx, cudaMemcpyAsync(pinned, gt_ptr<void>(src), bytes, cudaMemcpyDeviceToHost, ctx->copy_stream));
+  GT_CUDA(ctx, cudaEventRecord(r.done, ctx->copy_stream));
+  ctx->copy_pending = true;
+  const uint64_t ticket = ctx->next_ticket++;
+  ctx->async_reads[ticket] = r;
+  *out_ticket = ticket;
+  return GT_OK;
+}
+
+gt_status gt_read_fence(gt_ctx* ctx) {
+  if (!ctx->copy_pending) return GT_OK;
+  if (ctx->capturing) return gt_fail(ctx, GT_ERR_STATE, "gt_read_fence inside a graph capture");
+  GT_CUDA(ctx, cudaEventRecord(ctx->copy_done, ctx->copy_stream));
+  GT_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->copy_done, 0));
+  ctx->copy_pending = false;
+  return GT_OK;
+}
+
+gt_status gt_read_finish(gt_ctx* ctx, uint64_t ticket, void* host, uint64_t bytes) {
+  auto it = ctx->async_reads.find(ticket);
+  if (it == ctx->async_reads.end()) return gt_fail(ctx, GT_ERR_ARG, "gt_read_finish: unknown ticket %llu", (unsigned long long)ticket);
+  GT_REQUIRE(ctx, host && bytes <= it->second.bytes, "gt_read_finish: %llu bytes asked of a %llu-byte read", (unsigned long long)bytes,
+             (unsigned long long)it->second.bytes);
+  GT_CUDA(ctx, cudaEventSynchronize(it->second.done));
+  memcpy(host, it->second.pinned, bytes);
+  ctx->readback_bytes += bytes;
+  cudaEventDestroy(it->second.done);
+  ctx->pinned_free.emplace(it->second.bytes, it->second.pinned);
+  ctx->async_reads.erase(it);
   return GT_OK;
 }
 

@@ -12,7 +12,8 @@ constexpr int BM = 128, BN = 128, BK = 16, TM = 8, TN = 8, PAD = 4;
 template <bool A_KCONTIG, bool B_KCONTIG>
 __global__ void __launch_bounds__(256) gemm_f32_kernel(int M, int N, int K, const float* __restrict__ a, long sam, long sak,
                                                        const float* __restrict__ b, long sbn, long sbk,
-                                                       float* __restrict__ c, int accum, int ksplit, float alpha) {
+                                                       float* __restrict__ c, int accum, int ksplit, float alpha,
+                                                       float* __restrict__ part) {
   __shared__ __align__(16) float As[BK][BM + PAD];
   __shared__ __align__(16) float Bs[BK][BN + PAD];
   const int tid = threadIdx.x;
@@ -73,9 +74,18 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(int M, int N, int K, cons
       if (gn >= N) continue;
       float* dst = c + (long)gm * N + gn;
       const float v = acc[i][j] * alpha;
-      if (ksplit > 1) atomicAdd(dst, v);
+      if (ksplit > 1) part[((size_t)blockIdx.z * M + gm) * N + gn] = v;   // summed in slice order by splitk_sum_kernel
       else *dst = accum ? *dst + v : v;
     }
+  }
+}
+
+// c (+)= part[0] + part[1] + ... in slice order: split-K without atomics, the same bits on every run
+__global__ void splitk_sum_kernel(long n, int ksplit, const float* __restrict__ part, float* __restrict__ c, int accum) {
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    float acc = accum ? c[i] : 0.f;
+    for (int z = 0; z < ksplit; z++) acc += part[(size_t)z * n + i];
+    c[i] = acc;
   }
 }
 
@@ -83,33 +93,39 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(int M, int N, int K, cons
 
 gt_status gt_gemm_simt(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c, float alpha) {
   dim3 grid(gt_cdiv(N, BN), gt_cdiv(M, BM), 1);
-  // Few output tiles and a deep K (the dW product, K = rows): split K across CTAs and reduce with
-  // f32 atomics into C. Order of the partial sums then varies run to run at the 1e-7 level.
+  // Few output tiles and a deep K (the dW product, K = rows): split K across CTAs; the slices' partial products go
+  // to scratch and are added in slice order by a second kernel, so the result does not depend on scheduling.
   int ksplit = 1;
   long tiles = (long)grid.x * grid.y;
   if (tiles < ctx->sm_count && K >= 1024) {
     ksplit = (int)min((long)(2 * ctx->sm_count / tiles), (long)(K / 256));
     if (ksplit < 1) ksplit = 1;
   }
-  if (ksplit > 1 && !accum) {
-    cudaError_t e = cudaMemsetAsync(c, 0, sizeof(float) * (size_t)M * N, ctx->stream);
-    if (e != cudaSuccess) return gt_check_cuda(ctx, e, "gemm split-K clear");
+  float* part = nullptr;
+  if (ksplit > 1) {
+    gt_status s = gt_scratch(ctx, sizeof(float) * (size_t)ksplit * M * N, &part);
+    if (s) return s;
   }
   grid.z = ksplit;
   switch (kind) {
     case GT_GEMM_NT:
-      gemm_f32_kernel<true, true><<<grid, 256, 0, ctx->stream>>>(M, N, K, a, K, 1, b, K, 1, c, accum, ksplit, alpha);
+      gemm_f32_kernel<true, true><<<grid, 256, 0, ctx->stream>>>(M, N, K, a, K, 1, b, K, 1, c, accum, ksplit, alpha, part);
       break;
     case GT_GEMM_NN:
-      gemm_f32_kernel<true, false><<<grid, 256, 0, ctx->stream>>>(M, N, K, a, K, 1, b, 1, N, c, accum, ksplit, alpha);
+      gemm_f32_kernel<true, false><<<grid, 256, 0, ctx->stream>>>(M, N, K, a, K, 1, b, 1, N, c, accum, ksplit, alpha, part);
       break;
     case GT_GEMM_TN:
-      gemm_f32_kernel<false, false><<<grid, 256, 0, ctx->stream>>>(M, N, K, a, 1, M, b, 1, N, c, accum, ksplit, alpha);
+      gemm_f32_kernel<false, false><<<grid, 256, 0, ctx->stream>>>(M, N, K, a, 1, M, b, 1, N, c, accum, ksplit, alpha, part);
       break;
     default:
       return gt_fail(ctx, GT_ERR_ARG, "gt_gemm: unknown kind %d", kind);
   }
   GT_LAUNCHED(ctx, "gemm_f32_kernel");
+  if (ksplit > 1) {
+    const long n = (long)M * N;
+    splitk_sum_kernel<<<(int)min((long)ctx->sm_count * 8, (n + 255) / 256), 256, 0, ctx->stream>>>(n, ksplit, part, c, accum);
+    GT_LAUNCHED(ctx, "splitk_sum_kernel");
+  }
   return GT_OK;
 }
 

@@ -135,11 +135,6 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
       const uint64_t b_desc0 = B_K ? desc_kmajor(base + S::A_BYTES) : desc_mnmajor(base + S::A_BYTES);
       constexpr uint32_t A_STEP = A_K ? 32 : 1024, B_STEP = B_K ? 32 : 1024;   // bytes per K = 8 step
       uint32_t it = 0, tl = 0;
-#ifdef GT_ATTN_TRACE
-      const long long tr_c0 = clock64();
-      const uint64_t tr_t0 = gtimer();
-      long long tr_wait = 0;
-#endif
       for (int t = blockIdx.x; t < ntiles; t += gridDim.x, tl++) {
         const int z = (t % per_mat) / (tiles_n * tiles_m);
         const int kb0 = z * per, kb1 = min(kblocks, kb0 + per);
@@ -149,13 +144,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         tc_fence_after();
         for (int kb = kb0; kb < kb1; kb++, it++) {
           const int s = it % STAGES;
-#ifdef GT_ATTN_TRACE
-          const long long tr_w0 = clock64();
-#endif
           wait(full_bar(s), (it / STAGES) & 1, 2);
-#ifdef GT_ATTN_TRACE
-          tr_wait += clock64() - tr_w0;
-#endif
           tc_fence_after();
           const uint32_t soff = (uint32_t)(s * S::STAGE) >> 4;
 #pragma unroll
@@ -174,12 +163,6 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
           umma_commit(empty_bar(s));   // the stage is free once these MMAs have read it
         }
       }
-#ifdef GT_ATTN_TRACE
-      if (blockIdx.x == 0) {   // cycles, nanoseconds, K blocks, tiles and cycles spent waiting for operands
-        flag[64] = (int)(clock64() - tr_c0); flag[65] = (int)(gtimer() - tr_t0); flag[66] = (int)it; flag[67] = (int)tl;
-        flag[68] = (int)tr_wait;
-      }
-#endif
     }
   } else {
     // ---- epilogue: warp w may touch TMEM lanes [32*(w%4), 32*(w%4)+32) ----
@@ -716,12 +699,3 @@ gt_status gt_gemm_tc2(gt_ctx* ctx, int kind, int accum, int M, int N, int K, con
   return gemm_tc_dispatch(ctx, kind, accum, M, N, K, a, b, K2, a2, b2, c, 1, 1.f, handled);
 }
 
-#ifdef GT_ATTN_TRACE
-// Development aid (compiled out by default): copies the trace words a traced kernel left behind the device flag.
-extern "C" int gtx_debug_trace(gt_ctx* ctx, int* out, int n) {
-  int* f = g_flag[ctx->device];
-  if (!f) return -1;
-  cudaStreamSynchronize(ctx->stream);
-  return (int)cudaMemcpy(out, f + 64, sizeof(int) * n, cudaMemcpyDeviceToHost);
-}
-#endif

@@ -14,6 +14,40 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
+// Column sums for dw, two ways. Atomic: warps add into the CTA's shared array and CTAs into gw with f32 atomics, in
+// whatever order they arrive (the tensor-core modes, whose split-K products are order-dependent anyway). Ordered
+// (`part` given; strict-f32 mode): warps add one after the other, each CTA stores its sums to part[cta][d], and the
+// CTA that arrives last (a counter it leaves at zero again) adds the CTAs' rows in index order on top of gw or of
+// zero: the same bits on every run, which is what lets a recompute step equal a plain one bit for bit.
+template <typename AddOwn>
+__device__ __forceinline__ void dw_finish(float* sdw, int d, float* gw, int accum_w, float* part, int* counter, AddOwn add_own) {
+  if (part == nullptr) {
+    add_own(true);
+    __syncthreads();
+    for (int j = threadIdx.x; j < d; j += blockDim.x) atomicAdd(&gw[j], sdw[j]);
+    return;
+  }
+  const int wcta = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int wi = 0; wi < nw; wi++) {
+    if (wcta == wi) add_own(false);
+    __syncthreads();
+  }
+  for (int j = threadIdx.x; j < d; j += blockDim.x) part[(size_t)blockIdx.x * d + j] = sdw[j];
+  __threadfence();
+  __shared__ int s_last;
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(counter, 1) == (int)gridDim.x - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int j = threadIdx.x; j < d; j += blockDim.x) {
+    float acc = accum_w ? gw[j] : 0.f;
+    for (unsigned b = 0; b < gridDim.x; b++) acc += __ldcg(&part[(size_t)b * d + j]);
+    gw[j] = acc;
+  }
+  if (threadIdx.x == 0) *counter = 0;
+}
+
 // NPL = elements per lane (d <= 32*NPL)
 template <int NPL>
 __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(int rows, int d, const float* __restrict__ x,
@@ -44,7 +78,7 @@ template <int NPL>
 __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(int rows, int d, const float* __restrict__ x,
                                                           const float* __restrict__ w, const float* __restrict__ rinv,
                                                           const float* __restrict__ g, float* gx, int accum_x,
-                                                          float* gw) {
+                                                          float* gw, int accum_w, float* part, int* counter) {
   extern __shared__ float sdw[];  // [d] block-level column partials
   const int lane = threadIdx.x & 31;
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -87,10 +121,13 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(int rows, int d, const
     for (int i = 0; i < NPL; i++) dwv[i] = fmaf(gv[i] * xv[i], r, dwv[i]);
   }
   if (gw) {
+    dw_finish(sdw, d, gw, accum_w, part, counter, [&](bool atomic) {
 #pragma unroll
-    for (int i = 0; i < NPL; i++) { int j = lane + 32 * i; if (j < d) atomicAdd(&sdw[j], dwv[i]); }
-    __syncthreads();
-    for (int j = threadIdx.x; j < d; j += blockDim.x) atomicAdd(&gw[j], sdw[j]);
+      for (int i = 0; i < NPL; i++) {
+        int j = lane + 32 * i;
+        if (j < d) { if (atomic) atomicAdd(&sdw[j], dwv[i]); else sdw[j] += dwv[i]; }
+      }
+    });
   }
 }
 
@@ -99,7 +136,7 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(int rows, int d, const
 template <int V4, int TH>
 __global__ void __launch_bounds__(TH) rmsnorm_bwd_vec_kernel(int rows, int d, const float* __restrict__ x, const float* __restrict__ w,
                                                               const float* __restrict__ rinv, const float* __restrict__ g, float* gx,
-                                                              int accum_x, float* gw) {
+                                                              int accum_x, float* gw, int accum_w, float* part, int* counter) {
   extern __shared__ float sdw[];
   const int lane = threadIdx.x & 31;
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -162,27 +199,52 @@ __global__ void __launch_bounds__(TH) rmsnorm_bwd_vec_kernel(int rows, int d, co
     }
   }
   if (gw) {
+    dw_finish(sdw, d, gw, accum_w, part, counter, [&](bool atomic) {
 #pragma unroll
-    for (int i = 0; i < V4; i++) {
-      const int j = lane + 32 * i;
-      if (j < d4) {
-        atomicAdd(&sdw[4 * j + 0], dwv[i].x); atomicAdd(&sdw[4 * j + 1], dwv[i].y);
-        atomicAdd(&sdw[4 * j + 2], dwv[i].z); atomicAdd(&sdw[4 * j + 3], dwv[i].w);
+      for (int i = 0; i < V4; i++) {
+        const int j = lane + 32 * i;
+        if (j < d4) {
+          if (atomic) {
+            atomicAdd(&sdw[4 * j + 0], dwv[i].x); atomicAdd(&sdw[4 * j + 1], dwv[i].y);
+            atomicAdd(&sdw[4 * j + 2], dwv[i].z); atomicAdd(&sdw[4 * j + 3], dwv[i].w);
+          } else {
+            sdw[4 * j + 0] += dwv[i].x; sdw[4 * j + 1] += dwv[i].y; sdw[4 * j + 2] += dwv[i].z; sdw[4 * j + 3] += dwv[i].w;
+          }
+        }
       }
-    }
-    __syncthreads();
-    for (int j = threadIdx.x; j < d; j += blockDim.x) atomicAdd(&gw[j], sdw[j]);
+    });
   }
+}
+
+// Prepares dw's accumulation: ordered mode gets the per-CTA partial rows (context scratch) and the arrival counter;
+// atomic mode clears gw first unless it accumulates.
+gt_status dw_mode(gt_ctx* ctx, int blocks, int d, float* gw, int accum_w, bool ordered, float** part, int** counter) {
+  if (ordered) {
+    int* flags = gt_flags(ctx);
+    if (!flags) return gt_fail(ctx, GT_ERR_STATE, "gt_rmsnorm_bwd: first use inside a graph capture; run the step once eagerly first");
+    gt_status s = gt_scratch(ctx, sizeof(float) * (size_t)blocks * d, part);
+    if (s) return s;
+    *counter = flags + GT_FLAG_NORM_COUNTER;
+    return GT_OK;
+  }
+  if (!accum_w) GT_CUDA(ctx, cudaMemsetAsync(gw, 0, sizeof(float) * d, ctx->stream));
+  return GT_OK;
 }
 
 template <int V4, int TH = (V4 >= 8 ? 256 : 512)>
 gt_status launch_bwd_vec(gt_ctx* ctx, int rows, int d, const float* x, const float* w, const float* rinv, const float* g, float* gx,
-                         int accum_x, float* gw) {
+                         int accum_x, float* gw, int accum_w, bool ordered) {
   // Narrow rows (the per-head norms, d = 128 or 256) keep few bytes in flight per warp: more resident CTAs make up for it.
   // (Only with many rows: every CTA ends with d atomics on dw, which a short launch would feel.)
   const int per_sm = (V4 <= 2 && rows >= 65536) ? (V4 == 1 ? 4 : 3) : 512 / TH;
   int blocks = min(gt_cdiv(rows, TH / 32), ctx->sm_count * per_sm);
-  rmsnorm_bwd_vec_kernel<V4, TH><<<blocks, TH, sizeof(float) * d, ctx->stream>>>(rows, d, x, w, rinv, g, gx, accum_x, gw);
+  float* part = nullptr;
+  int* counter = nullptr;
+  if (gw) {
+    gt_status s = dw_mode(ctx, blocks, d, gw, accum_w, ordered, &part, &counter);
+    if (s) return s;
+  }
+  rmsnorm_bwd_vec_kernel<V4, TH><<<blocks, TH, sizeof(float) * d, ctx->stream>>>(rows, d, x, w, rinv, g, gx, accum_x, gw, accum_w, part, counter);
   GT_LAUNCHED(ctx, "rmsnorm_bwd_vec_kernel");
   return GT_OK;
 }
@@ -196,10 +258,16 @@ gt_status launch_fwd(gt_ctx* ctx, int rows, int d, const float* x, const float* 
 }
 template <int NPL>
 gt_status launch_bwd(gt_ctx* ctx, int rows, int d, const float* x, const float* w, const float* rinv, const float* g,
-                     float* gx, int accum_x, float* gw) {
+                     float* gx, int accum_x, float* gw, int accum_w, bool ordered) {
   // fewer, fatter blocks when dw is wanted: each block ends with d global atomics
   int blocks = min(gt_cdiv(rows, 8), ctx->sm_count * (gw ? 4 : 8));
-  rmsnorm_bwd_kernel<NPL><<<blocks, 256, sizeof(float) * d, ctx->stream>>>(rows, d, x, w, rinv, g, gx, accum_x, gw);
+  float* part = nullptr;
+  int* counter = nullptr;
+  if (gw) {
+    gt_status s = dw_mode(ctx, blocks, d, gw, accum_w, ordered, &part, &counter);
+    if (s) return s;
+  }
+  rmsnorm_bwd_kernel<NPL><<<blocks, 256, sizeof(float) * d, ctx->stream>>>(rows, d, x, w, rinv, g, gx, accum_x, gw, accum_w, part, counter);
   GT_LAUNCHED(ctx, "rmsnorm_bwd_kernel");
   return GT_OK;
 }
@@ -229,19 +297,19 @@ gt_status gt_rmsnorm_bwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf x, gt_buf 
   const float* px = gt_ptr<const float>(x); const float* pw = gt_ptr<const float>(w);
   const float* pr = gt_ptr<const float>(rinv); const float* pg = gt_ptr<const float>(gy);
   float* pgx = gt_ptr<float>(gx); float* pgw = gt_ptr<float>(gw);
-  if (pgw && !accum_w) GT_CUDA(ctx, cudaMemsetAsync(pgw, 0, sizeof(float) * d, ctx->stream));
+  const bool ordered = ctx->precision == GT_PREC_FP32;   // strict-f32 mode: dw bit-identical from run to run
   if ((d & 3) == 0 && d >= 128 && d <= 1024 && ((((uintptr_t)px) | ((uintptr_t)pw) | ((uintptr_t)pg) | ((uintptr_t)pgx)) & 15) == 0) {
-    if (d <= 128) return launch_bwd_vec<1>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw);
-    if (d <= 256) return launch_bwd_vec<2>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw);
-    if (d <= 640) return launch_bwd_vec<5>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw);
-    return launch_bwd_vec<8>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw);
+    if (d <= 128) return launch_bwd_vec<1>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw, accum_w, ordered);
+    if (d <= 256) return launch_bwd_vec<2>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw, accum_w, ordered);
+    if (d <= 640) return launch_bwd_vec<5>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw, accum_w, ordered);
+    return launch_bwd_vec<8>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw, accum_w, ordered);
   }
-  if (d <= 64) return launch_bwd<2>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw);
-  if (d <= 128) return launch_bwd<4>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw);
-  if (d <= 256) return launch_bwd<8>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw);
-  if (d <= 640) return launch_bwd<20>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw);
-  if (d <= 1024) return launch_bwd<32>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw);
-  return launch_bwd<64>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw);
+  if (d <= 64) return launch_bwd<2>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw, accum_w, ordered);
+  if (d <= 128) return launch_bwd<4>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw, accum_w, ordered);
+  if (d <= 256) return launch_bwd<8>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw, accum_w, ordered);
+  if (d <= 640) return launch_bwd<20>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw, accum_w, ordered);
+  if (d <= 1024) return launch_bwd<32>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw, accum_w, ordered);
+  return launch_bwd<64>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw, accum_w, ordered);
 }
 
 }  // extern "C"

@@ -111,6 +111,38 @@ gt_status rope_table(gt_ctx* ctx, int T, int hd, double base, int pos_offset, co
   return GT_OK;
 }
 
+// The same scatter-add with one owner per table row and a fixed order of additions (strict-f32 mode): the CTA of
+// position t does nothing unless t is the first occurrence of its id; otherwise it marks every later occurrence in a
+// shared-memory bitmap and each thread adds its columns over the marked rows in ascending position. This is the
+// reference's rule (one owner per gradient element, src/backend/webgpu.ts:21-26) without its O(V) scan.
+__global__ void __launch_bounds__(128) embedding_bwd_ordered_kernel(int rows, int d, const float* __restrict__ g,
+                                                                    const uint32_t* __restrict__ ids, float* gw) {
+  extern __shared__ uint32_t bits[];   // one bit per position
+  const int t = blockIdx.x;
+  const uint32_t id = ids[t];
+  int earlier = 0;
+  for (int u = threadIdx.x; u < t; u += blockDim.x) earlier |= (ids[u] == id);
+  if (__syncthreads_or(earlier)) return;
+  const int words = (rows + 31) >> 5;
+  for (int wd = threadIdx.x; wd < words; wd += blockDim.x) bits[wd] = 0u;
+  __syncthreads();
+  for (int u = t + (int)threadIdx.x; u < rows; u += blockDim.x)
+    if (ids[u] == id) atomicOr(&bits[u >> 5], 1u << (u & 31));
+  __syncthreads();
+  for (int j = threadIdx.x; j < d; j += blockDim.x) {
+    float acc = gw[(size_t)id * d + j];
+    for (int wd = t >> 5; wd < words; wd++) {
+      uint32_t m = bits[wd];
+      while (m) {
+        const int u = (wd << 5) + __ffs(m) - 1;
+        m &= m - 1;
+        acc += g[(size_t)u * d + j];
+      }
+    }
+    gw[(size_t)id * d + j] = acc;
+  }
+}
+
 template <bool BWD>
 gt_status rope_run(gt_ctx* ctx, int rows, int H, int hd, double base, int pos_offset, const float* in, float* out, int accum) {
   GT_REQUIRE(ctx, rows > 0 && H > 0 && hd > 0 && hd % 2 == 0, "gt_rope: rows %d H %d hd %d (hd must be even)", rows, H, hd);
@@ -159,6 +191,12 @@ gt_status gt_embedding_fwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf w, gt_bu
 gt_status gt_embedding_bwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf gy, gt_buf ids, gt_buf gw) {
   if (!gw) return GT_OK;
   GT_REQUIRE(ctx, rows > 0 && d > 0 && gy && ids, "gt_embedding_bwd: bad argument");
+  if (ctx->precision == GT_PREC_FP32 && rows <= 8 * 40960) {   // (the bitmap fits the default shared-memory limit)
+    embedding_bwd_ordered_kernel<<<rows, 128, sizeof(uint32_t) * ((rows + 31) / 32), ctx->stream>>>(rows, d, gt_ptr<const float>(gy),
+                                                                                                  gt_ptr<const uint32_t>(ids), gt_ptr<float>(gw));
+    GT_LAUNCHED(ctx, "embedding_bwd_ordered_kernel");
+    return GT_OK;
+  }
   long n = (long)rows * d;
   int grid = (int)min((long)ctx->sm_count * 16, (n + 255) / 256);
   embedding_bwd_kernel<<<grid, 256, 0, ctx->stream>>>(n, d, gt_ptr<const float>(gy), gt_ptr<const uint32_t>(ids), gt_ptr<float>(gw));

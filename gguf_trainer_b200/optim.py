@@ -18,6 +18,41 @@ from .backend import CudaBackend
 OPT_MAGIC = 0x4F505431  # "OPT1"
 
 
+class PendingCheckpoint:
+    """Weights and optimizer state on their way to the host while training goes on (`beginCheckpoint`). The copies
+    were ordered after the optimizer step that preceded the call and run on a copy stream beside the next step's
+    forward and backward; that step's optimizer waits for them on the device before it overwrites anything.
+    `finish()` blocks until they have landed, fills every parameter's host `data` (what `syncWeightsToHost` does) and
+    returns the state dict (what `exportState` returns)."""
+
+    def __init__(self, gpu: CudaBackend):
+        self.gpu = gpu
+        self._weights = []      # (tensor, ticket)
+        self._state = []        # (key, ticket, size)
+        self._scalars = {}
+        self._lists = []        # keys that are lists even when empty
+
+    def addWeight(self, t: Tensor):
+        self._weights.append((t, self.gpu.readAsync(self.gpu.buffersFor(t)["data"], t.size * 4)))
+
+    def addState(self, key: str, addr: int, size: int):
+        self._state.append((key, self.gpu.readAsync(addr, size * 4), size))
+
+    def finish(self):
+        for t, ticket in self._weights:
+            self.gpu.readFinish(ticket, t.data)
+        out: Dict[str, list] = {}
+        for key, ticket, size in self._state:
+            a = np.empty(size, np.float32)
+            self.gpu.readFinish(ticket, a)
+            out.setdefault(key, []).append(a)
+        for key in self._lists:
+            out.setdefault(key, [])
+        out.update(self._scalars)
+        self._weights, self._state = [], []
+        return out
+
+
 class AdamWGpu:
     def __init__(self, gpu: CudaBackend, params: Sequence[Tensor], lr: float, beta1: float = 0.9, beta2: float = 0.999,
                  eps: float = 1e-8, weightDecay: float = 0.0, clip: float = 1.0):
@@ -46,10 +81,25 @@ class AdamWGpu:
         """No-op: gradients are device-resident and restart at the next step's first write."""
 
     def recordStep(self):
+        self.gpu.readFence()      # a checkpoint still being copied out reads the values this step overwrites
         self.gpu._check(self.gpu.lib.gt_adamw_step(self.gpu.ctx, self.handle))
 
     def syncWeightsToHost(self):
         self.gpu.sync(self.params)
+
+    def beginCheckpoint(self, into: Optional[PendingCheckpoint] = None, keys=("m", "v", "t")) -> PendingCheckpoint:
+        """`syncWeightsToHost` + `exportState` without stopping the device: see PendingCheckpoint."""
+        ck = into or PendingCheckpoint(self.gpu)
+        for i, p in enumerate(self.params):
+            ck.addWeight(p)
+            m, v = self._state(i)
+            ck.addState(keys[0], m, p.size)
+            ck.addState(keys[1], v, p.size)
+        t = C.c_int32()
+        self.gpu._check(self.gpu.lib.gt_adamw_get_t(self.gpu.ctx, self.handle, C.byref(t)))
+        ck._scalars[keys[2]] = int(t.value)
+        ck._lists.extend(keys[:2])
+        return ck
 
     def _state(self, i):
         m, v = C.c_uint64(), C.c_uint64()
@@ -112,11 +162,21 @@ class MuonGpu:
         self.aux.zeroGrad()
 
     def recordStep(self):
+        self.gpu.readFence()
         self.gpu._check(self.gpu.lib.gt_muon_step(self.gpu.ctx, self.handle))
         self.aux.recordStep()
 
     def syncWeightsToHost(self):
         self.gpu.sync(self.muonParams + self.auxParams)
+
+    def beginCheckpoint(self) -> PendingCheckpoint:
+        """`syncWeightsToHost` + `exportState` (muon-gpu.ts:440-470) without stopping the device."""
+        ck = PendingCheckpoint(self.gpu)
+        ck._lists.append("muonMomentum")
+        for i, p in enumerate(self.muonParams):
+            ck.addWeight(p)
+            ck.addState("muonMomentum", self._momentum(i), p.size)
+        return self.aux.beginCheckpoint(ck, keys=("adamM", "adamV", "adamT"))
 
     def _momentum(self, i) -> int:
         b = C.c_uint64()

@@ -1,8 +1,9 @@
 """Step loops. `trainLMGpuResident` mirrors src/backend/train-gpu.ts:162-258 call for call (rng order,
-masks, two syncs per step, checkpoint cadence). `trainLMCuda` is its batched twin for this backend:
+masks, two syncs per step, checkpoint cadence). `CudaStep` is the batched form for this backend:
 the B sequences of a step travel as one [B*T]-row call, the forward+backward is captured once as a
-CUDA graph and replayed, and with several ranks the gradients are summed over NCCL before the
-optimizer step. Both consume the rng in the same order, so a given seed draws the same windows.
+CUDA graph and replayed, and with several ranks (`DataParallel`) the gradients are summed over NCCL
+before the optimizer step. `drawWindows` consumes the rng in the reference's order, so a given seed
+draws the same windows in both loops.
 """
 from __future__ import annotations
 
@@ -24,6 +25,12 @@ def sequenceLoss(model, inputIds, targetIds, lossChunk: int = 0) -> Tensor:
         r = model.forwardToReadout(inputIds)
         return fusedCrossEntropy(r["hidden"], r["readout"], targetIds, lossChunk)
     return crossEntropy(model.forward(inputIds), targetIds)
+
+
+def freezeForScoring(model) -> None:
+    """src/train/loss.ts:52-54: a model that is only scored gets no gradient buffers and stages nothing back."""
+    for p in model.params():
+        p.requiresGrad = False
 
 
 def maskWindow(targetIds: np.ndarray, supervised: np.ndarray, start: int) -> np.ndarray:
@@ -147,7 +154,8 @@ class CudaStep:
     loss is their mean, so gradients equal `batch` reference micro-batches seeded with 1/batch."""
 
     def __init__(self, model, gpu: CudaBackend, batch: int, seqLen: int, lossChunk: int = 0, world: int = 1,
-                 capture: bool = True, dp: Optional["DataParallel"] = None, arena=None, layersPerBucket: int = 6):
+                 capture: bool = True, dp: Optional["DataParallel"] = None, arena=None, layersPerBucket: int = 6,
+                 source=None):
         """`dp` + `arena` turn on the gradient exchange: `arena` is what `reserveGradArena(list(reversed(params)))`
         returned, i.e. the parameter gradients in the order backward completes them (last layer first, the tied
         embedding last). The arena is cut into buckets of `layersPerBucket` layers; each bucket's all-reduce is started
@@ -161,6 +169,10 @@ class CudaStep:
         self.graph = None
         self.lossTensor: Optional[Tensor] = None
         self.launchesPerReplay = 0
+        # `source` (an ingest.DeviceTokenSource) switches the step's input from ids/targets arrays to window starts:
+        # `runWindows(starts)` gathers ids and targets on the device as the first kernel of the (recorded) step.
+        self.source = source
+        self._winBufs = None
 
     def bucketPlan(self):
         """[(first layer of the bucket, arena offset, element count)] in the order the buckets complete, the last entry
@@ -231,11 +243,46 @@ class CudaStep:
                 self.graph = gpu.endCapture({"loss": loss})
                 self.launchesPerReplay = gpu.kernelLaunches() - before
                 self.lossTensor = loss
-            for (addr, count), arr in zip(self.graph.inputs, self.graphInputs(ids, targets)):
-                a = _as_u32(arr)
-                if a.size != count:
-                    raise ValueError(f"step input has {a.size} elements, recorded {count}")
-                gpu._check(gpu.lib.gt_write(gpu.ctx, addr, a.ctypes.data, a.nbytes))
+            self.graph.writeInputs(self.graphInputs(ids, targets))   # range-checked like the eager ops' inputs
+            self.replay()
+        finally:
+            gpu.setBatch(0)
+            gpu.uninstall()
+
+    def runWindows(self, starts: Sequence[int]) -> None:
+        """The same step fed by `batch` window starts into the device-resident corpus (`source`): 8 bytes per sequence
+        cross the bus instead of 8 bytes per token."""
+        from .ingest import DeviceInts
+        src, gpu, B, T = self.source, self.gpu, self.batch, self.seqLen
+        if src is None:
+            raise ValueError("runWindows needs a DeviceTokenSource (CudaStep(..., source=...))")
+        if len(starts) != B:
+            raise ValueError(f"{len(starts)} window starts for a batch of {B}")
+        seed = 1.0 / self.world
+        gpu.install()
+        gpu.setBatch(B, T)
+        try:
+            if not self.capture:
+                gpu.sync([])
+                ids, tg = src.gather(starts, T)
+                self.lossTensor = self._once(ids, tg, seed)
+                return
+            if self.graph is None:
+                sbuf = src.writeStarts(starts, T)
+                ids = DeviceInts(gpu._acquirePersistent(B * T * 4), B * T, src.vocabSize)
+                tg = DeviceInts(gpu._acquirePersistent(B * T * 4), B * T, src.vocabSize)
+                self._winBufs = (sbuf, ids, tg)
+                src.gatherInto(sbuf, B, T, ids.addr, tg.addr)
+                warm = self._once(ids, tg, seed)
+                gpu.sync([warm])
+                before = gpu.kernelLaunches()
+                gpu.beginCapture(seed=seed, accumulate=False)
+                src.gatherInto(sbuf, B, T, ids.addr, tg.addr)        # first node of the recorded step
+                loss = self._once(ids, tg, seed)
+                self.graph = gpu.endCapture({"loss": loss})
+                self.launchesPerReplay = gpu.kernelLaunches() - before
+                self.lossTensor = loss
+            src.writeStarts(starts, T)        # range-checked; lands in the buffer the recorded gather reads
             self.replay()
         finally:
             gpu.setBatch(0)

@@ -45,7 +45,8 @@ gt_status gt_init(int32_t device, gt_ctx** out);
 gt_status gt_destroy(gt_ctx* ctx);
 const char* gt_last_error(gt_ctx* ctx);            /* ctx may be NULL: last init error */
 gt_status gt_device_name(gt_ctx* ctx, char* out, int32_t cap); /* adapterName / describeDevice */
-/* Matrix-product precision: strict f32 FMA, or TF32 / BF16 tensor cores with f32 accumulation. */
+/* Matrix-product precision: GT_PREC_FP32 = strict f32 FMA, GT_PREC_TF32 = TF32 tensor cores with f32 accumulation.
+ * GT_PREC_BF16 is reserved: no BF16 kernels exist and the call answers GT_ERR_UNSUPPORTED, leaving the mode unchanged. */
 gt_status gt_set_precision(gt_ctx* ctx, int32_t mode);
 /* Rows handed to the ops are `batch` independent sequences of `seq_len` rows each (RoPE
  * positions wrap, attention is block-diagonal, losses are per sequence). batch=0 restores the
@@ -59,6 +60,16 @@ gt_status gt_alloc_state(gt_ctx* ctx, uint64_t bytes, gt_buf* out); /* zero-fill
 gt_status gt_free(gt_ctx* ctx, gt_buf buf);                         /* back to the pool */
 gt_status gt_write(gt_ctx* ctx, gt_buf dst, const void* host, uint64_t bytes);
 gt_status gt_read(gt_ctx* ctx, gt_buf src, void* host, uint64_t bytes); /* blocks until the data is on the host */
+/* The same read without blocking the caller or the compute stream (checkpoints taken while training goes on:
+ * MuonGpu.syncWeightsToHost / exportState, src/backend/muon-gpu.ts:440-470, built on readStateBuffer,
+ * src/backend/webgpu.ts:1492-1503). gt_read_async snapshots `bytes` at `src` as of the work enqueued so far into
+ * pinned memory owned by the library, on a copy stream that runs beside later compute. gt_read_fence makes the
+ * compute stream wait, on the device, for every read started so far: call it before enqueueing work that overwrites
+ * their sources (the next optimizer step). gt_read_finish blocks until that one read has landed and copies it to
+ * `host`; the pinned block is then recycled. */
+gt_status gt_read_async(gt_ctx* ctx, gt_buf src, uint64_t bytes, uint64_t* out_ticket);
+gt_status gt_read_fence(gt_ctx* ctx);
+gt_status gt_read_finish(gt_ctx* ctx, uint64_t ticket, void* host, uint64_t bytes);
 gt_status gt_zero(gt_ctx* ctx, gt_buf buf, uint64_t bytes);             /* clearBuffer */
 gt_status gt_copy(gt_ctx* ctx, gt_buf dst, gt_buf src, uint64_t bytes); /* seedGradFrom, webgpu.ts:748-761 */
 gt_status gt_sync(gt_ctx* ctx);                                         /* submit + wait; surfaces latched errors */
@@ -95,6 +106,17 @@ gt_status gt_rmsnorm_bwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf x, gt_buf 
 /* embedding gather / scatter-add (webgpu.ts:1090-1108, wgsl.ts:305-344); gw always accumulates */
 gt_status gt_embedding_fwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf w, gt_buf ids, gt_buf out);
 gt_status gt_embedding_bwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf gy, gt_buf ids, gt_buf gw);
+/* Token and mask ingest. `tokens` (and `mask`, 0 = none) are device copies of a token file as it is on disk: bare
+ * little-endian u16 or u32 values, bytes_per_token 2 or 4, `count` tokens (diskTokenSource, src/data/tokens.ts:158-185;
+ * the mask is read with the same width, src/commands/pretrain.ts:416). `starts` holds B window starts as u64 on the
+ * device. Writes ids[b*T+t] = tokens[start_b+t] and targets[b*T+t] = tokens[start_b+1+t], or 0xffffffff where
+ * mask[start_b+1+t] == 0 (maskWindow, src/train/trainer.ts:45-49; window draw src/backend/train-gpu.ts:206-208).
+ * A start beyond count-T-1 reads nothing: its rows come out ignored and the next gt_sync reports GT_ERR_ARG.
+ * gt_tokens_max returns the largest token value, so the host can refuse a corpus that does not fit the vocabulary
+ * once, at upload, instead of checking every window. */
+gt_status gt_gather_windows(gt_ctx* ctx, gt_buf tokens, gt_buf mask, int32_t bytes_per_token, uint64_t count, gt_buf starts,
+                            int32_t B, int32_t T, gt_buf ids, gt_buf targets);
+gt_status gt_tokens_max(gt_ctx* ctx, gt_buf tokens, int32_t bytes_per_token, uint64_t count, uint32_t* out_max);
 /* NeoX RoPE, x:[rows, H*hd], position = row (mod seq_len when a batch is set) + pos_offset (wgsl.ts:346-384) */
 gt_status gt_rope_fwd(gt_ctx* ctx, int32_t rows, int32_t H, int32_t hd, double base, int32_t pos_offset, gt_buf x, gt_buf y);
 gt_status gt_rope_bwd(gt_ctx* ctx, int32_t rows, int32_t H, int32_t hd, double base, int32_t pos_offset, gt_buf gy,
@@ -110,9 +132,12 @@ gt_status gt_attention_bwd(gt_ctx* ctx, int32_t rows, int32_t Hq, int32_t Hkv, i
  * cannot allocate device memory (hosts that give all of HBM to their own arena, or steps that cannot afford
  * cudaMalloc's device-wide synchronisation): its only scratch, the per-(head,row) dot products dO.O, sits
  * in a fixed 4 MiB array inside the library, so the call never allocates or frees. Limit: rows*Hq <=
- * 1048576, larger shapes are refused with GT_ERR_ARG. Always f32, whatever gt_set_precision says. The
- * first call on a device resolves the array's address (do it before any stream capture). All calls share
- * the array: calls that overlap on the GPU race, so keep them on one stream. */
+ * 1048576, larger shapes are refused with GT_ERR_ARG. Always f32, whatever gt_set_precision says: it
+ * recomputes the probabilities from q, k and lse in f32, so out and lse must come from a forward that ran in
+ * GT_PREC_FP32 (row statistics of a TF32 forward do not normalise f32 scores to better than about 1e-3). The
+ * first call on a device resolves the array's address, and may be what loads this part of the library onto
+ * the device (do it before any stream capture). All calls share the array: calls that overlap on the GPU
+ * race, so keep them on one stream. */
 gt_status gt_attention_bwd_static(gt_ctx* ctx, int32_t rows, int32_t Hq, int32_t Hkv, int32_t hd, int32_t window,
                                   gt_buf q, gt_buf k, gt_buf v, gt_buf out, gt_buf lse, gt_buf gout,
                                   gt_buf gq, int32_t accum_q, gt_buf gk, int32_t accum_k, gt_buf gv, int32_t accum_v);

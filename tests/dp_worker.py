@@ -1,5 +1,7 @@
 """Child process of tests/test_gpu_dp.py: one data-parallel rank on its own GPU.
-usage: dp_worker.py RANK WORLD WORKDIR STEPS BATCH_PER_RANK CAPTURE"""
+usage: dp_worker.py RANK WORLD WORKDIR STEPS BATCH_PER_RANK CAPTURE [OPTIMIZER]
+OPTIMIZER: adamw (default) or muon = Muon (5 Newton-Schulz iterations, momentum 0.95, Nesterov) on the hidden matrices
+and AdamW on embeddings and norms, the split of `paramGroups()` (src/backend/muon-gpu.ts:351-437)."""
 import os
 import sys
 import time
@@ -11,7 +13,7 @@ sys.path.insert(0, ROOT)
 
 from gguf_trainer_b200.arch import ModelConfig, buildModel  # noqa: E402
 from gguf_trainer_b200.backend import requireGPU  # noqa: E402
-from gguf_trainer_b200.optim import AdamWGpu  # noqa: E402
+from gguf_trainer_b200.optim import AdamWGpu, MuonGpu  # noqa: E402
 from gguf_trainer_b200.rng import Mulberry32  # noqa: E402
 from gguf_trainer_b200.train import CudaStep, DataParallel, drawWindows  # noqa: E402
 
@@ -21,6 +23,7 @@ T = 24
 
 def main():
     rank, world, work, steps, B, capture = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], int(sys.argv[4]), int(sys.argv[5]), sys.argv[6] == "1"
+    optimizer = sys.argv[7] if len(sys.argv) > 7 else "adamw"
     gpu = requireGPU("the data-parallel test", device=rank if world > 1 else 0)
     dp = None
     if world > 1:
@@ -42,7 +45,12 @@ def main():
     arena = gpu.reserveGradArena(list(reversed(m.params())))
     for p in m.params():
         gpu.keepGradOnDevice(p)
-    opt = AdamWGpu(gpu, m.params(), lr=1e-2, clip=1.0)
+    if optimizer == "muon":
+        g = m.paramGroups()
+        opt = MuonGpu(gpu, g["muon"], g["aux"], lr=0.02, momentum=0.95, nesterov=True, nsSteps=5,
+                      aux={"lr": 1e-2, "beta1": 0.9, "beta2": 0.95, "weightDecay": 0.0, "clip": 1.0})
+    else:
+        opt = AdamWGpu(gpu, m.params(), lr=1e-2, clip=1.0)
     tokens = Mulberry32(99).randint(400, CFG.vocabSize)
     rng = Mulberry32(7)
     step = CudaStep(m, gpu, B, T, world=world, capture=capture, dp=dp, arena=arena if dp else None, layersPerBucket=1)
@@ -56,7 +64,7 @@ def main():
         opt.recordStep()
         losses.append(step.losses()[1:].copy())
     gpu.sync(m.params())
-    np.savez(os.path.join(work, f"out_{world}_{rank}.npz"), losses=np.array(losses), *[p.data for p in m.params()])
+    np.savez(os.path.join(work, f"out_{optimizer}_{world}_{rank}.npz"), losses=np.array(losses), *[p.data for p in m.params()])
     gpu.destroy()
 
 

@@ -17,7 +17,7 @@ B, T, STEPS, WORLD = 2, 9, 2, 2
 
 
 def _windows(step, rank, world):
-    """The draw partition the benchmark and trainLMCuda use."""
+    """The draw partition the benchmark and `CudaStep` under `DataParallel` use."""
     sys.path.insert(0, ROOT)
     from gguf_trainer_b200.rng import Mulberry32
     from gguf_trainer_b200.train import drawWindows

@@ -1,0 +1,53 @@
+"""Whole-model parity in tf32 mode (the mode every benchmark number is measured in) at the depth and shapes the
+benchmark configurations run: loss, per-layer activations, every gradient and the post-AdamW weights against the CPU
+oracle, relative L2 <= 2e-3 each (the tensor-core modes' stated tolerance). The shape of the check follows the
+reference's whole-model parity case (tests/gpu-parity.ts:333-392); the cuts are described in tests/depth_cases.py."""
+import pytest
+
+from depth_cases import gemma3_cut, qwen3_cut, run_case, smollm2_cut
+from gpu_harness import REL_L2_TC
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def gpu():
+    from gguf_trainer_b200.backend import requireGPU
+    g = requireGPU("the depth parity suite", precision="tf32")
+    yield g
+    g.destroy()
+
+
+def check(res, what):
+    got, ref = res["loss"]
+    assert res["finite"], f"{what}: non-finite gradient"
+    assert abs(got - ref) <= REL_L2_TC * abs(ref), f"{what}: loss {got} vs {ref}"
+    for l, e in enumerate(res["layers"]):
+        assert e <= REL_L2_TC, f"{what}: output of layer {l}: relative L2 {e:.3e} (all layers: {[f'{x:.1e}' for x in res['layers']]})"
+    worst = max(res["grads"], key=lambda g: g[1])
+    for i, (shape, e) in enumerate(res["grads"]):
+        assert e <= REL_L2_TC, f"{what}: gradient {i} {shape}: relative L2 {e:.3e} (worst {worst})"
+    for i, (shape, e) in enumerate(res.get("weights", [])):
+        assert e <= REL_L2_TC, f"{what}: post-step weight {i} {shape}: relative L2 {e:.3e}"
+
+
+@pytest.mark.parametrize("round_weights", [False, True])
+def test_smollm2_depth_30_layers(gpu, oracle, round_weights):
+    """30 layers of the SmolLM2-135M shape. With `round_weights` every matrix holds bfloat16-exact values (what a
+    checkpoint loaded from a bf16 / f16 GGUF holds): operands that tf32 represents exactly."""
+    cfg, T = smollm2_cut()
+    check(run_case(gpu, oracle, cfg, T, round_weights=round_weights), f"smollm2 cut (bf16-exact weights: {round_weights})")
+
+
+def test_gemma3_depth_head_256_window(gpu, oracle):
+    """12 gemma3 layers: head size 256 (CTA-pair attention kernels), window 512 under a 640-row sequence on 5 of 6
+    layers, GeGLU, six norms per layer, scaled embedding."""
+    cfg, T = gemma3_cut()
+    check(run_case(gpu, oracle, cfg, T), "gemma3 cut")
+
+
+def test_qwen3_lora_recompute_fused_loss(gpu, oracle):
+    """28 Qwen3 layers with rank-16 adapters (alpha 32) on all seven projections over a frozen base, half of the
+    targets masked, recompute on, chunked readout loss with a ragged last chunk."""
+    cfg, T = qwen3_cut()
+    check(run_case(gpu, oracle, cfg, T, lora=(16, 32.0), mask_frac=0.5, recompute=True, loss_chunk=1024), "qwen3 lora cut")

@@ -5,7 +5,11 @@ HBM to its own arena, or a step loop that cannot take cudaMalloc's device-wide s
 the library keeps the one scratch array attention backward needs inside its own image. This test drives
 both entry points through the C ABI on the same inputs, twice in a row (the array is shared and keeps the
 previous call's contents), and checks the gradients agree; it also checks the size limit is refused with
-a message rather than overrun. Collected last so a failure here cannot hide any other test's result.
+a message rather than overrun. The allocation-free entry point runs FIRST on a fresh context, so nothing has
+warmed any scratch for it, and the device's free memory is read around its calls: the first call may load the
+library's code and its built-in array onto the device (documented set-up), later calls must leave free memory
+exactly as it was, while the regular entry point's first call visibly takes memory (its 8 MiB scratch block).
+Collected last so a failure here cannot hide any other test's result.
 """
 import ctypes as C
 
@@ -19,8 +23,13 @@ def test_static_scratch_attention_backward_matches_regular_entry_point(oracle):
     from gpu_harness import BWD, compare
     from gguf_trainer_b200.backend import requireGPU
 
+    import torch
+    free = lambda: torch.cuda.mem_get_info(0)[0]
+    free()                                     # (torch's own context set-up happens here, not inside a measurement)
     gpu = requireGPU("the allocation-free attention test")
     lib, ctx = gpu.lib, gpu.ctx
+    static_calls = 0
+    saw_regular_allocate = False
     try:
         for call, (T, Hq, Hkv, hd, window, seed) in enumerate([(70, 4, 2, 32, 0, 11), (193, 6, 3, 64, 50, 12)]):
             rng = oracle.Mulberry32(seed)
@@ -37,13 +46,20 @@ def test_static_scratch_attention_backward_matches_regular_entry_point(oracle):
             lse = gpu.createStateBuffer(Hq * T * 4)
             gpu._check(lib.gt_attention_fwd(ctx, T, Hq, Hkv, hd, window, dq, dk, dv, out, lse))
             grads = {}
-            for name, fn in (("regular", lib.gt_attention_bwd), ("static", lib.gt_attention_bwd_static)):
+            for name, fn in (("static", lib.gt_attention_bwd_static), ("regular", lib.gt_attention_bwd)):
                 gq, gk, gv = (gpu.createStateBuffer(x.nbytes) for x in (q, k, v))
-                before = gpu.stats()
+                gpu.sync([])
+                before, free_before = gpu.stats(), free()
                 gpu._check(fn(ctx, T, Hq, Hkv, hd, window, dq, dk, dv, out, lse, dgo, gq, 0, gk, 0, gv, 0))
+                gpu.sync([])
+                after, free_after = gpu.stats(), free()
                 if name == "static":
-                    after = gpu.stats()
+                    static_calls += 1
                     assert (after["pool"], after["state"]) == (before["pool"], before["state"])
+                    if static_calls > 1:       # past the documented first-call set-up: not a byte of device memory moves
+                        assert free_after == free_before, f"free memory {free_before} -> {free_after} across an allocation-free call"
+                elif free_after < free_before:
+                    saw_regular_allocate = True
                 grads[name] = [gpu.readStateBuffer(b, x.size) for b, x in ((gq, q), (gk, k), (gv, v))]
             for a, b, nm in zip(grads["static"], grads["regular"], ("dq", "dk", "dv")):
                 compare(f"call {call} {nm}", a, b, BWD, 1e-6)
@@ -51,6 +67,7 @@ def test_static_scratch_attention_backward_matches_regular_entry_point(oracle):
             _o, probs = oracle.attention_fwd(q, k, v, T, Hq, Hkv, hd, window)
             for a, b, nm in zip(grads["static"], oracle.attention_bwd(q, k, v, probs, go, T, Hq, Hkv, hd, window), ("dq", "dk", "dv")):
                 compare(f"call {call} {nm} vs oracle", a, b, BWD)
+        assert static_calls == 2 and saw_regular_allocate, "the free-memory probe never saw the regular path's scratch allocation"
         # beyond the built-in scratch: refused, with the limit in the message
         st = lib.gt_attention_bwd_static(ctx, 1 << 19, 4, 2, 32, 0, dq, dk, dv, out, lse, dgo, 0, 0, 0, 0, 0, 0)
         assert st == 2
