@@ -202,6 +202,52 @@ def backward_gemm_roofline(gpu, rows: int, iters: int = 5):
     return flops, ms, len(calls)
 
 
+def tf32_peak_and_comparator(rows: int, seconds: float = 3.0):
+    """Harness only (never on the product's path): the TF32 rate of this GPU measured the way MEASURED_PEAKS.json
+    measures BF16 (`torch.matmul` 8192^3 with allow_tf32, best of 10 and a seconds-long loop), and cuBLAS on the same 14
+    backward product shapes the roofline object times, as a same-box comparator."""
+    import torch
+    torch.backends.cuda.matmul.allow_tf32 = True
+
+    def timed(fn, n):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(n):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        return s.elapsed_time(e) / n
+
+    N = 8192
+    a, b = torch.randn(N, N, device="cuda"), torch.randn(N, N, device="cuda")
+    for _ in range(3):
+        a @ b
+    burst = 2 * N ** 3 / min(timed(lambda: a @ b, 1) for _ in range(10)) / 1e9
+    t0, tot, n = time.perf_counter(), 0.0, 0
+    while time.perf_counter() - t0 < seconds:
+        tot += timed(lambda: a @ b, 20) * 20
+        n += 20
+    sustained = 2 * N ** 3 / (tot / n) / 1e9
+    del a, b
+    h, q, kv, f = 576, 576, 192, 1536
+    flops, ops = 0, []
+    for out, inn in [(q, h), (kv, h), (kv, h), (h, q), (f, h), (f, h), (h, f)]:
+        dy, x, w = torch.randn(rows, out, device="cuda"), torch.randn(rows, inn, device="cuda"), torch.randn(out, inn, device="cuda")
+        ops.append((lambda dy=dy, w=w: dy @ w))
+        ops.append((lambda dy=dy, x=x: dy.t() @ x))
+        flops += 2 * 2 * rows * inn * out
+
+    def layer():
+        for op in ops:
+            op()
+
+    layer()
+    ms = timed(layer, 5)
+    torch.cuda.empty_cache()
+    return {"burst": burst, "sustained": sustained, "how": "torch.matmul allow_tf32 8192^3: best of 10, and back to back for 3 s"}, \
+        flops / (ms / 1e3) / 1e12
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -224,10 +270,15 @@ def run_ours(args):
 
     # The headline workload is the SmolLM2-135M shape; the other two configurations of the parity list can be timed too.
     cfg = {"smollm2": smolLM2_135M, "gemma3": gemma3_95M, "qwen3-lora": qwen3_0_6B}[args.config]()
-    B, T = args.batch, args.seq
+    # per-configuration defaults: the Qwen3 LoRA fine-tune runs batch 4 per GPU with the chunked (fused) readout loss
+    B = args.batch if args.batch > 0 else (4 if args.config == "qwen3-lora" else 8)
+    T = args.seq
     gpu = requireGPU("the benchmark", device=local, precision=args.precision)
+    if args.plain:
+        gpu.mergeInputGradients = False
+        gpu.fuseResidualNorm = False
     model = buildModel(cfg, 1234)       # same seed on every rank: replicated weights
-    loss_chunk = args.loss_chunk
+    loss_chunk = args.loss_chunk if args.loss_chunk >= 0 else (32768 if args.config == "qwen3-lora" else 0)
     mask = None
     if args.config == "qwen3-lora":      # frozen base, rank-16 adapters on the 7 projections, 50 % prompt mask, recompute
         from gguf_trainer_b200.lora import applyLora
@@ -243,16 +294,20 @@ def run_ours(args):
     arena = gpu.reserveGradArena(order)
     for p in params:
         gpu.keepGradOnDevice(p)
+    def make_muon():
+        return MuonGpu(gpu, groups["muon"], groups["aux"], lr=0.02, momentum=0.95, nesterov=True, nsSteps=5,
+                       aux={"lr": 1e-3, "beta1": 0.9, "beta2": 0.95, "weightDecay": 0.0, "clip": 1.0})
+
     if args.optimizer == "muon":
-        opt = MuonGpu(gpu, groups["muon"], groups["aux"], lr=0.02, aux={"lr": 1e-3, "beta1": 0.9, "beta2": 0.95,
-                                                                        "weightDecay": 0.0, "clip": 1.0})
+        opt = make_muon()
     else:
         opt = AdamWGpu(gpu, params, lr=1e-3, beta1=0.9, beta2=0.95, weightDecay=0.1, clip=1.0)
+    opts = {"cur": opt}
     dp = None
     if world > 1:
         uid = [DataParallel.uniqueId() if rank == 0 else None]
         dist.broadcast_object_list(uid, src=0)
-        dp = DataParallel(gpu, rank, world, uid[0])
+        dp = DataParallel(gpu, rank, world, uid[0], commCtas=args.comm_ctas)
 
     # synthetic stream; rank r takes draws [r*B, (r+1)*B) of each step's B*world windows
     need = (args.steps + args.warmup + 2) * B * world
@@ -288,7 +343,7 @@ def run_ours(args):
             pin_ids.numpy()[:] = ids
             pin_tg.numpy()[:] = tg
             step.run(pin_ids.numpy(), pin_tg.numpy())
-        opt.recordStep()                      # the gradient exchange is part of the step (started bucket by bucket in backward)
+        opts["cur"].recordStep()              # the gradient exchange is part of the step (started bucket by bucket in backward)
 
     def barrier():
         gpu.sync([])
@@ -326,6 +381,18 @@ def run_ours(args):
         sampler.start()
     ms_res, _ = timed(True, args.steps, args.warmup)
     ms_e2e, loss = timed(False, args.steps, args.warmup)
+    # Beside the headline (AdamW at every N, so the driver's scaling ratio compares like with like): the same step with
+    # the optimizer split of the multi-GPU configuration, Muon (5 Newton-Schulz iterations, momentum 0.95) on the hidden
+    # matrices and AdamW on embeddings and norms.
+    muon_line = None
+    if world > 1 and args.optimizer == "adamw" and args.config != "qwen3-lora" and groups["muon"]:
+        opts["cur"] = make_muon()
+        for i in range(3):
+            one_step(i, False)
+        ms_muon, _ = timed(True, args.steps, args.warmup)
+        muon_line = {"optimizer": "muon (5 Newton-Schulz iterations, momentum 0.95, Nesterov) on the hidden matrices + adamw on embeddings and norms",
+                     "value": B * T * world * args.steps / (ms_muon / 1e3), "unit": UNIT, "ms_per_step": ms_muon / args.steps}
+        opts["cur"] = opt
     clocks = sampler.stop() if rank == 0 else None
     eager_launches = gpu.kernelLaunches() - launches0
     tokens = B * T * world * args.steps
@@ -336,6 +403,9 @@ def run_ours(args):
         pk = peaks()
         flops, gms, ncalls = backward_gemm_roofline(gpu, B * T)
         achieved = flops / (gms / 1e3) / 1e12
+        tf32_peak, cublas_same = (None, None)
+        if not args.no_peak:
+            tf32_peak, cublas_same = tf32_peak_and_comparator(B * T)
         metric = METRIC if (args.config == "smollm2" and B == 8 and T == 2048) else f"train tokens/s, {args.config} shape seq{T} b{B}"
         line = {
             "metric": metric, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -344,9 +414,10 @@ def run_ours(args):
             "data": "synthetic",
             "config": {"workload": {"smollm2": "SmolLM2-135M shape llama (h576 L30 9/3 heads hd64 ffn1536 V49152, tied)",
                                     "gemma3": "gemma3 ~95M shape (h640 L12 4/1 heads hd256 ffn2048 V32768, window 512 on 5 of 6 layers)",
-                                    "qwen3-lora": "Qwen3-0.6B shape LoRA r16 (h1024 L28 16/8 heads hd128 ffn3072 V151936), frozen base, 50% loss mask, recompute"}[args.config]
+                                    "qwen3-lora": "Qwen3-0.6B shape LoRA r16 alpha 32 on q,k,v,o,gate,up,down (h1024 L28 16/8 heads hd128 ffn3072 V151936), frozen base, 50% loss mask, recompute"}[args.config]
                                    + f", full step fwd+bwd+{args.optimizer}, "
-                                   f"seq {T} x batch {B} per GPU, Zipf(1.1) ids, N(0,0.02) f32 weights",
+                                   + (f"chunked readout loss (chunk {loss_chunk}), " if loss_chunk else "dense readout loss, ")
+                                   + f"seq {T} x batch {B} per GPU, Zipf(1.1) ids, N(0,0.02) f32 weights",
                        "precision": args.precision, "graph_replay": not args.no_graph,
                        "l2": "per-step working set (activations > 20 GB) exceeds L2; no flush needed",
                        "parallelism": f"dp{world}"},
@@ -360,12 +431,20 @@ def run_ours(args):
                          # (profiles/gemm_tf32_rows16384.md), per launch; only meaningful at the default shape
                          "traffic": (1095.7e6 / 14) if (args.config == "smollm2" and B * T == 16384) else None,
                          "kernel": f"backward matrix products of one layer (dX and dW for 7 projections, {ncalls} launches, rows {B * T})",
-                         "peak_source": f"{pk['src']} bf16 sustained (tf32 runs at half the bf16 rate; no separate tf32 peak is measured)"},
+                         "peak_source": f"{pk['src']} bf16 sustained (the products run in tf32, whose own measured rate is tf32_peak)",
+                         "tf32_peak": tf32_peak,
+                         "frac_of_tf32_sustained": (achieved / (tf32_peak["sustained"] / 1e3)) if tf32_peak else None,
+                         "cublas_tf32_same_shapes": cublas_same},
         }
+        if muon_line is not None:
+            line["config3_optimizer"] = muon_line
         if args.gpus == 1 and not args.no_cpu:
             from oracle import oracle as orc
             orc.build()
             line["cpu_baseline"] = {k: v for k, v in cpu_slice(orc.max_threads(), T=args.cpu_tokens).items() if k != "seconds_measured"}
+            # the reference's CPU code is single-threaded: the same slice on one thread, on a shorter sequence to stay bounded
+            one = cpu_slice(1, T=64)
+            line["cpu_baseline"]["single_thread"] = {"value": one["value"], "unit": UNIT, "cores": 1, "sample": one["sample"]}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -382,7 +461,9 @@ def run_profile(args):
     from gguf_trainer_b200.optim import AdamWGpu
     from gguf_trainer_b200.train import CudaStep
     cfg = {"smollm2": smolLM2_135M, "gemma3": gemma3_95M, "qwen3-lora": qwen3_0_6B}[args.config]()
-    B, T = args.batch, args.seq
+    B = args.batch if args.batch > 0 else (4 if args.config == "qwen3-lora" else 8)
+    T = args.seq
+    loss_chunk = args.loss_chunk if args.loss_chunk >= 0 else (32768 if args.config == "qwen3-lora" else 0)
     gpu = requireGPU("the profile", precision=args.precision)
     m = buildModel(cfg, 1234)
     params = m.params()
@@ -399,7 +480,7 @@ def run_profile(args):
     for p in params:
         gpu.keepGradOnDevice(p)
     opt = AdamWGpu(gpu, params, lr=1e-3, beta1=0.9, beta2=0.95, weightDecay=0.1, clip=1.0)
-    step = CudaStep(m, gpu, B, T, lossChunk=args.loss_chunk, capture=False)
+    step = CudaStep(m, gpu, B, T, lossChunk=loss_chunk, capture=False)
     for _ in range(2):
         step.run(ids[:-1], tg); opt.recordStep(); gpu.sync([])
     gpu.startProfile()
@@ -478,19 +559,22 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--precision", default="tf32", choices=["fp32", "tf32"])
     ap.add_argument("--optimizer", default="adamw", choices=["adamw", "muon"])
-    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=0, help="sequences per GPU per step (default 8; 4 for qwen3-lora)")
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--cpu-tokens", type=int, default=256)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--config", default="smollm2", choices=["smollm2", "gemma3", "qwen3-lora"])
-    ap.add_argument("--loss-chunk", type=int, default=0)
+    ap.add_argument("--loss-chunk", type=int, default=-1, help="vocabulary chunk of the fused readout loss; 0 = dense (default: 0; 32768 for qwen3-lora)")
+    ap.add_argument("--no-peak", action="store_true", help="skip the torch.matmul TF32 peak and comparator")
     ap.add_argument("--recompute", action="store_true")
     ap.add_argument("--profile", action="store_true", help="per-entry-point GPU time of one eager step")
     ap.add_argument("--micro", default="", help="time one op of the step instead: attention | gemm")
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--window", type=int, default=0)
     ap.add_argument("--layers-per-bucket", type=int, default=6, help="data parallel: layers per gradient all-reduce bucket")
+    ap.add_argument("--comm-ctas", type=int, default=16, help="data parallel: CTAs left to the collective while it overlaps backward (0 = no cap, no reservation)")
+    ap.add_argument("--plain", action="store_true", help="launch every op as recorded: no merged input gradients, no residual add + norm fusion")
     ap.add_argument("--heads", default="", help="--micro attention: Hq,Hkv,hd instead of 9,3,64")
     args = ap.parse_args()
     if args.profile:

@@ -32,7 +32,7 @@ PRECISION = {"fp32": 0, "tf32": 1}   # (the C ABI reserves 2 for BF16 and refuse
 
 
 class _Entry:
-    __slots__ = ("data", "grad", "bytes", "external", "gradLive", "size")
+    __slots__ = ("data", "grad", "bytes", "external", "gradLive", "size", "pendingDx", "copyFrom")
 
     def __init__(self, data: int, grad: int, nbytes: int, external: bool, size: int):
         self.data = data
@@ -41,6 +41,8 @@ class _Entry:
         self.external = external
         self.gradLive = False     # has anything been written to grad in the current graph?
         self.size = size
+        self.pendingDx = None     # (rows, cols, [(dY address, W address, K)]): input-gradient products not launched yet
+        self.copyFrom = 0         # address whose contents are this gradient's value so far (a copy not made yet)
 
 
 class CapturedGraph:
@@ -195,6 +197,11 @@ class CudaBackend:
         self._readback = 0
         self._seedBuf = 0
         self._pendingAct = {}   # id(tensor) -> (tensor, op code, input tensor): activations not launched yet
+        self._pendingDx: Dict[int, _Entry] = {}   # entries whose gradient still lacks deferred dY.W products
+        self.mergeInputGradients = True
+        self._pendingAdd = {}   # id(tensor) -> (tensor, a, b): residual adds not launched yet (see add)
+        self._pendingCopy: Dict[int, _Entry] = {}  # entries whose gradient is still a view of another buffer (see add)
+        self.fuseResidualNorm = True
         self.fuseGatedUnits = True
         self.fuseLora = True               # adapter-carrying projections as one op (loraLinear) instead of four
         self._finalizer = weakref.finalize(self, _destroy_ctx, self.lib, self.ctx)
@@ -325,6 +332,8 @@ class CudaBackend:
         e = self._entries.get(t)
         if e is None and id(t) in self._pendingAct:
             e = self._materializeAct(t)
+        if e is None and id(t) in self._pendingAdd:
+            e = self._materializeAdd(t)
         if e is None:
             nbytes = t.size * 4
             if self._capturing:
@@ -342,6 +351,8 @@ class CudaBackend:
         e = self._entries.get(t)
         if e is None and id(t) in self._pendingAct:
             e = self._materializeAct(t)
+        if e is None and id(t) in self._pendingAdd:
+            e = self._materializeAdd(t)
         return e
 
     def _makeOut(self, shape, prev) -> tuple:
@@ -352,16 +363,75 @@ class CudaBackend:
         self._entries[t] = e
         return t, e
 
+    # The input gradient of `linear` is dX (+)= dY.W. An activation that feeds several projections (the normed input
+    # of q, k and v; of gate and up) collects one such product per consumer, and the reference issues them one by one,
+    # each re-reading and re-writing the [T, in] buffer (src/backend/webgpu.ts:884-903). Here a closure only notes its
+    # (dY, W, K); the products are launched together, as one matrix product whose contraction runs over all the K
+    # ranges (gt_gemm_multi), when the gradient is first needed: by the producer's own backward, by another writer, or
+    # at a sync, a region's end or a graph cut. Same terms, added in the same order.
+    def _deferDx(self, e: _Entry, rows: int, cols: int, dy: int, w: int, K: int):
+        if e.pendingDx is None:
+            e.pendingDx = (rows, cols, [])
+            self._pendingDx[id(e)] = e
+        e.pendingDx[2].append((dy, w, K))
+        if len(e.pendingDx[2]) == 8 or not self.mergeInputGradients:
+            self._flushDx(e)
+
+    # `add` backward hands the upstream gradient to both inputs (src/model/autograd.ts:382-397): two copies of a
+    # [T, hidden] buffer per residual connection. Here an input whose gradient has not been written yet only notes the
+    # upstream address (`copyFrom`). Readers of that gradient read the upstream buffer in place, and the one writer
+    # that follows in a transformer block, the norm's backward, adds its term on top of it while writing the real
+    # buffer (gt_rmsnorm_bwd_add). Any other writer, and every point where buffers may be recycled, makes the copy.
+    def _materializeCopy(self, e: _Entry):
+        self._check(self.lib.gt_copy(self.ctx, e.grad, e.copyFrom, e.bytes))
+        e.copyFrom = 0
+        e.gradLive = True
+        self._pendingCopy.pop(id(e), None)
+
+    def _flushAllCopies(self):
+        for e in list(self._pendingCopy.values()):
+            self._materializeCopy(e)
+
+    def _flushDx(self, e: _Entry):
+        if e.copyFrom:
+            self._materializeCopy(e)
+        rows, cols, parts = e.pendingDx
+        e.pendingDx = None
+        self._pendingDx.pop(id(e), None)
+        acc = 1 if e.gradLive else 0
+        e.gradLive = True
+        n = len(parts)
+        if n == 1:
+            self._gemm("NN", acc, rows, cols, parts[0][2], parts[0][0], parts[0][1], e.grad)
+            return
+        Ks = (C.c_int32 * n)(*[p[2] for p in parts])
+        As = (C.c_uint64 * n)(*[p[0] for p in parts])
+        Bs = (C.c_uint64 * n)(*[p[1] for p in parts])
+        self._check(self.lib.gt_gemm_multi(self.ctx, _KIND["NN"], acc, rows, cols, n, Ks, As, Bs, e.grad))
+
+    def _flushAllDx(self):
+        for e in list(self._pendingDx.values()):
+            self._flushDx(e)
+        self._flushAllCopies()
+
     def _gradTarget(self, t: Tensor, e: _Entry):
         """(grad address or 0, accum flag) for a backward kernel about to write into t's gradient."""
         if e.grad == 0 or (e.external and not t.requiresGrad):
             return 0, 0
+        if e.copyFrom:
+            self._materializeCopy(e)
+        if e.pendingDx is not None:
+            self._flushDx(e)
         acc = 1 if e.gradLive else 0
         e.gradLive = True
         return e.grad, acc
 
     def _gradSource(self, e: _Entry) -> int:
         """The upstream gradient of an op output. Never written means it is exactly zero."""
+        if e.pendingDx is not None:
+            self._flushDx(e)           # (a gradient that is still a view gets its copy made first: _flushDx writes into it)
+        if e.copyFrom:
+            return e.copyFrom          # still exactly the upstream buffer of an `add`: read it there, no copy
         if not e.gradLive:
             self._check(self.lib.gt_zero(self.ctx, e.grad, e.bytes))
             self.gradClearsIssued += 1
@@ -400,8 +470,10 @@ class CudaBackend:
         if self._capturing:
             raise _lib.GtError(4, "sync() inside a graph capture")
         self._readback = 0
+        self._flushAllDx()
         self._flushPendingActs(only=list(reads))
         self._pendingAct.clear()
+        self._pendingAdd.clear()
         seen = set()
         for t in reads:
             if id(t) in seen:
@@ -442,6 +514,7 @@ class CudaBackend:
 
     def reclaimStepTransients(self, keep: Sequence[Tensor] = ()):
         """webgpu.ts:612-633: recycle this micro-batch's transients without the readback."""
+        self._flushAllDx()
         keepBufs = set()
         for t in keep:
             e = self._entries.get(t)
@@ -500,6 +573,7 @@ class CudaBackend:
             raise RuntimeError(
                 f"endRegion: mark {mark} is past the {len(self._transients)} live transients; "
                 f"a sync() or reclaim ran inside the region")
+        self._flushAllDx()
         self._flushPendingActs(only=list(keep))
         keepBufs = set()
         for t in keep:
@@ -633,6 +707,7 @@ class CudaBackend:
         the host between two segments. Returns the number of segments closed so far."""
         if not self._capturing:
             raise _lib.GtError(4, "cutCapture: not capturing")
+        self._flushAllDx()
         h = C.c_uint64()
         self._check(self.lib.gt_graph_end(self.ctx, C.byref(h)))
         self._captureSegments.append(int(h.value))
@@ -641,6 +716,7 @@ class CudaBackend:
 
     def endCapture(self, outputs: Optional[Dict[str, Tensor]] = None) -> CapturedGraph:
         h = C.c_uint64()
+        self._flushAllDx()
         self._capturing = False
         self._check(self.lib.gt_graph_end(self.ctx, C.byref(h)))
         owned = self._transients[self._captureMark:] + self._regionFree
@@ -691,9 +767,8 @@ class CudaBackend:
         def _bw():
             self._ensureBackwardBegun()
             go = self._gradSource(eo)
-            gx, ax = self._gradTarget(x, ex)
-            if gx:
-                self._gemm("NN", ax, T, inDim, outDim, go, ew.data, gx)
+            if ex.grad and not (ex.external and not x.requiresGrad):
+                self._deferDx(ex, T, inDim, go, ew.data, outDim)
             if w.requiresGrad:
                 gw, aw = self._gradTarget(w, ew)
                 if gw:
@@ -726,7 +801,7 @@ class CudaBackend:
         def _bw():
             self._ensureBackwardBegun()
             go = self._gradSource(eo)
-            gx, ax = self._gradTarget(x, ex)
+            wantDx = bool(ex.grad) and not (ex.external and not x.requiresGrad)
             self._check(self.lib.gt_gemm_scaled(self.ctx, kNN, 0, T, r, outDim, go, eb.data, dt, s))   # dt = scale·(g·B)
             if b.requiresGrad:
                 gb, ab = self._gradTarget(b, eb)
@@ -736,8 +811,9 @@ class CudaBackend:
                 ga, aa = self._gradTarget(a, ea)
                 if ga:
                     self._gemm("TN", aa, r, inDim, T, dt, ex.data, ga)
-            if gx:
-                self._gemm2("NN", ax, T, inDim, outDim, go, ew.data, r, dt, ea.data, gx)
+            if wantDx:      # g·W + dt·A: two more K ranges of x's input-gradient product
+                self._deferDx(ex, T, inDim, go, ew.data, outDim)
+                self._deferDx(ex, T, inDim, dt, ea.data, r)
             if w.requiresGrad:
                 gw, aw = self._gradTarget(w, ew)
                 if gw:
@@ -771,7 +847,52 @@ class CudaBackend:
         return out
 
     def add(self, a, b):
-        return self._elementwise("add", a, b, 0.0)
+        """webgpu.ts:905-960. Not launched when recorded: if the first use of the sum is a norm (every residual
+        connection of a block), one kernel forms the sum and normalises it (gt_add_rmsnorm_fwd); any other use
+        launches the plain add then. Backward launches nothing where it can (see _materializeCopy)."""
+        if a is b or not self.fuseResidualNorm or a.shape != b.shape:
+            return self._elementwise("add", a, b, 0.0)
+        self._beginForwardOp()
+        ea, eb = self._entryFor(a), self._entryFor(b)
+        out = Tensor.zeros(a.shape)
+        out._prev = [a, b]
+        self._pendingAdd[id(out)] = (out, a, b)
+        n = a.size
+
+        def _bw():
+            eo = self._entries.get(out)
+            if eo is None:
+                return          # never used by anything: no gradient reaches it
+            self._ensureBackwardBegun()
+            go = self._gradSource(eo)
+            for t, e, first in ((a, ea, True), (b, eb, False)):
+                if e.grad == 0 or (e.external and not t.requiresGrad):
+                    continue
+                if e.pendingDx is not None:
+                    self._flushDx(e)
+                if e.gradLive or e.copyFrom:
+                    g, acc = self._gradTarget(t, e)
+                    self._check(self.lib.gt_ew_bwd(self.ctx, _EW["add"], n, ea.data, eb.data, 0.0, go,
+                                                   g if first else 0, acc, 0 if first else g, acc))
+                else:
+                    e.copyFrom = go
+                    self._pendingCopy[id(e)] = e
+
+        out._backward = _bw
+        return out
+
+    def _newEntry(self, t: Tensor) -> _Entry:
+        nbytes = t.size * 4
+        e = _Entry(self._acquireRecycled(nbytes), self._acquireRecycled(nbytes), nbytes, False, t.size)
+        self._entries[t] = e
+        return e
+
+    def _materializeAdd(self, t: Tensor) -> _Entry:
+        _t, a, b = self._pendingAdd.pop(id(t))
+        ea, eb = self._entries[a], self._entries[b]
+        e = self._newEntry(t)
+        self._check(self.lib.gt_ew_fwd(self.ctx, _EW["add"], t.size, ea.data, eb.data, 0.0, e.data))
+        return e
 
     def mul(self, a, b):
         if a is not b:
@@ -800,12 +921,13 @@ class CudaBackend:
 
         def _bw():
             e = self._entries.get(t)
-            if e is None or not e.gradLive:
+            if e is None or not (e.gradLive or e.copyFrom or e.pendingDx is not None):
                 return          # consumed only by fused products, which sent their gradient straight to x
             self._ensureBackwardBegun()
             ex = self._entries[x]
+            go = self._gradSource(e)
             gx, ax = self._gradTarget(x, ex)
-            self._check(self.lib.gt_ew_bwd(self.ctx, _EW[op], x.size, ex.data, 0, 0.0, e.grad, gx, ax, 0, 0))
+            self._check(self.lib.gt_ew_bwd(self.ctx, _EW[op], x.size, ex.data, 0, 0.0, go, gx, ax, 0, 0))
 
         t._backward = _bw
         return t
@@ -824,6 +946,10 @@ class CudaBackend:
             t = self._pendingAct[key][0]
             if only is None or any(t is o for o in only):
                 self._materializeAct(t)
+        for key in list(self._pendingAdd.keys()):
+            t = self._pendingAdd[key][0]
+            if only is None or any(t is o for o in only):
+                self._materializeAdd(t)
 
     def _gatedUnit(self, act: Tensor, u: Tensor) -> Tensor:
         _t, code, x = self._pendingAct[id(act)]
@@ -853,16 +979,37 @@ class CudaBackend:
     def _rmsNormRows(self, x: Tensor, w: Tensor, rows: int, d: int, eps: float, shape) -> Tensor:
         """webgpu.ts:1673-1701."""
         self._beginForwardOp()
-        ex, ew = self._entryFor(x), self._entryFor(w)
-        out, eo = self._makeOut(shape, [x, w])
-        rinv = self._acquireRecycled(rows * 4)
-        self._check(self.lib.gt_rmsnorm_fwd(self.ctx, rows, d, ex.data, ew.data, eps, eo.data, rinv))
+        ew = self._entryFor(w)
+        if id(x) in self._pendingAdd and x not in self._entries:
+            # x = a + b has not been launched and this norm is its first use: one kernel writes both
+            _t, a, b = self._pendingAdd.pop(id(x))
+            ea, eb = self._entries[a], self._entries[b]
+            ex = self._newEntry(x)
+            out, eo = self._makeOut(shape, [x, w])
+            rinv = self._acquireRecycled(rows * 4)
+            self._check(self.lib.gt_add_rmsnorm_fwd(self.ctx, rows, d, ea.data, eb.data, ew.data, eps, ex.data, eo.data, rinv))
+        else:
+            ex = self._entryFor(x)
+            out, eo = self._makeOut(shape, [x, w])
+            rinv = self._acquireRecycled(rows * 4)
+            self._check(self.lib.gt_rmsnorm_fwd(self.ctx, rows, d, ex.data, ew.data, eps, eo.data, rinv))
 
         def _bw():
             self._ensureBackwardBegun()
             go = self._gradSource(eo)
-            gx, ax = self._gradTarget(x, ex)
+            wantX = bool(ex.grad) and not (ex.external and not x.requiresGrad)
+            if wantX and ex.pendingDx is not None:
+                self._flushDx(ex)
             gw, aw = self._gradTarget(w, ew) if w.requiresGrad else (0, 0)
+            if wantX and ex.copyFrom and not ex.gradLive:
+                # the gradient so far is an `add`'s upstream buffer: dx = that buffer + this term, written in one pass
+                gadd = ex.copyFrom
+                ex.copyFrom = 0
+                self._pendingCopy.pop(id(ex), None)
+                ex.gradLive = True
+                self._check(self.lib.gt_rmsnorm_bwd_add(self.ctx, rows, d, ex.data, ew.data, rinv, go, gadd, ex.grad, gw, aw))
+                return
+            gx, ax = self._gradTarget(x, ex)
             self._check(self.lib.gt_rmsnorm_bwd(self.ctx, rows, d, ex.data, ew.data, rinv, go, gx, ax, gw, aw))
 
         out._backward = _bw
@@ -890,6 +1037,10 @@ class CudaBackend:
             if not weight.requiresGrad or not ew.grad:
                 return
             go = self._gradSource(eo)
+            if ew.pendingDx is not None:
+                self._flushDx(ew)
+            if ew.copyFrom:
+                self._materializeCopy(ew)
             if not ew.gradLive:
                 self._check(self.lib.gt_zero(self.ctx, ew.grad, ew.bytes))
                 self.gradClearsIssued += 1

@@ -21,6 +21,7 @@ struct gt_ctx {
   int precision = GT_PREC_FP32;
   int batch = 0, seq_len = 0;  // gt_set_batch
   int sm_count = 148;
+  int sm_reserved = 0;   // SMs left to a collective in flight (gt_dp_reserve_sms): persistent kernels size their grids without them
   // pool (BufferPool, webgpu.ts:214-262): exact-size free lists, 256-byte buckets
   std::map<uint64_t, std::vector<void*>> free_lists;
   std::unordered_map<void*, uint64_t> live;   // allocation -> bucket size (pooled)
@@ -100,8 +101,8 @@ gt_status gt_gemm_tc_batched(gt_ctx* ctx, int kind, int accum, int M, int N, int
                              int batch, bool* handled);
 // batch of same-shape products through whichever path gt_gemm would take for one of them
 gt_status gt_gemm_batched(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c, int batch);
-gt_status gt_gemm_tc2(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, int K2, const float* a2,
-                      const float* b2, float* c, bool* handled);
+gt_status gt_gemm_tc_multi(gt_ctx* ctx, int kind, int accum, int M, int N, int nparts, const int* Ks, const float* const* as,
+                           const float* const* bs, float* c, bool* handled);
 gt_status gt_gemm_tc_check(gt_ctx* ctx);
 void gt_optim_destroy(gt_ctx* ctx);
 void gt_dp_teardown(gt_ctx* ctx);

@@ -4,6 +4,7 @@
 // NCCL is resolved at run time (dlopen) so single-GPU users never need it.
 #include <dlfcn.h>
 #include <string.h>
+#include <time.h>
 
 #include "common.cuh"
 
@@ -93,6 +94,7 @@ gt_status gt_dp_init(gt_ctx* ctx, int32_t rank, int32_t world, const uint8_t* id
 gt_status gt_dp_allreduce_start(gt_ctx* ctx, gt_buf buf, uint64_t count) {
   GtDp* d = ctx->dp;
   if (!d) return gt_fail(ctx, GT_ERR_STATE, "gt_dp_allreduce_start: gt_dp_init has not run");
+  if (!d->comm) return gt_fail(ctx, GT_ERR_NCCL, "gt_dp_allreduce_start: the communicator was aborted; gt_dp_destroy and gt_dp_init again");
   if (count == 0) return GT_OK;
   GT_REQUIRE(ctx, buf, "gt_dp_allreduce_start: null buffer");
   GT_CUDA(ctx, cudaEventRecord(d->ready, ctx->stream));
@@ -111,8 +113,55 @@ gt_status gt_dp_wait(gt_ctx* ctx) {
   GT_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, d->done, 0));
   d->pending = false;
   ncclResult_t async = 0;
-  if (g_nccl.CommGetAsyncError(d->comm, &async) == 0 && async != 0)
+  if (d->comm && g_nccl.CommGetAsyncError(d->comm, &async) == 0 && async != 0 && async != 7 /* ncclInProgress */)
     return gt_fail(ctx, GT_ERR_NCCL, "NCCL asynchronous error: %s", g_nccl.GetErrorString(async));
+  return GT_OK;
+}
+
+// Host-side form of the wait, for callers that want to know that the exchange completed (or did not) before they
+// launch anything else: polls the last reduction's completion and the communicator's asynchronous error state for at
+// most timeout_ms. On expiry or on an NCCL error the communicator is aborted (ncclCommAbort ends its kernels, which
+// otherwise wait for the missing rank for ever) and the status is GT_ERR_NCCL; the context itself stays usable for
+// single-GPU work and gt_dp_init may be called again after gt_dp_destroy.
+gt_status gt_dp_wait_host(gt_ctx* ctx, int32_t timeout_ms) {
+  GtDp* d = ctx->dp;
+  if (!d) return gt_fail(ctx, GT_ERR_STATE, "gt_dp_wait_host: gt_dp_init has not run");
+  GT_REQUIRE(ctx, timeout_ms > 0, "gt_dp_wait_host: timeout %d ms", timeout_ms);
+  if (!d->comm) return gt_fail(ctx, GT_ERR_NCCL, "gt_dp_wait_host: the communicator was aborted");
+  if (d->pending) {
+    gt_status s = gt_dp_wait(ctx);
+    if (s) return s;
+  }
+  cudaEvent_t ev = d->done;
+  GT_CUDA(ctx, cudaEventRecord(ev, d->stream));
+  timespec t0;
+  clock_gettime(CLOCK_MONOTONIC, &t0);
+  for (;;) {
+    cudaError_t q = cudaEventQuery(ev);
+    if (q == cudaSuccess) return GT_OK;
+    if (q != cudaErrorNotReady) return gt_check_cuda(ctx, q, "gt_dp_wait_host");
+    ncclResult_t async = 0;
+    const bool bad = g_nccl.CommGetAsyncError(d->comm, &async) == 0 && async != 0 && async != 7 /* ncclInProgress */;
+    timespec t1;
+    clock_gettime(CLOCK_MONOTONIC, &t1);
+    const double ms = (t1.tv_sec - t0.tv_sec) * 1e3 + (t1.tv_nsec - t0.tv_nsec) / 1e6;
+    if (bad || ms > timeout_ms) {
+      g_nccl.CommAbort(d->comm);
+      d->comm = nullptr;
+      if (bad) return gt_fail(ctx, GT_ERR_NCCL, "NCCL asynchronous error: %s; communicator aborted", g_nccl.GetErrorString(async));
+      return gt_fail(ctx, GT_ERR_NCCL, "gradient exchange did not complete within %d ms (a rank is missing or stuck); communicator aborted", timeout_ms);
+    }
+    timespec nap = {0, 200000};
+    nanosleep(&nap, nullptr);
+  }
+}
+
+// While a reduction runs beside compute, its kernel holds a few SMs. A persistent kernel that still launches one CTA
+// per SM of the whole device then has CTAs that only start when others finish: its last wave doubles. Reserving those
+// SMs makes the persistent matrix-product kernels size their grids (and choose their tiles) for what is left.
+gt_status gt_dp_reserve_sms(gt_ctx* ctx, int32_t n) {
+  GT_REQUIRE(ctx, n >= 0 && n < ctx->sm_count, "gt_dp_reserve_sms: %d of %d SMs", n, ctx->sm_count);
+  ctx->sm_reserved = n;
   return GT_OK;
 }
 

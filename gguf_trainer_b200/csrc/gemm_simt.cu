@@ -159,19 +159,35 @@ extern "C" gt_status gt_gemm(gt_ctx* ctx, int32_t kind, int32_t accum, int32_t M
   return gt_gemm_scaled(ctx, kind, accum, M, N, K, a, b, c, 1.f);
 }
 
-// c (+)= op(a).op(b) + op(a2).op(b2): one launch on the tensor-core path (the second product's K blocks follow the
-// first's in the main loop), two accumulating products otherwise.
+// c (+)= sum_p op(a_p).op(b_p): one launch on the tensor-core path (each product's K blocks follow the previous one's in
+// the main loop), accumulating products otherwise.
+extern "C" gt_status gt_gemm_multi(gt_ctx* ctx, int32_t kind, int32_t accum, int32_t M, int32_t N, int32_t nparts, const int32_t* Ks,
+                                   const gt_buf* as, const gt_buf* bs, gt_buf c) {
+  GT_REQUIRE(ctx, M > 0 && N > 0 && nparts >= 1 && nparts <= 8 && Ks && as && bs && c, "gt_gemm_multi: %dx%d, %d products (1..8)", M, N, nparts);
+  const float* pa[8];
+  const float* pb[8];
+  int k[8];
+  for (int p = 0; p < nparts; p++) {
+    GT_REQUIRE(ctx, Ks[p] > 0 && as[p] && bs[p], "gt_gemm_multi: product %d is empty or has a null operand", p);
+    pa[p] = gt_ptr<const float>(as[p]); pb[p] = gt_ptr<const float>(bs[p]); k[p] = Ks[p];
+  }
+  if (ctx->precision != GT_PREC_FP32) {
+    bool handled = false;
+    gt_status s = gt_gemm_tc_multi(ctx, kind, accum, M, N, nparts, k, pa, pb, gt_ptr<float>(c), &handled);
+    if (s != GT_OK || handled) return s;
+  }
+  for (int p = 0; p < nparts; p++) {
+    gt_status s = gt_gemm(ctx, kind, p ? 1 : accum, M, N, k[p], as[p], bs[p], c);
+    if (s) return s;
+  }
+  return GT_OK;
+}
+
 extern "C" gt_status gt_gemm2(gt_ctx* ctx, int32_t kind, int32_t accum, int32_t M, int32_t N, int32_t K, gt_buf a, gt_buf b, int32_t K2,
                               gt_buf a2, gt_buf b2, gt_buf c) {
   GT_REQUIRE(ctx, M > 0 && N > 0 && K > 0 && K2 > 0, "gt_gemm2: empty product %dx%dx(%d+%d)", M, N, K, K2);
   GT_REQUIRE(ctx, a && b && a2 && b2 && c, "gt_gemm2: null operand");
-  if (ctx->precision != GT_PREC_FP32) {
-    bool handled = false;
-    gt_status s = gt_gemm_tc2(ctx, kind, accum, M, N, K, gt_ptr<const float>(a), gt_ptr<const float>(b), K2, gt_ptr<const float>(a2),
-                              gt_ptr<const float>(b2), gt_ptr<float>(c), &handled);
-    if (s != GT_OK || handled) return s;
-  }
-  gt_status s = gt_gemm(ctx, kind, accum, M, N, K, a, b, c);
-  if (s) return s;
-  return gt_gemm(ctx, kind, 1, M, N, K2, a2, b2, c);
+  const int32_t Ks[2] = {K, K2};
+  const gt_buf as[2] = {a, a2}, bs[2] = {b, b2};
+  return gt_gemm_multi(ctx, kind, accum, M, N, 2, Ks, as, bs, c);
 }

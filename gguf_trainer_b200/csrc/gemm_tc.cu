@@ -49,12 +49,19 @@ struct Smem {
 // Persistent: each CTA walks output tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... (n fastest, then m, then the
 // split-K slice), so CTAs running at the same time share their A row-blocks in L2.
 // A_K: A is K-major in memory (NT, NN); else MN-major ([K, M], TN). B_K: B is K-major (NT); else [K, N] (NN, TN).
+// Operands of one launch: up to MAX_PARTS products A_p.B_p of the same layout, K_p deep, summed into the same output
+// tiles. kb_end[p] is the number of K blocks of parts 0..p; only the TMA producer looks at it.
+constexpr int MAX_PARTS = 8;
+struct PartMaps {
+  CUtensorMap a[MAX_PARTS], b[MAX_PARTS];
+  int kb_end[MAX_PARTS];
+  int nparts;
+};
+
 template <bool A_K, bool B_K, int BN, int MT>
 __global__ void __launch_bounds__(Smem<BN, MT>::THREADS, 1)
-gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-                 const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapA2,
-                 const __grid_constant__ CUtensorMap mapB2, float* __restrict__ C, int M, int N, int K, int K2, int accum, int ksplit,
-                 int use_tma_store, int batch, float out_scale, int* __restrict__ flag) {
+gemm_tf32_kernel(const __grid_constant__ PartMaps maps, const __grid_constant__ CUtensorMap mapC, float* __restrict__ C, int M, int N,
+                 int accum, int ksplit, int use_tma_store, int batch, float out_scale, int* __restrict__ flag) {
   extern __shared__ uint8_t smem_raw[];
   using S = Smem<BN, MT>;
   constexpr int STAGES = S::STAGES, BM = S::BM;
@@ -72,10 +79,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
   const int tiles_n = (N + BN - 1) / BN, tiles_m = (M + BM - 1) / BM;
   const int per_mat = tiles_n * tiles_m * ksplit;
   const int ntiles = per_mat * batch;            // the matrices of a batch are just more tiles
-  // A second product A2.B2 of the same layout (K2 deep, 0 = none) is accumulated into the same tiles: its K blocks
-  // simply follow those of the first in the main loop, read through their own tensor maps.
-  const int kblocks1 = (K + BK - 1) / BK;
-  const int kblocks = kblocks1 + (K2 + BK - 1) / BK;
+  // Further products of the same layout are accumulated into the same tiles: their K blocks simply follow those of
+  // the first in the main loop, read through their own tensor maps.
+  const int kblocks = maps.kb_end[maps.nparts - 1];
   const int per = (kblocks + ksplit - 1) / ksplit;   // K blocks per split-K slice
   // TMEM slot of a 128-row accumulator and the parity of its hand-over barriers: with MT = 1 the tiles alternate
   // between two slots, with MT = 2 slot h holds half h of every tile.
@@ -83,8 +89,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
   auto par_of = [&](uint32_t tl) { return MT == 2 ? (tl & 1) : ((tl >> 1) & 1); };
 
   if (threadIdx.x == 0) {
-    tma_prefetch_map(&mapA); tma_prefetch_map(&mapB);
-    if (K2 > 0) { tma_prefetch_map(&mapA2); tma_prefetch_map(&mapB2); }
+    for (int p = 0; p < maps.nparts; p++) { tma_prefetch_map(&maps.a[p]); tma_prefetch_map(&maps.b[p]); }
     if (use_tma_store) tma_prefetch_map(&mapC);
     for (int s = 0; s < STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     for (int b = 0; b < 2; b++) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 128); }
@@ -109,14 +114,15 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         const int bi = t / per_mat, tt = t % per_mat;
         const int n0 = (tt % tiles_n) * BN, m0 = ((tt / tiles_n) % tiles_m) * BM, z = tt / (tiles_n * tiles_m);
         const int kb0 = z * per, kb1 = min(kblocks, kb0 + per);
+        int part = 0;
         for (int kb = kb0; kb < kb1; kb++, it++) {
           const int s = it % STAGES;
           wait(empty_bar(s), ((it / STAGES) & 1) ^ 1, 1);
           const uint32_t a_dst = base + s * S::STAGE, b_dst = a_dst + S::A_BYTES;
-          const bool second = kb >= kblocks1;
-          const CUtensorMap* pa = second ? &mapA2 : &mapA;
-          const CUtensorMap* pb = second ? &mapB2 : &mapB;
-          const int k0 = (second ? kb - kblocks1 : kb) * BK;
+          while (kb >= maps.kb_end[part]) part++;
+          const CUtensorMap* pa = &maps.a[part];
+          const CUtensorMap* pb = &maps.b[part];
+          const int k0 = (kb - (part ? maps.kb_end[part - 1] : 0)) * BK;
           mbar_expect_tx(full_bar(s), S::STAGE);
           if (A_K) tma_load_3d(a_dst, pa, k0, m0, bi, full_bar(s));
           else
@@ -439,8 +445,8 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
 int* g_flag[64] = {};
 
 template <bool A_K, bool B_K, int BN, int MT>
-gt_status launch(gt_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const CUtensorMap& ma2,
-                 const CUtensorMap& mb2, int tma_store, float* c, int M, int N, int K, int K2, int accum, int ksplit, int batch, float out_scale) {
+gt_status launch(gt_ctx* ctx, const PartMaps& maps, const CUtensorMap& mc, int tma_store, float* c, int M, int N, int accum, int ksplit,
+                 int batch, float out_scale) {
   auto kern = gemm_tf32_kernel<A_K, B_K, BN, MT>;
   using S = Smem<BN, MT>;
   static bool attr_set[64] = {};
@@ -449,8 +455,8 @@ gt_status launch(gt_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, cons
     attr_set[ctx->device] = true;
   }
   const long ntiles = (long)gt_cdiv(N, BN) * gt_cdiv(M, S::BM) * ksplit * batch;
-  dim3 grid((unsigned)min((long)ctx->sm_count, ntiles), 1, 1);
-  kern<<<grid, S::THREADS, S::TOTAL, ctx->stream>>>(ma, mb, mc, ma2, mb2, c, M, N, K, K2, accum, ksplit, tma_store, batch, out_scale, g_flag[ctx->device]);
+  dim3 grid((unsigned)min((long)(ctx->sm_count - ctx->sm_reserved), ntiles), 1, 1);
+  kern<<<grid, S::THREADS, S::TOTAL, ctx->stream>>>(maps, mc, c, M, N, accum, ksplit, tma_store, batch, out_scale, g_flag[ctx->device]);
   GT_LAUNCHED(ctx, "gemm_tf32_kernel");
   return GT_OK;
 }
@@ -504,11 +510,11 @@ int pair_capacity(gt_ctx* ctx) {
 }
 
 template <int BN, int MT>
-gt_status launch_kind(gt_ctx* ctx, int kind, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const CUtensorMap& ma2,
-                      const CUtensorMap& mb2, int tma_store, float* c, int M, int N, int K, int K2, int accum, int ksplit, int batch, float out_scale) {
-  if (kind == GT_GEMM_NT) return launch<true, true, BN, MT>(ctx, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch, out_scale);
-  if (kind == GT_GEMM_NN) return launch<true, false, BN, MT>(ctx, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch, out_scale);
-  return launch<false, false, BN, MT>(ctx, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch, out_scale);
+gt_status launch_kind(gt_ctx* ctx, int kind, const PartMaps& maps, const CUtensorMap& mc, int tma_store, float* c, int M, int N, int accum,
+                      int ksplit, int batch, float out_scale) {
+  if (kind == GT_GEMM_NT) return launch<true, true, BN, MT>(ctx, maps, mc, tma_store, c, M, N, accum, ksplit, batch, out_scale);
+  if (kind == GT_GEMM_NN) return launch<true, false, BN, MT>(ctx, maps, mc, tma_store, c, M, N, accum, ksplit, batch, out_scale);
+  return launch<false, false, BN, MT>(ctx, maps, mc, tma_store, c, M, N, accum, ksplit, batch, out_scale);
 }
 
 }  // namespace
@@ -580,6 +586,33 @@ int* tc::device_flag(gt_ctx* ctx) {
   return g_flag[ctx->device];
 }
 
+// Self-test of the bounded wait every pipeline kernel relies on: one thread waits on an mbarrier that nothing will
+// ever arrive on, with a caller-chosen limit instead of the kernels' 2 s, gives up when the limit has passed, raises
+// the device flag like a pipeline kernel would (code 99) and returns. Nothing spins beyond the limit and the context
+// stays usable; the next gt_sync reports the expiry.
+__global__ void bounded_wait_selftest_kernel(unsigned long long limit_ns, int* __restrict__ flag) {
+  __shared__ __align__(8) unsigned long long bar_storage;
+  const uint32_t bar = smem_u32(&bar_storage);
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    const uint64_t t0 = gtimer();
+    bool arrived = mbar_try(bar, 0);
+    while (!arrived && gtimer() - t0 <= limit_ns) arrived = mbar_try(bar, 0);
+    if (!arrived) atomicExch(flag, 99);
+  }
+}
+
+extern "C" gt_status gt_selftest_bounded_wait(gt_ctx* ctx, int32_t limit_us) {
+  GT_REQUIRE(ctx, limit_us >= 1 && limit_us <= 1000000, "gt_selftest_bounded_wait: limit %d us (1..1000000)", limit_us);
+  if (ctx->capturing) return gt_fail(ctx, GT_ERR_STATE, "gt_selftest_bounded_wait inside a graph capture");
+  int* flag = device_flag(ctx);
+  if (!flag) return gt_fail(ctx, GT_ERR_CUDA, "gt_selftest_bounded_wait: cannot allocate the device flag");
+  bounded_wait_selftest_kernel<<<1, 32, 0, ctx->stream>>>((unsigned long long)limit_us * 1000ull, flag);
+  GT_LAUNCHED(ctx, "bounded_wait_selftest_kernel");
+  return GT_OK;
+}
+
 // Reads and clears the device flag the kernels raise when a bounded wait expires.
 gt_status gt_gemm_tc_check(gt_ctx* ctx) {
   int* f = g_flag[ctx->device];
@@ -595,40 +628,39 @@ gt_status gt_gemm_tc_check(gt_ctx* ctx) {
 }
 
 // `batch` independent products of the same shape, matrix i of each operand `M*K`, `N*K`, `M*N` elements after matrix i-1.
-// With K2 > 0 (batch 1 only): c (+)= op(a).op(b) + op(a2).op(b2), the second product of the same kind and K2 deep.
-static gt_status gemm_tc_dispatch(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, int K2,
-                                  const float* a2, const float* b2, float* c, int batch, float alpha, bool* handled) {
+// With nparts > 1 (batch 1 only): c (+)= sum_p op(a_p).op(b_p), every product of the same kind, K_p deep.
+static gt_status gemm_tc_dispatch(gt_ctx* ctx, int kind, int accum, int M, int N, int nparts, const int* Ks, const float* const* as,
+                                  const float* const* bs, float* c, int batch, float alpha, bool* handled) {
   *handled = false;
-  if (batch < 1 || (K2 > 0 && batch != 1)) return GT_OK;
+  if (batch < 1 || nparts < 1 || nparts > MAX_PARTS || (nparts > 1 && batch != 1)) return GT_OK;
   // Small or oddly aligned products stay on the f32 kernel: TMA needs 16-byte row pitches and bases.
   const bool a_k = kind != GT_GEMM_TN, b_k = kind == GT_GEMM_NT;
-  const int a_inner = a_k ? K : M, b_inner = b_k ? K : N;
-  if (M < 16 || N < 16 || K < 16) return GT_OK;   // (rows of a tile past M or N are zero-filled by TMA and clipped on store)
-  if ((a_inner & 3) || (b_inner & 3)) return GT_OK;
-  if ((((uintptr_t)a) | ((uintptr_t)b) | ((uintptr_t)c)) & 15) return GT_OK;
-  if (K2 > 0) {
-    const int a2_inner = a_k ? K2 : M, b2_inner = b_k ? K2 : N;
-    if ((a2_inner & 3) || (b2_inner & 3) || ((((uintptr_t)a2) | ((uintptr_t)b2)) & 15)) return GT_OK;
+  if (M < 16 || N < 16 || Ks[0] < 16) return GT_OK;   // (rows of a tile past M or N are zero-filled by TMA and clipped on store)
+  if (((uintptr_t)c) & 15) return GT_OK;
+  int kblocks = 0;
+  for (int p = 0; p < nparts; p++) {
+    const int a_inner = a_k ? Ks[p] : M, b_inner = b_k ? Ks[p] : N;
+    if (Ks[p] < 1 || (a_inner & 3) || (b_inner & 3) || ((((uintptr_t)as[p]) | ((uintptr_t)bs[p])) & 15)) return GT_OK;
+    kblocks += gt_cdiv(Ks[p], BK);
   }
   if (ctx->device < 0 || ctx->device >= 64) return GT_OK;
   if (!device_flag(ctx)) return GT_OK;
   // Tile shape and split-K factor: the cheapest of the four shapes under a small cost model (cycles of the CTA with
   // the most work: waves x (K blocks x cycles per K block + epilogue)), calibrated on in-kernel cycle counts.
-  const int kblocks = gt_cdiv(K, BK) + gt_cdiv(K2, BK);
   struct Cfg { int mt, bn; };   // mt 1, 2: 128 / 256 rows on one CTA; mt 3: 256 rows on a CTA pair
   static const Cfg cfgs[6] = {{1, 192}, {1, 128}, {2, 256}, {2, 192}, {3, 192}, {3, 256}};
   const char* force = getenv("GT_GEMM_TILE");   // "mt,bn": forces one tile shape (read per call so tests can switch it)
-  const int npairs = pair_capacity(ctx);
+  const int npairs = max(0, pair_capacity(ctx) - (ctx->sm_reserved + 1) / 2);
   int best = 0, ksplit = 1;
   double best_cost = 1e30;
   for (int i = 0; i < 6; i++) {
     const int mt = cfgs[i].mt, bn = cfgs[i].bn, bm = mt == 1 ? BM1 : 2 * BM1;
-    if (mt == 3 && (npairs < 8 || K2 > 0)) continue;   // (the pair kernel takes one product)
+    if (mt == 3 && (npairs < 8 || nparts > 1)) continue;   // (the pair kernel takes one product)
     if (force) {
       int fm = 0, fb = 0;
       if (sscanf(force, "%d,%d", &fm, &fb) == 2 && (fm != mt || fb != bn)) continue;
     }
-    const long workers = mt == 3 ? npairs : ctx->sm_count;
+    const long workers = mt == 3 ? npairs : ctx->sm_count - ctx->sm_reserved;
     const long tiles = (long)gt_cdiv(N, bn) * gt_cdiv(M, bm) * batch;
     // split K when the output has few tiles and K is deep (dW: K = rows); partial sums meet in L2 with f32 adds
     int ks = 1;
@@ -655,30 +687,33 @@ static gt_status gemm_tc_dispatch(gt_ctx* ctx, int kind, int accum, int M, int N
   if (best_cost >= 1e30) return GT_OK;
   const int mt = cfgs[best].mt, bn = cfgs[best].bn;
   const int a_box = mt == 2 ? 2 * BM1 : BM1, b_box = mt == 3 ? bn / 2 : bn;   // rows one TMA copy brings
-  CUtensorMap ma, mb;
-  const uint64_t sa = (uint64_t)M * K, sb = (uint64_t)N * K, sc = (uint64_t)M * N;
-  const bool oka = a_k ? make_map_3d(&ma, a, K, M, batch, K, sa, a_box, true) : make_map_3d(&ma, a, M, K, batch, M, sa, BK, false);
-  const bool okb = b_k ? make_map_3d(&mb, b, K, N, batch, K, sb, b_box, true) : make_map_3d(&mb, b, N, K, batch, N, sb, BK, false);
-  if (!oka || !okb) return GT_OK;
-  CUtensorMap ma2 = ma, mb2 = mb;
-  if (K2 > 0) {
-    const uint64_t sa2 = (uint64_t)M * K2, sb2 = (uint64_t)N * K2;
-    const bool oka2 = a_k ? make_map_3d(&ma2, a2, K2, M, 1, K2, sa2, a_box, true) : make_map_3d(&ma2, a2, M, K2, 1, M, sa2, BK, false);
-    const bool okb2 = b_k ? make_map_3d(&mb2, b2, K2, N, 1, K2, sb2, b_box, true) : make_map_3d(&mb2, b2, N, K2, 1, N, sb2, BK, false);
-    if (!oka2 || !okb2) return GT_OK;
+  PartMaps maps;
+  maps.nparts = nparts;
+  int kb_sum = 0;
+  for (int p = 0; p < nparts; p++) {
+    const int K = Ks[p];
+    const uint64_t sa = (uint64_t)M * K, sb = (uint64_t)N * K;
+    const bool oka = a_k ? make_map_3d(&maps.a[p], as[p], K, M, batch, K, sa, a_box, true) : make_map_3d(&maps.a[p], as[p], M, K, batch, M, sa, BK, false);
+    const bool okb = b_k ? make_map_3d(&maps.b[p], bs[p], K, N, batch, K, sb, b_box, true) : make_map_3d(&maps.b[p], bs[p], N, K, batch, N, sb, BK, false);
+    if (!oka || !okb) return GT_OK;
+    kb_sum += gt_cdiv(K, BK);
+    maps.kb_end[p] = kb_sum;
   }
+  for (int p = nparts; p < MAX_PARTS; p++) { maps.a[p] = maps.a[0]; maps.b[p] = maps.b[0]; maps.kb_end[p] = kb_sum; }
   // the output goes through TMA (32x32 blocks of whole 128-byte rows) whenever its row pitch allows a tensor map
-  CUtensorMap mc = ma;
+  const uint64_t sc = (uint64_t)M * N;
+  CUtensorMap mc = maps.a[0];
   const int tma_store = ((N & 3) == 0 && make_map_3d(&mc, c, N, M, batch, N, sc, 32, true)) ? 1 : 0;
   if (ksplit > 1 && !accum) GT_CUDA(ctx, cudaMemsetAsync(c, 0, sizeof(float) * (size_t)M * N * batch, ctx->stream));
   const float out_scale = alpha * TRUNC_COMP;
+  const int K0 = Ks[0];
   gt_status s;
-  if (mt == 3 && bn == 192) s = launch_pair_kind<192>(ctx, kind, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch, npairs, out_scale);
-  else if (mt == 3) s = launch_pair_kind<256>(ctx, kind, ma, mb, mc, tma_store, c, M, N, K, accum, ksplit, batch, npairs, out_scale);
-  else if (mt == 1 && bn == 192) s = launch_kind<192, 1>(ctx, kind, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch, out_scale);
-  else if (mt == 1) s = launch_kind<128, 1>(ctx, kind, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch, out_scale);
-  else if (bn == 256) s = launch_kind<256, 2>(ctx, kind, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch, out_scale);
-  else s = launch_kind<192, 2>(ctx, kind, ma, mb, mc, ma2, mb2, tma_store, c, M, N, K, K2, accum, ksplit, batch, out_scale);
+  if (mt == 3 && bn == 192) s = launch_pair_kind<192>(ctx, kind, maps.a[0], maps.b[0], mc, tma_store, c, M, N, K0, accum, ksplit, batch, npairs, out_scale);
+  else if (mt == 3) s = launch_pair_kind<256>(ctx, kind, maps.a[0], maps.b[0], mc, tma_store, c, M, N, K0, accum, ksplit, batch, npairs, out_scale);
+  else if (mt == 1 && bn == 192) s = launch_kind<192, 1>(ctx, kind, maps, mc, tma_store, c, M, N, accum, ksplit, batch, out_scale);
+  else if (mt == 1) s = launch_kind<128, 1>(ctx, kind, maps, mc, tma_store, c, M, N, accum, ksplit, batch, out_scale);
+  else if (bn == 256) s = launch_kind<256, 2>(ctx, kind, maps, mc, tma_store, c, M, N, accum, ksplit, batch, out_scale);
+  else s = launch_kind<192, 2>(ctx, kind, maps, mc, tma_store, c, M, N, accum, ksplit, batch, out_scale);
   if (s) return s;
   *handled = true;
   return GT_OK;
@@ -686,16 +721,15 @@ static gt_status gemm_tc_dispatch(gt_ctx* ctx, int kind, int accum, int M, int N
 
 gt_status gt_gemm_tc_batched(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c, int batch,
                              bool* handled) {
-  return gemm_tc_dispatch(ctx, kind, accum, M, N, K, a, b, 0, nullptr, nullptr, c, batch, 1.f, handled);
+  return gemm_tc_dispatch(ctx, kind, accum, M, N, 1, &K, &a, &b, c, batch, 1.f, handled);
 }
 
 gt_status gt_gemm_tc(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c, float alpha,
                      bool* handled) {
-  return gemm_tc_dispatch(ctx, kind, accum, M, N, K, a, b, 0, nullptr, nullptr, c, 1, alpha, handled);
+  return gemm_tc_dispatch(ctx, kind, accum, M, N, 1, &K, &a, &b, c, 1, alpha, handled);
 }
 
-gt_status gt_gemm_tc2(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, int K2, const float* a2,
-                      const float* b2, float* c, bool* handled) {
-  return gemm_tc_dispatch(ctx, kind, accum, M, N, K, a, b, K2, a2, b2, c, 1, 1.f, handled);
+gt_status gt_gemm_tc_multi(gt_ctx* ctx, int kind, int accum, int M, int N, int nparts, const int* Ks, const float* const* as,
+                           const float* const* bs, float* c, bool* handled) {
+  return gemm_tc_dispatch(ctx, kind, accum, M, N, nparts, Ks, as, bs, c, 1, 1.f, handled);
 }
-

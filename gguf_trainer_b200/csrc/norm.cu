@@ -49,8 +49,11 @@ __device__ __forceinline__ void dw_finish(float* sdw, int d, float* gw, int accu
 }
 
 // NPL = elements per lane (d <= 32*NPL)
+// With `xb` the row normalised is x + xb, and that sum is also written to `sum` (the residual add that precedes the
+// norm in every block, src/arch/llama.ts:203-208, done in the same pass over the row).
 template <int NPL>
 __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(int rows, int d, const float* __restrict__ x,
+                                                          const float* __restrict__ xb, float* __restrict__ sum,
                                                           const float* __restrict__ w, float eps,
                                                           float* __restrict__ y, float* __restrict__ rinv) {
   const int lane = threadIdx.x & 31;
@@ -63,8 +66,20 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(int rows, int d, const
     const float* xr = x + (size_t)row * d;
     float v[NPL];
     float ss = 0.f;
+    if (xb) {
+      const float* br = xb + (size_t)row * d;
+      float* sr = sum + (size_t)row * d;
 #pragma unroll
-    for (int i = 0; i < NPL; i++) { int j = lane + 32 * i; v[i] = j < d ? xr[j] : 0.f; ss = fmaf(v[i], v[i], ss); }
+      for (int i = 0; i < NPL; i++) {
+        int j = lane + 32 * i;
+        v[i] = j < d ? xr[j] + br[j] : 0.f;
+        if (j < d) sr[j] = v[i];
+        ss = fmaf(v[i], v[i], ss);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < NPL; i++) { int j = lane + 32 * i; v[i] = j < d ? xr[j] : 0.f; ss = fmaf(v[i], v[i], ss); }
+    }
     ss = warp_sum(ss);
     float r = 1.f / sqrtf(ss / (float)d + eps);
     if (lane == 0) rinv[row] = r;
@@ -77,7 +92,7 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(int rows, int d, const
 template <int NPL>
 __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(int rows, int d, const float* __restrict__ x,
                                                           const float* __restrict__ w, const float* __restrict__ rinv,
-                                                          const float* __restrict__ g, float* gx, int accum_x,
+                                                          const float* __restrict__ g, const float* gadd, float* gx, int accum_x,
                                                           float* gw, int accum_w, float* part, int* counter) {
   extern __shared__ float sdw[];  // [d] block-level column partials
   const int lane = threadIdx.x & 31;
@@ -108,12 +123,13 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(int rows, int d, const
     const float k = r * r * r * S * invd;
     if (gx) {
       float* o = gx + (size_t)row * d;
+      const float* prev = gadd ? gadd + (size_t)row * d : o;   // what the term is added to: another buffer, or gx itself
 #pragma unroll
       for (int i = 0; i < NPL; i++) {
         int j = lane + 32 * i;
         if (j < d) {
           float v = wv[i] * r * gv[i] - xv[i] * k;
-          o[j] = accum_x ? o[j] + v : v;
+          o[j] = accum_x ? prev[j] + v : v;
         }
       }
     }
@@ -135,8 +151,9 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(int rows, int d, const
 // warps striding over the rows keeps the number of CTAs that finish with global atomics on dw at the SM count.
 template <int V4, int TH>
 __global__ void __launch_bounds__(TH) rmsnorm_bwd_vec_kernel(int rows, int d, const float* __restrict__ x, const float* __restrict__ w,
-                                                              const float* __restrict__ rinv, const float* __restrict__ g, float* gx,
-                                                              int accum_x, float* gw, int accum_w, float* part, int* counter) {
+                                                              const float* __restrict__ rinv, const float* __restrict__ g,
+                                                              const float* gadd, float* gx, int accum_x, float* gw, int accum_w,
+                                                              float* part, int* counter) {
   extern __shared__ float sdw[];
   const int lane = threadIdx.x & 31;
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -160,7 +177,7 @@ __global__ void __launch_bounds__(TH) rmsnorm_bwd_vec_kernel(int rows, int d, co
     float4 xv[V4], gv[V4], pv[V4];
     float S = 0.f;
     if (gx && accum_x) {   // the old dx values are fetched with the row, not after the reduction (one round trip, not two)
-      const float4* orow = reinterpret_cast<const float4*>(gx + (size_t)row * d);
+      const float4* orow = reinterpret_cast<const float4*>((gadd ? gadd : gx) + (size_t)row * d);
 #pragma unroll
       for (int i = 0; i < V4; i++) {
         const int j = lane + 32 * i;
@@ -232,8 +249,8 @@ gt_status dw_mode(gt_ctx* ctx, int blocks, int d, float* gw, int accum_w, bool o
 }
 
 template <int V4, int TH = (V4 >= 8 ? 256 : 512)>
-gt_status launch_bwd_vec(gt_ctx* ctx, int rows, int d, const float* x, const float* w, const float* rinv, const float* g, float* gx,
-                         int accum_x, float* gw, int accum_w, bool ordered) {
+gt_status launch_bwd_vec(gt_ctx* ctx, int rows, int d, const float* x, const float* w, const float* rinv, const float* g,
+                         const float* gadd, float* gx, int accum_x, float* gw, int accum_w, bool ordered) {
   // Narrow rows (the per-head norms, d = 128 or 256) keep few bytes in flight per warp: more resident CTAs make up for it.
   // (Only with many rows: every CTA ends with d atomics on dw, which a short launch would feel.)
   const int per_sm = (V4 <= 2 && rows >= 65536) ? (V4 == 1 ? 4 : 3) : 512 / TH;
@@ -244,21 +261,22 @@ gt_status launch_bwd_vec(gt_ctx* ctx, int rows, int d, const float* x, const flo
     gt_status s = dw_mode(ctx, blocks, d, gw, accum_w, ordered, &part, &counter);
     if (s) return s;
   }
-  rmsnorm_bwd_vec_kernel<V4, TH><<<blocks, TH, sizeof(float) * d, ctx->stream>>>(rows, d, x, w, rinv, g, gx, accum_x, gw, accum_w, part, counter);
+  rmsnorm_bwd_vec_kernel<V4, TH><<<blocks, TH, sizeof(float) * d, ctx->stream>>>(rows, d, x, w, rinv, g, gadd, gx, accum_x, gw, accum_w, part, counter);
   GT_LAUNCHED(ctx, "rmsnorm_bwd_vec_kernel");
   return GT_OK;
 }
 
 template <int NPL>
-gt_status launch_fwd(gt_ctx* ctx, int rows, int d, const float* x, const float* w, float eps, float* y, float* rinv) {
+gt_status launch_fwd(gt_ctx* ctx, int rows, int d, const float* x, const float* xb, float* sum, const float* w, float eps, float* y,
+                     float* rinv) {
   int blocks = min(gt_cdiv(rows, 8), ctx->sm_count * 8);
-  rmsnorm_fwd_kernel<NPL><<<blocks, 256, 0, ctx->stream>>>(rows, d, x, w, eps, y, rinv);
+  rmsnorm_fwd_kernel<NPL><<<blocks, 256, 0, ctx->stream>>>(rows, d, x, xb, sum, w, eps, y, rinv);
   GT_LAUNCHED(ctx, "rmsnorm_fwd_kernel");
   return GT_OK;
 }
 template <int NPL>
 gt_status launch_bwd(gt_ctx* ctx, int rows, int d, const float* x, const float* w, const float* rinv, const float* g,
-                     float* gx, int accum_x, float* gw, int accum_w, bool ordered) {
+                     const float* gadd, float* gx, int accum_x, float* gw, int accum_w, bool ordered) {
   // fewer, fatter blocks when dw is wanted: each block ends with d global atomics
   int blocks = min(gt_cdiv(rows, 8), ctx->sm_count * (gw ? 4 : 8));
   float* part = nullptr;
@@ -267,7 +285,7 @@ gt_status launch_bwd(gt_ctx* ctx, int rows, int d, const float* x, const float* 
     gt_status s = dw_mode(ctx, blocks, d, gw, accum_w, ordered, &part, &counter);
     if (s) return s;
   }
-  rmsnorm_bwd_kernel<NPL><<<blocks, 256, sizeof(float) * d, ctx->stream>>>(rows, d, x, w, rinv, g, gx, accum_x, gw, accum_w, part, counter);
+  rmsnorm_bwd_kernel<NPL><<<blocks, 256, sizeof(float) * d, ctx->stream>>>(rows, d, x, w, rinv, g, gadd, gx, accum_x, gw, accum_w, part, counter);
   GT_LAUNCHED(ctx, "rmsnorm_bwd_kernel");
   return GT_OK;
 }
@@ -276,40 +294,64 @@ gt_status launch_bwd(gt_ctx* ctx, int rows, int d, const float* x, const float* 
 
 extern "C" {
 
+static gt_status rmsnorm_fwd_any(gt_ctx* ctx, int rows, int d, const float* px, const float* pb, float* ps, const float* pw, float eps,
+                                 float* py, float* pr) {
+  if (d <= 64) return launch_fwd<2>(ctx, rows, d, px, pb, ps, pw, eps, py, pr);
+  if (d <= 128) return launch_fwd<4>(ctx, rows, d, px, pb, ps, pw, eps, py, pr);
+  if (d <= 256) return launch_fwd<8>(ctx, rows, d, px, pb, ps, pw, eps, py, pr);
+  if (d <= 640) return launch_fwd<20>(ctx, rows, d, px, pb, ps, pw, eps, py, pr);
+  if (d <= 1024) return launch_fwd<32>(ctx, rows, d, px, pb, ps, pw, eps, py, pr);
+  return launch_fwd<64>(ctx, rows, d, px, pb, ps, pw, eps, py, pr);
+}
+
 gt_status gt_rmsnorm_fwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf x, gt_buf w, float eps, gt_buf y, gt_buf rinv) {
   GT_REQUIRE(ctx, rows > 0 && d > 0 && d <= 2048, "gt_rmsnorm_fwd: rows %d d %d (d must be in 1..2048)", rows, d);
   GT_REQUIRE(ctx, x && w && y && rinv, "gt_rmsnorm_fwd: null operand");
-  const float* px = gt_ptr<const float>(x); const float* pw = gt_ptr<const float>(w);
-  float* py = gt_ptr<float>(y); float* pr = gt_ptr<float>(rinv);
-  if (d <= 64) return launch_fwd<2>(ctx, rows, d, px, pw, eps, py, pr);
-  if (d <= 128) return launch_fwd<4>(ctx, rows, d, px, pw, eps, py, pr);
-  if (d <= 256) return launch_fwd<8>(ctx, rows, d, px, pw, eps, py, pr);
-  if (d <= 640) return launch_fwd<20>(ctx, rows, d, px, pw, eps, py, pr);
-  if (d <= 1024) return launch_fwd<32>(ctx, rows, d, px, pw, eps, py, pr);
-  return launch_fwd<64>(ctx, rows, d, px, pw, eps, py, pr);
+  return rmsnorm_fwd_any(ctx, rows, d, gt_ptr<const float>(x), nullptr, nullptr, gt_ptr<const float>(w), eps, gt_ptr<float>(y),
+                         gt_ptr<float>(rinv));
 }
 
-gt_status gt_rmsnorm_bwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf x, gt_buf w, gt_buf rinv, gt_buf gy, gt_buf gx,
-                         int32_t accum_x, gt_buf gw, int32_t accum_w) {
+gt_status gt_add_rmsnorm_fwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf a, gt_buf b, gt_buf w, float eps, gt_buf sum, gt_buf y,
+                             gt_buf rinv) {
+  GT_REQUIRE(ctx, rows > 0 && d > 0 && d <= 2048, "gt_add_rmsnorm_fwd: rows %d d %d (d must be in 1..2048)", rows, d);
+  GT_REQUIRE(ctx, a && b && w && sum && y && rinv, "gt_add_rmsnorm_fwd: null operand");
+  return rmsnorm_fwd_any(ctx, rows, d, gt_ptr<const float>(a), gt_ptr<const float>(b), gt_ptr<float>(sum), gt_ptr<const float>(w), eps,
+                         gt_ptr<float>(y), gt_ptr<float>(rinv));
+}
+
+static gt_status rmsnorm_bwd_any(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf x, gt_buf w, gt_buf rinv, gt_buf gy, gt_buf gadd, gt_buf gx,
+                                 int32_t accum_x, gt_buf gw, int32_t accum_w) {
   GT_REQUIRE(ctx, rows > 0 && d > 0 && d <= 2048, "gt_rmsnorm_bwd: rows %d d %d (d must be in 1..2048)", rows, d);
   GT_REQUIRE(ctx, x && w && rinv && gy, "gt_rmsnorm_bwd: null operand");
   if (!gx && !gw) return GT_OK;
+  const float* pa = gt_ptr<const float>(gadd);
   const float* px = gt_ptr<const float>(x); const float* pw = gt_ptr<const float>(w);
   const float* pr = gt_ptr<const float>(rinv); const float* pg = gt_ptr<const float>(gy);
   float* pgx = gt_ptr<float>(gx); float* pgw = gt_ptr<float>(gw);
   const bool ordered = ctx->precision == GT_PREC_FP32;   // strict-f32 mode: dw bit-identical from run to run
-  if ((d & 3) == 0 && d >= 128 && d <= 1024 && ((((uintptr_t)px) | ((uintptr_t)pw) | ((uintptr_t)pg) | ((uintptr_t)pgx)) & 15) == 0) {
-    if (d <= 128) return launch_bwd_vec<1>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw, accum_w, ordered);
-    if (d <= 256) return launch_bwd_vec<2>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw, accum_w, ordered);
-    if (d <= 640) return launch_bwd_vec<5>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw, accum_w, ordered);
-    return launch_bwd_vec<8>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw, accum_w, ordered);
+  if ((d & 3) == 0 && d >= 128 && d <= 1024 && ((((uintptr_t)px) | ((uintptr_t)pw) | ((uintptr_t)pg) | ((uintptr_t)pgx) | ((uintptr_t)pa)) & 15) == 0) {
+    if (d <= 128) return launch_bwd_vec<1>(ctx, rows, d, px, pw, pr, pg, pa, pgx, accum_x, pgw, accum_w, ordered);
+    if (d <= 256) return launch_bwd_vec<2>(ctx, rows, d, px, pw, pr, pg, pa, pgx, accum_x, pgw, accum_w, ordered);
+    if (d <= 640) return launch_bwd_vec<5>(ctx, rows, d, px, pw, pr, pg, pa, pgx, accum_x, pgw, accum_w, ordered);
+    return launch_bwd_vec<8>(ctx, rows, d, px, pw, pr, pg, pa, pgx, accum_x, pgw, accum_w, ordered);
   }
-  if (d <= 64) return launch_bwd<2>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw, accum_w, ordered);
-  if (d <= 128) return launch_bwd<4>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw, accum_w, ordered);
-  if (d <= 256) return launch_bwd<8>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw, accum_w, ordered);
-  if (d <= 640) return launch_bwd<20>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw, accum_w, ordered);
-  if (d <= 1024) return launch_bwd<32>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw, accum_w, ordered);
-  return launch_bwd<64>(ctx, rows, d, px, pw, pr, pg, pgx, accum_x, pgw, accum_w, ordered);
+  if (d <= 64) return launch_bwd<2>(ctx, rows, d, px, pw, pr, pg, pa, pgx, accum_x, pgw, accum_w, ordered);
+  if (d <= 128) return launch_bwd<4>(ctx, rows, d, px, pw, pr, pg, pa, pgx, accum_x, pgw, accum_w, ordered);
+  if (d <= 256) return launch_bwd<8>(ctx, rows, d, px, pw, pr, pg, pa, pgx, accum_x, pgw, accum_w, ordered);
+  if (d <= 640) return launch_bwd<20>(ctx, rows, d, px, pw, pr, pg, pa, pgx, accum_x, pgw, accum_w, ordered);
+  if (d <= 1024) return launch_bwd<32>(ctx, rows, d, px, pw, pr, pg, pa, pgx, accum_x, pgw, accum_w, ordered);
+  return launch_bwd<64>(ctx, rows, d, px, pw, pr, pg, pa, pgx, accum_x, pgw, accum_w, ordered);
+}
+
+gt_status gt_rmsnorm_bwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf x, gt_buf w, gt_buf rinv, gt_buf gy, gt_buf gx,
+                         int32_t accum_x, gt_buf gw, int32_t accum_w) {
+  return rmsnorm_bwd_any(ctx, rows, d, x, w, rinv, gy, 0, gx, accum_x, gw, accum_w);
+}
+
+gt_status gt_rmsnorm_bwd_add(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf x, gt_buf w, gt_buf rinv, gt_buf gy, gt_buf gadd, gt_buf gx,
+                             gt_buf gw, int32_t accum_w) {
+  GT_REQUIRE(ctx, gadd && gx, "gt_rmsnorm_bwd_add: null operand");
+  return rmsnorm_bwd_any(ctx, rows, d, x, w, rinv, gy, gadd, gx, 1, gw, accum_w);
 }
 
 }  // extern "C"

@@ -110,11 +110,21 @@ class DataParallel:
     """One process per GPU. Rank r runs micro-batches [r*B, (r+1)*B) of each step's global draw order;
     the only exchange is an f32 sum of the gradient arena over NCCL, in buckets, on a side stream."""
 
-    def __init__(self, gpu: CudaBackend, rank: int, world: int, unique_id: bytes):
+    def __init__(self, gpu: CudaBackend, rank: int, world: int, unique_id: bytes, commCtas: int = 0):
+        """`commCtas` > 0 caps the collective's kernel at that many CTAs (NCCL_MAX_CTAS, unless the environment already
+        sets it) and makes the step leave as many SMs free for it while a reduction is in flight (`reserve`)."""
         import ctypes as C
+        import os
         self.gpu, self.rank, self.world = gpu, rank, world
+        self.commCtas = commCtas if world > 1 else 0
+        if self.commCtas > 0:
+            os.environ.setdefault("NCCL_MAX_CTAS", str(self.commCtas))
         buf = (C.c_uint8 * 128).from_buffer_copy(unique_id)
         gpu._check(gpu.lib.gt_dp_init(gpu.ctx, rank, world, buf))
+
+    def reserve(self, on: bool):
+        if self.commCtas > 0:
+            self.gpu._check(self.gpu.lib.gt_dp_reserve_sms(self.gpu.ctx, self.commCtas if on else 0))
 
     @staticmethod
     def uniqueId() -> bytes:
@@ -208,6 +218,7 @@ class CudaStep:
                         self.gpu.cutCapture()         # the replayer starts this bucket's reduction here
                     else:
                         self.dp.start(base + start * 4, count)
+                    self.dp.reserve(True)             # what follows runs (and is recorded) beside a reduction
                     orig()
 
                 t._backward = hooked
@@ -216,6 +227,7 @@ class CudaStep:
             if not self.gpu._capturing:
                 self.dp.start(base + start * 4, count)
                 self.dp.wait()
+            self.dp.reserve(False)
         else:
             backward(loss, seed)
         return loss

@@ -90,6 +90,12 @@ gt_status gt_gemm_scaled(gt_ctx* ctx, int32_t kind, int32_t accum, int32_t M, in
  * (`linear`, src/model/autograd.ts:311-319, records them as separate ops joined by `add`). */
 gt_status gt_gemm2(gt_ctx* ctx, int32_t kind, int32_t accum, int32_t M, int32_t N, int32_t K, gt_buf a, gt_buf b, int32_t K2,
                    gt_buf a2, gt_buf b2, gt_buf c);
+/* The general form: C[M,N] (+)= sum over p < nparts (1..8) of op(A_p)*op(B_p), product p being Ks[p] deep, all of
+ * layout `kind`. One launch and one write of C where the reference issues nparts accumulating products: the input
+ * gradient of an activation that feeds several projections, dX = dQ.Wq + dK.Wk + dV.Wv (each `linear` backward adds
+ * its term, src/backend/webgpu.ts:884-903). */
+gt_status gt_gemm_multi(gt_ctx* ctx, int32_t kind, int32_t accum, int32_t M, int32_t N, int32_t nparts, const int32_t* Ks,
+                        const gt_buf* as, const gt_buf* bs, gt_buf c);
 /* add/mul/silu/gelu/scale (webgpu.ts:905-1078, srcElementwise wgsl.ts:199-209) */
 gt_status gt_ew_fwd(gt_ctx* ctx, int32_t op, uint64_t n, gt_buf a, gt_buf b, float c, gt_buf out);
 gt_status gt_ew_bwd(gt_ctx* ctx, int32_t op, uint64_t n, gt_buf a, gt_buf b, float c, gt_buf gout,
@@ -103,6 +109,15 @@ gt_status gt_glu_bwd(gt_ctx* ctx, int32_t op, uint64_t n, gt_buf x, gt_buf u, gt
 gt_status gt_rmsnorm_fwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf x, gt_buf w, float eps, gt_buf y, gt_buf rinv);
 gt_status gt_rmsnorm_bwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf x, gt_buf w, gt_buf rinv, gt_buf gy,
                          gt_buf gx, int32_t accum_x, gt_buf gw, int32_t accum_w);
+/* The residual add that precedes a norm, in the norm's pass over the row: sum = a + b, y = rmsNorm(sum)
+ * (`add` then `rmsNorm`, src/arch/llama.ts:203-208, as one kernel: the sum is not read back). */
+gt_status gt_add_rmsnorm_fwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf a, gt_buf b, gt_buf w, float eps, gt_buf sum, gt_buf y,
+                             gt_buf rinv);
+/* rmsNorm backward whose input-gradient term lands on top of another buffer: gx = gadd + term. `add` backward hands
+ * its upstream gradient to both inputs; when the next thing added to it is this term, gadd is that upstream buffer
+ * and the copy `add` backward would have made never happens. gw as in gt_rmsnorm_bwd. */
+gt_status gt_rmsnorm_bwd_add(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf x, gt_buf w, gt_buf rinv, gt_buf gy, gt_buf gadd, gt_buf gx,
+                             gt_buf gw, int32_t accum_w);
 /* embedding gather / scatter-add (webgpu.ts:1090-1108, wgsl.ts:305-344); gw always accumulates */
 gt_status gt_embedding_fwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf w, gt_buf ids, gt_buf out);
 gt_status gt_embedding_bwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf gy, gt_buf ids, gt_buf gw);
@@ -193,6 +208,12 @@ gt_status gt_graph_destroy(gt_ctx* ctx, uint64_t graph);
 gt_status gt_event_record(gt_ctx* ctx, int32_t slot);            /* slots 0..63 */
 gt_status gt_event_elapsed_ms(gt_ctx* ctx, int32_t start_slot, int32_t end_slot, float* ms); /* blocks on end_slot */
 
+/* ---- self-test: no counterpart in the reference. Every wait inside the tensor-core kernels is bounded (2 s) and, on
+ *      expiry, raises a device flag that the next gt_sync turns into GT_ERR_CUDA "a pipeline wait expired". This
+ *      entry point runs that wait on a barrier nothing arrives on, with a limit of limit_us, so the expiry path can be
+ *      exercised without a fault: the kernel returns after limit_us and the next gt_sync reports code 99. ---- */
+gt_status gt_selftest_bounded_wait(gt_ctx* ctx, int32_t limit_us);
+
 /* ---- data parallel: no counterpart in the reference (single device). One process per GPU;
  *      gradients are summed across ranks with NCCL on a side stream. ---- */
 gt_status gt_dp_unique_id(uint8_t* out128);                       /* rank 0 creates, host broadcasts */
@@ -201,6 +222,14 @@ gt_status gt_dp_init(gt_ctx* ctx, int32_t rank, int32_t world, const uint8_t* id
  * stream; later compute does not wait for it until gt_dp_wait. */
 gt_status gt_dp_allreduce_start(gt_ctx* ctx, gt_buf buf, uint64_t count);
 gt_status gt_dp_wait(gt_ctx* ctx);                                /* compute stream waits for all started reductions */
+/* The same, observed from the host with a limit: returns once every started reduction has completed, or aborts the
+ * communicator and returns GT_ERR_NCCL when that takes longer than timeout_ms or NCCL reports an error (a rank that
+ * left or hangs). The context stays usable; gt_dp_destroy + gt_dp_init build a new communicator. */
+gt_status gt_dp_wait_host(gt_ctx* ctx, int32_t timeout_ms);
+/* From now on the persistent kernels size their grids for the device's SMs minus n (0 restores): call it with the
+ * number of CTAs the collective uses when the first reduction of a step starts, and with 0 after gt_dp_wait. Grid
+ * sizes are recorded into captured graphs, so record under the same setting the replay will run under. */
+gt_status gt_dp_reserve_sms(gt_ctx* ctx, int32_t n);
 gt_status gt_dp_destroy(gt_ctx* ctx);
 
 #ifdef __cplusplus

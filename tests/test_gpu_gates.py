@@ -95,8 +95,9 @@ def test_clears_per_window_and_late_backward_refusal():
     """tests/gpu-parity.ts:1752-1900. This backend never clears a buffer whose first writer can overwrite it, so a
     training window issues no clear per parameter or per intermediate at all: only a gradient that is read before
     anything wrote it (none in a language-model step) or scatter-added into first (the embedding table when it is not
-    tied to the readout). A forward-only window issues none, and a backward over a graph that a sync has already
-    recycled is refused."""
+    tied to the readout). A forward-only window clears nothing but the accumulators of trainable parameters that its
+    sync is about to stage back unwritten (one each, none when frozen), and a backward over a graph that a sync has
+    already recycled is refused."""
     cfg = gemma3_config(64, 64, 4, 256, 16)
     ids = np.array([(i * 11 + 5) % cfg.vocabSize for i in range(33)])
     out = {}
@@ -133,7 +134,7 @@ def test_clears_per_window_and_late_backward_refusal():
         before = gpu.gradClearsIssued
         loss = sequenceLoss(m, ids[:-1], ids[1:], 0)
         gpu.sync([loss])
-        assert gpu.gradClearsIssued == before
+        assert gpu.gradClearsIssued - before == len(m.params())      # staged-back accumulators only: no intermediate
         with pytest.raises(RuntimeError, match="graph built before a sync"):
             ag.backward(loss, 1.0)
     finally:
@@ -438,5 +439,47 @@ def test_replayed_inputs_are_range_checked(oracle):
         step.run(ids, tg)
         assert np.array_equal(step.losses(), good)                 # and a refused call left the recorded inputs untouched
         gpu.sync([])
+    finally:
+        gpu.destroy()
+
+
+def test_bounded_wait_expires_and_is_reported_at_the_next_sync():
+    """Every mbarrier wait in the tensor-core kernels gives up after a time limit, raises a device flag and lets the
+    kernel return; gt_sync turns the flag into an error. Exercised on a barrier nothing arrives on, with a 2 ms limit:
+    the kernel returns by itself, the sync reports the expiry once, and the context works afterwards."""
+    import time
+    from gguf_trainer_b200 import _lib
+    gpu = requireGPU("the bounded-wait gate", precision="tf32")
+    try:
+        gpu.sync([])
+        t0 = time.perf_counter()
+        gpu._check(gpu.lib.gt_selftest_bounded_wait(gpu.ctx, 2000))
+        with pytest.raises(_lib.GtError, match="a pipeline wait expired \\(code 99\\)"):
+            gpu.sync([])
+        assert time.perf_counter() - t0 < 1.0          # gave up after ~2 ms, not after the kernels' 2 s
+        gpu.sync([])                                    # reported once; the flag is clear again
+        a = gpu.createStateBuffer(64 * 64 * 4)
+        c = gpu.createStateBuffer(64 * 64 * 4)
+        gpu.writeStateBuffer(a, np.eye(64, dtype=np.float32))
+        gpu._gemm("NT", 0, 64, 64, 64, a, a, c)         # and the tensor-core path still runs
+        assert np.allclose(gpu.readStateBuffer(c, 64 * 64).reshape(64, 64), np.eye(64), atol=2e-3)
+        gpu.sync([])
+    finally:
+        gpu.destroy()
+
+
+def test_exchange_wait_on_the_host_returns_when_the_reductions_are_done():
+    """gt_dp_wait_host on a communicator of one rank: the reductions complete, so it returns GT_OK well inside its
+    limit. (Its other outcome, aborting the communicator when a rank is missing, needs a stuck collective on the GPU
+    and is not run here.)"""
+    from gguf_trainer_b200.train import DataParallel
+    gpu = requireGPU("the exchange gate")
+    try:
+        DataParallel(gpu, 0, 1, DataParallel.uniqueId())
+        buf = gpu.createStateBuffer(4096 * 4)
+        gpu.writeStateBuffer(buf, np.arange(4096, dtype=np.float32))
+        gpu._check(gpu.lib.gt_dp_allreduce_start(gpu.ctx, buf, 4096))
+        gpu._check(gpu.lib.gt_dp_wait_host(gpu.ctx, 20000))
+        assert np.array_equal(gpu.readStateBuffer(buf, 4096), np.arange(4096, dtype=np.float32))
     finally:
         gpu.destroy()

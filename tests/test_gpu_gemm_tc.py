@@ -83,6 +83,39 @@ def test_gemm2_two_products_into_one_tile(gpu, oracle, kind, M, N, K, K2):
         gpu._check(gpu.lib.gt_free(gpu.ctx, b))
 
 
+@pytest.mark.parametrize("kind", ["NT", "NN", "TN"])
+@pytest.mark.parametrize("M,N,Ks", [(2048, 576, (576, 192, 192)), (300, 200, (100, 16, 40, 8)), (1000, 1536, (64,) * 8),
+                                    (16384, 576, (1536, 1536))])
+def test_gemm_multi_sums_products_in_one_launch(gpu, oracle, kind, M, N, Ks):
+    """gt_gemm_multi: C (+)= sum_p A_p.B_p, the K blocks of each product following the previous one's in one main loop
+    (dX = dQ.Wq + dK.Wk + dV.Wv of the activation that feeds three projections; dGate.Wg + dUp.Wu), ragged K, up to
+    eight products, accumulate."""
+    import ctypes as C
+    rng = oracle.Mulberry32(M + 3 * N + sum(Ks))
+    As = [rng.randn((M, K), 0.5) for K in Ks]
+    Bs = [rng.randn((N, K), 0.5) for K in Ks]
+    C0 = rng.randn((M, N), 0.5)
+    want = sum(a.astype(np.float64) @ b.astype(np.float64).T for a, b in zip(As, Bs))
+    sa = (lambda X: X if kind != "TN" else np.ascontiguousarray(X.T))
+    sb = (lambda X: X if kind == "NT" else np.ascontiguousarray(X.T))
+    da, db = [_dev(gpu, sa(a)) for a in As], [_dev(gpu, sb(b)) for b in Bs]
+    n = len(Ks)
+    kinds = {"NT": 0, "NN": 1, "TN": 2}
+    launches = gpu.kernelLaunches()
+    for accum in (0, 1):
+        dc = _dev(gpu, C0)
+        gpu._check(gpu.lib.gt_gemm_multi(gpu.ctx, kinds[kind], accum, M, N, n, (C.c_int32 * n)(*Ks), (C.c_uint64 * n)(*da),
+                                         (C.c_uint64 * n)(*db), dc))
+        got = gpu.readStateBuffer(dc, M * N).reshape(M, N)
+        r = rel_l2(got, want + (C0.astype(np.float64) if accum else 0.0))
+        assert np.isfinite(got).all() and r <= REL_L2_TC, f"{kind} {M}x{N}x{Ks} accum={accum}: relative L2 {r:.3e}"
+        gpu._check(gpu.lib.gt_free(gpu.ctx, dc))
+    gpu.sync([])
+    assert gpu.kernelLaunches() - launches == 2, "each call must be a single launch on the tensor-core path"
+    for b in da + db:
+        gpu._check(gpu.lib.gt_free(gpu.ctx, b))
+
+
 @pytest.mark.parametrize("kind,M,N,K,accum", [("NT", 2048, 16, 1024, 0), ("NN", 300, 16, 200, 1), ("TN", 576, 1536, 4096, 1),
                                               ("NT", 513, 200, 96, 0)])
 def test_gemm_scaled(gpu, oracle, kind, M, N, K, accum):

@@ -328,3 +328,45 @@ def test_gemm_scaled_and_gemm2_strict_f32(gpu, oracle, kind):
     gpu.sync([])
     for b in (da, db, da2, db2, dc):
         gpu._check(gpu.lib.gt_free(gpu.ctx, b))
+
+
+def test_residual_add_feeding_a_norm_is_one_kernel_and_its_backward_copies_nothing(gpu, oracle):
+    """`n = rmsNorm(add(a, b), w)`, the residual connection of every block (src/arch/llama.ts:203-208): the forward is
+    one launch that writes the sum and the normalised row; in backward the `add` hands its upstream gradient to both
+    inputs without a copy kernel (readers read it in place; a second writer would add on top of it). Values equal the
+    two reference ops."""
+    rng = oracle.Mulberry32(71)
+    T, d = 37, 96
+    a = rand_tensor(rng, [T, d]); b = rand_tensor(rng, [T, d]); w = rand_tensor(rng, [d], 0.5)
+    for t in (a, b, w):
+        t.zeroGrad()
+    up = oracle.Mulberry32(0xBEEF).uniform_pm1((T * d,))
+    up2 = oracle.Mulberry32(0xF00D).uniform_pm1((T * d,))
+    gpu.install()
+    try:
+        gpu.sync([])
+        l0 = gpu.kernelLaunches()
+        s = ag.add(a, b)
+        n = ag.rmsNorm(s, w, 1e-5)
+        assert gpu.kernelLaunches() - l0 == 1
+        z = ag.add(s, n)                       # the sum has a second consumer, like the residual stream
+        z.grad[:] = up
+        gpu.seedGradFromHost(z)
+        l1 = gpu.kernelLaunches()
+        z._backward()                          # add: s and n take the upstream gradient as views
+        n._backward()                          # norm: dx = (view of z's gradient) + term, written into s's own buffer
+        s._backward()                          # add: a and b take s's gradient as views
+        assert gpu.kernelLaunches() - l1 == 1, "only the norm's backward may launch"
+        gpu.sync([s, n, z])
+    finally:
+        gpu.uninstall()
+    sw = a.data.astype(np.float64) + b.data
+    y, rinv = oracle.rmsnorm_fwd(sw.astype(np.float32).reshape(T, d), w.data, 1e-5)
+    compare("sum", s.data, sw, FWD)
+    compare("norm", n.data, y, FWD)
+    compare("z", z.data, sw + y.reshape(-1), FWD)
+    gx, gw = oracle.rmsnorm_bwd(sw.astype(np.float32).reshape(T, d), w.data, rinv, up.reshape(T, d))
+    want = up.astype(np.float64) + gx.reshape(-1)
+    compare("d a", a.grad, want, BWD)
+    compare("d b", b.grad, want, BWD)
+    compare("d w", w.grad, gw, BWD)
