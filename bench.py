@@ -296,7 +296,8 @@ def run_ours(args):
         gpu.keepGradOnDevice(p)
     def make_muon():
         return MuonGpu(gpu, groups["muon"], groups["aux"], lr=0.02, momentum=0.95, nesterov=True, nsSteps=5,
-                       aux={"lr": 1e-3, "beta1": 0.9, "beta2": 0.95, "weightDecay": 0.0, "clip": 1.0})
+                       aux={"lr": 1e-3, "beta1": 0.9, "beta2": 0.95, "weightDecay": 0.0, "clip": 1.0},
+                       shardOverRanks=dp is not None and not args.no_shard_muon)
 
     if args.optimizer == "muon":
         opt = make_muon()
@@ -534,6 +535,15 @@ def run_micro(args):
             cases.append((f"NT {rows}x{out}x{inn}", (lambda x=x, w=w, y=y, out=out, inn=inn: lib.gt_gemm(ctx, 0, 0, rows, out, inn, x, w, y)), fl))
             cases.append((f"NN {rows}x{inn}x{out}", (lambda w=w, y=y, dx=dx, out=out, inn=inn: lib.gt_gemm(ctx, 1, 0, rows, inn, out, y, w, dx)), fl))
             cases.append((f"TN {out}x{inn}x{rows}", (lambda x=x, y=y, dw=dw, out=out, inn=inn: lib.gt_gemm(ctx, 2, 0, out, inn, rows, y, x, dw)), fl))
+        # the merged input-gradient products of a layer: dX = dQ.Wq + dK.Wk + dV.Wv and dX = dGate.Wg + dUp.Wu, one launch each
+        import ctypes as C
+        for label, outs in (("qkv", (q, kv, kv)), ("gate+up", (f, f))):
+            dys, ws = [buf(rows * o) for o in outs], [buf(o * h) for o in outs]
+            dx = buf(rows * h, False)
+            n = len(outs)
+            Ks, As, Bs = (C.c_int32 * n)(*outs), (C.c_uint64 * n)(*dys), (C.c_uint64 * n)(*ws)
+            cases.append((f"NN multi {rows}x{h}x({'+'.join(map(str, outs))}) [{label}]",
+                          (lambda Ks=Ks, As=As, Bs=Bs, dx=dx, n=n: lib.gt_gemm_multi(ctx, 1, 0, rows, h, n, Ks, As, Bs, dx)), 2 * rows * h * sum(outs)))
         unit, peak = "TFLOP/s", pk["tflops_sustained"]
     else:
         raise SystemExit(f"unknown --micro {name}")
@@ -573,7 +583,8 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--window", type=int, default=0)
     ap.add_argument("--layers-per-bucket", type=int, default=6, help="data parallel: layers per gradient all-reduce bucket")
-    ap.add_argument("--comm-ctas", type=int, default=16, help="data parallel: CTAs left to the collective while it overlaps backward (0 = no cap, no reservation)")
+    ap.add_argument("--comm-ctas", type=int, default=0, help="data parallel: CTAs left to the collective while it overlaps backward (0 = no cap, no reservation)")
+    ap.add_argument("--no-shard-muon", action="store_true", help="data parallel: every rank runs all Newton-Schulz iterations")
     ap.add_argument("--plain", action="store_true", help="launch every op as recorded: no merged input gradients, no residual add + norm fusion")
     ap.add_argument("--heads", default="", help="--micro attention: Hq,Hkv,hd instead of 9,3,64")
     args = ap.parse_args()

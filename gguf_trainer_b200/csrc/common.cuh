@@ -106,3 +106,7 @@ gt_status gt_gemm_tc_multi(gt_ctx* ctx, int kind, int accum, int M, int N, int n
 gt_status gt_gemm_tc_check(gt_ctx* ctx);
 void gt_optim_destroy(gt_ctx* ctx);
 void gt_dp_teardown(gt_ctx* ctx);
+// rank and world of the context's communicator (an error when gt_dp_init has not run)
+gt_status gt_dp_rank(gt_ctx* ctx, int* rank, int* world);
+// in place on the compute stream: rank r's `count` floats at buf + r*count reach every rank
+gt_status gt_dp_allgather(gt_ctx* ctx, float* buf, size_t count);

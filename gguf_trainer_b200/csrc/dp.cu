@@ -17,6 +17,7 @@ struct Nccl {
   ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
   ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
   ncclResult_t (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*AllGather)(const void*, void*, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
   ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
   ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
   const char* (*GetErrorString)(ncclResult_t) = nullptr;
@@ -32,7 +33,7 @@ bool load_nccl() {
   for (const char* n : names) { h = dlopen(n, RTLD_NOW | RTLD_GLOBAL); if (h) break; }
   if (!h) { g_nccl_err = std::string("cannot load libnccl.so.2: ") + dlerror(); return false; }
 #define SYM(field, name) *(void**)(&g_nccl.field) = dlsym(h, name); if (!g_nccl.field) { g_nccl_err = "libnccl lacks " name; return false; }
-  SYM(GetUniqueId, "ncclGetUniqueId") SYM(CommInitRank, "ncclCommInitRank") SYM(AllReduce, "ncclAllReduce")
+  SYM(GetUniqueId, "ncclGetUniqueId") SYM(CommInitRank, "ncclCommInitRank") SYM(AllReduce, "ncclAllReduce") SYM(AllGather, "ncclAllGather")
   SYM(CommDestroy, "ncclCommDestroy") SYM(CommAbort, "ncclCommAbort") SYM(GetErrorString, "ncclGetErrorString")
   SYM(CommGetAsyncError, "ncclCommGetAsyncError")
 #undef SYM
@@ -59,6 +60,21 @@ void gt_dp_teardown(gt_ctx* ctx) {
   if (d->stream) cudaStreamDestroy(d->stream);
   delete d;
   ctx->dp = nullptr;
+}
+
+gt_status gt_dp_rank(gt_ctx* ctx, int* rank, int* world) {
+  if (!ctx->dp) return gt_fail(ctx, GT_ERR_STATE, "no communicator: gt_dp_init has not run");
+  *rank = ctx->dp->rank;
+  *world = ctx->dp->world;
+  return GT_OK;
+}
+
+gt_status gt_dp_allgather(gt_ctx* ctx, float* buf, size_t count) {
+  GtDp* d = ctx->dp;
+  if (!d || !d->comm) return gt_fail(ctx, GT_ERR_STATE, "gt_dp_allgather: no communicator");
+  ncclResult_t r = g_nccl.AllGather(buf + (size_t)d->rank * count, buf, count, /*ncclFloat32*/ 7, d->comm, ctx->stream);
+  if (r != 0) return gt_fail(ctx, GT_ERR_NCCL, "ncclAllGather: %s", g_nccl.GetErrorString(r));
+  return GT_OK;
 }
 
 extern "C" {

@@ -293,6 +293,7 @@ struct GtMuon {
   std::vector<int> rows, cols;
   float lr, mu;
   int nesterov, ns;
+  bool sharded = false;   // Newton-Schulz work split over the data-parallel ranks (gt_muon_set_sharded)
   // workspaces sized for the largest matrix
   float *U = nullptr, *X = nullptr, *BX = nullptr, *A = nullptr, *AA = nullptr, *partials = nullptr, *inv = nullptr;
   size_t maxel = 0;
@@ -519,9 +520,45 @@ gt_status gt_muon_set_lr(gt_ctx* ctx, uint64_t h, float lr) {
   return GT_OK;
 }
 
+// Every rank of a data-parallel job holds the same gradients after the exchange and would run the same Newton-Schulz
+// iterations on all matrices. Sharded, rank r orthogonalises matrices [r*slice, (r+1)*slice) of each same-shape group
+// (slice = ceil(nb / world)) and the ranks exchange the results with one all-gather per group, so the iteration's
+// products cost 1/world per rank; momentum and the apply pass stay replicated (they are what keeps state and weights
+// identical everywhere). The group's two iteration buffers are re-made with room for world*slice matrices.
+gt_status gt_muon_set_sharded(gt_ctx* ctx, uint64_t h, int32_t on) {
+  GtMuon* m = muon_of(ctx, h);
+  GT_REQUIRE(ctx, m, "gt_muon_set_sharded: bad handle");
+  if (ctx->capturing) return gt_fail(ctx, GT_ERR_STATE, "gt_muon_set_sharded inside a graph capture");
+  if (!on) { m->sharded = false; return GT_OK; }
+  int rank = 0, world = 1;
+  gt_status s = gt_dp_rank(ctx, &rank, &world);
+  if (s) return s;
+  GT_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  for (auto& g : m->groups) {
+    if (!g.v4) continue;
+    const size_t el = (size_t)g.rows * g.cols;
+    const int slice = gt_cdiv(g.nb, world);
+    const size_t want = sizeof(float) * el * (size_t)slice * world;
+    if (want > sizeof(float) * el * g.nb) {
+      cudaFree(g.X); cudaFree(g.BX);
+      g.X = g.BX = nullptr;
+      s = dev_alloc(ctx, (void**)&g.X, want, true);
+      if (!s) s = dev_alloc(ctx, (void**)&g.BX, want, true);
+      if (s) return s;
+    }
+  }
+  m->sharded = true;
+  return GT_OK;
+}
+
 gt_status gt_muon_step(gt_ctx* ctx, uint64_t h) {
   GtMuon* m = muon_of(ctx, h);
   GT_REQUIRE(ctx, m, "gt_muon_step: bad handle");
+  int dp_rank = 0, dp_world = 1;
+  if (m->sharded) {
+    gt_status s = gt_dp_rank(ctx, &dp_rank, &dp_world);
+    if (s) return s;
+  }
   for (auto& g : m->groups) {
     const int rows = g.rows, cols = g.cols, nb = g.nb;
     const size_t el = (size_t)rows * cols;
@@ -546,19 +583,30 @@ gt_status gt_muon_step(gt_ctx* ctx, uint64_t h) {
       float *X = g.X, *Y = g.BX;
       muon_scale_batched_v4_kernel<<<eg, 256, 0, ctx->stream>>>(el4, g.U, g.inv, X);
       GT_LAUNCHED(ctx, "muon_scale_batched_v4_kernel");
+      // this rank's share of the group's matrices: all of them, or its slice when the work is sharded
+      const int slice = gt_cdiv(nb, dp_world);
+      const int lo = m->sharded ? min(nb, dp_rank * slice) : 0, hi = m->sharded ? min(nb, lo + slice) : nb;
+      const int mine = hi - lo;
       for (int it = 0; it < m->ns; it++) {
-        gt_status st = flip ? gt_gemm_batched(ctx, GT_GEMM_TN, 0, r, r, c, X, X, g.A, nb)     // X is [c, r]: A = X^T.X
-                            : gt_gemm_batched(ctx, GT_GEMM_NT, 0, r, r, c, X, X, g.A, nb);    // X is [r, c]: A = X.X^T
-        if (st) return st;
-        st = gt_gemm_batched(ctx, GT_GEMM_NN, 0, r, r, r, g.A, g.A, g.AA, nb);
-        if (st) return st;
-        const size_t rr = (size_t)r * r * nb;
-        ns_poly_batched_kernel<<<egrid(ctx, rr), 256, 0, ctx->stream>>>(rr, r, 3.4445f, -4.7750f, g.A, 2.0315f, g.AA);
-        GT_LAUNCHED(ctx, "ns_poly_batched_kernel");
-        st = flip ? gt_gemm_batched(ctx, GT_GEMM_NT, 0, c, r, r, X, g.AA, Y, nb)               // [c, r] = X.B'^T
-                  : gt_gemm_batched(ctx, GT_GEMM_NN, 0, r, c, r, g.AA, X, Y, nb);              // [r, c] = B'.X
-        if (st) return st;
+        float *Xs = X + (size_t)lo * el, *Ys = Y + (size_t)lo * el;
+        if (mine > 0) {
+          gt_status st = flip ? gt_gemm_batched(ctx, GT_GEMM_TN, 0, r, r, c, Xs, Xs, g.A, mine)   // X is [c, r]: A = X^T.X
+                              : gt_gemm_batched(ctx, GT_GEMM_NT, 0, r, r, c, Xs, Xs, g.A, mine);  // X is [r, c]: A = X.X^T
+          if (st) return st;
+          st = gt_gemm_batched(ctx, GT_GEMM_NN, 0, r, r, r, g.A, g.A, g.AA, mine);
+          if (st) return st;
+          const size_t rr = (size_t)r * r * mine;
+          ns_poly_batched_kernel<<<egrid(ctx, rr), 256, 0, ctx->stream>>>(rr, r, 3.4445f, -4.7750f, g.A, 2.0315f, g.AA);
+          GT_LAUNCHED(ctx, "ns_poly_batched_kernel");
+          st = flip ? gt_gemm_batched(ctx, GT_GEMM_NT, 0, c, r, r, Xs, g.AA, Ys, mine)             // [c, r] = X.B'^T
+                    : gt_gemm_batched(ctx, GT_GEMM_NN, 0, r, c, r, g.AA, Xs, Ys, mine);            // [r, c] = B'.X
+          if (st) return st;
+        }
         float* t = X; X = Y; Y = t;
+      }
+      if (m->sharded && dp_world > 1) {   // every rank's slice of the orthogonalised matrices, to every rank
+        gt_status st = gt_dp_allgather(ctx, X, (size_t)slice * el);
+        if (st) return st;
       }
       muon_apply_batched_v4_kernel<<<eg, 256, 0, ctx->stream>>>(el4, f, X, P + 2 * nb);
       GT_LAUNCHED(ctx, "muon_apply_batched_v4_kernel");

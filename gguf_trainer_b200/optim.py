@@ -132,7 +132,8 @@ class MuonGpu:
     """Muon on the hidden matrices, AdamW on the aux group (muon-gpu.ts:351-437)."""
 
     def __init__(self, gpu: CudaBackend, muonParams: Sequence[Tensor], auxParams: Sequence[Tensor], lr: float,
-                 momentum: float = 0.95, nesterov: bool = True, nsSteps: int = 5, aux: Optional[dict] = None):
+                 momentum: float = 0.95, nesterov: bool = True, nsSteps: int = 5, aux: Optional[dict] = None,
+                 shardOverRanks: bool = False):
         self.gpu = gpu
         self.muonParams = list(muonParams)
         self.auxParams = list(auxParams)
@@ -153,6 +154,10 @@ class MuonGpu:
         gpu._check(gpu.lib.gt_muon_create(gpu.ctx, n, data, grad, rows, cols, lr, momentum, 1 if nesterov else 0,
                                           nsSteps, C.byref(h)))
         self.handle = int(h.value)
+        if shardOverRanks:
+            # data parallel (gt_dp_init has run, every rank steps alike): each rank runs the Newton-Schulz iterations of
+            # its share of the matrices and the results are all-gathered
+            gpu._check(gpu.lib.gt_muon_set_sharded(gpu.ctx, self.handle, 1))
 
     def setLrScale(self, scale: float):
         self.gpu._check(self.gpu.lib.gt_muon_set_lr(self.gpu.ctx, self.handle, self.baseLr * scale))

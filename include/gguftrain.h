@@ -194,6 +194,10 @@ gt_status gt_muon_create(gt_ctx* ctx, int32_t n, const gt_buf* data, const gt_bu
 gt_status gt_muon_set_lr(gt_ctx* ctx, uint64_t h, float lr);
 gt_status gt_muon_step(gt_ctx* ctx, uint64_t h);
 gt_status gt_muon_state(gt_ctx* ctx, uint64_t h, int32_t i, gt_buf* momentum);
+/* Data parallel only (after gt_dp_init, on every rank alike): split the Newton-Schulz iterations of each same-shape
+ * group of matrices over the ranks and all-gather the orthogonalised matrices, instead of every rank repeating all of
+ * them. Results are the same bits on every rank; momentum and the weight update stay replicated. */
+gt_status gt_muon_set_sharded(gt_ctx* ctx, uint64_t h, int32_t on);
 /* newtonSchulzGpu (muon-gpu.ts:258-282): out[m,n] = NS_steps(g[m,n]) */
 gt_status gt_newton_schulz(gt_ctx* ctx, int32_t m, int32_t n, int32_t steps, gt_buf g, gt_buf out);
 

@@ -81,6 +81,7 @@ const SYMBOLS = {
   gt_muon_set_lr: { parameters: ["pointer", "u64", "f32"], result: "i32" },
   gt_muon_step: { parameters: ["pointer", "u64"], result: "i32" },
   gt_muon_state: { parameters: ["pointer", "u64", "i32", "buffer"], result: "i32" },
+  gt_muon_set_sharded: { parameters: ["pointer", "u64", "i32"], result: "i32" },
   gt_newton_schulz: { parameters: ["pointer", "i32", "i32", "i32", "u64", "u64"], result: "i32" },
   gt_graph_begin: { parameters: ["pointer"], result: "i32" },
   gt_graph_end: { parameters: ["pointer", "buffer"], result: "i32", nonblocking: true },
@@ -94,6 +95,7 @@ const SYMBOLS = {
   gt_dp_allreduce_start: { parameters: ["pointer", "u64", "u64"], result: "i32" },
   gt_dp_wait: { parameters: ["pointer"], result: "i32" },
   gt_dp_wait_host: { parameters: ["pointer", "i32"], result: "i32", nonblocking: true },
+  gt_dp_reserve_sms: { parameters: ["pointer", "i32"], result: "i32" },
   gt_dp_destroy: { parameters: ["pointer"], result: "i32" },
 } as const;
 
@@ -802,7 +804,7 @@ export class MuonCuda {
 //     gt_graph_launch / gt_graph_destroy, with ids and targets rewritten by gt_write before each launch;
 //   device-resident corpus: gt_tokens_max once at upload, then gt_gather_windows as the first recorded call of the step;
 //   data parallel: gt_dp_unique_id, gt_dp_init, gt_dp_allreduce_start per gradient bucket, gt_dp_wait (or gt_dp_wait_host
-//     with a limit) before the optimizer, gt_dp_destroy;
+//     with a limit) before the optimizer, gt_dp_reserve_sms, gt_muon_set_sharded, gt_dp_destroy;
 //   adapters: gt_gemm_scaled, gt_gemm2 / gt_gemm_multi (the adapter-carrying projection as one product);
 //   fused kernels of the launch-deferring mirror: gt_glu_fwd / gt_glu_bwd, gt_add_rmsnorm_fwd, gt_rmsnorm_bwd_add;
 //   gt_newton_schulz (newtonSchulzGpu, src/backend/muon-gpu.ts:258-282), gt_attention_bwd_static, gt_selftest_bounded_wait.

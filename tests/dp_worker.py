@@ -48,7 +48,8 @@ def main():
     if optimizer == "muon":
         g = m.paramGroups()
         opt = MuonGpu(gpu, g["muon"], g["aux"], lr=0.02, momentum=0.95, nesterov=True, nsSteps=5,
-                      aux={"lr": 1e-2, "beta1": 0.9, "beta2": 0.95, "weightDecay": 0.0, "clip": 1.0})
+                      aux={"lr": 1e-2, "beta1": 0.9, "beta2": 0.95, "weightDecay": 0.0, "clip": 1.0},
+                      shardOverRanks=dp is not None)       # each rank orthogonalises its share of the matrices
     else:
         opt = AdamWGpu(gpu, m.params(), lr=1e-2, clip=1.0)
     tokens = Mulberry32(99).randint(400, CFG.vocabSize)

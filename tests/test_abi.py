@@ -60,3 +60,17 @@ def test_product_code_never_touches_the_oracle():
                 text = open(os.path.join(dirpath, f)).read()
                 assert not re.search(r"^\s*(from|import)\s+oracle", text, re.M), f"{f} imports the oracle"
                 assert "liboracle" not in text, f"{f} names the oracle library"
+
+
+def test_typescript_binding_lists_every_entry_point_with_the_declared_arity():
+    """integration/src/backend/cuda.ts cannot run here, but its Deno.dlopen table can be held to the header: same set
+    of names, same number of parameters, pointer-like results only for gt_last_error."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    text = open(os.path.join(root, "integration", "src", "backend", "cuda.ts")).read()
+    table = text[text.index("const SYMBOLS = {"):text.index("} as const;")]
+    bound = {}
+    for m in re.finditer(r"^\s*(gt_\w+): \{ parameters: \[([^\]]*)\], result: \"(\w+)\"", table, re.M):
+        params = [p for p in m.group(2).split(",") if p.strip()]
+        bound[m.group(1)] = (len(params), m.group(3))
+    declared = {name: (len(args), "pointer" if ret.startswith("const char") else "i32") for name, ret, args in _lib.declared_functions()}
+    assert bound == declared, f"only in cuda.ts: {sorted(set(bound) - set(declared))}, missing: {sorted(set(declared) - set(bound))}"

@@ -117,7 +117,8 @@ def test_world_of_one_goes_through_the_exchange_and_changes_nothing(capture, opt
             arena = gpu.reserveGradArena(list(reversed(m.params())))
             if optimizer == "muon":
                 g = m.paramGroups()
-                opt = MuonGpu(gpu, g["muon"], g["aux"], lr=0.02, aux={"lr": 1e-2, "beta1": 0.9, "beta2": 0.95, "clip": 1.0})
+                opt = MuonGpu(gpu, g["muon"], g["aux"], lr=0.02, aux={"lr": 1e-2, "beta1": 0.9, "beta2": 0.95, "clip": 1.0},
+                              shardOverRanks=with_dp)       # one rank: its share is everything, the all-gather is skipped
             else:
                 opt = AdamWGpu(gpu, m.params(), lr=1e-2, clip=1.0)
             step = CudaStep(m, gpu, B, T, world=1, capture=capture, dp=dp, arena=arena if dp else None, layersPerBucket=1)
