@@ -170,34 +170,47 @@ def run_reference(args):
 # GPU arm
 # ---------------------------------------------------------------------------------------------
 def backward_gemm_roofline(gpu, rows: int, iters: int = 5):
-    """The backward matrix products of one layer at this shape (dX = dY.W and dW = dY^T.X for q, k, v, o,
-    gate, up, down), launched back to back between two events on the library's stream. Operands are far
-    larger than L2 in aggregate (rows x 1536 f32 alone is 100 MB) and rotate between launches."""
+    """The backward matrix products of one layer at this shape as the step issues them: the weight gradients
+    dW = dY^T.X of q, k, v, o, gate, up, down as ONE grouped launch, and the input gradients dX = dY.W, those of the
+    activations that feed several projections as one launch each (dQ.Wq + dK.Wk + dV.Wv; dGate.Wg + dUp.Wu) and those of
+    o and down on their own: 5 launches, 2 x 2 x rows x in x out flop per projection. Launched back to back between two
+    events on the library's stream. Operands are far larger than L2 in aggregate (rows x 1536 f32 alone is 100 MB)."""
+    import ctypes as C
     h, q, kv, f = 576, 576, 192, 1536
-    shapes = [(q, h), (kv, h), (kv, h), (h, q), (f, h), (f, h), (h, f)]      # (out, in)
-    bufs = {}
+    bufs = []
 
     def buf(n):
-        if n not in bufs:
-            bufs[n] = gpu.createStateBuffer(n * 4)
-        return bufs[n]
+        bufs.append(gpu.createStateBuffer(n * 4))
+        return bufs[-1]
 
-    flops = 0
-    calls = []
-    for out, inn in shapes:
-        dy, x, w, dx, dw = buf(rows * out + 1), buf(rows * inn + 2), buf(out * inn + 3), buf(rows * inn + 4), buf(out * inn + 5)
-        calls.append(("NN", rows, inn, out, dy, w, dx))
-        calls.append(("TN", out, inn, rows, dy, x, dw))
-        flops += 2 * 2 * rows * inn * out
+    projections = [(q, h), (kv, h), (kv, h), (h, q), (f, h), (f, h), (h, f)]      # (out, in): q k v o gate up down
+    dys = [buf(rows * o) for o, _i in projections]
+    xs = {h: buf(rows * h), q + 1: buf(rows * q), f: buf(rows * f)}               # n1/n2 share a width; attention out; gated unit
+    x_of = [xs[h], xs[h], xs[h], xs[q + 1], xs[h], xs[h], xs[f]]
+    ws = [buf(o * i) for o, i in projections]
+    gws = [buf(o * i) for o, i in projections]
+    gx = {0: buf(rows * h), 3: buf(rows * q), 4: buf(rows * h), 6: buf(rows * f)}
+    flops = sum(2 * 2 * rows * i * o for o, i in projections)
+    n = len(projections)
+    Ms, Ns = (C.c_int32 * n)(*[o for o, _i in projections]), (C.c_int32 * n)(*[i for _o, i in projections])
+    As, Bs, Cs, acc = (C.c_uint64 * n)(*dys), (C.c_uint64 * n)(*x_of), (C.c_uint64 * n)(*gws), (C.c_int32 * n)(*([0] * n))
+
+    def multi(idx, inn, out):
+        k = len(idx)
+        Ks, A2, B2 = (C.c_int32 * k)(*[projections[j][0] for j in idx]), (C.c_uint64 * k)(*[dys[j] for j in idx]), (C.c_uint64 * k)(*[ws[j] for j in idx])
+        return lambda: gpu._check(gpu.lib.gt_gemm_multi(gpu.ctx, 1, 0, rows, inn, k, Ks, A2, B2, out))
+
+    calls = [lambda: gpu._check(gpu.lib.gt_gemm_grouped(gpu.ctx, 2, n, Ms, Ns, rows, As, Bs, Cs, acc)),
+             multi((0, 1, 2), h, gx[0]), multi((3,), q, gx[3]), multi((4, 5), h, gx[4]), multi((6,), f, gx[6])]
     for c in calls:
-        gpu._gemm(c[0], 0, *c[1:])
+        c()
     gpu.recordEvent(10)
     for _ in range(iters):
         for c in calls:
-            gpu._gemm(c[0], 0, *c[1:])
+            c()
     gpu.recordEvent(11)
     ms = gpu.elapsedMs(10, 11) / iters
-    for a in bufs.values():
+    for a in bufs:
         gpu._check(gpu.lib.gt_free(gpu.ctx, a))
     return flops, ms, len(calls)
 
@@ -244,7 +257,7 @@ def tf32_peak_and_comparator(rows: int, seconds: float = 3.0):
     layer()
     ms = timed(layer, 5)
     torch.cuda.empty_cache()
-    return {"burst": burst, "sustained": sustained, "how": "torch.matmul allow_tf32 8192^3: best of 10, and back to back for 3 s"}, \
+    return {"burst": burst, "sustained": sustained, "unit": "TFLOP/s", "how": "torch.matmul allow_tf32 8192^3: best of 10, and back to back for 3 s"}, \
         flops / (ms / 1e3) / 1e12
 
 
@@ -277,6 +290,7 @@ def run_ours(args):
     if args.plain:
         gpu.mergeInputGradients = False
         gpu.fuseResidualNorm = False
+        gpu.groupWeightGradients = False
     model = buildModel(cfg, 1234)       # same seed on every rank: replicated weights
     loss_chunk = args.loss_chunk if args.loss_chunk >= 0 else (32768 if args.config == "qwen3-lora" else 0)
     mask = None
@@ -428,13 +442,13 @@ def run_ours(args):
             "clocks": clocks,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": pk["tflops_sustained"], "unit": "TFLOP/s",
                          "frac": achieved / pk["tflops_sustained"],
-                         # dram__bytes_read.sum + dram__bytes_write.sum of these 14 launches at rows 16384 from one ncu capture
-                         # (profiles/gemm_tf32_rows16384.md), per launch; only meaningful at the default shape
-                         "traffic": (1095.7e6 / 14) if (args.config == "smollm2" and B * T == 16384) else None,
-                         "kernel": f"backward matrix products of one layer (dX and dW for 7 projections, {ncalls} launches, rows {B * T})",
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one layer's backward products at rows 16384 from one
+                         # ncu capture (profiles/gemm_tf32_rows16384.md), per launch; only meaningful at the default shape
+                         "traffic": (1095.7e6 / ncalls) if (args.config == "smollm2" and B * T == 16384) else None,
+                         "kernel": f"backward matrix products of one layer (dW of 7 projections grouped, dX merged per shared input: {ncalls} launches, rows {B * T})",
                          "peak_source": f"{pk['src']} bf16 sustained (the products run in tf32, whose own measured rate is tf32_peak)",
                          "tf32_peak": tf32_peak,
-                         "frac_of_tf32_sustained": (achieved / (tf32_peak["sustained"] / 1e3)) if tf32_peak else None,
+                         "frac_of_tf32_sustained": (achieved / tf32_peak["sustained"]) if tf32_peak else None,
                          "cublas_tf32_same_shapes": cublas_same},
         }
         if muon_line is not None:
@@ -515,9 +529,16 @@ def run_micro(args):
         return b
 
     lib, ctx = gpu.lib, gpu.ctx
-    gpu.setBatch(B, T)
     name = args.micro
     pk = peaks()
+    if name == "bwd-gemm":       # the roofline object itself: one layer's backward products, as the step issues them
+        flops, ms, n = backward_gemm_roofline(gpu, rows, iters=args.steps)
+        rate = flops / (ms / 1e3) / 1e12
+        print(json.dumps({"micro": f"backward matrix products of one layer (grouped dW, merged dX), {n} launches", "ms": ms, "achieved": rate, "unit": "TFLOP/s",
+                          "peak": pk["tflops_sustained"], "frac": rate / pk["tflops_sustained"], "rows": rows}), flush=True)
+        gpu.sync([])
+        return
+    gpu.setBatch(B, T)
     if name == "attention":
         Q, K, Vv, O, G = buf(rows * q), buf(rows * kv), buf(rows * kv), buf(rows * q, False), buf(rows * q)
         L = buf(Hq * rows, False)
@@ -544,6 +565,14 @@ def run_micro(args):
             Ks, As, Bs = (C.c_int32 * n)(*outs), (C.c_uint64 * n)(*dys), (C.c_uint64 * n)(*ws)
             cases.append((f"NN multi {rows}x{h}x({'+'.join(map(str, outs))}) [{label}]",
                           (lambda Ks=Ks, As=As, Bs=Bs, dx=dx, n=n: lib.gt_gemm_multi(ctx, 1, 0, rows, h, n, Ks, As, Bs, dx)), 2 * rows * h * sum(outs)))
+        # the weight gradients of a layer's seven projections as one grouped launch
+        shapes = [(q, h), (kv, h), (kv, h), (h, q), (f, h), (f, h), (h, f)]
+        n = len(shapes)
+        dys, xs, gws = [buf(rows * o) for o, _i in shapes], [buf(rows * i) for _o, i in shapes], [buf(o * i, False) for o, i in shapes]
+        Ms, Ns = (C.c_int32 * n)(*[o for o, _i in shapes]), (C.c_int32 * n)(*[i for _o, i in shapes])
+        As, Bs, Cs, acc = (C.c_uint64 * n)(*dys), (C.c_uint64 * n)(*xs), (C.c_uint64 * n)(*gws), (C.c_int32 * n)(*([0] * n))
+        cases.append((f"TN grouped: dW of q,k,v,o,gate,up,down at rows {rows}",
+                      (lambda: lib.gt_gemm_grouped(ctx, 2, n, Ms, Ns, rows, As, Bs, Cs, acc)), sum(2 * rows * o * i for o, i in shapes)))
         unit, peak = "TFLOP/s", pk["tflops_sustained"]
     else:
         raise SystemExit(f"unknown --micro {name}")
@@ -579,7 +608,7 @@ def main():
     ap.add_argument("--no-peak", action="store_true", help="skip the torch.matmul TF32 peak and comparator")
     ap.add_argument("--recompute", action="store_true")
     ap.add_argument("--profile", action="store_true", help="per-entry-point GPU time of one eager step")
-    ap.add_argument("--micro", default="", help="time one op of the step instead: attention | gemm")
+    ap.add_argument("--micro", default="", help="time one op of the step instead: attention | gemm | bwd-gemm")
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--window", type=int, default=0)
     ap.add_argument("--layers-per-bucket", type=int, default=6, help="data parallel: layers per gradient all-reduce bucket")

@@ -32,7 +32,7 @@ PRECISION = {"fp32": 0, "tf32": 1}   # (the C ABI reserves 2 for BF16 and refuse
 
 
 class _Entry:
-    __slots__ = ("data", "grad", "bytes", "external", "gradLive", "size", "pendingDx", "copyFrom")
+    __slots__ = ("data", "grad", "bytes", "external", "gradLive", "size", "pendingDx", "copyFrom", "pendingDw")
 
     def __init__(self, data: int, grad: int, nbytes: int, external: bool, size: int):
         self.data = data
@@ -43,6 +43,7 @@ class _Entry:
         self.size = size
         self.pendingDx = None     # (rows, cols, [(dY address, W address, K)]): input-gradient products not launched yet
         self.copyFrom = 0         # address whose contents are this gradient's value so far (a copy not made yet)
+        self.pendingDw = False    # a weight-gradient product into this gradient is noted in _pendingDw, not launched yet
 
 
 class CapturedGraph:
@@ -199,6 +200,9 @@ class CudaBackend:
         self._pendingAct = {}   # id(tensor) -> (tensor, op code, input tensor): activations not launched yet
         self._pendingDx: Dict[int, _Entry] = {}   # entries whose gradient still lacks deferred dY.W products
         self.mergeInputGradients = True
+        self._pendingDw: List[tuple] = []   # weight-gradient products not launched yet (see _deferDw)
+        self._pendingDwRows = 0
+        self.groupWeightGradients = True
         self._pendingAdd = {}   # id(tensor) -> (tensor, a, b): residual adds not launched yet (see add)
         self._pendingCopy: Dict[int, _Entry] = {}  # entries whose gradient is still a view of another buffer (see add)
         self.fuseResidualNorm = True
@@ -302,6 +306,8 @@ class CudaBackend:
 
     def _read(self, addr: int, out: np.ndarray):
         assert out.flags["C_CONTIGUOUS"]
+        if not self._capturing:
+            self._flushAllDx()          # whatever is read must not be missing a launch that was put off
         self._check(self.lib.gt_read(self.ctx, addr, out.ctypes.data, out.nbytes))
         self._readback += out.nbytes
 
@@ -413,11 +419,53 @@ class CudaBackend:
         for e in list(self._pendingDx.values()):
             self._flushDx(e)
         self._flushAllCopies()
+        self._flushDw()
+
+    # The weight gradient of `linear` is dW (+)= dY^T.X: a small output (out x in) contracted over every row. Each has
+    # too few output tiles to fill the GPU, so each is cut along K into slices, with a clear before, partial sums
+    # combined in L2 and a last wave of its own. Up to eight of them (the projections of a layer) are launched together
+    # as one grouped product (gt_gemm_grouped): their tiles share the SMs and one split-K factor. A closure notes its
+    # (dY, X, dW); the group is launched when it is full, before anything else touches one of its gradients, and at
+    # every point where buffers may be recycled or gradients are handed over (sync, region end, graph cut, optimizer).
+    def _deferDw(self, ew: _Entry, gw: int, accum: int, rows: int, outDim: int, inDim: int, dy: int, x: int):
+        if self._pendingDw and (self._pendingDwRows != rows or len(self._pendingDw) == 8):
+            self._flushDw()
+        self._pendingDwRows = rows
+        self._pendingDw.append((dy, x, gw, accum, outDim, inDim, ew))
+        ew.pendingDw = True
+
+    def _flushDw(self):
+        parts = self._pendingDw
+        if not parts:
+            return
+        self._pendingDw = []
+        rows = self._pendingDwRows
+        for p in parts:
+            p[6].pendingDw = False
+        n = len(parts)
+        if n == 1:
+            dy, x, gw, acc, outDim, inDim, _e = parts[0]
+            self._gemm("TN", acc, outDim, inDim, rows, dy, x, gw)
+            return
+        Ms = (C.c_int32 * n)(*[p[4] for p in parts])
+        Ns = (C.c_int32 * n)(*[p[5] for p in parts])
+        As = (C.c_uint64 * n)(*[p[0] for p in parts])
+        Bs = (C.c_uint64 * n)(*[p[1] for p in parts])
+        Cs = (C.c_uint64 * n)(*[p[2] for p in parts])
+        acc = (C.c_int32 * n)(*[p[3] for p in parts])
+        self._check(self.lib.gt_gemm_grouped(self.ctx, _KIND["TN"], n, Ms, Ns, rows, As, Bs, Cs, acc))
+
+    def flushDeferred(self):
+        """Launch everything whose launch was put off (merged input gradients, grouped weight gradients, copies):
+        called by whoever is about to use gradients outside the ops, e.g. an optimizer step or a gradient exchange."""
+        self._flushAllDx()
 
     def _gradTarget(self, t: Tensor, e: _Entry):
         """(grad address or 0, accum flag) for a backward kernel about to write into t's gradient."""
         if e.grad == 0 or (e.external and not t.requiresGrad):
             return 0, 0
+        if e.pendingDw:
+            self._flushDw()             # an earlier product into this gradient goes first
         if e.copyFrom:
             self._materializeCopy(e)
         if e.pendingDx is not None:
@@ -428,6 +476,8 @@ class CudaBackend:
 
     def _gradSource(self, e: _Entry) -> int:
         """The upstream gradient of an op output. Never written means it is exactly zero."""
+        if e.pendingDw:
+            self._flushDw()
         if e.pendingDx is not None:
             self._flushDx(e)           # (a gradient that is still a view gets its copy made first: _flushDx writes into it)
         if e.copyFrom:
@@ -772,7 +822,11 @@ class CudaBackend:
             if w.requiresGrad:
                 gw, aw = self._gradTarget(w, ew)
                 if gw:
-                    self._gemm("TN", aw, outDim, inDim, T, go, ex.data, gw)
+                    # (a product with many output tiles, the readout's, fills the GPU alone and is launched as it comes)
+                    if self.groupWeightGradients and ((outDim + 255) // 256) * ((inDim + 191) // 192) <= 64:
+                        self._deferDw(ew, gw, aw, T, outDim, inDim, go, ex.data)
+                    else:
+                        self._gemm("TN", aw, outDim, inDim, T, go, ex.data, gw)
 
         out._backward = _bw
         return out
@@ -1037,6 +1091,8 @@ class CudaBackend:
             if not weight.requiresGrad or not ew.grad:
                 return
             go = self._gradSource(eo)
+            if ew.pendingDw:
+                self._flushDw()
             if ew.pendingDx is not None:
                 self._flushDx(ew)
             if ew.copyFrom:

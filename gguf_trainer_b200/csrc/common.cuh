@@ -103,6 +103,8 @@ gt_status gt_gemm_tc_batched(gt_ctx* ctx, int kind, int accum, int M, int N, int
 gt_status gt_gemm_batched(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c, int batch);
 gt_status gt_gemm_tc_multi(gt_ctx* ctx, int kind, int accum, int M, int N, int nparts, const int* Ks, const float* const* as,
                            const float* const* bs, float* c, bool* handled);
+gt_status gt_gemm_tc_grouped(gt_ctx* ctx, int kind, int ngroups, const int* Ms, const int* Ns, int K, const float* const* as,
+                             const float* const* bs, float* const* cs, const int* accums, bool* handled);
 gt_status gt_gemm_tc_check(gt_ctx* ctx);
 void gt_optim_destroy(gt_ctx* ctx);
 void gt_dp_teardown(gt_ctx* ctx);

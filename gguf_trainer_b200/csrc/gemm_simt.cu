@@ -183,6 +183,32 @@ extern "C" gt_status gt_gemm_multi(gt_ctx* ctx, int32_t kind, int32_t accum, int
   return GT_OK;
 }
 
+// ngroups products of one layout and one depth K, each with its own operands, extents and accumulate flag: one launch
+// on the tensor-core path, one product after the other otherwise.
+extern "C" gt_status gt_gemm_grouped(gt_ctx* ctx, int32_t kind, int32_t ngroups, const int32_t* Ms, const int32_t* Ns, int32_t K,
+                                     const gt_buf* as, const gt_buf* bs, const gt_buf* cs, const int32_t* accums) {
+  GT_REQUIRE(ctx, ngroups >= 1 && ngroups <= 8 && K > 0 && Ms && Ns && as && bs && cs && accums, "gt_gemm_grouped: %d products (1..8), K %d", ngroups, K);
+  const float* pa[8];
+  const float* pb[8];
+  float* pc[8];
+  int m[8], n[8], acc[8];
+  for (int g = 0; g < ngroups; g++) {
+    GT_REQUIRE(ctx, Ms[g] > 0 && Ns[g] > 0 && as[g] && bs[g] && cs[g], "gt_gemm_grouped: product %d is empty or has a null operand", g);
+    pa[g] = gt_ptr<const float>(as[g]); pb[g] = gt_ptr<const float>(bs[g]); pc[g] = gt_ptr<float>(cs[g]);
+    m[g] = Ms[g]; n[g] = Ns[g]; acc[g] = accums[g];
+  }
+  if (ctx->precision != GT_PREC_FP32 && ngroups > 1) {
+    bool handled = false;
+    gt_status s = gt_gemm_tc_grouped(ctx, kind, ngroups, m, n, K, pa, pb, pc, acc, &handled);
+    if (s != GT_OK || handled) return s;
+  }
+  for (int g = 0; g < ngroups; g++) {
+    gt_status s = gt_gemm(ctx, kind, acc[g], m[g], n[g], K, as[g], bs[g], cs[g]);
+    if (s) return s;
+  }
+  return GT_OK;
+}
+
 extern "C" gt_status gt_gemm2(gt_ctx* ctx, int32_t kind, int32_t accum, int32_t M, int32_t N, int32_t K, gt_buf a, gt_buf b, int32_t K2,
                               gt_buf a2, gt_buf b2, gt_buf c) {
   GT_REQUIRE(ctx, M > 0 && N > 0 && K > 0 && K2 > 0, "gt_gemm2: empty product %dx%dx(%d+%d)", M, N, K, K2);

@@ -56,14 +56,21 @@ struct PartMaps {
   CUtensorMap a[MAX_PARTS], b[MAX_PARTS];
   int kb_end[MAX_PARTS];
   int nparts;
+  // Grouped form (ngroups > 1, one part): group g is its own product A_g.B_g -> C_g of gM[g] x gN[g], all of one
+  // layout and one K; its tiles are units [unit_end[g-1], unit_end[g]) of the launch (n fastest, then m, then the
+  // split-K slice). c[g] is its output map (c[0] the only one when ngroups == 1).
+  CUtensorMap c[MAX_PARTS];
+  int ngroups;
+  int gM[MAX_PARTS], gN[MAX_PARTS], g_accum[MAX_PARTS], unit_end[MAX_PARTS];
 };
 
 template <bool A_K, bool B_K, int BN, int MT>
 __global__ void __launch_bounds__(Smem<BN, MT>::THREADS, 1)
-gemm_tf32_kernel(const __grid_constant__ PartMaps maps, const __grid_constant__ CUtensorMap mapC, float* __restrict__ C, int M, int N,
-                 int accum, int ksplit, int use_tma_store, int batch, float out_scale, int* __restrict__ flag) {
+gemm_tf32_kernel(const __grid_constant__ PartMaps maps, float* __restrict__ C, int M_, int N_,
+                 int accum_, int ksplit, int use_tma_store, int batch, float out_scale, int* __restrict__ flag) {
   extern __shared__ uint8_t smem_raw[];
   using S = Smem<BN, MT>;
+  const int M = M_, N = N_;   // (of the single product; a grouped launch takes each group's from `maps`)
   constexpr int STAGES = S::STAGES, BM = S::BM;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t epi = base + STAGES * S::STAGE;    // staging tiles of the epilogue warps
@@ -78,7 +85,25 @@ gemm_tf32_kernel(const __grid_constant__ PartMaps maps, const __grid_constant__ 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_n = (N + BN - 1) / BN, tiles_m = (M + BM - 1) / BM;
   const int per_mat = tiles_n * tiles_m * ksplit;
-  const int ntiles = per_mat * batch;            // the matrices of a batch are just more tiles
+  const int ngroups = maps.ngroups;
+  const int ntiles = ngroups > 1 ? maps.unit_end[ngroups - 1] : per_mat * batch;   // the matrices of a batch are just more tiles
+  // where tile t lies: batch matrix (or group), first column, first row (of the 256-row tile when MT = 2), K slice
+  struct Where { int bi, g, n0, m0, z; };
+  auto where = [&](int t) {
+    Where w;
+    if (ngroups > 1) {
+      int g = 0;
+      while (t >= maps.unit_end[g]) g++;
+      const int tt = t - (g ? maps.unit_end[g - 1] : 0);
+      const int tn = (maps.gN[g] + BN - 1) / BN, tmn = tn * ((maps.gM[g] + BM - 1) / BM);
+      const int rem = tt % tmn;
+      w.bi = 0; w.g = g; w.z = tt / tmn; w.n0 = (rem % tn) * BN; w.m0 = (rem / tn) * BM;
+    } else {
+      const int tt = t % per_mat;
+      w.bi = t / per_mat; w.g = 0; w.n0 = (tt % tiles_n) * BN; w.m0 = ((tt / tiles_n) % tiles_m) * BM; w.z = tt / (tiles_n * tiles_m);
+    }
+    return w;
+  };
   // Further products of the same layout are accumulated into the same tiles: their K blocks simply follow those of
   // the first in the main loop, read through their own tensor maps.
   const int kblocks = maps.kb_end[maps.nparts - 1];
@@ -90,7 +115,9 @@ gemm_tf32_kernel(const __grid_constant__ PartMaps maps, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     for (int p = 0; p < maps.nparts; p++) { tma_prefetch_map(&maps.a[p]); tma_prefetch_map(&maps.b[p]); }
-    if (use_tma_store) tma_prefetch_map(&mapC);
+    for (int g = 1; g < ngroups; g++) { tma_prefetch_map(&maps.a[g]); tma_prefetch_map(&maps.b[g]); }
+    if (use_tma_store)
+      for (int g = 0; g < ngroups; g++) tma_prefetch_map(&maps.c[g]);
     for (int s = 0; s < STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     for (int b = 0; b < 2; b++) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 128); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -111,18 +138,18 @@ gemm_tf32_kernel(const __grid_constant__ PartMaps maps, const __grid_constant__ 
       // ---- TMA producer ----
       uint32_t it = 0;
       for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
-        const int bi = t / per_mat, tt = t % per_mat;
-        const int n0 = (tt % tiles_n) * BN, m0 = ((tt / tiles_n) % tiles_m) * BM, z = tt / (tiles_n * tiles_m);
+        const Where wh = where(t);
+        const int bi = wh.bi, n0 = wh.n0, m0 = wh.m0, z = wh.z;
         const int kb0 = z * per, kb1 = min(kblocks, kb0 + per);
-        int part = 0;
+        int part = wh.g;        // (a grouped launch has one K range per group: the group's operands)
         for (int kb = kb0; kb < kb1; kb++, it++) {
           const int s = it % STAGES;
           wait(empty_bar(s), ((it / STAGES) & 1) ^ 1, 1);
           const uint32_t a_dst = base + s * S::STAGE, b_dst = a_dst + S::A_BYTES;
-          while (kb >= maps.kb_end[part]) part++;
+          if (ngroups == 1) while (kb >= maps.kb_end[part]) part++;
           const CUtensorMap* pa = &maps.a[part];
           const CUtensorMap* pb = &maps.b[part];
-          const int k0 = (kb - (part ? maps.kb_end[part - 1] : 0)) * BK;
+          const int k0 = (ngroups == 1 ? kb - (part ? maps.kb_end[part - 1] : 0) : kb) * BK;
           mbar_expect_tx(full_bar(s), S::STAGE);
           if (A_K) tma_load_3d(a_dst, pa, k0, m0, bi, full_bar(s));
           else
@@ -142,7 +169,7 @@ gemm_tf32_kernel(const __grid_constant__ PartMaps maps, const __grid_constant__ 
       constexpr uint32_t A_STEP = A_K ? 32 : 1024, B_STEP = B_K ? 32 : 1024;   // bytes per K = 8 step
       uint32_t it = 0, tl = 0;
       for (int t = blockIdx.x; t < ntiles; t += gridDim.x, tl++) {
-        const int z = (t % per_mat) / (tiles_n * tiles_m);
+        const int z = where(t).z;
         const int kb0 = z * per, kb1 = min(kblocks, kb0 + per);
         const uint32_t par = par_of(tl) ^ 1;
         wait(acc_empty(slot_of(tl, 0)), par, 4);   // the epilogue has drained this accumulator
@@ -176,8 +203,11 @@ gemm_tf32_kernel(const __grid_constant__ PartMaps maps, const __grid_constant__ 
     const bool vec = (N & 3) == 0;
     uint32_t tl = 0, nst = 0;   // nst: TMA stores issued by this warp
     for (int t = blockIdx.x; t < ntiles; t += gridDim.x, tl++) {
-      const int bi = t / per_mat, tt = t % per_mat;
-      const int n0 = (tt % tiles_n) * BN, m0 = ((tt / tiles_n) % tiles_m) * BM + half * BM1, z = tt / (tiles_n * tiles_m);
+      const Where wh = where(t);
+      const int bi = wh.bi, n0 = wh.n0, m0 = wh.m0 + half * BM1, z = wh.z;
+      const int M = ngroups > 1 ? maps.gM[wh.g] : M_, N = ngroups > 1 ? maps.gN[wh.g] : N_;
+      const int accum = ngroups > 1 ? maps.g_accum[wh.g] : accum_;
+      const CUtensorMap* mapC = &maps.c[wh.g];
       const int b = slot_of(tl, half);
       const bool have = z * per < kblocks;     // an empty split-K slice issues no MMA and contributes nothing
       const int row = m0 + q * 32 + lane;
@@ -207,8 +237,8 @@ gemm_tf32_kernel(const __grid_constant__ PartMaps maps, const __grid_constant__ 
             fence_async_smem();
             __syncwarp();
             if (lane == 0 && !dead && m0 + q * 32 < M) {
-              if (ksplit > 1 || accum) tma_reduce_add_3d(&mapC, tile, col0, m0 + q * 32, bi);
-              else tma_store_3d(&mapC, tile, col0, m0 + q * 32, bi);
+              if (ksplit > 1 || accum) tma_reduce_add_3d(mapC, tile, col0, m0 + q * 32, bi);
+              else tma_store_3d(mapC, tile, col0, m0 + q * 32, bi);
             }
             if (lane == 0) tma_commit_group();
             nst++;
@@ -445,7 +475,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
 int* g_flag[64] = {};
 
 template <bool A_K, bool B_K, int BN, int MT>
-gt_status launch(gt_ctx* ctx, const PartMaps& maps, const CUtensorMap& mc, int tma_store, float* c, int M, int N, int accum, int ksplit,
+gt_status launch(gt_ctx* ctx, const PartMaps& maps, long ntiles, int tma_store, float* c, int M, int N, int accum, int ksplit,
                  int batch, float out_scale) {
   auto kern = gemm_tf32_kernel<A_K, B_K, BN, MT>;
   using S = Smem<BN, MT>;
@@ -454,9 +484,8 @@ gt_status launch(gt_ctx* ctx, const PartMaps& maps, const CUtensorMap& mc, int t
     GT_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
     attr_set[ctx->device] = true;
   }
-  const long ntiles = (long)gt_cdiv(N, BN) * gt_cdiv(M, S::BM) * ksplit * batch;
   dim3 grid((unsigned)min((long)(ctx->sm_count - ctx->sm_reserved), ntiles), 1, 1);
-  kern<<<grid, S::THREADS, S::TOTAL, ctx->stream>>>(maps, mc, c, M, N, accum, ksplit, tma_store, batch, out_scale, g_flag[ctx->device]);
+  kern<<<grid, S::THREADS, S::TOTAL, ctx->stream>>>(maps, c, M, N, accum, ksplit, tma_store, batch, out_scale, g_flag[ctx->device]);
   GT_LAUNCHED(ctx, "gemm_tf32_kernel");
   return GT_OK;
 }
@@ -510,11 +539,11 @@ int pair_capacity(gt_ctx* ctx) {
 }
 
 template <int BN, int MT>
-gt_status launch_kind(gt_ctx* ctx, int kind, const PartMaps& maps, const CUtensorMap& mc, int tma_store, float* c, int M, int N, int accum,
+gt_status launch_kind(gt_ctx* ctx, int kind, const PartMaps& maps, long ntiles, int tma_store, float* c, int M, int N, int accum,
                       int ksplit, int batch, float out_scale) {
-  if (kind == GT_GEMM_NT) return launch<true, true, BN, MT>(ctx, maps, mc, tma_store, c, M, N, accum, ksplit, batch, out_scale);
-  if (kind == GT_GEMM_NN) return launch<true, false, BN, MT>(ctx, maps, mc, tma_store, c, M, N, accum, ksplit, batch, out_scale);
-  return launch<false, false, BN, MT>(ctx, maps, mc, tma_store, c, M, N, accum, ksplit, batch, out_scale);
+  if (kind == GT_GEMM_NT) return launch<true, true, BN, MT>(ctx, maps, ntiles, tma_store, c, M, N, accum, ksplit, batch, out_scale);
+  if (kind == GT_GEMM_NN) return launch<true, false, BN, MT>(ctx, maps, ntiles, tma_store, c, M, N, accum, ksplit, batch, out_scale);
+  return launch<false, false, BN, MT>(ctx, maps, ntiles, tma_store, c, M, N, accum, ksplit, batch, out_scale);
 }
 
 }  // namespace
@@ -702,21 +731,94 @@ static gt_status gemm_tc_dispatch(gt_ctx* ctx, int kind, int accum, int M, int N
   for (int p = nparts; p < MAX_PARTS; p++) { maps.a[p] = maps.a[0]; maps.b[p] = maps.b[0]; maps.kb_end[p] = kb_sum; }
   // the output goes through TMA (32x32 blocks of whole 128-byte rows) whenever its row pitch allows a tensor map
   const uint64_t sc = (uint64_t)M * N;
-  CUtensorMap mc = maps.a[0];
-  const int tma_store = ((N & 3) == 0 && make_map_3d(&mc, c, N, M, batch, N, sc, 32, true)) ? 1 : 0;
+  maps.ngroups = 1;
+  maps.c[0] = maps.a[0];
+  const int tma_store = ((N & 3) == 0 && make_map_3d(&maps.c[0], c, N, M, batch, N, sc, 32, true)) ? 1 : 0;
+  for (int p = 1; p < MAX_PARTS; p++) maps.c[p] = maps.c[0];
+  for (int p = 0; p < MAX_PARTS; p++) { maps.gM[p] = M; maps.gN[p] = N; maps.g_accum[p] = accum; maps.unit_end[p] = 0; }
   if (ksplit > 1 && !accum) GT_CUDA(ctx, cudaMemsetAsync(c, 0, sizeof(float) * (size_t)M * N * batch, ctx->stream));
   const float out_scale = alpha * TRUNC_COMP;
   const int K0 = Ks[0];
+  const long ntiles = (long)gt_cdiv(N, bn) * gt_cdiv(M, mt == 1 ? BM1 : 2 * BM1) * ksplit * batch;
   gt_status s;
-  if (mt == 3 && bn == 192) s = launch_pair_kind<192>(ctx, kind, maps.a[0], maps.b[0], mc, tma_store, c, M, N, K0, accum, ksplit, batch, npairs, out_scale);
-  else if (mt == 3) s = launch_pair_kind<256>(ctx, kind, maps.a[0], maps.b[0], mc, tma_store, c, M, N, K0, accum, ksplit, batch, npairs, out_scale);
-  else if (mt == 1 && bn == 192) s = launch_kind<192, 1>(ctx, kind, maps, mc, tma_store, c, M, N, accum, ksplit, batch, out_scale);
-  else if (mt == 1) s = launch_kind<128, 1>(ctx, kind, maps, mc, tma_store, c, M, N, accum, ksplit, batch, out_scale);
-  else if (bn == 256) s = launch_kind<256, 2>(ctx, kind, maps, mc, tma_store, c, M, N, accum, ksplit, batch, out_scale);
-  else s = launch_kind<192, 2>(ctx, kind, maps, mc, tma_store, c, M, N, accum, ksplit, batch, out_scale);
+  if (mt == 3 && bn == 192) s = launch_pair_kind<192>(ctx, kind, maps.a[0], maps.b[0], maps.c[0], tma_store, c, M, N, K0, accum, ksplit, batch, npairs, out_scale);
+  else if (mt == 3) s = launch_pair_kind<256>(ctx, kind, maps.a[0], maps.b[0], maps.c[0], tma_store, c, M, N, K0, accum, ksplit, batch, npairs, out_scale);
+  else if (mt == 1 && bn == 192) s = launch_kind<192, 1>(ctx, kind, maps, ntiles, tma_store, c, M, N, accum, ksplit, batch, out_scale);
+  else if (mt == 1) s = launch_kind<128, 1>(ctx, kind, maps, ntiles, tma_store, c, M, N, accum, ksplit, batch, out_scale);
+  else if (bn == 256) s = launch_kind<256, 2>(ctx, kind, maps, ntiles, tma_store, c, M, N, accum, ksplit, batch, out_scale);
+  else s = launch_kind<192, 2>(ctx, kind, maps, ntiles, tma_store, c, M, N, accum, ksplit, batch, out_scale);
   if (s) return s;
   *handled = true;
   return GT_OK;
+}
+
+// ngroups independent products of one layout and one K, each with its own operands, extents and accumulate flag, as
+// ONE launch: the weight gradients dW_g = dY_g^T.X_g of several projections (K = rows for all of them). Their tiles
+// are so few per product that each would need its own split-K launch with its own tail; together they fill the SMs.
+static gt_status gemm_tc_grouped(gt_ctx* ctx, int kind, int ngroups, const int* Ms, const int* Ns, int K, const float* const* as,
+                                 const float* const* bs, float* const* cs, const int* accums, bool* handled) {
+  *handled = false;
+  if (ngroups < 2 || ngroups > MAX_PARTS || K < 16) return GT_OK;
+  const bool a_k = kind != GT_GEMM_TN, b_k = kind == GT_GEMM_NT;
+  for (int g = 0; g < ngroups; g++) {
+    const int a_inner = a_k ? K : Ms[g], b_inner = b_k ? K : Ns[g];
+    if (Ms[g] < 16 || Ns[g] < 16 || (a_inner & 3) || (b_inner & 3) || (Ns[g] & 3)) return GT_OK;
+    if ((((uintptr_t)as[g]) | ((uintptr_t)bs[g]) | ((uintptr_t)cs[g])) & 15) return GT_OK;
+  }
+  if (ctx->device < 0 || ctx->device >= 64 || !device_flag(ctx)) return GT_OK;
+  const int kblocks = gt_cdiv(K, BK);
+  const long workers = ctx->sm_count - ctx->sm_reserved;
+  // 256 x 192 or 128 x 192 tiles; the split-K factor (one for the whole launch) that wastes least of the last wave,
+  // among those that leave a slice at least 8 K blocks and add at most 8 partial sums per output element
+  int best_mt = 1, best_ks = 1;
+  double best_cost = 1e30;
+  const char* force = getenv("GT_GEMM_TILE");
+  for (int mt = 1; mt <= 2; mt++) {
+    if (force) { int fm = 0, fb = 0; if (sscanf(force, "%d,%d", &fm, &fb) == 2 && (fm != mt || fb != 192)) continue; }
+    long tiles = 0;
+    for (int g = 0; g < ngroups; g++) tiles += (long)gt_cdiv(Ns[g], 192) * gt_cdiv(Ms[g], mt * BM1);
+    const double per_kb = 0.92 * ((mt * BM1 * 128.0 + 192 * 128.0) + mt * (BM1 * 128.0 + 192 * 128.0)) / 128.0;
+    const double epilogue = mt == 2 ? 14.0 * 192 + 900.0 : 1500.0;
+    for (int ks = 1; ks <= 8 && (ks == 1 || kblocks / ks >= 8); ks++) {
+      const long waves = gt_cdiv(tiles * ks, workers);
+      const double cost = waves * (gt_cdiv(kblocks, ks) * per_kb + epilogue + (ks > 1 ? 600.0 : 0.0));
+      if (cost < best_cost) { best_cost = cost; best_mt = mt; best_ks = ks; }
+    }
+  }
+  if (best_cost >= 1e30) return GT_OK;
+  const int mt = best_mt, ksplit = best_ks, bm = mt * BM1;
+  PartMaps maps;
+  maps.nparts = 1;
+  maps.ngroups = ngroups;
+  int units = 0;
+  for (int g = 0; g < ngroups; g++) {
+    const int M = Ms[g], N = Ns[g];
+    const bool oka = a_k ? make_map_3d(&maps.a[g], as[g], K, M, 1, K, (uint64_t)M * K, bm, true) : make_map_3d(&maps.a[g], as[g], M, K, 1, M, (uint64_t)M * K, BK, false);
+    const bool okb = b_k ? make_map_3d(&maps.b[g], bs[g], K, N, 1, K, (uint64_t)N * K, 192, true) : make_map_3d(&maps.b[g], bs[g], N, K, 1, N, (uint64_t)N * K, BK, false);
+    const bool okc = make_map_3d(&maps.c[g], cs[g], N, M, 1, N, (uint64_t)M * N, 32, true);
+    if (!oka || !okb || !okc) return GT_OK;
+    units += gt_cdiv(N, 192) * gt_cdiv(M, bm) * ksplit;
+    maps.unit_end[g] = units;
+    maps.gM[g] = M; maps.gN[g] = N; maps.g_accum[g] = accums[g];
+    maps.kb_end[g] = kblocks;
+  }
+  for (int g = ngroups; g < MAX_PARTS; g++) {
+    maps.a[g] = maps.a[0]; maps.b[g] = maps.b[0]; maps.c[g] = maps.c[0];
+    maps.unit_end[g] = units; maps.gM[g] = Ms[0]; maps.gN[g] = Ns[0]; maps.g_accum[g] = accums[0]; maps.kb_end[g] = kblocks;
+  }
+  if (ksplit > 1)
+    for (int g = 0; g < ngroups; g++)
+      if (!accums[g]) GT_CUDA(ctx, cudaMemsetAsync(cs[g], 0, sizeof(float) * (size_t)Ms[g] * Ns[g], ctx->stream));
+  gt_status s = mt == 1 ? launch_kind<192, 1>(ctx, kind, maps, units, 1, cs[0], Ms[0], Ns[0], accums[0], ksplit, 1, TRUNC_COMP)
+                        : launch_kind<192, 2>(ctx, kind, maps, units, 1, cs[0], Ms[0], Ns[0], accums[0], ksplit, 1, TRUNC_COMP);
+  if (s) return s;
+  *handled = true;
+  return GT_OK;
+}
+
+gt_status gt_gemm_tc_grouped(gt_ctx* ctx, int kind, int ngroups, const int* Ms, const int* Ns, int K, const float* const* as,
+                             const float* const* bs, float* const* cs, const int* accums, bool* handled) {
+  return gemm_tc_grouped(ctx, kind, ngroups, Ms, Ns, K, as, bs, cs, accums, handled);
 }
 
 gt_status gt_gemm_tc_batched(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c, int batch,

@@ -81,6 +81,7 @@ class AdamWGpu:
         """No-op: gradients are device-resident and restart at the next step's first write."""
 
     def recordStep(self):
+        self.gpu.flushDeferred()  # gradient products whose launch was put off
         self.gpu.readFence()      # a checkpoint still being copied out reads the values this step overwrites
         self.gpu._check(self.gpu.lib.gt_adamw_step(self.gpu.ctx, self.handle))
 
@@ -167,6 +168,7 @@ class MuonGpu:
         self.aux.zeroGrad()
 
     def recordStep(self):
+        self.gpu.flushDeferred()
         self.gpu.readFence()
         self.gpu._check(self.gpu.lib.gt_muon_step(self.gpu.ctx, self.handle))
         self.aux.recordStep()

@@ -217,6 +217,7 @@ class CudaStep:
                     if self.gpu._capturing:
                         self.gpu.cutCapture()         # the replayer starts this bucket's reduction here
                     else:
+                        self.gpu.flushDeferred()      # the bucket's gradients must all have been launched
                         self.dp.start(base + start * 4, count)
                     self.dp.reserve(True)             # what follows runs (and is recorded) beside a reduction
                     orig()
@@ -225,6 +226,7 @@ class CudaStep:
             backward(loss, seed)
             _l, start, count = plan[-1]
             if not self.gpu._capturing:
+                self.gpu.flushDeferred()
                 self.dp.start(base + start * 4, count)
                 self.dp.wait()
             self.dp.reserve(False)

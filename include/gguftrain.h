@@ -96,6 +96,12 @@ gt_status gt_gemm2(gt_ctx* ctx, int32_t kind, int32_t accum, int32_t M, int32_t 
  * its term, src/backend/webgpu.ts:884-903). */
 gt_status gt_gemm_multi(gt_ctx* ctx, int32_t kind, int32_t accum, int32_t M, int32_t N, int32_t nparts, const int32_t* Ks,
                         const gt_buf* as, const gt_buf* bs, gt_buf c);
+/* ngroups (1..8) independent products of one layout and one depth K as one launch: C_g[Ms[g], Ns[g]] (+)= op(A_g)*op(B_g)
+ * with accums[g] per product. The weight gradients dW = dY^T.X of the projections of a layer (every `linear` backward
+ * issues its own, src/backend/webgpu.ts:898-901) have few output tiles each and a contraction over all rows; grouped,
+ * their tiles share the SMs and one split-K factor instead of each paying a launch, a clear and a last wave. */
+gt_status gt_gemm_grouped(gt_ctx* ctx, int32_t kind, int32_t ngroups, const int32_t* Ms, const int32_t* Ns, int32_t K,
+                          const gt_buf* as, const gt_buf* bs, const gt_buf* cs, const int32_t* accums);
 /* add/mul/silu/gelu/scale (webgpu.ts:905-1078, srcElementwise wgsl.ts:199-209) */
 gt_status gt_ew_fwd(gt_ctx* ctx, int32_t op, uint64_t n, gt_buf a, gt_buf b, float c, gt_buf out);
 gt_status gt_ew_bwd(gt_ctx* ctx, int32_t op, uint64_t n, gt_buf a, gt_buf b, float c, gt_buf gout,

@@ -295,3 +295,82 @@ def test_muon_batched_groups_in_tf32_mode(gpu, oracle):
         # the update itself (15 chained tf32 products per step) is held to 1e-2
         d = rel_l2(p.data.reshape(shapes[i]) - w0[i], w - w0[i])
         assert d <= 1e-2, f"matrix {i} {shapes[i]}: update relative L2 {d:.3e}"
+
+
+def test_fused_cross_entropy_large_vocab_tf32(gpu, oracle):
+    """The chunked readout loss on the tensor-core path at a large vocabulary: V = 40000 in chunks of 16384 (two full
+    spans and a ragged one of 7232), a third of the rows masked out, against the f64 dense formula: loss, dHidden and
+    dW (webgpu.ts:1214-1278 is the op; the case follows tests/gpu-parity.ts:174-207 at a size where spans are real)."""
+    from gpu_harness import rand_tensor
+    from gguf_trainer_b200 import autograd as ag
+    T, H, V, chunk = 192, 128, 40000, 16384
+    rng = oracle.Mulberry32(0xCE)
+    hidden = rand_tensor(rng, [T, H], 1.0)
+    w = rand_tensor(rng, [V, H], 0.05)
+    targets = oracle.Mulberry32(9).randint(T, V)
+    targets[::3] = -1
+    targets[5] = V - 1                     # a target inside the ragged last span
+    for t in (hidden, w):
+        t.zeroGrad()
+    gpu.install()
+    try:
+        loss = ag.fusedCrossEntropy(hidden, w, targets, chunk)
+        ag.backward(loss, 1.0)
+        gpu.sync([loss])
+    finally:
+        gpu.uninstall()
+    Hd, W = hidden.data.astype(np.float64).reshape(T, H), w.data.astype(np.float64).reshape(V, H)
+    z = Hd @ W.T
+    z -= z.max(axis=1, keepdims=True)
+    p = np.exp(z)
+    p /= p.sum(axis=1, keepdims=True)
+    kept = targets >= 0
+    rows = np.nonzero(kept)[0]
+    ref_loss = -np.log(p[rows, targets[rows]]).mean()
+    dz = p.copy()
+    dz[rows, targets[rows]] -= 1.0
+    dz[~kept] = 0.0
+    dz /= kept.sum()
+    assert abs(float(loss.data[0]) - ref_loss) <= REL_L2_TC * ref_loss
+    for name, got, want in (("dHidden", hidden.grad, dz @ W), ("dW", w.grad, dz.T @ Hd)):
+        r = rel_l2(got, want)
+        assert r <= REL_L2_TC, f"{name}: relative L2 {r:.3e}"
+    assert not hidden.grad.reshape(T, H)[~kept].any()      # masked rows get exactly no gradient
+
+
+@pytest.mark.parametrize("tile", ["", "1,192", "2,192"])
+@pytest.mark.parametrize("kind,K,shapes", [
+    ("TN", 2048, [(576, 576), (192, 576), (192, 576), (576, 576), (1536, 576), (1536, 576), (576, 1536)]),   # a layer's dW
+    ("TN", 300, [(100, 200), (16, 64), (132, 36)]),
+    ("NT", 96, [(513, 200), (64, 48)]),
+    ("NN", 1024, [(256, 192), (256, 192), (128, 576), (40, 24), (300, 100), (16, 16), (700, 64), (64, 700)])])
+def test_gemm_grouped_products_in_one_launch(gpu, oracle, monkeypatch, tile, kind, K, shapes):
+    """gt_gemm_grouped: independent products of one layout and one K, each with its own extents, operands and
+    accumulate flag, as one launch (the weight gradients of a layer's projections). Both tile shapes forced in turn
+    and the dispatcher's own choice; every other product accumulates."""
+    import ctypes as C
+    if tile:
+        monkeypatch.setenv("GT_GEMM_TILE", tile)
+    rng = oracle.Mulberry32(K + 17 * len(shapes))
+    As = [rng.randn((M, K), 0.5) for M, _N in shapes]
+    Bs = [rng.randn((N, K), 0.5) for _M, N in shapes]
+    C0 = [rng.randn(s, 0.5) for s in shapes]
+    accs = [g % 2 for g in range(len(shapes))]
+    sa = (lambda X: X if kind != "TN" else np.ascontiguousarray(X.T))
+    sb = (lambda X: X if kind == "NT" else np.ascontiguousarray(X.T))
+    da, db, dc = [_dev(gpu, sa(a)) for a in As], [_dev(gpu, sb(b)) for b in Bs], [_dev(gpu, c) for c in C0]
+    n = len(shapes)
+    launches = gpu.kernelLaunches()
+    gpu._check(gpu.lib.gt_gemm_grouped(gpu.ctx, {"NT": 0, "NN": 1, "TN": 2}[kind], n, (C.c_int32 * n)(*[s[0] for s in shapes]),
+                                       (C.c_int32 * n)(*[s[1] for s in shapes]), K, (C.c_uint64 * n)(*da), (C.c_uint64 * n)(*db),
+                                       (C.c_uint64 * n)(*dc), (C.c_int32 * n)(*accs)))
+    got = [gpu.readStateBuffer(c, s[0] * s[1]).reshape(s) for c, s in zip(dc, shapes)]
+    gpu.sync([])
+    assert gpu.kernelLaunches() - launches == 1
+    for g, (a, b, c0, acc) in enumerate(zip(As, Bs, C0, accs)):
+        want = a.astype(np.float64) @ b.astype(np.float64).T + (c0.astype(np.float64) if acc else 0.0)
+        r = rel_l2(got[g], want)
+        assert np.isfinite(got[g]).all() and r <= REL_L2_TC, f"product {g} {shapes[g]} accum={acc}: relative L2 {r:.3e}"
+        assert r > 1e-7, "the strict-f32 kernel answered"
+    for b in da + db + dc:
+        gpu._check(gpu.lib.gt_free(gpu.ctx, b))
