@@ -442,9 +442,9 @@ def run_ours(args):
             "clocks": clocks,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": pk["tflops_sustained"], "unit": "TFLOP/s",
                          "frac": achieved / pk["tflops_sustained"],
-                         # dram__bytes_read.sum + dram__bytes_write.sum of one layer's backward products at rows 16384 from one
-                         # ncu capture (profiles/gemm_tf32_rows16384.md), per launch; only meaningful at the default shape
-                         "traffic": (1095.7e6 / ncalls) if (args.config == "smollm2" and B * T == 16384) else None,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of these launches at rows 16384 from one ncu capture
+                         # (profiles/gemm_tf32_rows16384.md: 1063.1 MB for the five), per launch; only meaningful at the default shape
+                         "traffic": (1063.1e6 / ncalls) if (args.config == "smollm2" and B * T == 16384) else None,
                          "kernel": f"backward matrix products of one layer (dW of 7 projections grouped, dX merged per shared input: {ncalls} launches, rows {B * T})",
                          "peak_source": f"{pk['src']} bf16 sustained (the products run in tf32, whose own measured rate is tf32_peak)",
                          "tf32_peak": tf32_peak,
