@@ -291,6 +291,7 @@ def run_ours(args):
         gpu.mergeInputGradients = False
         gpu.fuseResidualNorm = False
         gpu.groupWeightGradients = False
+        gpu.groupForward = False
     model = buildModel(cfg, 1234)       # same seed on every rank: replicated weights
     loss_chunk = args.loss_chunk if args.loss_chunk >= 0 else (32768 if args.config == "qwen3-lora" else 0)
     mask = None
@@ -308,6 +309,12 @@ def run_ours(args):
     arena = gpu.reserveGradArena(order)
     for p in params:
         gpu.keepGradOnDevice(p)
+    dp = None
+    if world > 1:       # (before the optimizers: a sharded Muon asks the communicator for its rank)
+        uid = [DataParallel.uniqueId() if rank == 0 else None]
+        dist.broadcast_object_list(uid, src=0)
+        dp = DataParallel(gpu, rank, world, uid[0], commCtas=args.comm_ctas)
+
     def make_muon():
         return MuonGpu(gpu, groups["muon"], groups["aux"], lr=0.02, momentum=0.95, nesterov=True, nsSteps=5,
                        aux={"lr": 1e-3, "beta1": 0.9, "beta2": 0.95, "weightDecay": 0.0, "clip": 1.0},
@@ -318,11 +325,6 @@ def run_ours(args):
     else:
         opt = AdamWGpu(gpu, params, lr=1e-3, beta1=0.9, beta2=0.95, weightDecay=0.1, clip=1.0)
     opts = {"cur": opt}
-    dp = None
-    if world > 1:
-        uid = [DataParallel.uniqueId() if rank == 0 else None]
-        dist.broadcast_object_list(uid, src=0)
-        dp = DataParallel(gpu, rank, world, uid[0], commCtas=args.comm_ctas)
 
     # synthetic stream; rank r takes draws [r*B, (r+1)*B) of each step's B*world windows
     need = (args.steps + args.warmup + 2) * B * world

@@ -32,7 +32,7 @@ PRECISION = {"fp32": 0, "tf32": 1}   # (the C ABI reserves 2 for BF16 and refuse
 
 
 class _Entry:
-    __slots__ = ("data", "grad", "bytes", "external", "gradLive", "size", "pendingDx", "copyFrom", "pendingDw")
+    __slots__ = ("data", "grad", "bytes", "external", "gradLive", "size", "pendingDx", "copyFrom", "pendingDw", "pendingFwd")
 
     def __init__(self, data: int, grad: int, nbytes: int, external: bool, size: int):
         self.data = data
@@ -44,6 +44,7 @@ class _Entry:
         self.pendingDx = None     # (rows, cols, [(dY address, W address, K)]): input-gradient products not launched yet
         self.copyFrom = 0         # address whose contents are this gradient's value so far (a copy not made yet)
         self.pendingDw = False    # a weight-gradient product into this gradient is noted in _pendingDw, not launched yet
+        self.pendingFwd = False   # the projection that produces this tensor is noted in _pendingFwd, not launched yet
 
 
 class CapturedGraph:
@@ -200,6 +201,8 @@ class CudaBackend:
         self._pendingAct = {}   # id(tensor) -> (tensor, op code, input tensor): activations not launched yet
         self._pendingDx: Dict[int, _Entry] = {}   # entries whose gradient still lacks deferred dY.W products
         self.mergeInputGradients = True
+        self._pendingFwd: List[dict] = []   # projections of one input not launched yet (see _deferLinear)
+        self.groupForward = True
         self._pendingDw: List[tuple] = []   # weight-gradient products not launched yet (see _deferDw)
         self._pendingDwRows = 0
         self.groupWeightGradients = True
@@ -348,6 +351,8 @@ class CudaBackend:
                        nbytes, True, t.size)
             self._entries[t] = e
             self._write(e.data, t.data)
+        if e.pendingFwd:
+            self._flushFwd()
         if e.external and id(t) not in self._touched:
             self._touched[id(t)] = t
         return e
@@ -359,6 +364,8 @@ class CudaBackend:
             e = self._materializeAct(t)
         if e is None and id(t) in self._pendingAdd:
             e = self._materializeAdd(t)
+        if e is not None and e.pendingFwd:
+            self._flushFwd()
         return e
 
     def _makeOut(self, shape, prev) -> tuple:
@@ -415,7 +422,37 @@ class CudaBackend:
         Bs = (C.c_uint64 * n)(*[p[1] for p in parts])
         self._check(self.lib.gt_gemm_multi(self.ctx, _KIND["NN"], acc, rows, cols, n, Ks, As, Bs, e.grad))
 
+    # Projections of the same activation (q, k and v of the normed input; gate and up) are noted when recorded and
+    # launched together when the first of their outputs is needed: q/k/v as one grouped product (gt_gemm_grouped), gate and
+    # up, when a gated unit consumes both, as one launch that also applies the unit (gt_glu_linear_fwd, see _gatedUnit).
+    def _deferLinear(self, ex: _Entry, ew: _Entry, eo: _Entry, T: int, inDim: int, outDim: int):
+        if self._pendingFwd and (self._pendingFwd[0]["ex"] is not ex or len(self._pendingFwd) == 8):
+            self._flushFwd()
+        self._pendingFwd.append(dict(ex=ex, ew=ew, eo=eo, T=T, inDim=inDim, outDim=outDim))
+        eo.pendingFwd = True
+
+    def _flushFwd(self):
+        parts = self._pendingFwd
+        if not parts:
+            return
+        self._pendingFwd = []
+        for p in parts:
+            p["eo"].pendingFwd = False
+        n = len(parts)
+        T, inDim = parts[0]["T"], parts[0]["inDim"]
+        if n == 1:
+            self._gemm("NT", 0, T, parts[0]["outDim"], inDim, parts[0]["ex"].data, parts[0]["ew"].data, parts[0]["eo"].data)
+            return
+        Ms = (C.c_int32 * n)(*([T] * n))
+        Ns = (C.c_int32 * n)(*[p["outDim"] for p in parts])
+        As = (C.c_uint64 * n)(*[p["ex"].data for p in parts])
+        Bs = (C.c_uint64 * n)(*[p["ew"].data for p in parts])
+        Cs = (C.c_uint64 * n)(*[p["eo"].data for p in parts])
+        acc = (C.c_int32 * n)(*([0] * n))
+        self._check(self.lib.gt_gemm_grouped(self.ctx, _KIND["NT"], n, Ms, Ns, inDim, As, Bs, Cs, acc))
+
     def _flushAllDx(self):
+        self._flushFwd()
         for e in list(self._pendingDx.values()):
             self._flushDx(e)
         self._flushAllCopies()
@@ -675,7 +712,11 @@ class CudaBackend:
         self._write(e.grad, t.grad)
         e.gradLive = True
 
-    def _beginForwardOp(self):
+    def _beginForwardOp(self, keepPending: bool = False):
+        """Every forward op starts here. Unless the op launches nothing itself (`keepPending`), projections noted but
+        not launched yet go first, so no kernel can read an output that does not exist yet."""
+        if self._pendingFwd and not keepPending:
+            self._flushFwd()
         self._backwardBegun = False
         self._graphSynced = False
         self._graphOpen = True
@@ -683,6 +724,8 @@ class CudaBackend:
     def _ensureBackwardBegun(self):
         """webgpu.ts:1397-1429. A sync() between a graph's forward and its backward recycled the graph's
         buffers; refuse to accumulate into them."""
+        if self._pendingFwd:
+            self._flushFwd()
         if self._backwardBegun:
             return
         if self._graphSynced:
@@ -807,12 +850,16 @@ class CudaBackend:
 
     def linear(self, x: Tensor, w: Tensor) -> Tensor:
         """webgpu.ts:884-903."""
-        self._beginForwardOp()
+        self._beginForwardOp(keepPending=True)
         T, inDim = x.shape
         outDim = w.shape[0]
         ex, ew = self._entryFor(x), self._entryFor(w)
         out, eo = self._makeOut([T, outDim], [x, w])
-        self._gemm("NT", 0, T, outDim, inDim, ex.data, ew.data, eo.data)
+        if self.groupForward:
+            self._deferLinear(ex, ew, eo, T, inDim, outDim)
+        else:
+            self._flushFwd()
+            self._gemm("NT", 0, T, outDim, inDim, ex.data, ew.data, eo.data)
 
         def _bw():
             self._ensureBackwardBegun()
@@ -906,7 +953,7 @@ class CudaBackend:
         launches the plain add then. Backward launches nothing where it can (see _materializeCopy)."""
         if a is b or not self.fuseResidualNorm or a.shape != b.shape:
             return self._elementwise("add", a, b, 0.0)
-        self._beginForwardOp()
+        self._beginForwardOp(keepPending=True)
         ea, eb = self._entryFor(a), self._entryFor(b)
         out = Tensor.zeros(a.shape)
         out._prev = [a, b]
@@ -944,6 +991,7 @@ class CudaBackend:
     def _materializeAdd(self, t: Tensor) -> _Entry:
         _t, a, b = self._pendingAdd.pop(id(t))
         ea, eb = self._entries[a], self._entries[b]
+        self._flushFwd()
         e = self._newEntry(t)
         self._check(self.lib.gt_ew_fwd(self.ctx, _EW["add"], t.size, ea.data, eb.data, 0.0, e.data))
         return e
@@ -967,8 +1015,10 @@ class CudaBackend:
     def _activation(self, op: str, x: Tensor) -> Tensor:
         if not self.fuseGatedUnits:
             return self._elementwise(op, x, None, 0.0)
-        self._beginForwardOp()
-        self._entryFor(x)
+        self._beginForwardOp(keepPending=True)
+        e0 = self._entries.get(x)
+        if e0 is None or not e0.pendingFwd:      # (a projection still waiting to be launched stays waiting: see _gatedUnit)
+            self._entryFor(x)
         t = Tensor.zeros(x.shape)
         t._prev = [x]
         self._pendingAct[id(t)] = (t, _EW[op], x)
@@ -989,6 +1039,7 @@ class CudaBackend:
     def _materializeAct(self, t: Tensor) -> _Entry:
         _t, code, x = self._pendingAct.pop(id(t))
         ex = self._entries[x]
+        self._flushFwd()
         nbytes = t.size * 4
         e = _Entry(self._acquireRecycled(nbytes), self._acquireRecycled(nbytes), nbytes, False, t.size)
         self._entries[t] = e
@@ -1007,11 +1058,24 @@ class CudaBackend:
 
     def _gatedUnit(self, act: Tensor, u: Tensor) -> Tensor:
         _t, code, x = self._pendingAct[id(act)]
-        self._beginForwardOp()
-        ex, eu = self._entries[x], self._entryFor(u)
-        out, eo = self._makeOut(act.shape, [act, u])
+        self._beginForwardOp(keepPending=True)
+        ex, eu = self._entries[x], self._entries.get(u)
+        pend = self._pendingFwd
+        if (eu is not None and len(pend) == 2 and ex.pendingFwd and eu.pendingFwd and ex is not eu
+                and {id(pend[0]["eo"]), id(pend[1]["eo"])} == {id(ex), id(eu)} and pend[0]["outDim"] == pend[1]["outDim"]):
+            # gate and up are the two projections waiting to be launched: one launch writes both and the gated unit
+            pg, pu = (pend[0], pend[1]) if pend[0]["eo"] is ex else (pend[1], pend[0])
+            self._pendingFwd = []
+            ex.pendingFwd = eu.pendingFwd = False
+            out, eo = self._makeOut(act.shape, [act, u])
+            self._check(self.lib.gt_glu_linear_fwd(self.ctx, code, pg["T"], pg["outDim"], pg["inDim"], pg["ex"].data, pg["ew"].data,
+                                                   pu["ew"].data, ex.data, eu.data, eo.data))
+        else:
+            self._flushFwd()
+            eu = self._entryFor(u)
+            out, eo = self._makeOut(act.shape, [act, u])
+            self._check(self.lib.gt_glu_fwd(self.ctx, code, act.size, ex.data, eu.data, eo.data))
         n = act.size
-        self._check(self.lib.gt_glu_fwd(self.ctx, code, n, ex.data, eu.data, eo.data))
 
         def _bw():
             self._ensureBackwardBegun()

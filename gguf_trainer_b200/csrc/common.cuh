@@ -105,6 +105,8 @@ gt_status gt_gemm_tc_multi(gt_ctx* ctx, int kind, int accum, int M, int N, int n
                            const float* const* bs, float* c, bool* handled);
 gt_status gt_gemm_tc_grouped(gt_ctx* ctx, int kind, int ngroups, const int* Ms, const int* Ns, int K, const float* const* as,
                              const float* const* bs, float* const* cs, const int* accums, bool* handled);
+gt_status gt_glu_linear_tc(gt_ctx* ctx, int op, int rows, int ffn, int in, const float* x, const float* wg, const float* wu, float* gate,
+                           float* up, float* out, bool* handled);
 gt_status gt_gemm_tc_check(gt_ctx* ctx);
 void gt_optim_destroy(gt_ctx* ctx);
 void gt_dp_teardown(gt_ctx* ctx);

@@ -211,6 +211,24 @@ gt_status gt_glu_fwd(gt_ctx* ctx, int32_t op, uint64_t n, gt_buf x, gt_buf u, gt
   return GT_OK;
 }
 
+// gate = x.Wg^T, up = x.Wu^T, out = act(gate) * up: the two projections of a gated FFN and the gated unit. One launch on
+// the tensor-core path (the unit is applied where the projections' tiles are written), three otherwise.
+gt_status gt_glu_linear_fwd(gt_ctx* ctx, int32_t op, int32_t rows, int32_t ffn, int32_t in, gt_buf x, gt_buf wg, gt_buf wu, gt_buf gate,
+                            gt_buf up, gt_buf out) {
+  GT_REQUIRE(ctx, rows > 0 && ffn > 0 && in > 0 && x && wg && wu && gate && up && out, "gt_glu_linear_fwd: bad argument");
+  GT_REQUIRE(ctx, op == GT_EW_SILU || op == GT_EW_GELU, "gt_glu_linear_fwd: the gate activation must be silu or gelu, got op %d", op);
+  if (ctx->precision != GT_PREC_FP32) {
+    bool handled = false;
+    gt_status s = gt_glu_linear_tc(ctx, op, rows, ffn, in, gt_ptr<const float>(x), gt_ptr<const float>(wg), gt_ptr<const float>(wu),
+                                   gt_ptr<float>(gate), gt_ptr<float>(up), gt_ptr<float>(out), &handled);
+    if (s != GT_OK || handled) return s;
+  }
+  gt_status s = gt_gemm(ctx, GT_GEMM_NT, 0, rows, ffn, in, x, wg, gate);
+  if (!s) s = gt_gemm(ctx, GT_GEMM_NT, 0, rows, ffn, in, x, wu, up);
+  if (!s) s = gt_glu_fwd(ctx, op, (uint64_t)rows * ffn, gate, up, out);
+  return s;
+}
+
 gt_status gt_glu_bwd(gt_ctx* ctx, int32_t op, uint64_t n, gt_buf x, gt_buf u, gt_buf gout, gt_buf gx, int32_t accum_x, gt_buf gu,
                      int32_t accum_u) {
   if (n == 0 || (!gx && !gu)) return GT_OK;

@@ -64,7 +64,12 @@ struct PartMaps {
   int gM[MAX_PARTS], gN[MAX_PARTS], g_accum[MAX_PARTS], unit_end[MAX_PARTS];
 };
 
-template <bool A_K, bool B_K, int BN, int MT>
+// GLU != 0 (GT_EW_SILU or GT_EW_GELU; NT layout, BN = 192 only): the gated unit of the FFN in the projection that
+// feeds it. B is two weight matrices: the tile's first 96 columns are rows [n0/2, n0/2 + 96) of b[0] (gate), the other 96
+// the same rows of b[1] (up). The epilogue writes the gate and up projections (backward needs them) through c[0] and
+// c[1] and act(gate) * up through c[2], so the separate pass that read both and wrote the product is not launched.
+// N_ is 2 x the FFN width.
+template <bool A_K, bool B_K, int BN, int MT, int GLU = 0>
 __global__ void __launch_bounds__(Smem<BN, MT>::THREADS, 1)
 gemm_tf32_kernel(const __grid_constant__ PartMaps maps, float* __restrict__ C, int M_, int N_,
                  int accum_, int ksplit, int use_tma_store, int batch, float out_scale, int* __restrict__ flag) {
@@ -154,7 +159,10 @@ gemm_tf32_kernel(const __grid_constant__ PartMaps maps, float* __restrict__ C, i
           if (A_K) tma_load_3d(a_dst, pa, k0, m0, bi, full_bar(s));
           else
             for (int c = 0; c < BM / 32; c++) tma_load_3d(a_dst + c * 4096, pa, m0 + 32 * c, k0, bi, full_bar(s));
-          if (B_K) tma_load_3d(b_dst, pb, k0, n0, bi, full_bar(s));
+          if (GLU != 0) {
+            tma_load_3d(b_dst, &maps.b[0], k0, n0 >> 1, bi, full_bar(s));
+            tma_load_3d(b_dst + (BN / 2) * 128, &maps.b[1], k0, n0 >> 1, bi, full_bar(s));
+          } else if (B_K) tma_load_3d(b_dst, pb, k0, n0, bi, full_bar(s));
           else
             for (int c = 0; c < BN / 32; c++) tma_load_3d(b_dst + c * 4096, pb, n0 + 32 * c, k0, bi, full_bar(s));
         }
@@ -214,7 +222,46 @@ gemm_tf32_kernel(const __grid_constant__ PartMaps maps, float* __restrict__ C, i
       if (have) wait(acc_full(b), par_of(tl), 3);
       dead = __any_sync(0xffffffffu, dead);
       tc_fence_after();
-      if (have) {
+      if (GLU != 0 && have) {
+        // gate | up halves of the accumulator: three outputs per 32-column block, each through its own tensor map
+        auto put = [&](const float* v, const CUtensorMap* map, int col0) {
+          const uint32_t tile = epi + (uint32_t)(ew * S::EPI_TILES + (nst % S::EPI_TILES)) * 4096u;
+          if (nst >= S::EPI_TILES) tma_wait_read<S::EPI_TILES - 1>();
+          __syncwarp();
+          uint8_t* tp = smem_raw + (tile - smem_u32(smem_raw)) + lane * 128;
+#pragma unroll
+          for (int c4 = 0; c4 < 8; c4++)
+            *reinterpret_cast<float4*>(tp + ((c4 ^ (lane & 7)) * 16)) = make_float4(v[4 * c4], v[4 * c4 + 1], v[4 * c4 + 2], v[4 * c4 + 3]);
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0 && !dead && m0 + q * 32 < M) tma_store_3d(map, tile, col0, m0 + q * 32, bi);
+          if (lane == 0) tma_commit_group();
+          nst++;
+        };
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; c++) {
+          const int col0 = (n0 >> 1) + c * 32;
+          if (col0 >= (N >> 1)) break;   // uniform across the warp
+          float vg[32], vu[32];
+          const uint32_t ta = tmem + b * BN + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32);
+          tmem_ld32_issue(ta, vg);
+          tmem_ld32_issue(ta + BN / 2, vu);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; j++) { vg[j] *= out_scale; vu[j] *= out_scale; }
+          put(vg, &maps.c[0], col0);
+          put(vu, &maps.c[1], col0);
+#pragma unroll
+          for (int j = 0; j < 32; j++) {
+            const float a = vg[j];
+            float act;
+            if (GLU == GT_EW_SILU) act = a / (1.f + __expf(-a));
+            else act = 0.5f * a * (1.f + tanhf(0.7978845608028654f * (a + 0.044715f * a * a * a)));
+            vg[j] = act * vu[j];
+          }
+          put(vg, &maps.c[2], col0);
+        }
+      } else if (have) {
 #pragma unroll 1
         for (int c = 0; c < BN / 32; c++) {
           const int col0 = n0 + c * 32;
@@ -474,10 +521,10 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
 // ---------------------------------------------------------------------------------------------
 int* g_flag[64] = {};
 
-template <bool A_K, bool B_K, int BN, int MT>
+template <bool A_K, bool B_K, int BN, int MT, int GLU = 0>
 gt_status launch(gt_ctx* ctx, const PartMaps& maps, long ntiles, int tma_store, float* c, int M, int N, int accum, int ksplit,
                  int batch, float out_scale) {
-  auto kern = gemm_tf32_kernel<A_K, B_K, BN, MT>;
+  auto kern = gemm_tf32_kernel<A_K, B_K, BN, MT, GLU>;
   using S = Smem<BN, MT>;
   static bool attr_set[64] = {};
   if (!attr_set[ctx->device]) {
@@ -811,6 +858,41 @@ static gt_status gemm_tc_grouped(gt_ctx* ctx, int kind, int ngroups, const int* 
       if (!accums[g]) GT_CUDA(ctx, cudaMemsetAsync(cs[g], 0, sizeof(float) * (size_t)Ms[g] * Ns[g], ctx->stream));
   gt_status s = mt == 1 ? launch_kind<192, 1>(ctx, kind, maps, units, 1, cs[0], Ms[0], Ns[0], accums[0], ksplit, 1, TRUNC_COMP)
                         : launch_kind<192, 2>(ctx, kind, maps, units, 1, cs[0], Ms[0], Ns[0], accums[0], ksplit, 1, TRUNC_COMP);
+  if (s) return s;
+  *handled = true;
+  return GT_OK;
+}
+
+// gate = x.Wg^T, up = x.Wu^T and out = act(gate) * up as one launch (see the GLU form of the kernel).
+gt_status gt_glu_linear_tc(gt_ctx* ctx, int op, int rows, int ffn, int in, const float* x, const float* wg, const float* wu, float* gate,
+                           float* up, float* out, bool* handled) {
+  *handled = false;
+  if (rows < 16 || ffn < 96 || in < 16 || (in & 3) || (ffn & 3)) return GT_OK;
+  if ((((uintptr_t)x) | ((uintptr_t)wg) | ((uintptr_t)wu) | ((uintptr_t)gate) | ((uintptr_t)up) | ((uintptr_t)out)) & 15) return GT_OK;
+  if (ctx->device < 0 || ctx->device >= 64 || !device_flag(ctx)) return GT_OK;
+  constexpr int BN = 192;
+  PartMaps maps;
+  maps.nparts = 1;
+  maps.ngroups = 1;
+  const int kblocks = gt_cdiv(in, BK);
+  bool ok = make_map_3d(&maps.a[0], x, in, rows, 1, in, (uint64_t)rows * in, BM1, true);
+  ok = ok && make_map_3d(&maps.b[0], wg, in, ffn, 1, in, (uint64_t)ffn * in, BN / 2, true);
+  ok = ok && make_map_3d(&maps.b[1], wu, in, ffn, 1, in, (uint64_t)ffn * in, BN / 2, true);
+  ok = ok && make_map_3d(&maps.c[0], gate, ffn, rows, 1, ffn, (uint64_t)rows * ffn, 32, true);
+  ok = ok && make_map_3d(&maps.c[1], up, ffn, rows, 1, ffn, (uint64_t)rows * ffn, 32, true);
+  ok = ok && make_map_3d(&maps.c[2], out, ffn, rows, 1, ffn, (uint64_t)rows * ffn, 32, true);
+  if (!ok) return GT_OK;
+  for (int p = 0; p < MAX_PARTS; p++) {
+    if (p > 0) maps.a[p] = maps.a[0];
+    if (p > 1) maps.b[p] = maps.b[0];
+    if (p > 2) maps.c[p] = maps.c[0];
+    maps.kb_end[p] = kblocks; maps.gM[p] = rows; maps.gN[p] = 2 * ffn; maps.g_accum[p] = 0; maps.unit_end[p] = 0;
+  }
+  const int N2 = 2 * gt_cdiv(ffn, BN / 2) * (BN / 2);   // whole tiles of 96 + 96 columns; the maps clip at ffn
+  const long ntiles = (long)gt_cdiv(N2, BN) * gt_cdiv(rows, BM1);
+  gt_status s = op == GT_EW_SILU
+                    ? launch<true, true, BN, 1, GT_EW_SILU>(ctx, maps, ntiles, 1, out, rows, N2, 0, 1, 1, TRUNC_COMP)
+                    : launch<true, true, BN, 1, GT_EW_GELU>(ctx, maps, ntiles, 1, out, rows, N2, 0, 1, 1, TRUNC_COMP);
   if (s) return s;
   *handled = true;
   return GT_OK;

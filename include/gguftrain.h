@@ -111,6 +111,12 @@ gt_status gt_ew_bwd(gt_ctx* ctx, int32_t op, uint64_t n, gt_buf a, gt_buf b, flo
 gt_status gt_glu_fwd(gt_ctx* ctx, int32_t op, uint64_t n, gt_buf x, gt_buf u, gt_buf out);
 gt_status gt_glu_bwd(gt_ctx* ctx, int32_t op, uint64_t n, gt_buf x, gt_buf u, gt_buf gout,
                      gt_buf gx, int32_t accum_x, gt_buf gu, int32_t accum_u);
+/* The whole entry of a gated FFN: gate = x.Wg^T, up = x.Wu^T (both [rows, ffn], kept for backward) and out = act(gate)*up,
+ * x:[rows, in], Wg, Wu:[ffn, in] (src/arch/llama.ts:209-211: two `linear`, an activation and a `mul`). On the tensor
+ * cores one launch: each output tile holds 96 gate and the matching 96 up columns and the unit is applied as the tile
+ * is written. */
+gt_status gt_glu_linear_fwd(gt_ctx* ctx, int32_t op, int32_t rows, int32_t ffn, int32_t in, gt_buf x, gt_buf wg, gt_buf wu, gt_buf gate,
+                            gt_buf up, gt_buf out);
 /* rmsNorm and rmsNormHeads ([rows, d] view; webgpu.ts:1673-1701, wgsl.ts:217-303) */
 gt_status gt_rmsnorm_fwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf x, gt_buf w, float eps, gt_buf y, gt_buf rinv);
 gt_status gt_rmsnorm_bwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf x, gt_buf w, gt_buf rinv, gt_buf gy,

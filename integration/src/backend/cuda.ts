@@ -52,6 +52,7 @@ const SYMBOLS = {
   gt_ew_bwd: { parameters: ["pointer", "i32", "u64", "u64", "u64", "f32", "u64", "u64", "i32", "u64", "i32"], result: "i32" },
   gt_glu_fwd: { parameters: ["pointer", "i32", "u64", "u64", "u64", "u64"], result: "i32" },
   gt_glu_bwd: { parameters: ["pointer", "i32", "u64", "u64", "u64", "u64", "u64", "i32", "u64", "i32"], result: "i32" },
+  gt_glu_linear_fwd: { parameters: ["pointer", "i32", "i32", "i32", "i32", "u64", "u64", "u64", "u64", "u64", "u64"], result: "i32" },
   gt_rmsnorm_fwd: { parameters: ["pointer", "i32", "i32", "u64", "u64", "f32", "u64", "u64"], result: "i32" },
   gt_rmsnorm_bwd: { parameters: ["pointer", "i32", "i32", "u64", "u64", "u64", "u64", "u64", "i32", "u64", "i32"], result: "i32" },
   gt_add_rmsnorm_fwd: { parameters: ["pointer", "i32", "i32", "u64", "u64", "u64", "f32", "u64", "u64", "u64"], result: "i32" },

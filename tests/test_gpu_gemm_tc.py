@@ -374,3 +374,75 @@ def test_gemm_grouped_products_in_one_launch(gpu, oracle, monkeypatch, tile, kin
         assert r > 1e-7, "the strict-f32 kernel answered"
     for b in da + db + dc:
         gpu._check(gpu.lib.gt_free(gpu.ctx, b))
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu"])
+@pytest.mark.parametrize("T,din,ffn", [(300, 96, 200), (2048, 576, 1536), (130, 64, 96)])
+def test_gated_ffn_entry_is_one_launch(gpu, oracle, act, T, din, ffn):
+    """`mul(act(linear(x, Wg)), linear(x, Wu))`, the entry of a gated FFN (src/arch/llama.ts:209-211): the two
+    projections and the gated unit run as ONE launch (gt_glu_linear_fwd: each output tile holds 96 gate and the matching
+    96 up columns), ragged widths included; values and all three gradients against f64 formulas."""
+    from gpu_harness import rand_tensor, upstream
+    from gguf_trainer_b200 import autograd as ag
+    rng = oracle.Mulberry32(T + 3 * din + 7 * ffn)
+    x = rand_tensor(rng, [T, din]); wg = rand_tensor(rng, [ffn, din], 0.2); wu = rand_tensor(rng, [ffn, din], 0.2)
+    for t in (x, wg, wu):
+        t.zeroGrad()
+    f = ag.silu if act == "silu" else ag.gelu
+    gpu.install()
+    try:
+        gpu.sync([])
+        l0 = gpu.kernelLaunches()
+        gate = ag.linear(x, wg)
+        up = ag.linear(x, wu)
+        out = ag.mul(f(gate), up)
+        assert gpu.kernelLaunches() - l0 == 1, "projections and gated unit must be one launch"
+        g = upstream(oracle, out.size)
+        out.grad[:] = g
+        gpu.seedGradFromHost(out)
+        # closures in reverse creation order: product, activation (a no-op here), up, gate
+        out._backward(); out._prev[0]._backward(); up._backward(); gate._backward()
+        gpu.sync([out, gate, up])
+    finally:
+        gpu.uninstall()
+    X, Wg, Wu = (t.data.astype(np.float64).reshape(t.shape) for t in (x, wg, wu))
+    G, U = X @ Wg.T, X @ Wu.T
+    if act == "silu":
+        sig = 1 / (1 + np.exp(-G))
+        A, dA = G * sig, sig + G * sig * (1 - sig)
+    else:
+        k, a = 0.7978845608028654, 0.044715
+        th = np.tanh(k * (G + a * G ** 3))
+        A, dA = 0.5 * G * (1 + th), 0.5 * (1 + th) + 0.5 * G * (1 - th ** 2) * k * (1 + 3 * a * G ** 2)
+    go = g.astype(np.float64).reshape(T, ffn)
+    dG, dU = go * U * dA, go * A
+    want = {"gate": G, "up": U, "out": A * U, "dx": dG @ Wg + dU @ Wu, "dWg": dG.T @ X, "dWu": dU.T @ X}
+    got = {"gate": gate.data, "up": up.data, "out": out.data, "dx": x.grad, "dWg": wg.grad, "dWu": wu.grad}
+    for k_ in want:
+        e = rel_l2(got[k_], want[k_])
+        assert np.isfinite(np.asarray(got[k_])).all() and e <= REL_L2_TC, f"{k_}: relative L2 {e:.3e}"
+
+
+def test_projections_of_one_input_are_one_grouped_launch(gpu, oracle):
+    """q, k and v of the same normed input: three `linear` calls, one launch (the products are noted and launched when
+    the first output is needed), results as three separate products."""
+    from gpu_harness import rand_tensor
+    from gguf_trainer_b200 import autograd as ag
+    rng = oracle.Mulberry32(404)
+    T, din = 513, 576
+    x = rand_tensor(rng, [T, din])
+    ws = [rand_tensor(rng, [o, din], 0.1) for o in (576, 192, 192)]
+    gpu.install()
+    try:
+        gpu.sync([])
+        l0 = gpu.kernelLaunches()
+        outs = [ag.linear(x, w) for w in ws]
+        assert gpu.kernelLaunches() == l0                       # nothing launched yet
+        gpu.sync(outs)
+        assert gpu.kernelLaunches() - l0 == 1
+    finally:
+        gpu.uninstall()
+    X = x.data.astype(np.float64).reshape(T, din)
+    for o, w in zip(outs, ws):
+        e = rel_l2(o.data, X @ w.data.astype(np.float64).reshape(w.shape).T)
+        assert e <= REL_L2_TC and e > 1e-7, f"relative L2 {e:.3e}"
