@@ -549,6 +549,21 @@ def run_micro(args):
         cases = [("attention fwd", lambda: lib.gt_attention_fwd(ctx, rows, Hq, Hkv, hd, args.window, Q, K, Vv, O, L), 4 * Hq * hd * P * B),
                  ("attention bwd", lambda: lib.gt_attention_bwd(ctx, rows, Hq, Hkv, hd, args.window, Q, K, Vv, O, L, G, gq, 0, gk, 0, gv, 0), 10 * Hq * hd * P * B)]
         unit, peak = "TFLOP/s", pk["tflops_sustained"]
+    elif name == "ffn":
+        # the gated FFN's fused launches against their separate forms (rows x 576 -> 1536 -> 576)
+        x, wg, wu, wd = buf(rows * h), buf(f * h), buf(f * h), buf(h * f)
+        gate, up, hid = buf(rows * f, False), buf(rows * f, False), buf(rows * f, False)
+        n = rows * f
+        fl_f = 2 * 2 * rows * h * f
+
+        def fwd_sep():
+            st = lib.gt_gemm(ctx, 0, 0, rows, f, h, x, wg, gate)
+            st = st or lib.gt_gemm(ctx, 0, 0, rows, f, h, x, wu, up)
+            return st or lib.gt_glu_fwd(ctx, 2, n, gate, up, hid)
+
+        cases = [("ffn entry, one launch (gate, up, gated unit)", lambda: lib.gt_glu_linear_fwd(ctx, 2, rows, f, h, x, wg, wu, gate, up, hid), fl_f),
+                 ("ffn entry, three launches", fwd_sep, fl_f)]
+        unit, peak = "TFLOP/s", pk["tflops_sustained"]
     elif name == "gemm":
         cases = []
         for out, inn in [(q, h), (kv, h), (f, h), (h, f)]:
@@ -610,7 +625,7 @@ def main():
     ap.add_argument("--no-peak", action="store_true", help="skip the torch.matmul TF32 peak and comparator")
     ap.add_argument("--recompute", action="store_true")
     ap.add_argument("--profile", action="store_true", help="per-entry-point GPU time of one eager step")
-    ap.add_argument("--micro", default="", help="time one op of the step instead: attention | gemm | bwd-gemm")
+    ap.add_argument("--micro", default="", help="time one op of the step instead: attention | gemm | bwd-gemm | ffn")
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--window", type=int, default=0)
     ap.add_argument("--layers-per-bucket", type=int, default=6, help="data parallel: layers per gradient all-reduce bucket")

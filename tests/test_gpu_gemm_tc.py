@@ -377,16 +377,19 @@ def test_gemm_grouped_products_in_one_launch(gpu, oracle, monkeypatch, tile, kin
 
 
 @pytest.mark.parametrize("act", ["silu", "gelu"])
-@pytest.mark.parametrize("T,din,ffn", [(300, 96, 200), (2048, 576, 1536), (130, 64, 96)])
-def test_gated_ffn_entry_is_one_launch(gpu, oracle, act, T, din, ffn):
-    """`mul(act(linear(x, Wg)), linear(x, Wu))`, the entry of a gated FFN (src/arch/llama.ts:209-211): the two
-    projections and the gated unit run as ONE launch (gt_glu_linear_fwd: each output tile holds 96 gate and the matching
-    96 up columns), ragged widths included; values and all three gradients against f64 formulas."""
+@pytest.mark.parametrize("T,din,ffn", [(300, 96, 200), (2048, 576, 1536), (130, 64, 96), (257, 64, 224)])
+def test_gated_ffn_is_two_launches_forward_and_four_backward(gpu, oracle, act, T, din, ffn):
+    """`linear(mul(act(linear(x, Wg)), linear(x, Wu)), Wd)`, the FFN of every block (src/arch/llama.ts:209-212). Forward:
+    the gate and up projections and the gated unit are ONE launch (gt_glu_linear_fwd: each output tile holds 96 gate and
+    the matching 96 up columns), then the down projection. Backward: the down projection's input gradient, the unit's
+    backward, the three weight gradients as one grouped launch, the input gradient of gate and up as one launch over
+    both K ranges. Values and every gradient against f64 formulas, ragged widths included."""
     from gpu_harness import rand_tensor, upstream
     from gguf_trainer_b200 import autograd as ag
     rng = oracle.Mulberry32(T + 3 * din + 7 * ffn)
     x = rand_tensor(rng, [T, din]); wg = rand_tensor(rng, [ffn, din], 0.2); wu = rand_tensor(rng, [ffn, din], 0.2)
-    for t in (x, wg, wu):
+    wd = rand_tensor(rng, [din, ffn], 0.2)
+    for t in (x, wg, wu, wd):
         t.zeroGrad()
     f = ag.silu if act == "silu" else ag.gelu
     gpu.install()
@@ -395,17 +398,20 @@ def test_gated_ffn_entry_is_one_launch(gpu, oracle, act, T, din, ffn):
         l0 = gpu.kernelLaunches()
         gate = ag.linear(x, wg)
         up = ag.linear(x, wu)
-        out = ag.mul(f(gate), up)
+        hidden = ag.mul(f(gate), up)
         assert gpu.kernelLaunches() - l0 == 1, "projections and gated unit must be one launch"
-        g = upstream(oracle, out.size)
-        out.grad[:] = g
-        gpu.seedGradFromHost(out)
-        # closures in reverse creation order: product, activation (a no-op here), up, gate
-        out._backward(); out._prev[0]._backward(); up._backward(); gate._backward()
-        gpu.sync([out, gate, up])
+        y = ag.linear(hidden, wd)
+        g = upstream(oracle, y.size)
+        y.grad[:] = g
+        gpu.seedGradFromHost(y)                    # (launches the down projection)
+        l1 = gpu.kernelLaunches()
+        # closures in reverse creation order: down, product, activation (a no-op here), up, gate
+        y._backward(); hidden._backward(); hidden._prev[0]._backward(); up._backward(); gate._backward()
+        gpu.sync([y, hidden, gate, up])
+        assert gpu.kernelLaunches() - l1 == 4, gpu.kernelLaunches() - l1
     finally:
         gpu.uninstall()
-    X, Wg, Wu = (t.data.astype(np.float64).reshape(t.shape) for t in (x, wg, wu))
+    X, Wg, Wu, Wd = (t.data.astype(np.float64).reshape(t.shape) for t in (x, wg, wu, wd))
     G, U = X @ Wg.T, X @ Wu.T
     if act == "silu":
         sig = 1 / (1 + np.exp(-G))
@@ -414,10 +420,12 @@ def test_gated_ffn_entry_is_one_launch(gpu, oracle, act, T, din, ffn):
         k, a = 0.7978845608028654, 0.044715
         th = np.tanh(k * (G + a * G ** 3))
         A, dA = 0.5 * G * (1 + th), 0.5 * (1 + th) + 0.5 * G * (1 - th ** 2) * k * (1 + 3 * a * G ** 2)
-    go = g.astype(np.float64).reshape(T, ffn)
+    Hh = A * U
+    gy = g.astype(np.float64).reshape(T, din)
+    go = gy @ Wd
     dG, dU = go * U * dA, go * A
-    want = {"gate": G, "up": U, "out": A * U, "dx": dG @ Wg + dU @ Wu, "dWg": dG.T @ X, "dWu": dU.T @ X}
-    got = {"gate": gate.data, "up": up.data, "out": out.data, "dx": x.grad, "dWg": wg.grad, "dWu": wu.grad}
+    want = {"gate": G, "up": U, "hidden": Hh, "y": Hh @ Wd.T, "dx": dG @ Wg + dU @ Wu, "dWg": dG.T @ X, "dWu": dU.T @ X, "dWd": gy.T @ Hh}
+    got = {"gate": gate.data, "up": up.data, "hidden": hidden.data, "y": y.data, "dx": x.grad, "dWg": wg.grad, "dWu": wu.grad, "dWd": wd.grad}
     for k_ in want:
         e = rel_l2(got[k_], want[k_])
         assert np.isfinite(np.asarray(got[k_])).all() and e <= REL_L2_TC, f"{k_}: relative L2 {e:.3e}"
