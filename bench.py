@@ -292,6 +292,9 @@ def run_ours(args):
         gpu.fuseResidualNorm = False
         gpu.groupWeightGradients = False
         gpu.groupForward = False
+        gpu.fuseRope = False
+    if args.no_rope_fusion:
+        gpu.fuseRope = False
     model = buildModel(cfg, 1234)       # same seed on every rank: replicated weights
     loss_chunk = args.loss_chunk if args.loss_chunk >= 0 else (32768 if args.config == "qwen3-lora" else 0)
     mask = None
@@ -546,8 +549,38 @@ def run_micro(args):
         L = buf(Hq * rows, False)
         gq, gk, gv = buf(rows * q, False), buf(rows * kv, False), buf(rows * kv, False)
         P = T * (T + 1) // 2
+        gq0, gk0 = buf(rows * q, False), buf(rows * kv, False)
+
+        def bwd_then_rope():
+            st = lib.gt_attention_bwd(ctx, rows, Hq, Hkv, hd, args.window, Q, K, Vv, O, L, G, gq, 0, gk, 0, gv, 0)
+            st = st or lib.gt_rope_bwd(ctx, rows, Hq, hd, 10000.0, 0, gq, gq0, 0)
+            return st or lib.gt_rope_bwd(ctx, rows, Hkv, hd, 10000.0, 0, gk, gk0, 0)
+
         cases = [("attention fwd", lambda: lib.gt_attention_fwd(ctx, rows, Hq, Hkv, hd, args.window, Q, K, Vv, O, L), 4 * Hq * hd * P * B),
-                 ("attention bwd", lambda: lib.gt_attention_bwd(ctx, rows, Hq, Hkv, hd, args.window, Q, K, Vv, O, L, G, gq, 0, gk, 0, gv, 0), 10 * Hq * hd * P * B)]
+                 ("attention bwd", lambda: lib.gt_attention_bwd(ctx, rows, Hq, Hkv, hd, args.window, Q, K, Vv, O, L, G, gq, 0, gk, 0, gv, 0), 10 * Hq * hd * P * B),
+                 ("attention bwd, then the rotations' backward (3 + 2 launches)", bwd_then_rope, 10 * Hq * hd * P * B),
+                 ("attention bwd rotating dQ and dK as it stores them (3 launches)",
+                  lambda: lib.gt_attention_bwd_rope(ctx, rows, Hq, Hkv, hd, args.window, Q, K, Vv, O, L, G, gq0, 0, gk0, 0, gv, 0, 10000.0, 0), 10 * Hq * hd * P * B)]
+        unit, peak = "TFLOP/s", pk["tflops_sustained"]
+    elif name == "qkv":
+        # q, k, v projections of one input and the rotary embedding of q and k: one launch against three
+        import ctypes as C
+        x, ws = buf(rows * h), [buf(o * h) for o in (q, kv, kv)]
+        ys, yr = [buf(rows * o, False) for o in (q, kv, kv)], [buf(rows * o, False) for o in (q, kv)]
+        Ms, Ns = (C.c_int32 * 3)(rows, rows, rows), (C.c_int32 * 3)(q, kv, kv)
+        As, Bs, Cs, acc = (C.c_uint64 * 3)(x, x, x), (C.c_uint64 * 3)(*ws), (C.c_uint64 * 3)(*ys), (C.c_int32 * 3)(0, 0, 0)
+        Cr, Hs = (C.c_uint64 * 3)(yr[0], yr[1], ys[2]), (C.c_int32 * 3)(Hq, Hkv, 0)
+
+        def sep():
+            st = lib.gt_gemm_grouped(ctx, 0, 3, Ms, Ns, h, As, Bs, Cs, acc)
+            st = st or lib.gt_rope_fwd(ctx, rows, Hq, hd, 10000.0, 0, ys[0], yr[0])
+            return st or lib.gt_rope_fwd(ctx, rows, Hkv, hd, 10000.0, 0, ys[1], yr[1])
+
+        fl = 2 * rows * h * (q + 2 * kv)
+        cases = [("q/k/v projections, grouped launch", lambda: lib.gt_gemm_grouped(ctx, 0, 3, Ms, Ns, h, As, Bs, Cs, acc), fl),
+                 ("q/k/v grouped, then the two rotations (3 launches)", sep, fl),
+                 ("q/k/v grouped with the rotations applied as the tiles are written (1 launch)",
+                  lambda: lib.gt_linear_rope_grouped(ctx, 3, rows, h, x, Ns, Bs, Cr, Hs, hd, 10000.0, 0), fl)]
         unit, peak = "TFLOP/s", pk["tflops_sustained"]
     elif name == "ffn":
         # the gated FFN's fused launches against their separate forms (rows x 576 -> 1536 -> 576)
@@ -625,12 +658,13 @@ def main():
     ap.add_argument("--no-peak", action="store_true", help="skip the torch.matmul TF32 peak and comparator")
     ap.add_argument("--recompute", action="store_true")
     ap.add_argument("--profile", action="store_true", help="per-entry-point GPU time of one eager step")
-    ap.add_argument("--micro", default="", help="time one op of the step instead: attention | gemm | bwd-gemm | ffn")
+    ap.add_argument("--micro", default="", help="time one op of the step instead: attention | gemm | bwd-gemm | ffn | qkv")
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--window", type=int, default=0)
     ap.add_argument("--layers-per-bucket", type=int, default=6, help="data parallel: layers per gradient all-reduce bucket")
     ap.add_argument("--comm-ctas", type=int, default=0, help="data parallel: CTAs left to the collective while it overlaps backward (0 = no cap, no reservation)")
     ap.add_argument("--no-shard-muon", action="store_true", help="data parallel: every rank runs all Newton-Schulz iterations")
+    ap.add_argument("--no-rope-fusion", action="store_true", help="rotary embeddings as launches of their own (for comparison)")
     ap.add_argument("--plain", action="store_true", help="launch every op as recorded: no merged input gradients, no residual add + norm fusion")
     ap.add_argument("--heads", default="", help="--micro attention: Hq,Hkv,hd instead of 9,3,64")
     args = ap.parse_args()

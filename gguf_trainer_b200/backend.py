@@ -32,7 +32,8 @@ PRECISION = {"fp32": 0, "tf32": 1}   # (the C ABI reserves 2 for BF16 and refuse
 
 
 class _Entry:
-    __slots__ = ("data", "grad", "bytes", "external", "gradLive", "size", "pendingDx", "copyFrom", "pendingDw", "pendingFwd")
+    __slots__ = ("data", "grad", "bytes", "external", "gradLive", "size", "pendingDx", "copyFrom", "pendingDw", "pendingFwd",
+                 "lazy", "ropeOf", "ropeFused")
 
     def __init__(self, data: int, grad: int, nbytes: int, external: bool, size: int):
         self.data = data
@@ -45,6 +46,10 @@ class _Entry:
         self.copyFrom = 0         # address whose contents are this gradient's value so far (a copy not made yet)
         self.pendingDw = False    # a weight-gradient product into this gradient is noted in _pendingDw, not launched yet
         self.pendingFwd = False   # the projection that produces this tensor is noted in _pendingFwd, not launched yet
+        self.lazy = None          # (x entry, w entry, T, in, out): a projection whose only reader took it rotated; `data` is
+                                  # unwritten until someone else asks for it (_materializeLazy)
+        self.ropeOf = None        # for a rotary embedding's output: (input tensor, its entry, H, hd, base, posOffset)
+        self.ropeFused = False    # its gradient went straight to the rotation's input (attention backward applied it)
 
 
 class CapturedGraph:
@@ -210,6 +215,7 @@ class CudaBackend:
         self._pendingCopy: Dict[int, _Entry] = {}  # entries whose gradient is still a view of another buffer (see add)
         self.fuseResidualNorm = True
         self.fuseGatedUnits = True
+        self.fuseRope = True               # rotary embeddings applied by the launches before and after them (see rope, attention)
         self.fuseLora = True               # adapter-carrying projections as one op (loraLinear) instead of four
         self._finalizer = weakref.finalize(self, _destroy_ctx, self.lib, self.ctx)
 
@@ -353,6 +359,8 @@ class CudaBackend:
             self._write(e.data, t.data)
         if e.pendingFwd:
             self._flushFwd()
+        if e.lazy is not None:
+            self._materializeLazy(e)
         if e.external and id(t) not in self._touched:
             self._touched[id(t)] = t
         return e
@@ -366,6 +374,8 @@ class CudaBackend:
             e = self._materializeAdd(t)
         if e is not None and e.pendingFwd:
             self._flushFwd()
+        if e is not None and e.lazy is not None:
+            self._materializeLazy(e)
         return e
 
     def _makeOut(self, shape, prev) -> tuple:
@@ -440,6 +450,20 @@ class CudaBackend:
             p["eo"].pendingFwd = False
         n = len(parts)
         T, inDim = parts[0]["T"], parts[0]["inDim"]
+        roped = [p for p in parts if "rope" in p]
+        if roped:
+            # projections whose one reader so far is a rotary embedding: the launch writes the rotated values into the
+            # embedding's output; the projection's own buffer stays unwritten unless someone else asks for it
+            _er, _H, hd, base, posOffset = roped[0]["rope"]
+            for p in roped:
+                p["rope"][0].pendingFwd = False
+                p["eo"].lazy = (p["ex"], p["ew"], T, inDim, p["outDim"])
+            Ns = (C.c_int32 * n)(*[p["outDim"] for p in parts])
+            Ws = (C.c_uint64 * n)(*[p["ew"].data for p in parts])
+            Ys = (C.c_uint64 * n)(*[(p["rope"][0].data if "rope" in p else p["eo"].data) for p in parts])
+            Hs = (C.c_int32 * n)(*[(p["rope"][1] if "rope" in p else 0) for p in parts])
+            self._check(self.lib.gt_linear_rope_grouped(self.ctx, n, T, inDim, parts[0]["ex"].data, Ns, Ws, Ys, Hs, hd, float(base), posOffset))
+            return
         if n == 1:
             self._gemm("NT", 0, T, parts[0]["outDim"], inDim, parts[0]["ex"].data, parts[0]["ew"].data, parts[0]["eo"].data)
             return
@@ -450,6 +474,11 @@ class CudaBackend:
         Cs = (C.c_uint64 * n)(*[p["eo"].data for p in parts])
         acc = (C.c_int32 * n)(*([0] * n))
         self._check(self.lib.gt_gemm_grouped(self.ctx, _KIND["NT"], n, Ms, Ns, inDim, As, Bs, Cs, acc))
+
+    def _materializeLazy(self, e: _Entry):
+        ex, ew, T, inDim, outDim = e.lazy
+        e.lazy = None
+        self._gemm("NT", 0, T, outDim, inDim, ex.data, ew.data, e.data)
 
     def _flushAllDx(self):
         self._flushFwd()
@@ -569,6 +598,8 @@ class CudaBackend:
             e = self._entries.get(t)
             if e is None:
                 continue
+            if e.lazy is not None:
+                self._materializeLazy(e)
             self._read(e.data, t.data)
         for t in list(self._touched.values()):
             e = self._entries.get(t)
@@ -1028,7 +1059,7 @@ class CudaBackend:
             if e is None or not (e.gradLive or e.copyFrom or e.pendingDx is not None):
                 return          # consumed only by fused products, which sent their gradient straight to x
             self._ensureBackwardBegun()
-            ex = self._entries[x]
+            ex = self._entryOf(x)
             go = self._gradSource(e)
             gx, ax = self._gradTarget(x, ex)
             self._check(self.lib.gt_ew_bwd(self.ctx, _EW[op], x.size, ex.data, 0, 0.0, go, gx, ax, 0, 0))
@@ -1040,6 +1071,8 @@ class CudaBackend:
         _t, code, x = self._pendingAct.pop(id(t))
         ex = self._entries[x]
         self._flushFwd()
+        if ex.lazy is not None:
+            self._materializeLazy(ex)
         nbytes = t.size * 4
         e = _Entry(self._acquireRecycled(nbytes), self._acquireRecycled(nbytes), nbytes, False, t.size)
         self._entries[t] = e
@@ -1062,7 +1095,8 @@ class CudaBackend:
         ex, eu = self._entries[x], self._entries.get(u)
         pend = self._pendingFwd
         if (eu is not None and len(pend) == 2 and ex.pendingFwd and eu.pendingFwd and ex is not eu
-                and {id(pend[0]["eo"]), id(pend[1]["eo"])} == {id(ex), id(eu)} and pend[0]["outDim"] == pend[1]["outDim"]):
+                and {id(pend[0]["eo"]), id(pend[1]["eo"])} == {id(ex), id(eu)} and pend[0]["outDim"] == pend[1]["outDim"]
+                and "rope" not in pend[0] and "rope" not in pend[1]):
             # gate and up are the two projections waiting to be launched: one launch writes both and the gated unit
             pg, pu = (pend[0], pend[1]) if pend[0]["eo"] is ex else (pend[1], pend[0])
             self._pendingFwd = []
@@ -1072,6 +1106,8 @@ class CudaBackend:
                                                    pu["ew"].data, ex.data, eu.data, eo.data))
         else:
             self._flushFwd()
+            if ex.lazy is not None:
+                self._materializeLazy(ex)
             eu = self._entryFor(u)
             out, eo = self._makeOut(act.shape, [act, u])
             self._check(self.lib.gt_glu_fwd(self.ctx, code, act.size, ex.data, eu.data, eo.data))
@@ -1178,14 +1214,35 @@ class CudaBackend:
             raise ValueError(f"{where}: T={T} but the tensor has {rows} rows")
 
     def rope(self, x: Tensor, T: int, H: int, hd: int, base: float, posOffset: int = 0) -> Tensor:
-        self._beginForwardOp()
+        """webgpu.ts:1110-1123. Where the input is a projection that has not been launched yet (`rope(linear(x, Wq))`, the
+        llama block) and the heads are 64 wide, the rotation is applied by the projection's launch as its tiles are
+        written (gt_linear_rope_grouped) and no pass of its own runs; the gradient side is in `attention`."""
         self._checkT(T, x.shape[0], "rope")
-        ex = self._entryFor(x)
-        out, eo = self._makeOut([T, H * hd], [x])
-        self._check(self.lib.gt_rope_fwd(self.ctx, T, H, hd, float(base), posOffset, ex.data, eo.data))
+        e0 = self._entries.get(x)
+        part = None
+        if (self.fuseRope and e0 is not None and e0.pendingFwd and hd == 64 and self.precision == "tf32" and T >= 16):
+            part = next((p for p in self._pendingFwd if p["eo"] is e0), None)
+            first = next((p["rope"] for p in self._pendingFwd if "rope" in p), None)
+            if part is not None and ("rope" in part or part["outDim"] != H * hd or
+                                     (first is not None and first[2:] != (hd, base, posOffset))):
+                part = None
+        if part is not None:
+            self._beginForwardOp(keepPending=True)
+            ex = e0
+            out, eo = self._makeOut([T, H * hd], [x])
+            part["rope"] = (eo, H, hd, base, posOffset)
+            eo.pendingFwd = True
+        else:
+            self._beginForwardOp()
+            ex = self._entryFor(x)
+            out, eo = self._makeOut([T, H * hd], [x])
+            self._check(self.lib.gt_rope_fwd(self.ctx, T, H, hd, float(base), posOffset, ex.data, eo.data))
+        eo.ropeOf = (x, ex, H, hd, base, posOffset)
 
         def _bw():
             self._ensureBackwardBegun()
+            if eo.ropeFused and not (eo.gradLive or eo.copyFrom or eo.pendingDx is not None):
+                return                       # attention's backward already delivered this gradient to x
             go = self._gradSource(eo)
             gx, ax = self._gradTarget(x, ex)
             self._check(self.lib.gt_rope_bwd(self.ctx, T, H, hd, float(base), posOffset, go, gx, ax))
@@ -1218,6 +1275,20 @@ class CudaBackend:
         def _bw():
             self._ensureBackwardBegun()
             go = self._gradSource(eo)
+            rq, rk = eq.ropeOf, ek.ropeOf
+            fresh = lambda e: not (e.gradLive or e.copyFrom or e.pendingDx is not None)
+            if (self.fuseRope and rq is not None and rk is not None and eq is not ek and rq[3:] == rk[3:] and rq[3] == hd
+                    and rq[2] == Hq and rk[2] == Hkv and hd in (64, 128) and T >= 64 and self.precision == "tf32"
+                    and fresh(eq) and fresh(ek)):
+                # q and k came out of rotary embeddings and nothing else has written their gradients: the kernels rotate
+                # dQ and dK back as they store them, into the gradients of the embeddings' inputs
+                gq, aq = self._gradTarget(rq[0], rq[1])
+                gk, ak = self._gradTarget(rk[0], rk[1])
+                gv, av = self._gradTarget(v, ev)
+                self._check(self.lib.gt_attention_bwd_rope(self.ctx, T, Hq, Hkv, hd, window, eq.data, ek.data, ev.data, eo.data,
+                                                           lse, go, gq, aq, gk, ak, gv, av, float(rq[4]), rq[5]))
+                eq.ropeFused = ek.ropeFused = True
+                return
             gq, aq = self._gradTarget(q, eq)
             gk, ak = self._gradTarget(k, ek)
             gv, av = self._gradTarget(v, ev)

@@ -95,6 +95,47 @@ __device__ __forceinline__ void tmem_ld(uint32_t taddr, float* v) {
     for (int c = 0; c < N / 32; c++) tmem_ld32(taddr + c * 32, v + c * 32);
   }
 }
+// The gradient of a rotary embedding in the epilogue of the kernel that produced the gradient of its output: the two
+// threads that share a row of a head 2 * HH wide each take half of its HH pairs (j, j + HH). With (c, s) the cosine and
+// sine of (position, pair j) the input gradient of a pair is (c.g0 + s.g1, -s.g0 + c.g1). fetch() loads the thread's
+// HH / 2 (cos, sin) pairs and is called before the wait for the last products, so the latency of that read (a piece of
+// a table row per thread, from L2) is not added to the kernel's tail; store() reads both members of the thread's
+// pairs from tensor memory (warp-wide loads: call it under warp-uniform control flow) and writes two runs of HH / 2
+// values. Head sizes 64 and 128 (HH / 2 = 16 or 32 columns per load).
+template <int HH>
+struct RopeRow {
+  static constexpr int P = HH / 2;   // pairs per thread
+  static_assert(P == 16 || P == 32, "head size 64 or 128");
+  float4 cs[P / 2];
+  __device__ __forceinline__ void fetch(const float2* __restrict__ row, int half) {
+    const float4* src = reinterpret_cast<const float4*>(row + half * P);
+#pragma unroll
+    for (int i = 0; i < P / 2; i++) cs[i] = __ldg(src + i);
+  }
+  // acc: tensor-memory address of the head's first column in this thread's lane; dst: the head's first column in
+  // this thread's output row
+  __device__ __forceinline__ void store(uint32_t acc, float* dst, int half, int accum, bool st, float factor) const {
+    float g0[P], g1[P];
+    tmem_ld_issue<P>(acc + half * P, g0);
+    tmem_ld_issue<P>(acc + HH + half * P, g1);
+    tmem_wait_ld();
+    if (!st) return;
+    float* d0 = dst + half * P;
+    float* d1 = d0 + HH;
+#pragma unroll
+    for (int j = 0; j < P; j += 4) {
+      const float4 u = cs[j >> 1], v = cs[(j >> 1) + 1];   // cos, sin of pairs j, j + 1; of pairs j + 2, j + 3
+      float4 o0 = accum ? *reinterpret_cast<float4*>(d0 + j) : make_float4(0, 0, 0, 0);
+      float4 o1 = accum ? *reinterpret_cast<float4*>(d1 + j) : make_float4(0, 0, 0, 0);
+      o0.x += (u.x * g0[j] + u.y * g1[j]) * factor;             o1.x += (u.x * g1[j] - u.y * g0[j]) * factor;
+      o0.y += (u.z * g0[j + 1] + u.w * g1[j + 1]) * factor;     o1.y += (u.z * g1[j + 1] - u.w * g0[j + 1]) * factor;
+      o0.z += (v.x * g0[j + 2] + v.y * g1[j + 2]) * factor;     o1.z += (v.x * g1[j + 2] - v.y * g0[j + 2]) * factor;
+      o0.w += (v.z * g0[j + 3] + v.w * g1[j + 3]) * factor;     o1.w += (v.z * g1[j + 3] - v.w * g0[j + 3]) * factor;
+      *reinterpret_cast<float4*>(d0 + j) = o0;
+      *reinterpret_cast<float4*>(d1 + j) = o1;
+    }
+  }
+};
 __device__ __forceinline__ void pair_sync(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
 
 // A bounded wait that becomes a no-op once any wait of this thread has expired.
@@ -427,7 +468,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
                        const __grid_constant__ CUtensorMap mapQk, const __grid_constant__ CUtensorMap mapQm,
                        const __grid_constant__ CUtensorMap mapGk, const __grid_constant__ CUtensorMap mapGm,
                        const float* __restrict__ lse, const float* __restrict__ Ds, float* gk, int accum_k, float* gv, int accum_v,
-                       int rows, int T, int Hq, int Hkv, int window, float scale2, float dp_scale, int* __restrict__ flag) {
+                       int rows, int T, int Hq, int Hkv, int window, float scale2, float dp_scale, const float2* __restrict__ rope,
+                       int* __restrict__ flag) {
   extern __shared__ uint8_t smem_raw[];
   using S = DkvSmem<HD, NQ, KBUF, MBUF, SPLIT>;
   constexpr int ATOMS = HD / 32, NH = NQ / 2, HH = HD / 2, HDF = HD * SPLIT;
@@ -644,6 +686,9 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
       tc_fence_before();
       mbar_arrive(p_bar(i));
     }
+    RopeRow<HD >= 64 ? HH : 32> rr;   // (unused below head size 64: the host then launches the rotation's backward itself)
+    const bool roped = SPLIT == 1 && HD >= 64 && rope != nullptr && gk != nullptr;
+    if (roped) rr.fetch(rope + (size_t)(kg < T ? kg : 0) * HH, half);
     w.wait(all_done, 0, 28);
     tc_fence_after();
     {   // warp-uniform: the TMEM loads are warp-wide instructions, only the stores are per-row
@@ -662,7 +707,9 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
           }
         }
       }
-      if (gk) {
+      if (roped) {
+        if constexpr (SPLIT == 1 && HD >= 64) rr.store(tm_dk + lane_base, gk + off - half * HH, half, accum_k, st, TRUNC_COMP);
+      } else if (gk) {
         tmem_ld<HH>(tm_dk + half * HH + lane_base, t);
         float* dst = gk + off;
         if (st) {
@@ -707,7 +754,7 @@ __global__ void __launch_bounds__(THREADS, SB ? 2 : 1)
 attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapG,
                       const __grid_constant__ CUtensorMap mapKk, const __grid_constant__ CUtensorMap mapVk,
                       const __grid_constant__ CUtensorMap mapKm, const float* __restrict__ lse, const float* __restrict__ Ds,
-                      float* gq, int accum_q, int rows, int T, int Hq, int Hkv, int window, float scale2, float dp_scale,
+                      float* gq, int accum_q, int rows, int T, int Hq, int Hkv, int window, float scale2, float dp_scale, const float2* __restrict__ rope,
                       int* __restrict__ flag) {
   extern __shared__ uint8_t smem_raw[];
   using S = DqSmem<HD, NK, KBUF, SB, SPLIT>;
@@ -888,9 +935,15 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       tc_fence_before();
       mbar_arrive(p_bar(i));
     }
+    RopeRow<HD >= 64 ? HH : 32> rr;
+    const bool roped = SPLIT == 1 && HD >= 64 && rope != nullptr;
+    if (roped) rr.fetch(rope + (size_t)(valid ? tq : 0) * HH, half);
     w.wait(all_done, 0, 38);
     tc_fence_after();
-    {   // warp-uniform TMEM load, per-row store
+    if (roped) {
+      if constexpr (SPLIT == 1 && HD >= 64)
+        rr.store(tm_dq + lane_base, gq + (size_t)(row0 + (valid ? tq : 0)) * Hq * HDF + (size_t)h * HDF, half, accum_q, !w.dead && valid, TRUNC_COMP);
+    } else {   // warp-uniform TMEM load, per-row store
       float t[HH];
       tmem_ld<HH>(tm_dq + half * HH + lane_base, t);
       if (!w.dead && valid) {
@@ -967,7 +1020,7 @@ gt_status launch_fwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, 
 template <int HD, int NQ, int NK, int DKV_KBUF, int DKV_MBUF, int DQ_KBUF, bool DQ_SB, int SPLIT>
 gt_status launch_bwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, const float* q, const float* k, const float* v,
                      const float* out, const float* lse, const float* go, float* gq, int accum_q, float* gk, int accum_k, float* gv,
-                     int accum_v, int* flag) {
+                     int accum_v, const float2* rope, int* flag) {
   float* D = nullptr;
   gt_status st = gt_scratch(ctx, sizeof(float) * (size_t)rows * Hq, &D);
   if (st) return st;
@@ -995,10 +1048,10 @@ gt_status launch_bwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, 
     dim3 grid(Hkv * nseq * SPLIT, gt_cdiv(T, ROWS), 1);
     if (SPLIT == 1)
       kern<<<grid, THREADS, SM::TOTAL, ctx->stream>>>(mK, mV, mQk, mQm, mGk, mGm, lse, D, gk, accum_k, gv, accum_v, rows, T, Hq, Hkv, window, scale2,
-                                                      dp_scale, flag);
+                                                      dp_scale, rope, flag);
     else
       GT_CUDA(ctx, launch_split(kern, grid, THREADS, SM::TOTAL, ctx->stream, SPLIT, mK, mV, mQk, mQm, mGk, mGm, lse, D, gk, accum_k, gv, accum_v,
-                                rows, T, Hq, Hkv, window, scale2, dp_scale, flag));
+                                rows, T, Hq, Hkv, window, scale2, dp_scale, rope, flag));
     GT_LAUNCHED(ctx, "attn_bwd_dkv_tc_kernel");
   }
   if (gq) {
@@ -1014,10 +1067,10 @@ gt_status launch_bwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, 
     if (st) return st;
     dim3 grid(Hq * nseq * SPLIT, gt_cdiv(T, ROWS), 1);
     if (SPLIT == 1)
-      kern<<<grid, THREADS, SM::TOTAL, ctx->stream>>>(mQ, mG, mKk, mVk, mKm, lse, D, gq, accum_q, rows, T, Hq, Hkv, window, scale2, dp_scale, flag);
+      kern<<<grid, THREADS, SM::TOTAL, ctx->stream>>>(mQ, mG, mKk, mVk, mKm, lse, D, gq, accum_q, rows, T, Hq, Hkv, window, scale2, dp_scale, rope, flag);
     else
       GT_CUDA(ctx, launch_split(kern, grid, THREADS, SM::TOTAL, ctx->stream, SPLIT, mQ, mG, mKk, mVk, mKm, lse, D, gq, accum_q, rows, T, Hq, Hkv,
-                                window, scale2, dp_scale, flag));
+                                window, scale2, dp_scale, rope, flag));
     GT_LAUNCHED(ctx, "attn_bwd_dq_tc_kernel");
   }
   return GT_OK;
@@ -1046,18 +1099,19 @@ gt_status gt_attention_fwd_tc(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int
 
 gt_status gt_attention_bwd_tc(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int hd, int window, const float* q, const float* k,
                               const float* v, const float* out, const float* lse, const float* go, float* gq, int accum_q, float* gk,
-                              int accum_k, float* gv, int accum_v, bool* handled) {
+                              int accum_k, float* gv, int accum_v, const float2* rope, bool* handled) {
   *handled = false;
   if (!tc_shape_ok(T, hd)) return GT_OK;
+  if (rope && hd != 64 && hd != 128) return GT_OK;   // (at 256 a CTA of a pair holds half a head: a rotation's pairs straddle the two)
   if ((((uintptr_t)q) | ((uintptr_t)k) | ((uintptr_t)v) | ((uintptr_t)out) | ((uintptr_t)go) | ((uintptr_t)gq) | ((uintptr_t)gk) | ((uintptr_t)gv)) & 15)
     return GT_OK;
   int* flag = device_flag(ctx);
   if (!flag) return GT_OK;
   gt_status s;
-  if (hd == 32) s = launch_bwd<32, 64, 64, 2, 2, 1, true, 1>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
-  else if (hd == 64) s = launch_bwd<64, 64, 64, 2, 2, 1, true, 1>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
-  else if (hd == 128) s = launch_bwd<128, 32, 32, 2, 1, 2, false, 1>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
-  else s = launch_bwd<128, 32, 32, 1, 1, 1, false, 2>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, flag);
+  if (hd == 32) s = launch_bwd<32, 64, 64, 2, 2, 1, true, 1>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, rope, flag);
+  else if (hd == 64) s = launch_bwd<64, 64, 64, 2, 2, 1, true, 1>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, rope, flag);
+  else if (hd == 128) s = launch_bwd<128, 32, 32, 2, 1, 2, false, 1>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, rope, flag);
+  else s = launch_bwd<128, 32, 32, 1, 1, 1, false, 2>(ctx, rows, T, Hq, Hkv, window, q, k, v, out, lse, go, gq, accum_q, gk, accum_k, gv, accum_v, rope, flag);
   if (s) return s;
   *handled = true;
   return GT_OK;

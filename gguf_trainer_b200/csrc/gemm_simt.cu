@@ -199,11 +199,51 @@ extern "C" gt_status gt_gemm_grouped(gt_ctx* ctx, int32_t kind, int32_t ngroups,
   }
   if (ctx->precision != GT_PREC_FP32 && ngroups > 1) {
     bool handled = false;
-    gt_status s = gt_gemm_tc_grouped(ctx, kind, ngroups, m, n, K, pa, pb, pc, acc, &handled);
+    gt_status s = gt_gemm_tc_grouped(ctx, kind, ngroups, m, n, K, pa, pb, pc, acc, nullptr, nullptr, 0, &handled);
     if (s != GT_OK || handled) return s;
   }
   for (int g = 0; g < ngroups; g++) {
     gt_status s = gt_gemm(ctx, kind, acc[g], m[g], n[g], K, as[g], bs[g], cs[g]);
+    if (s) return s;
+  }
+  return GT_OK;
+}
+
+// Projections y_g = x.W_g^T of one input launched together, the rotary embedding applied to the outputs that take one
+// (heads[g] > 0) as their tiles are written; elsewhere each product followed by the rotation as a pass over its output.
+extern "C" gt_status gt_linear_rope_grouped(gt_ctx* ctx, int32_t ngroups, int32_t rows, int32_t K, gt_buf x, const int32_t* Ns,
+                                            const gt_buf* ws, const gt_buf* ys, const int32_t* heads, int32_t hd, double base,
+                                            int32_t pos_offset) {
+  GT_REQUIRE(ctx, ngroups >= 1 && ngroups <= 8 && rows > 0 && K > 0 && x && Ns && ws && ys && heads, "gt_linear_rope_grouped: %d projections (1..8), rows %d, K %d",
+             ngroups, rows, K);
+  GT_REQUIRE(ctx, hd > 0 && hd % 2 == 0, "gt_linear_rope_grouped: head size %d (must be even)", hd);
+  const float* pa[8];
+  const float* pb[8];
+  float* pc[8];
+  int m[8], n[8], acc[8], rp[8];
+  bool any = false;
+  for (int g = 0; g < ngroups; g++) {
+    GT_REQUIRE(ctx, Ns[g] > 0 && ws[g] && ys[g], "gt_linear_rope_grouped: projection %d is empty or has a null operand", g);
+    GT_REQUIRE(ctx, heads[g] == 0 || heads[g] * hd == Ns[g], "gt_linear_rope_grouped: projection %d is %d wide, not %d heads of %d", g, Ns[g], heads[g], hd);
+    pa[g] = gt_ptr<const float>(x); pb[g] = gt_ptr<const float>(ws[g]); pc[g] = gt_ptr<float>(ys[g]);
+    m[g] = rows; n[g] = Ns[g]; acc[g] = 0; rp[g] = heads[g] > 0;
+    any = any || rp[g];
+  }
+  const float2* tab = nullptr;
+  int period = 0;
+  if (any) {
+    gt_status s = gt_rope_table(ctx, rows, hd, base, pos_offset, &tab, &period);
+    if (s) return s;
+  }
+  if (ctx->precision != GT_PREC_FP32 && ngroups > 1 && (!any || hd == 64)) {
+    bool handled = false;
+    gt_status s = gt_gemm_tc_grouped(ctx, GT_GEMM_NT, ngroups, m, n, K, pa, pb, pc, acc, rp, tab, period, &handled);
+    if (s != GT_OK || handled) return s;
+  }
+  for (int g = 0; g < ngroups; g++) {
+    gt_status s = gt_gemm(ctx, GT_GEMM_NT, 0, rows, n[g], K, x, ws[g], ys[g]);
+    if (s) return s;
+    if (rp[g]) s = gt_rope_apply(ctx, false, rows, heads[g], hd, base, pos_offset, pc[g], pc[g], 0);
     if (s) return s;
   }
   return GT_OK;

@@ -62,13 +62,23 @@ struct PartMaps {
   CUtensorMap c[MAX_PARTS];
   int ngroups;
   int gM[MAX_PARTS], gN[MAX_PARTS], g_accum[MAX_PARTS], unit_end[MAX_PARTS];
+  // Rotary form (EPI_ROPE): the outputs of the groups with g_rope[g] set are rotated as they are written (see the kernel).
+  int g_rope[MAX_PARTS];
+  const float2* rope_tab;   // [rope_period][32] (cos, sin) of the 32 pairs of a 64-wide head
+  int rope_period;          // positions per sequence: row r is position r % rope_period
 };
+constexpr int EPI_ROPE = 8;   // a value of the kernel's GLU argument that is neither activation
 
 // GLU != 0 (GT_EW_SILU or GT_EW_GELU; NT layout, BN = 192 only): the gated unit of the FFN in the projection that
 // feeds it. B is two weight matrices: the tile's first 96 columns are rows [n0/2, n0/2 + 96) of b[0] (gate), the other 96
 // the same rows of b[1] (up). The epilogue writes the gate and up projections (backward needs them) through c[0] and
 // c[1] and act(gate) * up through c[2], so the separate pass that read both and wrote the product is not launched.
 // N_ is 2 x the FFN width.
+// GLU == EPI_ROPE (grouped NT launches, BN = 192, heads 64 wide): the rotary embedding that follows the q and k
+// projections (src/arch/llama.ts:195-199 records `rope(linear(x, Wq))`) applied to the accumulator on its way out. A
+// 192-column tile is three whole heads; the thread that owns a row loads the two 32-column halves of a head, rotates
+// pair (j, j + 32) by the angle of (row's position, j) from the table, and both halves go out as they would have.
+// The unrotated projection is never written.
 template <bool A_K, bool B_K, int BN, int MT, int GLU = 0>
 __global__ void __launch_bounds__(Smem<BN, MT>::THREADS, 1)
 gemm_tf32_kernel(const __grid_constant__ PartMaps maps, float* __restrict__ C, int M_, int N_,
@@ -87,6 +97,7 @@ gemm_tf32_kernel(const __grid_constant__ PartMaps maps, float* __restrict__ C, i
   const uint32_t tmem_slot = bars + 8u * (2 * STAGES + 4);
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
+  constexpr bool IS_GLU = GLU == GT_EW_SILU || GLU == GT_EW_GELU;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_n = (N + BN - 1) / BN, tiles_m = (M + BM - 1) / BM;
   const int per_mat = tiles_n * tiles_m * ksplit;
@@ -159,7 +170,7 @@ gemm_tf32_kernel(const __grid_constant__ PartMaps maps, float* __restrict__ C, i
           if (A_K) tma_load_3d(a_dst, pa, k0, m0, bi, full_bar(s));
           else
             for (int c = 0; c < BM / 32; c++) tma_load_3d(a_dst + c * 4096, pa, m0 + 32 * c, k0, bi, full_bar(s));
-          if (GLU != 0) {
+          if (IS_GLU) {
             tma_load_3d(b_dst, &maps.b[0], k0, n0 >> 1, bi, full_bar(s));
             tma_load_3d(b_dst + (BN / 2) * 128, &maps.b[1], k0, n0 >> 1, bi, full_bar(s));
           } else if (B_K) tma_load_3d(b_dst, pb, k0, n0, bi, full_bar(s));
@@ -222,7 +233,7 @@ gemm_tf32_kernel(const __grid_constant__ PartMaps maps, float* __restrict__ C, i
       if (have) wait(acc_full(b), par_of(tl), 3);
       dead = __any_sync(0xffffffffu, dead);
       tc_fence_after();
-      if (GLU != 0 && have) {
+      if (IS_GLU && have) {
         // gate | up halves of the accumulator: three outputs per 32-column block, each through its own tensor map
         auto put = [&](const float* v, const CUtensorMap* map, int col0) {
           const uint32_t tile = epi + (uint32_t)(ew * S::EPI_TILES + (nst % S::EPI_TILES)) * 4096u;
@@ -260,6 +271,47 @@ gemm_tf32_kernel(const __grid_constant__ PartMaps maps, float* __restrict__ C, i
             vg[j] = act * vu[j];
           }
           put(vg, &maps.c[2], col0);
+        }
+      } else if (GLU == EPI_ROPE && have && maps.g_rope[wh.g]) {
+        auto put = [&](const float* v, int col0) {
+          const uint32_t tile = epi + (uint32_t)(ew * S::EPI_TILES + (nst % S::EPI_TILES)) * 4096u;
+          if (nst >= S::EPI_TILES) tma_wait_read<S::EPI_TILES - 1>();
+          __syncwarp();
+          uint8_t* tp = smem_raw + (tile - smem_u32(smem_raw)) + lane * 128;
+#pragma unroll
+          for (int c4 = 0; c4 < 8; c4++)
+            *reinterpret_cast<float4*>(tp + ((c4 ^ (lane & 7)) * 16)) = make_float4(v[4 * c4], v[4 * c4 + 1], v[4 * c4 + 2], v[4 * c4 + 3]);
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0 && !dead && m0 + q * 32 < M) {
+            if (ksplit > 1 || accum) tma_reduce_add_3d(mapC, tile, col0, m0 + q * 32, bi);   // (a rotation is linear)
+            else tma_store_3d(mapC, tile, col0, m0 + q * 32, bi);
+          }
+          if (lane == 0) tma_commit_group();
+          nst++;
+        };
+        // (cos, sin) of this row's position, pairs 0..31; rows past M are clipped by the store and read row M - 1's
+        const float4* tab4 = reinterpret_cast<const float4*>(maps.rope_tab + (size_t)((row < M ? row : M - 1) % maps.rope_period) * 32);
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; c++) {
+          const int col0 = n0 + c * 64;
+          if (col0 >= N) break;   // uniform across the warp
+          float v0[32], v1[32];
+          const uint32_t ta = tmem + b * BN + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 64);
+          tmem_ld32_issue(ta, v0);
+          tmem_ld32_issue(ta + 32, v1);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const float4 cs = __ldg(tab4 + (j >> 1));   // cos, sin of pair j; cos, sin of pair j + 1
+            const float a0 = v0[j] * out_scale, a1 = v1[j] * out_scale, b0 = v0[j + 1] * out_scale, b1 = v1[j + 1] * out_scale;
+            v0[j] = a0 * cs.x - a1 * cs.y;
+            v1[j] = a0 * cs.y + a1 * cs.x;
+            v0[j + 1] = b0 * cs.z - b1 * cs.w;
+            v1[j + 1] = b0 * cs.w + b1 * cs.z;
+          }
+          put(v0, col0);
+          put(v1, col0 + 32);
         }
       } else if (have) {
 #pragma unroll 1
@@ -803,9 +855,16 @@ static gt_status gemm_tc_dispatch(gt_ctx* ctx, int kind, int accum, int M, int N
 // ONE launch: the weight gradients dW_g = dY_g^T.X_g of several projections (K = rows for all of them). Their tiles
 // are so few per product that each would need its own split-K launch with its own tail; together they fill the SMs.
 static gt_status gemm_tc_grouped(gt_ctx* ctx, int kind, int ngroups, const int* Ms, const int* Ns, int K, const float* const* as,
-                                 const float* const* bs, float* const* cs, const int* accums, bool* handled) {
+                                 const float* const* bs, float* const* cs, const int* accums, const int* ropes, const float2* rope_tab,
+                                 int rope_period, bool* handled) {
   *handled = false;
   if (ngroups < 2 || ngroups > MAX_PARTS || K < 16) return GT_OK;
+  bool any_rope = false;
+  for (int g = 0; ropes && g < ngroups; g++) {
+    if (!ropes[g]) continue;
+    if (kind != GT_GEMM_NT || (Ns[g] & 63) || !rope_tab || rope_period <= 0) return GT_OK;
+    any_rope = true;
+  }
   const bool a_k = kind != GT_GEMM_TN, b_k = kind == GT_GEMM_NT;
   for (int g = 0; g < ngroups; g++) {
     const int a_inner = a_k ? K : Ms[g], b_inner = b_k ? K : Ns[g];
@@ -847,17 +906,26 @@ static gt_status gemm_tc_grouped(gt_ctx* ctx, int kind, int ngroups, const int* 
     units += gt_cdiv(N, 192) * gt_cdiv(M, bm) * ksplit;
     maps.unit_end[g] = units;
     maps.gM[g] = M; maps.gN[g] = N; maps.g_accum[g] = accums[g];
+    maps.g_rope[g] = any_rope ? ropes[g] : 0;
     maps.kb_end[g] = kblocks;
   }
+  maps.rope_tab = rope_tab;
+  maps.rope_period = rope_period;
   for (int g = ngroups; g < MAX_PARTS; g++) {
     maps.a[g] = maps.a[0]; maps.b[g] = maps.b[0]; maps.c[g] = maps.c[0];
     maps.unit_end[g] = units; maps.gM[g] = Ms[0]; maps.gN[g] = Ns[0]; maps.g_accum[g] = accums[0]; maps.kb_end[g] = kblocks;
+    maps.g_rope[g] = 0;
   }
   if (ksplit > 1)
     for (int g = 0; g < ngroups; g++)
       if (!accums[g]) GT_CUDA(ctx, cudaMemsetAsync(cs[g], 0, sizeof(float) * (size_t)Ms[g] * Ns[g], ctx->stream));
-  gt_status s = mt == 1 ? launch_kind<192, 1>(ctx, kind, maps, units, 1, cs[0], Ms[0], Ns[0], accums[0], ksplit, 1, TRUNC_COMP)
-                        : launch_kind<192, 2>(ctx, kind, maps, units, 1, cs[0], Ms[0], Ns[0], accums[0], ksplit, 1, TRUNC_COMP);
+  gt_status s;
+  if (any_rope)
+    s = mt == 1 ? launch<true, true, 192, 1, EPI_ROPE>(ctx, maps, units, 1, cs[0], Ms[0], Ns[0], accums[0], ksplit, 1, TRUNC_COMP)
+                : launch<true, true, 192, 2, EPI_ROPE>(ctx, maps, units, 1, cs[0], Ms[0], Ns[0], accums[0], ksplit, 1, TRUNC_COMP);
+  else
+    s = mt == 1 ? launch_kind<192, 1>(ctx, kind, maps, units, 1, cs[0], Ms[0], Ns[0], accums[0], ksplit, 1, TRUNC_COMP)
+                : launch_kind<192, 2>(ctx, kind, maps, units, 1, cs[0], Ms[0], Ns[0], accums[0], ksplit, 1, TRUNC_COMP);
   if (s) return s;
   *handled = true;
   return GT_OK;
@@ -899,8 +967,9 @@ gt_status gt_glu_linear_tc(gt_ctx* ctx, int op, int rows, int ffn, int in, const
 }
 
 gt_status gt_gemm_tc_grouped(gt_ctx* ctx, int kind, int ngroups, const int* Ms, const int* Ns, int K, const float* const* as,
-                             const float* const* bs, float* const* cs, const int* accums, bool* handled) {
-  return gemm_tc_grouped(ctx, kind, ngroups, Ms, Ns, K, as, bs, cs, accums, handled);
+                             const float* const* bs, float* const* cs, const int* accums, const int* ropes, const float2* rope_tab,
+                             int rope_period, bool* handled) {
+  return gemm_tc_grouped(ctx, kind, ngroups, Ms, Ns, K, as, bs, cs, accums, ropes, rope_tab, rope_period, handled);
 }
 
 gt_status gt_gemm_tc_batched(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c, int batch,

@@ -19,7 +19,7 @@ __global__ void rope_table_kernel(int T, int half, int hd, double base, int pos_
 // one thread per (row, head, pair); pairs are the fastest index so loads coalesce
 template <bool BWD>
 __global__ void rope_kernel(long npairs, int H, int hd, int period, const float2* __restrict__ tab,
-                            const float* __restrict__ in, float* out, int accum) {
+                            const float* in, float* out, int accum) {   // in == out is allowed: a thread reads its pair before it writes it
   const int half = hd >> 1;
   long stride = (long)gridDim.x * blockDim.x;
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < npairs; i += stride) {
@@ -42,7 +42,7 @@ __global__ void rope_kernel(long npairs, int H, int hd, int period, const float2
 // the row, two of the table, two 16-byte stores, 32-bit index arithmetic.
 template <bool BWD>
 __global__ void rope_vec_kernel(unsigned nvec, int H, int hd, int period, const float2* __restrict__ tab,
-                                const float* __restrict__ in, float* out, int accum) {
+                                const float* in, float* out, int accum) {   // in == out is allowed, as above
   const unsigned half = hd >> 1, hv = half >> 2;
   const unsigned stride = gridDim.x * blockDim.x;
   for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
@@ -167,6 +167,19 @@ gt_status rope_run(gt_ctx* ctx, int rows, int H, int hd, double base, int pos_of
 }
 
 }  // namespace
+
+// For the kernels that apply the rotation themselves: the table of this shape (built on first use) and the number of
+// positions it holds (the sequence length when a batch is set, else the row count).
+gt_status gt_rope_table(gt_ctx* ctx, int rows, int hd, double base, int pos_offset, const float2** tab, int* period) {
+  *period = ctx->batch ? ctx->seq_len : rows;
+  if (ctx->batch) GT_REQUIRE(ctx, rows == ctx->batch * ctx->seq_len, "gt_rope: %d rows but the batch is %d x %d", rows, ctx->batch, ctx->seq_len);
+  return rope_table(ctx, *period, hd, base, pos_offset, tab);
+}
+
+// The rotation (or its transpose) as a pass of its own; `in` may be `out` when accum is 0.
+gt_status gt_rope_apply(gt_ctx* ctx, bool bwd, int rows, int H, int hd, double base, int pos_offset, const float* in, float* out, int accum) {
+  return bwd ? rope_run<true>(ctx, rows, H, hd, base, pos_offset, in, out, accum) : rope_run<false>(ctx, rows, H, hd, base, pos_offset, in, out, accum);
+}
 
 extern "C" {
 

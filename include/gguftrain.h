@@ -155,6 +155,22 @@ gt_status gt_attention_fwd(gt_ctx* ctx, int32_t rows, int32_t Hq, int32_t Hkv, i
 gt_status gt_attention_bwd(gt_ctx* ctx, int32_t rows, int32_t Hq, int32_t Hkv, int32_t hd, int32_t window,
                            gt_buf q, gt_buf k, gt_buf v, gt_buf out, gt_buf lse, gt_buf gout,
                            gt_buf gq, int32_t accum_q, gt_buf gk, int32_t accum_k, gt_buf gv, int32_t accum_v);
+/* The rotary embedding merged into its neighbours (the reference records `rope(linear(x, Wq))`, `rope(linear(x, Wk))`
+ * and then `attention`, src/arch/llama.ts:195-201; every op is its own dispatch, src/backend/webgpu.ts:1110-1123).
+ * gt_linear_rope_grouped: ngroups (1..8) projections y_g = x.W_g^T of one input x:[rows, K] as one launch; the outputs
+ * with heads[g] > 0 (y_g:[rows, heads[g]*hd]) leave the kernel already rotated, so the unrotated projection is never
+ * written and the rotation's pass over it is not launched. heads[g] = 0: a plain projection (v).
+ * gt_attention_bwd_rope: gt_attention_bwd for q and k that came out of such a rotation; gq and gk receive the
+ * gradients with respect to the rotation's inputs (the transposed rotation is applied to the dQ and dK tiles as they
+ * are written). Both fall back to the separate launches where the fused kernels do not apply (strict f32, head sizes
+ * other than 64 in forward or 256 in backward), with the same results to summation order. */
+gt_status gt_linear_rope_grouped(gt_ctx* ctx, int32_t ngroups, int32_t rows, int32_t K, gt_buf x, const int32_t* Ns,
+                                 const gt_buf* ws, const gt_buf* ys, const int32_t* heads, int32_t hd, double base,
+                                 int32_t pos_offset);
+gt_status gt_attention_bwd_rope(gt_ctx* ctx, int32_t rows, int32_t Hq, int32_t Hkv, int32_t hd, int32_t window,
+                                gt_buf q, gt_buf k, gt_buf v, gt_buf out, gt_buf lse, gt_buf gout,
+                                gt_buf gq, int32_t accum_q, gt_buf gk, int32_t accum_k, gt_buf gv, int32_t accum_v,
+                                double base, int32_t pos_offset);
 /* No counterpart in the reference. The same f32 attention backward as gt_attention_bwd for callers that
  * cannot allocate device memory (hosts that give all of HBM to their own arena, or steps that cannot afford
  * cudaMalloc's device-wide synchronisation): its only scratch, the per-(head,row) dot products dO.O, sits

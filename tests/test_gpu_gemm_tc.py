@@ -454,3 +454,76 @@ def test_projections_of_one_input_are_one_grouped_launch(gpu, oracle):
     for o, w in zip(outs, ws):
         e = rel_l2(o.data, X @ w.data.astype(np.float64).reshape(w.shape).T)
         assert e <= REL_L2_TC and e > 1e-7, f"relative L2 {e:.3e}"
+
+
+def _attention_block(gpu, oracle, T, B, din, Hq, Hkv, hd, window, fuse, read_q=False):
+    """q = rope(linear(x, Wq)), k = rope(linear(x, Wk)), v = linear(x, Wv), a = attention(q, k, v), the attention half
+    of a llama block (src/arch/llama.ts:195-201), forward and backward with a fixed upstream gradient. Returns the
+    launch counts and every value a caller can observe."""
+    from gpu_harness import rand_tensor, upstream
+    from gguf_trainer_b200 import autograd as ag
+    rng = oracle.Mulberry32(T + 7 * din + 13 * Hq + hd)
+    rows = T * max(B, 1)
+    x = rand_tensor(rng, [rows, din])
+    wq, wk, wv = (rand_tensor(rng, [h * hd, din], 0.1) for h in (Hq, Hkv, Hkv))
+    for t in (x, wq, wk, wv):
+        t.zeroGrad()
+    gpu.fuseRope = fuse
+    gpu.install()
+    if B:
+        gpu.setBatch(B, T)
+    try:
+        gpu.sync([])
+        l0 = gpu.kernelLaunches()
+        q0, k0 = ag.linear(x, wq), ag.linear(x, wk)
+        v = ag.linear(x, wv)
+        q, k = ag.rope(q0, rows, Hq, hd, 10000.0), ag.rope(k0, rows, Hkv, hd, 10000.0)
+        a = ag.attention(q, k, v, rows, Hq, Hkv, hd, window)
+        fwd = gpu.kernelLaunches() - l0
+        g = upstream(oracle, a.size)
+        a.grad[:] = g
+        gpu.seedGradFromHost(a)
+        l1 = gpu.kernelLaunches()
+        a._backward(); k._backward(); q._backward(); v._backward(); k0._backward(); q0._backward()
+        reads = [a, q, k, v] + ([q0] if read_q else [])
+        gpu.sync(reads)
+        bwd = gpu.kernelLaunches() - l1
+    finally:
+        gpu.setBatch(0)
+        gpu.uninstall()
+        gpu.fuseRope = True
+    vals = {"a": a.data.copy(), "q": q.data.copy(), "k": k.data.copy(), "v": v.data.copy(), "dx": x.grad.copy(),
+            "dWq": wq.grad.copy(), "dWk": wk.grad.copy(), "dWv": wv.grad.copy()}
+    if read_q:
+        vals["q0"] = q0.data.copy()
+    return fwd, bwd, vals
+
+
+@pytest.mark.parametrize("T,B,din,Hq,Hkv,hd,window", [(256, 0, 192, 4, 2, 64, 0), (200, 2, 576, 9, 3, 64, 0), (192, 3, 128, 2, 1, 64, 96),
+                                                     (128, 2, 256, 2, 2, 128, 0), (160, 0, 96, 4, 1, 32, 0)])
+def test_rotary_embedding_runs_inside_its_neighbours(gpu, oracle, T, B, din, Hq, Hkv, hd, window):
+    """`rope` between `linear` and `attention`: with 64-wide heads the q/k/v launch writes q and k already rotated, and
+    for head sizes 64 and 128 attention's backward rotates dQ and dK back as it stores them, so neither rotation is
+    a launch of its own. Every observable value against the same block with the rotations launched separately (which
+    the op tests hold to the oracle). The rotated values themselves agree to f32 rounding (1e-6). What then passes through
+    another TF32 product (the attention output, dx, dW) can differ more: an operand that moved by a few f32 units in the last
+    place, as a difference of two rotated terms does, can fall on the other side of a TF32 truncation (2^-11 on that
+    element). Measured 3e-5 at most; bound 1e-4, a twentieth of the mode's own tolerance."""
+    _attention_block(gpu, oracle, T, B, din, Hq, Hkv, hd, window, False)     # (builds the angle table of this shape: one more launch)
+    f_fwd, f_bwd, fused = _attention_block(gpu, oracle, T, B, din, Hq, Hkv, hd, window, True)
+    p_fwd, p_bwd, plain = _attention_block(gpu, oracle, T, B, din, Hq, Hkv, hd, window, False)
+    assert p_fwd == 4 and p_bwd == 3 + 2 + 2, (p_fwd, p_bwd)      # q/k/v, 2 rotations, attention; D, dKV, dQ, 2 rotations, dW, dX
+    assert f_fwd == (2 if hd == 64 else 4), f_fwd
+    assert f_bwd == (5 if hd >= 64 else 7), f_bwd
+    for name in plain:
+        e = rel_l2(fused[name], plain[name])
+        assert np.isfinite(fused[name]).all() and e <= (1e-6 if name in ("q", "k", "v") else 1e-4), f"{name}: relative L2 {e:.3e}"
+
+
+def test_projection_consumed_rotated_is_still_readable(gpu, oracle):
+    """The unrotated projection is not written when its only reader took it rotated; a later reader (here a sync that
+    asks for it) gets it from a product launched then."""
+    _f, _b, fused = _attention_block(gpu, oracle, 256, 0, 192, 4, 2, 64, 0, True, read_q=True)
+    _f, _b, plain = _attention_block(gpu, oracle, 256, 0, 192, 4, 2, 64, 0, False, read_q=True)
+    assert np.abs(plain["q0"]).max() > 0
+    assert rel_l2(fused["q0"], plain["q0"]) <= 1e-6
