@@ -46,8 +46,8 @@ class _Entry:
         self.copyFrom = 0         # address whose contents are this gradient's value so far (a copy not made yet)
         self.pendingDw = False    # a weight-gradient product into this gradient is noted in _pendingDw, not launched yet
         self.pendingFwd = False   # the projection that produces this tensor is noted in _pendingFwd, not launched yet
-        self.lazy = None          # (x entry, w entry, T, in, out): a projection whose only reader took it rotated; `data` is
-                                  # unwritten until someone else asks for it (_materializeLazy)
+        self.lazy = None          # a launch that fills `data`: set on a projection (or per-head norm) whose only reader took it
+                                  # rotated, so that it was never written; run if someone else asks for it (_materializeLazy)
         self.ropeOf = None        # for a rotary embedding's output: (input tensor, its entry, H, hd, base, posOffset)
         self.ropeFused = False    # its gradient went straight to the rotation's input (attention backward applied it)
 
@@ -436,9 +436,19 @@ class CudaBackend:
     # launched together when the first of their outputs is needed: q/k/v as one grouped product (gt_gemm_grouped), gate and
     # up, when a gated unit consumes both, as one launch that also applies the unit (gt_glu_linear_fwd, see _gatedUnit).
     def _deferLinear(self, ex: _Entry, ew: _Entry, eo: _Entry, T: int, inDim: int, outDim: int):
-        if self._pendingFwd and (self._pendingFwd[0]["ex"] is not ex or len(self._pendingFwd) == 8):
+        first = self._pendingFwd[0] if self._pendingFwd else None
+        if first is not None and ("norm" in first or first["ex"] is not ex or len(self._pendingFwd) == 8):
             self._flushFwd()
         self._pendingFwd.append(dict(ex=ex, ew=ew, eo=eo, T=T, inDim=inDim, outDim=outDim))
+        eo.pendingFwd = True
+
+    # A per-head norm (q and k of the Qwen3 and Gemma 3 blocks) waits the same way for the rotary embedding that follows
+    # it: if that is its first reader, one pass normalises and rotates (gt_rmsnorm_heads_rope_fwd).
+    def _deferHeadNorm(self, ex: _Entry, ew: _Entry, eo: _Entry, rinv: int, T: int, H: int, hd: int, eps: float):
+        first = self._pendingFwd[0] if self._pendingFwd else None
+        if first is not None and ("norm" not in first or len(self._pendingFwd) == 8):
+            self._flushFwd()
+        self._pendingFwd.append(dict(norm=True, ex=ex, ew=ew, eo=eo, rinv=rinv, T=T, H=H, hd=hd, eps=eps, outDim=H * hd))
         eo.pendingFwd = True
 
     def _flushFwd(self):
@@ -448,6 +458,20 @@ class CudaBackend:
         self._pendingFwd = []
         for p in parts:
             p["eo"].pendingFwd = False
+        if "norm" in parts[0]:
+            for p in parts:
+                T, H, hd = p["T"], p["H"], p["hd"]
+                plain = (lambda p=p: self._check(self.lib.gt_rmsnorm_fwd(self.ctx, p["T"] * p["H"], p["hd"], p["ex"].data, p["ew"].data,
+                                                                          p["eps"], p["eo"].data, p["rinv"])))
+                if "rope" in p:
+                    er, _H, _hd, base, posOffset = p["rope"]
+                    er.pendingFwd = False
+                    self._check(self.lib.gt_rmsnorm_heads_rope_fwd(self.ctx, T, H, hd, p["ex"].data, p["ew"].data, p["eps"], er.data,
+                                                                   p["rinv"], float(base), posOffset))
+                    p["eo"].lazy = plain        # (the same row statistics are written again if it ever runs)
+                else:
+                    plain()
+            return
         n = len(parts)
         T, inDim = parts[0]["T"], parts[0]["inDim"]
         roped = [p for p in parts if "rope" in p]
@@ -457,7 +481,7 @@ class CudaBackend:
             _er, _H, hd, base, posOffset = roped[0]["rope"]
             for p in roped:
                 p["rope"][0].pendingFwd = False
-                p["eo"].lazy = (p["ex"], p["ew"], T, inDim, p["outDim"])
+                p["eo"].lazy = (lambda p=p: self._gemm("NT", 0, p["T"], p["outDim"], p["inDim"], p["ex"].data, p["ew"].data, p["eo"].data))
             Ns = (C.c_int32 * n)(*[p["outDim"] for p in parts])
             Ws = (C.c_uint64 * n)(*[p["ew"].data for p in parts])
             Ys = (C.c_uint64 * n)(*[(p["rope"][0].data if "rope" in p else p["eo"].data) for p in parts])
@@ -476,9 +500,9 @@ class CudaBackend:
         self._check(self.lib.gt_gemm_grouped(self.ctx, _KIND["NT"], n, Ms, Ns, inDim, As, Bs, Cs, acc))
 
     def _materializeLazy(self, e: _Entry):
-        ex, ew, T, inDim, outDim = e.lazy
+        launch = e.lazy
         e.lazy = None
-        self._gemm("NT", 0, T, outDim, inDim, ex.data, ew.data, e.data)
+        launch()
 
     def _flushAllDx(self):
         self._flushFwd()
@@ -1130,9 +1154,9 @@ class CudaBackend:
     def scale(self, x, c):
         return self._elementwise("scale", x, None, float(c))
 
-    def _rmsNormRows(self, x: Tensor, w: Tensor, rows: int, d: int, eps: float, shape) -> Tensor:
-        """webgpu.ts:1673-1701."""
-        self._beginForwardOp()
+    def _rmsNormRows(self, x: Tensor, w: Tensor, rows: int, d: int, eps: float, shape, heads=None) -> Tensor:
+        """webgpu.ts:1673-1701. `heads` = (T, H): a per-head norm that may wait for the rotary embedding after it."""
+        self._beginForwardOp(keepPending=heads is not None)
         ew = self._entryFor(w)
         if id(x) in self._pendingAdd and x not in self._entries:
             # x = a + b has not been launched and this norm is its first use: one kernel writes both
@@ -1146,7 +1170,10 @@ class CudaBackend:
             ex = self._entryFor(x)
             out, eo = self._makeOut(shape, [x, w])
             rinv = self._acquireRecycled(rows * 4)
-            self._check(self.lib.gt_rmsnorm_fwd(self.ctx, rows, d, ex.data, ew.data, eps, eo.data, rinv))
+            if heads is not None:
+                self._deferHeadNorm(ex, ew, eo, rinv, heads[0], heads[1], d, eps)
+            else:
+                self._check(self.lib.gt_rmsnorm_fwd(self.ctx, rows, d, ex.data, ew.data, eps, eo.data, rinv))
 
         def _bw():
             self._ensureBackwardBegun()
@@ -1174,7 +1201,8 @@ class CudaBackend:
         return self._rmsNormRows(x, weight, T, d, eps, [T, d])
 
     def rmsNormHeads(self, x, weight, T, H, hd, eps):
-        return self._rmsNormRows(x, weight, T * H, hd, eps, [T, H * hd])
+        wait = self.fuseRope and hd in (64, 128, 256) and not (id(x) in self._pendingAdd and x not in self._entries)
+        return self._rmsNormRows(x, weight, T * H, hd, eps, [T, H * hd], heads=(T, H) if wait else None)
 
     def embedding(self, weight: Tensor, ids) -> Tensor:
         """webgpu.ts:1090-1108."""
@@ -1216,16 +1244,24 @@ class CudaBackend:
     def rope(self, x: Tensor, T: int, H: int, hd: int, base: float, posOffset: int = 0) -> Tensor:
         """webgpu.ts:1110-1123. Where the input is a projection that has not been launched yet (`rope(linear(x, Wq))`, the
         llama block) and the heads are 64 wide, the rotation is applied by the projection's launch as its tiles are
-        written (gt_linear_rope_grouped) and no pass of its own runs; the gradient side is in `attention`."""
+        written (gt_linear_rope_grouped); where it is a per-head norm that has not been launched yet (the Qwen3 and
+        Gemma 3 blocks), by the norm's pass (gt_rmsnorm_heads_rope_fwd). No pass of its own runs in either case; the
+        gradient side is in `attention`."""
         self._checkT(T, x.shape[0], "rope")
         e0 = self._entries.get(x)
         part = None
-        if (self.fuseRope and e0 is not None and e0.pendingFwd and hd == 64 and self.precision == "tf32" and T >= 16):
+        if self.fuseRope and e0 is not None and e0.pendingFwd:
             part = next((p for p in self._pendingFwd if p["eo"] is e0), None)
-            first = next((p["rope"] for p in self._pendingFwd if "rope" in p), None)
-            if part is not None and ("rope" in part or part["outDim"] != H * hd or
-                                     (first is not None and first[2:] != (hd, base, posOffset))):
-                part = None
+            if part is not None and "norm" in part:
+                # a per-head norm waiting to be launched: it normalises and rotates in one pass
+                if "rope" in part or (part["T"], part["H"], part["hd"]) != (T, H, hd):
+                    part = None
+            elif part is not None:
+                # a projection waiting to be launched (64-wide heads, tensor-core mode): its launch writes the rotated values
+                first = next((p["rope"] for p in self._pendingFwd if "rope" in p), None)
+                if ("rope" in part or part["outDim"] != H * hd or hd != 64 or self.precision != "tf32" or T < 16 or
+                        (first is not None and first[2:] != (hd, base, posOffset))):
+                    part = None
         if part is not None:
             self._beginForwardOp(keepPending=True)
             ex = e0

@@ -51,11 +51,15 @@ __device__ __forceinline__ void dw_finish(float* sdw, int d, float* gw, int accu
 // NPL = elements per lane (d <= 32*NPL)
 // With `xb` the row normalised is x + xb, and that sum is also written to `sum` (the residual add that precedes the
 // norm in every block, src/arch/llama.ts:203-208, done in the same pass over the row).
+// With `rope` (per-head norms of 64, 128 or 256 columns, d == 32 * NPL; a row is one head of one token, row = token * H +
+// head) the normalised head is rotated before it is written (the `rope` that follows the q and k norms in
+// src/arch/qwen3.ts:169-172): lane l holds columns l + 32 i, so both members of pair (j, j + d/2) sit in one lane.
 template <int NPL>
 __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(int rows, int d, const float* __restrict__ x,
                                                           const float* __restrict__ xb, float* __restrict__ sum,
                                                           const float* __restrict__ w, float eps,
-                                                          float* __restrict__ y, float* __restrict__ rinv) {
+                                                          float* __restrict__ y, float* __restrict__ rinv,
+                                                          const float2* __restrict__ rope, int H, int period) {
   const int lane = threadIdx.x & 31;
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
@@ -85,7 +89,19 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(int rows, int d, const
     if (lane == 0) rinv[row] = r;
     float* yr = y + (size_t)row * d;
 #pragma unroll
-    for (int i = 0; i < NPL; i++) { int j = lane + 32 * i; if (j < d) yr[j] = v[i] * r * wv[i]; }
+    for (int i = 0; i < NPL; i++) v[i] = v[i] * r * wv[i];
+    if (rope) {
+      const float2* tr = rope + (size_t)((row / H) % period) * (d >> 1);
+#pragma unroll
+      for (int i = 0; i < NPL / 2; i++) {
+        const float2 cs = __ldg(tr + lane + 32 * i);
+        const float a0 = v[i], a1 = v[i + NPL / 2];
+        v[i] = a0 * cs.x - a1 * cs.y;
+        v[i + NPL / 2] = a0 * cs.y + a1 * cs.x;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < NPL; i++) { int j = lane + 32 * i; if (j < d) yr[j] = v[i]; }
   }
 }
 
@@ -268,9 +284,9 @@ gt_status launch_bwd_vec(gt_ctx* ctx, int rows, int d, const float* x, const flo
 
 template <int NPL>
 gt_status launch_fwd(gt_ctx* ctx, int rows, int d, const float* x, const float* xb, float* sum, const float* w, float eps, float* y,
-                     float* rinv) {
+                     float* rinv, const float2* rope = nullptr, int H = 1, int period = 1) {
   int blocks = min(gt_cdiv(rows, 8), ctx->sm_count * 8);
-  rmsnorm_fwd_kernel<NPL><<<blocks, 256, 0, ctx->stream>>>(rows, d, x, xb, sum, w, eps, y, rinv);
+  rmsnorm_fwd_kernel<NPL><<<blocks, 256, 0, ctx->stream>>>(rows, d, x, xb, sum, w, eps, y, rinv, rope, H, period);
   GT_LAUNCHED(ctx, "rmsnorm_fwd_kernel");
   return GT_OK;
 }
@@ -317,6 +333,26 @@ gt_status gt_add_rmsnorm_fwd(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf a, gt_
   GT_REQUIRE(ctx, a && b && w && sum && y && rinv, "gt_add_rmsnorm_fwd: null operand");
   return rmsnorm_fwd_any(ctx, rows, d, gt_ptr<const float>(a), gt_ptr<const float>(b), gt_ptr<float>(sum), gt_ptr<const float>(w), eps,
                          gt_ptr<float>(y), gt_ptr<float>(rinv));
+}
+
+// rmsNormHeads followed by rope (src/arch/qwen3.ts:169-172, src/arch/gemma3.ts:194-197) as one pass over the heads.
+gt_status gt_rmsnorm_heads_rope_fwd(gt_ctx* ctx, int32_t rows, int32_t H, int32_t hd, gt_buf x, gt_buf w, float eps, gt_buf y, gt_buf rinv,
+                                    double base, int32_t pos_offset) {
+  GT_REQUIRE(ctx, rows > 0 && H > 0 && hd > 0 && hd <= 2048 && hd % 2 == 0, "gt_rmsnorm_heads_rope_fwd: rows %d H %d hd %d", rows, H, hd);
+  GT_REQUIRE(ctx, x && w && y && rinv, "gt_rmsnorm_heads_rope_fwd: null operand");
+  const float* px = gt_ptr<const float>(x); const float* pw = gt_ptr<const float>(w);
+  float* py = gt_ptr<float>(y); float* pr = gt_ptr<float>(rinv);
+  const float2* tab = nullptr;
+  int period = 0;
+  gt_status s = gt_rope_table(ctx, rows, hd, base, pos_offset, &tab, &period);
+  if (s) return s;
+  const int n = rows * H;
+  if (hd == 64) return launch_fwd<2>(ctx, n, hd, px, nullptr, nullptr, pw, eps, py, pr, tab, H, period);
+  if (hd == 128) return launch_fwd<4>(ctx, n, hd, px, nullptr, nullptr, pw, eps, py, pr, tab, H, period);
+  if (hd == 256) return launch_fwd<8>(ctx, n, hd, px, nullptr, nullptr, pw, eps, py, pr, tab, H, period);
+  s = rmsnorm_fwd_any(ctx, n, hd, px, nullptr, nullptr, pw, eps, py, pr);     // other head sizes: two passes
+  if (s) return s;
+  return gt_rope_apply(ctx, false, rows, H, hd, base, pos_offset, py, py, 0);
 }
 
 static gt_status rmsnorm_bwd_any(gt_ctx* ctx, int32_t rows, int32_t d, gt_buf x, gt_buf w, gt_buf rinv, gt_buf gy, gt_buf gadd, gt_buf gx,

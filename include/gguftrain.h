@@ -164,6 +164,10 @@ gt_status gt_attention_bwd(gt_ctx* ctx, int32_t rows, int32_t Hq, int32_t Hkv, i
  * gradients with respect to the rotation's inputs (the transposed rotation is applied to the dQ and dK tiles as they
  * are written). Both fall back to the separate launches where the fused kernels do not apply (strict f32, head sizes
  * other than 64 in forward or 256 in backward), with the same results to summation order. */
+/* rope(rmsNormHeads(x, w)) as one pass (src/arch/qwen3.ts:169-172, src/arch/gemma3.ts:194-197 record the two ops one after
+ * the other): x, y:[rows, H*hd], w:[hd], rinv:[rows*H] as gt_rmsnorm_fwd over rows*H heads would write it. */
+gt_status gt_rmsnorm_heads_rope_fwd(gt_ctx* ctx, int32_t rows, int32_t H, int32_t hd, gt_buf x, gt_buf w, float eps, gt_buf y,
+                                    gt_buf rinv, double base, int32_t pos_offset);
 gt_status gt_linear_rope_grouped(gt_ctx* ctx, int32_t ngroups, int32_t rows, int32_t K, gt_buf x, const int32_t* Ns,
                                  const gt_buf* ws, const gt_buf* ys, const int32_t* heads, int32_t hd, double base,
                                  int32_t pos_offset);

@@ -65,6 +65,7 @@ const SYMBOLS = {
   gt_rope_bwd: { parameters: ["pointer", "i32", "i32", "i32", "f64", "i32", "u64", "u64", "i32"], result: "i32" },
   gt_attention_fwd: { parameters: ["pointer", "i32", "i32", "i32", "i32", "i32", "u64", "u64", "u64", "u64", "u64"], result: "i32" },
   gt_attention_bwd: { parameters: ["pointer", "i32", "i32", "i32", "i32", "i32", "u64", "u64", "u64", "u64", "u64", "u64", "u64", "i32", "u64", "i32", "u64", "i32"], result: "i32" },
+  gt_rmsnorm_heads_rope_fwd: { parameters: ["pointer", "i32", "i32", "i32", "u64", "u64", "f32", "u64", "u64", "f64", "i32"], result: "i32" },
   gt_linear_rope_grouped: { parameters: ["pointer", "i32", "i32", "i32", "u64", "buffer", "buffer", "buffer", "buffer", "i32", "f64", "i32"], result: "i32" },
   gt_attention_bwd_rope: { parameters: ["pointer", "i32", "i32", "i32", "i32", "i32", "u64", "u64", "u64", "u64", "u64", "u64", "u64", "i32", "u64", "i32", "u64", "i32", "f64", "i32"], result: "i32" },
   gt_attention_bwd_static: { parameters: ["pointer", "i32", "i32", "i32", "i32", "i32", "u64", "u64", "u64", "u64", "u64", "u64", "u64", "i32", "u64", "i32", "u64", "i32"], result: "i32" },

@@ -456,7 +456,7 @@ def test_projections_of_one_input_are_one_grouped_launch(gpu, oracle):
         assert e <= REL_L2_TC and e > 1e-7, f"relative L2 {e:.3e}"
 
 
-def _attention_block(gpu, oracle, T, B, din, Hq, Hkv, hd, window, fuse, read_q=False):
+def _attention_block(gpu, oracle, T, B, din, Hq, Hkv, hd, window, fuse, read_q=False, head_norm=False):
     """q = rope(linear(x, Wq)), k = rope(linear(x, Wk)), v = linear(x, Wv), a = attention(q, k, v), the attention half
     of a llama block (src/arch/llama.ts:195-201), forward and backward with a fixed upstream gradient. Returns the
     launch counts and every value a caller can observe."""
@@ -466,7 +466,8 @@ def _attention_block(gpu, oracle, T, B, din, Hq, Hkv, hd, window, fuse, read_q=F
     rows = T * max(B, 1)
     x = rand_tensor(rng, [rows, din])
     wq, wk, wv = (rand_tensor(rng, [h * hd, din], 0.1) for h in (Hq, Hkv, Hkv))
-    for t in (x, wq, wk, wv):
+    nq, nk = rand_tensor(rng, [hd], 0.5), rand_tensor(rng, [hd], 0.5)
+    for t in (x, wq, wk, wv, nq, nk):
         t.zeroGrad()
     gpu.fuseRope = fuse
     gpu.install()
@@ -477,15 +478,21 @@ def _attention_block(gpu, oracle, T, B, din, Hq, Hkv, hd, window, fuse, read_q=F
         l0 = gpu.kernelLaunches()
         q0, k0 = ag.linear(x, wq), ag.linear(x, wk)
         v = ag.linear(x, wv)
-        q, k = ag.rope(q0, rows, Hq, hd, 10000.0), ag.rope(k0, rows, Hkv, hd, 10000.0)
+        q1, k1 = q0, k0
+        if head_norm:            # the Qwen3 / Gemma 3 block: per-head norms between the projections and the rotations
+            q1, k1 = ag.rmsNormHeads(q0, nq, rows, Hq, hd, 1e-6), ag.rmsNormHeads(k0, nk, rows, Hkv, hd, 1e-6)
+        q, k = ag.rope(q1, rows, Hq, hd, 10000.0), ag.rope(k1, rows, Hkv, hd, 10000.0)
         a = ag.attention(q, k, v, rows, Hq, Hkv, hd, window)
         fwd = gpu.kernelLaunches() - l0
         g = upstream(oracle, a.size)
         a.grad[:] = g
         gpu.seedGradFromHost(a)
         l1 = gpu.kernelLaunches()
-        a._backward(); k._backward(); q._backward(); v._backward(); k0._backward(); q0._backward()
-        reads = [a, q, k, v] + ([q0] if read_q else [])
+        a._backward(); k._backward(); q._backward()
+        if head_norm:
+            k1._backward(); q1._backward()
+        v._backward(); k0._backward(); q0._backward()
+        reads = [a, q, k, v] + ([q0, q1] if read_q else [])
         gpu.sync(reads)
         bwd = gpu.kernelLaunches() - l1
     finally:
@@ -494,8 +501,10 @@ def _attention_block(gpu, oracle, T, B, din, Hq, Hkv, hd, window, fuse, read_q=F
         gpu.fuseRope = True
     vals = {"a": a.data.copy(), "q": q.data.copy(), "k": k.data.copy(), "v": v.data.copy(), "dx": x.grad.copy(),
             "dWq": wq.grad.copy(), "dWk": wk.grad.copy(), "dWv": wv.grad.copy()}
+    if head_norm:
+        vals["dnq"], vals["dnk"] = nq.grad.copy(), nk.grad.copy()
     if read_q:
-        vals["q0"] = q0.data.copy()
+        vals["q0"], vals["q1"] = q0.data.copy(), q1.data.copy()
     return fwd, bwd, vals
 
 
@@ -520,10 +529,27 @@ def test_rotary_embedding_runs_inside_its_neighbours(gpu, oracle, T, B, din, Hq,
         assert np.isfinite(fused[name]).all() and e <= (1e-6 if name in ("q", "k", "v") else 1e-4), f"{name}: relative L2 {e:.3e}"
 
 
-def test_projection_consumed_rotated_is_still_readable(gpu, oracle):
-    """The unrotated projection is not written when its only reader took it rotated; a later reader (here a sync that
-    asks for it) gets it from a product launched then."""
-    _f, _b, fused = _attention_block(gpu, oracle, 256, 0, 192, 4, 2, 64, 0, True, read_q=True)
-    _f, _b, plain = _attention_block(gpu, oracle, 256, 0, 192, 4, 2, 64, 0, False, read_q=True)
-    assert np.abs(plain["q0"]).max() > 0
-    assert rel_l2(fused["q0"], plain["q0"]) <= 1e-6
+@pytest.mark.parametrize("T,B,din,Hq,Hkv,hd,window", [(200, 2, 256, 4, 2, 128, 0), (128, 2, 128, 2, 1, 256, 96), (192, 0, 192, 4, 2, 64, 0)])
+def test_per_head_norm_and_rotary_embedding_are_one_pass(gpu, oracle, T, B, din, Hq, Hkv, hd, window):
+    """`rope(rmsNormHeads(linear(x, W)))`, the q and k of the Qwen3 and Gemma 3 blocks: the norm waits for its first
+    reader and, when that is the rotation, one pass normalises and rotates; attention's backward delivers dQ and dK to
+    the norms' outputs (head sizes 64 and 128). Against the same block with every op launched."""
+    _attention_block(gpu, oracle, T, B, din, Hq, Hkv, hd, window, False, head_norm=True)
+    f_fwd, f_bwd, fused = _attention_block(gpu, oracle, T, B, din, Hq, Hkv, hd, window, True, head_norm=True)
+    p_fwd, p_bwd, plain = _attention_block(gpu, oracle, T, B, din, Hq, Hkv, hd, window, False, head_norm=True)
+    assert (p_fwd, p_bwd) == (6, 9), (p_fwd, p_bwd)
+    assert f_fwd == 4 and f_bwd == (7 if hd <= 128 else 9), (f_fwd, f_bwd)
+    for name in plain:
+        e = rel_l2(fused[name], plain[name])
+        assert np.isfinite(fused[name]).all() and e <= (1e-6 if name in ("q", "k", "v") else 1e-4), f"{name}: relative L2 {e:.3e}"
+
+
+@pytest.mark.parametrize("head_norm", [False, True])
+def test_tensor_consumed_rotated_is_still_readable(gpu, oracle, head_norm):
+    """The unrotated projection (or per-head norm) is not written when its only reader took it rotated; a later reader
+    (here a sync that asks for it) gets it from a launch made then."""
+    _f, _b, fused = _attention_block(gpu, oracle, 256, 0, 192, 4, 2, 64, 0, True, read_q=True, head_norm=head_norm)
+    _f, _b, plain = _attention_block(gpu, oracle, 256, 0, 192, 4, 2, 64, 0, False, read_q=True, head_norm=head_norm)
+    for name in ("q0", "q1"):
+        assert np.abs(plain[name]).max() > 0
+        assert rel_l2(fused[name], plain[name]) <= 1e-6
