@@ -485,6 +485,8 @@ def run_profile(args):
     T = args.seq
     loss_chunk = args.loss_chunk if args.loss_chunk >= 0 else (32768 if args.config == "qwen3-lora" else 0)
     gpu = requireGPU("the profile", precision=args.precision)
+    if args.no_rope_fusion:
+        gpu.fuseRope = False
     m = buildModel(cfg, 1234)
     params = m.params()
     ids = zipf_tokens(B * T + 1, cfg.vocabSize, 1.1, 99)

@@ -70,6 +70,12 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(int rows, int d, const
     const float* xr = x + (size_t)row * d;
     float v[NPL];
     float ss = 0.f;
+    float2 cs[NPL / 2];
+    if (rope) {   // requested with the row itself, so that the two reads are in flight together
+      const float2* tr = rope + (size_t)((row / H) % period) * (d >> 1);
+#pragma unroll
+      for (int i = 0; i < NPL / 2; i++) cs[i] = __ldg(tr + lane + 32 * i);
+    }
     if (xb) {
       const float* br = xb + (size_t)row * d;
       float* sr = sum + (size_t)row * d;
@@ -91,13 +97,11 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(int rows, int d, const
 #pragma unroll
     for (int i = 0; i < NPL; i++) v[i] = v[i] * r * wv[i];
     if (rope) {
-      const float2* tr = rope + (size_t)((row / H) % period) * (d >> 1);
 #pragma unroll
       for (int i = 0; i < NPL / 2; i++) {
-        const float2 cs = __ldg(tr + lane + 32 * i);
         const float a0 = v[i], a1 = v[i + NPL / 2];
-        v[i] = a0 * cs.x - a1 * cs.y;
-        v[i + NPL / 2] = a0 * cs.y + a1 * cs.x;
+        v[i] = a0 * cs[i].x - a1 * cs[i].y;
+        v[i + NPL / 2] = a0 * cs[i].y + a1 * cs[i].x;
       }
     }
 #pragma unroll
