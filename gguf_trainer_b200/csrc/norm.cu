@@ -109,6 +109,79 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(int rows, int d, const
   }
 }
 
+// The same forward pass with 16-byte accesses (d a multiple of 4, 16-byte aligned operands, d <= 128 * V4): lane l
+// holds the float4s l, l + 32, ... of its row. Every load of the row (and of the row added to it) is issued before
+// anything is stored. With `rope`, pair (c, c + d/2) is rotated after the norm: for d = 256 both members sit in one
+// lane (float4 i and i + 1), for d = 128 and 64 in lanes 16 and 8 apart, fetched by shuffle.
+template <int V4>
+__global__ void __launch_bounds__(256) rmsnorm_fwd_vec_kernel(int rows, int d, const float* __restrict__ x,
+                                                              const float* __restrict__ xb, float* __restrict__ sum,
+                                                              const float* __restrict__ w, float eps,
+                                                              float* __restrict__ y, float* __restrict__ rinv,
+                                                              const float2* __restrict__ rope, int H, int period) {
+  const int lane = threadIdx.x & 31;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const int d4 = d >> 2, h4 = d4 >> 1;   // float4s per row, per half row
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 wv[V4];
+#pragma unroll
+  for (int i = 0; i < V4; i++) { const int j = lane + 32 * i; wv[i] = j < d4 ? __ldg(reinterpret_cast<const float4*>(w) + j) : zero; }
+  for (int row = warp; row < rows; row += nwarps) {
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)row * d);
+    float4 v[V4];
+#pragma unroll
+    for (int i = 0; i < V4; i++) { const int j = lane + 32 * i; v[i] = j < d4 ? __ldg(xr + j) : zero; }
+    float4 cs0 = zero, cs1 = zero;   // (cos, sin) of this lane's four pairs (d <= 256: one float4 per half row and lane)
+    if (rope) {
+      const int jl = lane & (h4 - 1);   // float4 index within the half row (h4 is 8, 16 or 32)
+      const float4* tr = reinterpret_cast<const float4*>(rope + (size_t)((row / H) % period) * (d >> 1)) + 2 * jl;
+      cs0 = __ldg(tr);
+      cs1 = __ldg(tr + 1);
+    }
+    if (xb) {
+      const float4* br = reinterpret_cast<const float4*>(xb + (size_t)row * d);
+      float4 b[V4];
+#pragma unroll
+      for (int i = 0; i < V4; i++) { const int j = lane + 32 * i; b[i] = j < d4 ? __ldg(br + j) : zero; }
+      float4* sr = reinterpret_cast<float4*>(sum + (size_t)row * d);
+#pragma unroll
+      for (int i = 0; i < V4; i++) {
+        const int j = lane + 32 * i;
+        v[i] = make_float4(v[i].x + b[i].x, v[i].y + b[i].y, v[i].z + b[i].z, v[i].w + b[i].w);
+        if (j < d4) sr[j] = v[i];
+      }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < V4; i++) ss = fmaf(v[i].x, v[i].x, fmaf(v[i].y, v[i].y, fmaf(v[i].z, v[i].z, fmaf(v[i].w, v[i].w, ss))));
+    ss = warp_sum(ss);
+    const float r = 1.f / sqrtf(ss / (float)d + eps);
+    if (lane == 0) rinv[row] = r;
+#pragma unroll
+    for (int i = 0; i < V4; i++) v[i] = make_float4(v[i].x * r * wv[i].x, v[i].y * r * wv[i].y, v[i].z * r * wv[i].z, v[i].w * r * wv[i].w);
+    if (rope) {
+      if (V4 == 2 && h4 == 32) {          // d = 256: float4 0 is the first half, float4 1 the second
+        const float4 a0 = v[0], a1 = v[V4 - 1];
+        v[0] = make_float4(a0.x * cs0.x - a1.x * cs0.y, a0.y * cs0.z - a1.y * cs0.w, a0.z * cs1.x - a1.z * cs1.y, a0.w * cs1.z - a1.w * cs1.w);
+        v[V4 - 1] = make_float4(a0.x * cs0.y + a1.x * cs0.x, a0.y * cs0.w + a1.y * cs0.z, a0.z * cs1.y + a1.z * cs1.x, a0.w * cs1.w + a1.w * cs1.z);
+      } else {                            // d = 128 or 64: the other member is in lane ^ h4
+        const float4 own = v[0];
+        float4 oth;
+        oth.x = __shfl_xor_sync(0xffffffffu, own.x, h4); oth.y = __shfl_xor_sync(0xffffffffu, own.y, h4);
+        oth.z = __shfl_xor_sync(0xffffffffu, own.z, h4); oth.w = __shfl_xor_sync(0xffffffffu, own.w, h4);
+        if ((lane & h4) == 0)   // first half: a0 = own, a1 = other
+          v[0] = make_float4(own.x * cs0.x - oth.x * cs0.y, own.y * cs0.z - oth.y * cs0.w, own.z * cs1.x - oth.z * cs1.y, own.w * cs1.z - oth.w * cs1.w);
+        else                    // second half: a0 = other, a1 = own
+          v[0] = make_float4(oth.x * cs0.y + own.x * cs0.x, oth.y * cs0.w + own.y * cs0.z, oth.z * cs1.y + own.z * cs1.x, oth.w * cs1.w + own.w * cs1.z);
+      }
+    }
+    float4* yr = reinterpret_cast<float4*>(y + (size_t)row * d);
+#pragma unroll
+    for (int i = 0; i < V4; i++) { const int j = lane + 32 * i; if (j < d4) yr[j] = v[i]; }
+  }
+}
+
 template <int NPL>
 __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(int rows, int d, const float* __restrict__ x,
                                                           const float* __restrict__ w, const float* __restrict__ rinv,
@@ -294,6 +367,14 @@ gt_status launch_fwd(gt_ctx* ctx, int rows, int d, const float* x, const float* 
   GT_LAUNCHED(ctx, "rmsnorm_fwd_kernel");
   return GT_OK;
 }
+template <int V4>
+gt_status launch_fwd_vec(gt_ctx* ctx, int rows, int d, const float* x, const float* xb, float* sum, const float* w, float eps, float* y,
+                         float* rinv, const float2* rope, int H, int period) {
+  int blocks = min(gt_cdiv(rows, 8), ctx->sm_count * 8);
+  rmsnorm_fwd_vec_kernel<V4><<<blocks, 256, 0, ctx->stream>>>(rows, d, x, xb, sum, w, eps, y, rinv, rope, H, period);
+  GT_LAUNCHED(ctx, "rmsnorm_fwd_vec_kernel");
+  return GT_OK;
+}
 template <int NPL>
 gt_status launch_bwd(gt_ctx* ctx, int rows, int d, const float* x, const float* w, const float* rinv, const float* g,
                      const float* gadd, float* gx, int accum_x, float* gw, int accum_w, bool ordered) {
@@ -315,7 +396,19 @@ gt_status launch_bwd(gt_ctx* ctx, int rows, int d, const float* x, const float* 
 extern "C" {
 
 static gt_status rmsnorm_fwd_any(gt_ctx* ctx, int rows, int d, const float* px, const float* pb, float* ps, const float* pw, float eps,
-                                 float* py, float* pr) {
+                                 float* py, float* pr, const float2* rope = nullptr, int H = 1, int period = 1) {
+  const bool aligned = ((((uintptr_t)px) | ((uintptr_t)pb) | ((uintptr_t)ps) | ((uintptr_t)pw) | ((uintptr_t)py)) & 15) == 0;
+  if ((d & 3) == 0 && d >= 64 && d <= 1024 && aligned && (!rope || d == 64 || d == 128 || d == 256)) {
+    if (d <= 128) return launch_fwd_vec<1>(ctx, rows, d, px, pb, ps, pw, eps, py, pr, rope, H, period);
+    if (d <= 256) return launch_fwd_vec<2>(ctx, rows, d, px, pb, ps, pw, eps, py, pr, rope, H, period);
+    if (d <= 640) return launch_fwd_vec<5>(ctx, rows, d, px, pb, ps, pw, eps, py, pr, rope, H, period);
+    return launch_fwd_vec<8>(ctx, rows, d, px, pb, ps, pw, eps, py, pr, rope, H, period);
+  }
+  if (rope) {   // (unaligned operands) the scalar kernels, which hold both members of a pair in one lane
+    if (d == 64) return launch_fwd<2>(ctx, rows, d, px, pb, ps, pw, eps, py, pr, rope, H, period);
+    if (d == 128) return launch_fwd<4>(ctx, rows, d, px, pb, ps, pw, eps, py, pr, rope, H, period);
+    return launch_fwd<8>(ctx, rows, d, px, pb, ps, pw, eps, py, pr, rope, H, period);
+  }
   if (d <= 64) return launch_fwd<2>(ctx, rows, d, px, pb, ps, pw, eps, py, pr);
   if (d <= 128) return launch_fwd<4>(ctx, rows, d, px, pb, ps, pw, eps, py, pr);
   if (d <= 256) return launch_fwd<8>(ctx, rows, d, px, pb, ps, pw, eps, py, pr);
@@ -351,9 +444,7 @@ gt_status gt_rmsnorm_heads_rope_fwd(gt_ctx* ctx, int32_t rows, int32_t H, int32_
   gt_status s = gt_rope_table(ctx, rows, hd, base, pos_offset, &tab, &period);
   if (s) return s;
   const int n = rows * H;
-  if (hd == 64) return launch_fwd<2>(ctx, n, hd, px, nullptr, nullptr, pw, eps, py, pr, tab, H, period);
-  if (hd == 128) return launch_fwd<4>(ctx, n, hd, px, nullptr, nullptr, pw, eps, py, pr, tab, H, period);
-  if (hd == 256) return launch_fwd<8>(ctx, n, hd, px, nullptr, nullptr, pw, eps, py, pr, tab, H, period);
+  if (hd == 64 || hd == 128 || hd == 256) return rmsnorm_fwd_any(ctx, n, hd, px, nullptr, nullptr, pw, eps, py, pr, tab, H, period);
   s = rmsnorm_fwd_any(ctx, n, hd, px, nullptr, nullptr, pw, eps, py, pr);     // other head sizes: two passes
   if (s) return s;
   return gt_rope_apply(ctx, false, rows, H, hd, base, pos_offset, py, py, 0);
