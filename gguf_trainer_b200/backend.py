@@ -316,7 +316,7 @@ class CudaBackend:
     def _read(self, addr: int, out: np.ndarray):
         assert out.flags["C_CONTIGUOUS"]
         if not self._capturing:
-            self._flushAllDx()          # whatever is read must not be missing a launch that was put off
+            self._flushAllDx("keep")    # whatever is read must not be missing a launch that was put off
         self._check(self.lib.gt_read(self.ctx, addr, out.ctypes.data, out.nbytes))
         self._readback += out.nbytes
 
@@ -404,16 +404,26 @@ class CudaBackend:
     # [T, hidden] buffer per residual connection. Here an input whose gradient has not been written yet only notes the
     # upstream address (`copyFrom`). Readers of that gradient read the upstream buffer in place, and the one writer
     # that follows in a transformer block, the norm's backward, adds its term on top of it while writing the real
-    # buffer (gt_rmsnorm_bwd_add). Any other writer, and every point where buffers may be recycled, makes the copy.
+    # buffer (gt_rmsnorm_bwd_add). Any other writer makes the copy, and so does every point where the upstream buffer
+    # may be recycled while the entry lives on (a region's end, a reclaim). The gradient of an op's OUTPUT (the
+    # projection on the other side of the residual connection) is only ever read by that op's backward, in place: where
+    # gradients are handed to someone outside the ops (an optimizer, an exchange, a sync) only parameters matter, so the
+    # copy into a transient's gradient is not made there (60 copies of [T, hidden] per step of a 30-layer model).
     def _materializeCopy(self, e: _Entry):
         self._check(self.lib.gt_copy(self.ctx, e.grad, e.copyFrom, e.bytes))
         e.copyFrom = 0
         e.gradLive = True
         self._pendingCopy.pop(id(e), None)
 
-    def _flushAllCopies(self):
+    def _flushAllCopies(self, transients: str = "copy"):
+        """`transients`: what to do with notes on gradients of op outputs: "copy" (make them), "keep" (leave them
+        noted: nothing is being recycled) or "drop" (their entries are about to be recycled with the upstream buffers)."""
         for e in list(self._pendingCopy.values()):
-            self._materializeCopy(e)
+            if e.external or transients == "copy":
+                self._materializeCopy(e)
+            elif transients == "drop":
+                e.copyFrom = 0
+                self._pendingCopy.pop(id(e), None)
 
     def _flushDx(self, e: _Entry):
         if e.copyFrom:
@@ -504,11 +514,11 @@ class CudaBackend:
         e.lazy = None
         launch()
 
-    def _flushAllDx(self):
+    def _flushAllDx(self, transients: str = "copy"):
         self._flushFwd()
         for e in list(self._pendingDx.values()):
             self._flushDx(e)
-        self._flushAllCopies()
+        self._flushAllCopies(transients)
         self._flushDw()
 
     # The weight gradient of `linear` is dW (+)= dY^T.X: a small output (out x in) contracted over every row. Each has
@@ -548,7 +558,7 @@ class CudaBackend:
     def flushDeferred(self):
         """Launch everything whose launch was put off (merged input gradients, grouped weight gradients, copies):
         called by whoever is about to use gradients outside the ops, e.g. an optimizer step or a gradient exchange."""
-        self._flushAllDx()
+        self._flushAllDx("keep")
 
     def _gradTarget(self, t: Tensor, e: _Entry):
         """(grad address or 0, accum flag) for a backward kernel about to write into t's gradient."""
@@ -610,7 +620,7 @@ class CudaBackend:
         if self._capturing:
             raise _lib.GtError(4, "sync() inside a graph capture")
         self._readback = 0
-        self._flushAllDx()
+        self._flushAllDx("drop")
         self._flushPendingActs(only=list(reads))
         self._pendingAct.clear()
         self._pendingAdd.clear()
@@ -855,7 +865,7 @@ class CudaBackend:
         the host between two segments. Returns the number of segments closed so far."""
         if not self._capturing:
             raise _lib.GtError(4, "cutCapture: not capturing")
-        self._flushAllDx()
+        self._flushAllDx("keep")
         h = C.c_uint64()
         self._check(self.lib.gt_graph_end(self.ctx, C.byref(h)))
         self._captureSegments.append(int(h.value))
@@ -864,7 +874,7 @@ class CudaBackend:
 
     def endCapture(self, outputs: Optional[Dict[str, Tensor]] = None) -> CapturedGraph:
         h = C.c_uint64()
-        self._flushAllDx()
+        self._flushAllDx("drop")
         self._capturing = False
         self._check(self.lib.gt_graph_end(self.ctx, C.byref(h)))
         owned = self._transients[self._captureMark:] + self._regionFree
