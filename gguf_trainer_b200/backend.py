@@ -969,14 +969,22 @@ class CudaBackend:
             go = self._gradSource(eo)
             wantDx = bool(ex.grad) and not (ex.external and not x.requiresGrad)
             self._check(self.lib.gt_gemm_scaled(self.ctx, kNN, 0, T, r, outDim, go, eb.data, dt, s))   # dt = scale·(g·B)
+            # dB = gᵀ·ts and dA = dtᵀ·x: thin outputs contracted over every row, bound by reading g and x; the fourteen of a
+            # layer go out as two grouped launches (_deferDw) instead of one launch each
             if b.requiresGrad:
                 gb, ab = self._gradTarget(b, eb)
                 if gb:
-                    self._gemm("TN", ab, outDim, r, T, go, ts, gb)
+                    if self.groupWeightGradients:
+                        self._deferDw(eb, gb, ab, T, outDim, r, go, ts)
+                    else:
+                        self._gemm("TN", ab, outDim, r, T, go, ts, gb)
             if a.requiresGrad:
                 ga, aa = self._gradTarget(a, ea)
                 if ga:
-                    self._gemm("TN", aa, r, inDim, T, dt, ex.data, ga)
+                    if self.groupWeightGradients:
+                        self._deferDw(ea, ga, aa, T, r, inDim, dt, ex.data)
+                    else:
+                        self._gemm("TN", aa, r, inDim, T, dt, ex.data, ga)
             if wantDx:      # g·W + dt·A: two more K ranges of x's input-gradient product
                 self._deferDx(ex, T, inDim, go, ew.data, outDim)
                 self._deferDx(ex, T, inDim, dt, ea.data, r)
