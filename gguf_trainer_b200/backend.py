@@ -447,7 +447,7 @@ class CudaBackend:
     # up, when a gated unit consumes both, as one launch that also applies the unit (gt_glu_linear_fwd, see _gatedUnit).
     def _deferLinear(self, ex: _Entry, ew: _Entry, eo: _Entry, T: int, inDim: int, outDim: int):
         first = self._pendingFwd[0] if self._pendingFwd else None
-        if first is not None and ("norm" in first or first["ex"] is not ex or len(self._pendingFwd) == 8):
+        if first is not None and ("norm" in first or "lora" in first or first["ex"] is not ex or len(self._pendingFwd) == 8):
             self._flushFwd()
         self._pendingFwd.append(dict(ex=ex, ew=ew, eo=eo, T=T, inDim=inDim, outDim=outDim))
         eo.pendingFwd = True
@@ -468,6 +468,22 @@ class CudaBackend:
         self._pendingFwd = []
         for p in parts:
             p["eo"].pendingFwd = False
+        if "lora" in parts[0]:
+            n = len(parts)
+            p0 = parts[0]
+            T, inDim, r, s = p0["T"], p0["inDim"], p0["r"], p0["s"]
+            if n == 1:
+                self._check(self.lib.gt_gemm_scaled(self.ctx, _KIND["NT"], 0, T, r, inDim, p0["ex"].data, p0["ea"].data, p0["ts"], s))
+            else:
+                Ms, Ns = (C.c_int32 * n)(*([T] * n)), (C.c_int32 * n)(*([r] * n))
+                As = (C.c_uint64 * n)(*([p0["ex"].data] * n))
+                Bs = (C.c_uint64 * n)(*[p["ea"].data for p in parts])
+                Cs = (C.c_uint64 * n)(*[p["ts"] for p in parts])
+                acc = (C.c_int32 * n)(*([0] * n))
+                self._check(self.lib.gt_gemm_grouped_scaled(self.ctx, _KIND["NT"], n, Ms, Ns, inDim, As, Bs, Cs, acc, s))
+            for p in parts:
+                self._gemm2("NT", 0, T, p["outDim"], inDim, p["ex"].data, p["ew"].data, r, p["ts"], p["eb"].data, p["eo"].data)
+            return
         if "norm" in parts[0]:
             for p in parts:
                 T, H, hd = p["T"], p["H"], p["hd"]
@@ -951,7 +967,7 @@ class CudaBackend:
         once and not read back. (scale·t)·Bᵀ equals scale·(t·Bᵀ) up to rounding, exactly when scale is a power of two, e.g. the
         usual alpha/r = 2.) Gradients: dx += g·W + (scale·(g·B))·A, dB += gᵀ·(scale·t), dA += (scale·(g·B))ᵀ·x,
         and dW += gᵀ·x when the base weight is not frozen."""
-        self._beginForwardOp()
+        self._beginForwardOp(keepPending=self.groupForward)
         T, inDim = x.shape
         outDim, r = w.shape[0], a.shape[0]
         ex, ew, ea, eb = self._entryFor(x), self._entryFor(w), self._entryFor(a), self._entryFor(b)
@@ -960,9 +976,19 @@ class CudaBackend:
         ts, dt = self._acquireRecycled(small), self._acquireRecycled(small)
         s = float(scale)
         kNT, kNN = _KIND["NT"], _KIND["NN"]
-        # ts = scale·(x·Aᵀ): the factor rides on the product's epilogue (gt_gemm_scaled), no pass of its own
-        self._check(self.lib.gt_gemm_scaled(self.ctx, kNT, 0, T, r, inDim, ex.data, ea.data, ts, s))
-        self._gemm2("NT", 0, T, outDim, inDim, ex.data, ew.data, r, ts, eb.data, eo.data)
+        if self.groupForward:
+            # noted, not launched: projections of the same input (q, k, v; gate, up) form their thin products
+            # ts = scale·(x·Aᵀ) in one grouped launch, which reads x once (_flushFwd)
+            first = self._pendingFwd[0] if self._pendingFwd else None
+            if first is not None and ("lora" not in first or first["ex"] is not ex or first["r"] != r or first["s"] != s
+                                      or len(self._pendingFwd) == 8):
+                self._flushFwd()
+            self._pendingFwd.append(dict(lora=True, ex=ex, ew=ew, ea=ea, eb=eb, eo=eo, ts=ts, T=T, inDim=inDim, outDim=outDim, r=r, s=s))
+            eo.pendingFwd = True
+        else:
+            # ts = scale·(x·Aᵀ): the factor rides on the product's epilogue (gt_gemm_scaled), no pass of its own
+            self._check(self.lib.gt_gemm_scaled(self.ctx, kNT, 0, T, r, inDim, ex.data, ea.data, ts, s))
+            self._gemm2("NT", 0, T, outDim, inDim, ex.data, ew.data, r, ts, eb.data, eo.data)
 
         def _bw():
             self._ensureBackwardBegun()
@@ -1138,7 +1164,7 @@ class CudaBackend:
         pend = self._pendingFwd
         if (eu is not None and len(pend) == 2 and ex.pendingFwd and eu.pendingFwd and ex is not eu
                 and {id(pend[0]["eo"]), id(pend[1]["eo"])} == {id(ex), id(eu)} and pend[0]["outDim"] == pend[1]["outDim"]
-                and "rope" not in pend[0] and "rope" not in pend[1]):
+                and "rope" not in pend[0] and "rope" not in pend[1] and "lora" not in pend[0]):
             # gate and up are the two projections waiting to be launched: one launch writes both and the gated unit
             pg, pu = (pend[0], pend[1]) if pend[0]["eo"] is ex else (pend[1], pend[0])
             self._pendingFwd = []
@@ -1277,7 +1303,7 @@ class CudaBackend:
             elif part is not None:
                 # a projection waiting to be launched (64-wide heads, tensor-core mode): its launch writes the rotated values
                 first = next((p["rope"] for p in self._pendingFwd if "rope" in p), None)
-                if ("rope" in part or part["outDim"] != H * hd or hd != 64 or self.precision != "tf32" or T < 16 or
+                if ("rope" in part or "lora" in part or part["outDim"] != H * hd or hd != 64 or self.precision != "tf32" or T < 16 or
                         (first is not None and first[2:] != (hd, base, posOffset))):
                     part = None
         if part is not None:

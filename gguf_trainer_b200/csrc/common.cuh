@@ -107,7 +107,7 @@ gt_status gt_gemm_tc_multi(gt_ctx* ctx, int kind, int accum, int M, int N, int n
 // gt_rope_table gives
 gt_status gt_gemm_tc_grouped(gt_ctx* ctx, int kind, int ngroups, const int* Ms, const int* Ns, int K, const float* const* as,
                              const float* const* bs, float* const* cs, const int* accums, const int* ropes, const float2* rope_tab,
-                             int rope_period, bool* handled);
+                             int rope_period, float alpha, bool* handled);
 gt_status gt_rope_table(gt_ctx* ctx, int rows, int hd, double base, int pos_offset, const float2** tab, int* period);
 gt_status gt_rope_apply(gt_ctx* ctx, bool bwd, int rows, int H, int hd, double base, int pos_offset, const float* in, float* out, int accum);
 gt_status gt_glu_linear_tc(gt_ctx* ctx, int op, int rows, int ffn, int in, const float* x, const float* wg, const float* wu, float* gate,

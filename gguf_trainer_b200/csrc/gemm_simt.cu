@@ -184,9 +184,9 @@ extern "C" gt_status gt_gemm_multi(gt_ctx* ctx, int32_t kind, int32_t accum, int
 }
 
 // ngroups products of one layout and one depth K, each with its own operands, extents and accumulate flag: one launch
-// on the tensor-core path, one product after the other otherwise.
-extern "C" gt_status gt_gemm_grouped(gt_ctx* ctx, int32_t kind, int32_t ngroups, const int32_t* Ms, const int32_t* Ns, int32_t K,
-                                     const gt_buf* as, const gt_buf* bs, const gt_buf* cs, const int32_t* accums) {
+// on the tensor-core path, one product after the other otherwise. alpha multiplies every product.
+extern "C" gt_status gt_gemm_grouped_scaled(gt_ctx* ctx, int32_t kind, int32_t ngroups, const int32_t* Ms, const int32_t* Ns, int32_t K,
+                                            const gt_buf* as, const gt_buf* bs, const gt_buf* cs, const int32_t* accums, float alpha) {
   GT_REQUIRE(ctx, ngroups >= 1 && ngroups <= 8 && K > 0 && Ms && Ns && as && bs && cs && accums, "gt_gemm_grouped: %d products (1..8), K %d", ngroups, K);
   const float* pa[8];
   const float* pb[8];
@@ -199,14 +199,19 @@ extern "C" gt_status gt_gemm_grouped(gt_ctx* ctx, int32_t kind, int32_t ngroups,
   }
   if (ctx->precision != GT_PREC_FP32 && ngroups > 1) {
     bool handled = false;
-    gt_status s = gt_gemm_tc_grouped(ctx, kind, ngroups, m, n, K, pa, pb, pc, acc, nullptr, nullptr, 0, &handled);
+    gt_status s = gt_gemm_tc_grouped(ctx, kind, ngroups, m, n, K, pa, pb, pc, acc, nullptr, nullptr, 0, alpha, &handled);
     if (s != GT_OK || handled) return s;
   }
   for (int g = 0; g < ngroups; g++) {
-    gt_status s = gt_gemm(ctx, kind, acc[g], m[g], n[g], K, as[g], bs[g], cs[g]);
+    gt_status s = gt_gemm_scaled(ctx, kind, acc[g], m[g], n[g], K, as[g], bs[g], cs[g], alpha);
     if (s) return s;
   }
   return GT_OK;
+}
+
+extern "C" gt_status gt_gemm_grouped(gt_ctx* ctx, int32_t kind, int32_t ngroups, const int32_t* Ms, const int32_t* Ns, int32_t K,
+                                     const gt_buf* as, const gt_buf* bs, const gt_buf* cs, const int32_t* accums) {
+  return gt_gemm_grouped_scaled(ctx, kind, ngroups, Ms, Ns, K, as, bs, cs, accums, 1.f);
 }
 
 // Projections y_g = x.W_g^T of one input launched together, the rotary embedding applied to the outputs that take one
@@ -237,7 +242,7 @@ extern "C" gt_status gt_linear_rope_grouped(gt_ctx* ctx, int32_t ngroups, int32_
   }
   if (ctx->precision != GT_PREC_FP32 && ngroups > 1 && (!any || hd == 64)) {
     bool handled = false;
-    gt_status s = gt_gemm_tc_grouped(ctx, GT_GEMM_NT, ngroups, m, n, K, pa, pb, pc, acc, rp, tab, period, &handled);
+    gt_status s = gt_gemm_tc_grouped(ctx, GT_GEMM_NT, ngroups, m, n, K, pa, pb, pc, acc, rp, tab, period, 1.f, &handled);
     if (s != GT_OK || handled) return s;
   }
   for (int g = 0; g < ngroups; g++) {

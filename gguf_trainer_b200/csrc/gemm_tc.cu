@@ -856,7 +856,7 @@ static gt_status gemm_tc_dispatch(gt_ctx* ctx, int kind, int accum, int M, int N
 // are so few per product that each would need its own split-K launch with its own tail; together they fill the SMs.
 static gt_status gemm_tc_grouped(gt_ctx* ctx, int kind, int ngroups, const int* Ms, const int* Ns, int K, const float* const* as,
                                  const float* const* bs, float* const* cs, const int* accums, const int* ropes, const float2* rope_tab,
-                                 int rope_period, bool* handled) {
+                                 int rope_period, float alpha, bool* handled) {
   *handled = false;
   if (ngroups < 2 || ngroups > MAX_PARTS || K < 16) return GT_OK;
   bool any_rope = false;
@@ -921,11 +921,11 @@ static gt_status gemm_tc_grouped(gt_ctx* ctx, int kind, int ngroups, const int* 
       if (!accums[g]) GT_CUDA(ctx, cudaMemsetAsync(cs[g], 0, sizeof(float) * (size_t)Ms[g] * Ns[g], ctx->stream));
   gt_status s;
   if (any_rope)
-    s = mt == 1 ? launch<true, true, 192, 1, EPI_ROPE>(ctx, maps, units, 1, cs[0], Ms[0], Ns[0], accums[0], ksplit, 1, TRUNC_COMP)
-                : launch<true, true, 192, 2, EPI_ROPE>(ctx, maps, units, 1, cs[0], Ms[0], Ns[0], accums[0], ksplit, 1, TRUNC_COMP);
+    s = mt == 1 ? launch<true, true, 192, 1, EPI_ROPE>(ctx, maps, units, 1, cs[0], Ms[0], Ns[0], accums[0], ksplit, 1, alpha * TRUNC_COMP)
+                : launch<true, true, 192, 2, EPI_ROPE>(ctx, maps, units, 1, cs[0], Ms[0], Ns[0], accums[0], ksplit, 1, alpha * TRUNC_COMP);
   else
-    s = mt == 1 ? launch_kind<192, 1>(ctx, kind, maps, units, 1, cs[0], Ms[0], Ns[0], accums[0], ksplit, 1, TRUNC_COMP)
-                : launch_kind<192, 2>(ctx, kind, maps, units, 1, cs[0], Ms[0], Ns[0], accums[0], ksplit, 1, TRUNC_COMP);
+    s = mt == 1 ? launch_kind<192, 1>(ctx, kind, maps, units, 1, cs[0], Ms[0], Ns[0], accums[0], ksplit, 1, alpha * TRUNC_COMP)
+                : launch_kind<192, 2>(ctx, kind, maps, units, 1, cs[0], Ms[0], Ns[0], accums[0], ksplit, 1, alpha * TRUNC_COMP);
   if (s) return s;
   *handled = true;
   return GT_OK;
@@ -968,8 +968,8 @@ gt_status gt_glu_linear_tc(gt_ctx* ctx, int op, int rows, int ffn, int in, const
 
 gt_status gt_gemm_tc_grouped(gt_ctx* ctx, int kind, int ngroups, const int* Ms, const int* Ns, int K, const float* const* as,
                              const float* const* bs, float* const* cs, const int* accums, const int* ropes, const float2* rope_tab,
-                             int rope_period, bool* handled) {
-  return gemm_tc_grouped(ctx, kind, ngroups, Ms, Ns, K, as, bs, cs, accums, ropes, rope_tab, rope_period, handled);
+                             int rope_period, float alpha, bool* handled) {
+  return gemm_tc_grouped(ctx, kind, ngroups, Ms, Ns, K, as, bs, cs, accums, ropes, rope_tab, rope_period, alpha, handled);
 }
 
 gt_status gt_gemm_tc_batched(gt_ctx* ctx, int kind, int accum, int M, int N, int K, const float* a, const float* b, float* c, int batch,

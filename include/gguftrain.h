@@ -102,6 +102,10 @@ gt_status gt_gemm_multi(gt_ctx* ctx, int32_t kind, int32_t accum, int32_t M, int
  * their tiles share the SMs and one split-K factor instead of each paying a launch, a clear and a last wave. */
 gt_status gt_gemm_grouped(gt_ctx* ctx, int32_t kind, int32_t ngroups, const int32_t* Ms, const int32_t* Ns, int32_t K,
                           const gt_buf* as, const gt_buf* bs, const gt_buf* cs, const int32_t* accums);
+/* The same with a factor applied to every product as it is written (the thin products x.A^T of the adapters of
+ * projections that share an input, src/model/autograd.ts:311-319, carry the adapter scale this way). */
+gt_status gt_gemm_grouped_scaled(gt_ctx* ctx, int32_t kind, int32_t ngroups, const int32_t* Ms, const int32_t* Ns, int32_t K,
+                                 const gt_buf* as, const gt_buf* bs, const gt_buf* cs, const int32_t* accums, float alpha);
 /* add/mul/silu/gelu/scale (webgpu.ts:905-1078, srcElementwise wgsl.ts:199-209) */
 gt_status gt_ew_fwd(gt_ctx* ctx, int32_t op, uint64_t n, gt_buf a, gt_buf b, float c, gt_buf out);
 gt_status gt_ew_bwd(gt_ctx* ctx, int32_t op, uint64_t n, gt_buf a, gt_buf b, float c, gt_buf gout,

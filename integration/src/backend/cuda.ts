@@ -48,6 +48,7 @@ const SYMBOLS = {
   gt_gemm2: { parameters: ["pointer", "i32", "i32", "i32", "i32", "i32", "u64", "u64", "i32", "u64", "u64", "u64"], result: "i32" },
   gt_gemm_multi: { parameters: ["pointer", "i32", "i32", "i32", "i32", "i32", "buffer", "buffer", "buffer", "u64"], result: "i32" },
   gt_gemm_grouped: { parameters: ["pointer", "i32", "i32", "buffer", "buffer", "i32", "buffer", "buffer", "buffer", "buffer"], result: "i32" },
+  gt_gemm_grouped_scaled: { parameters: ["pointer", "i32", "i32", "buffer", "buffer", "i32", "buffer", "buffer", "buffer", "buffer", "f32"], result: "i32" },
   gt_ew_fwd: { parameters: ["pointer", "i32", "u64", "u64", "u64", "f32", "u64"], result: "i32" },
   gt_ew_bwd: { parameters: ["pointer", "i32", "u64", "u64", "u64", "f32", "u64", "u64", "i32", "u64", "i32"], result: "i32" },
   gt_glu_fwd: { parameters: ["pointer", "i32", "u64", "u64", "u64", "u64"], result: "i32" },
