@@ -811,7 +811,9 @@ export class MuonCuda {
 //   device-resident corpus: gt_tokens_max once at upload, then gt_gather_windows as the first recorded call of the step;
 //   data parallel: gt_dp_unique_id, gt_dp_init, gt_dp_allreduce_start per gradient bucket, gt_dp_wait (or gt_dp_wait_host
 //     with a limit) before the optimizer, gt_dp_reserve_sms, gt_muon_set_sharded, gt_dp_destroy;
-//   adapters: gt_gemm_scaled, gt_gemm2 / gt_gemm_multi (the adapter-carrying projection as one product);
-//   fused kernels of the launch-deferring mirror: gt_glu_fwd / gt_glu_bwd, gt_add_rmsnorm_fwd, gt_rmsnorm_bwd_add;
+//   adapters: gt_gemm_scaled, gt_gemm_grouped_scaled, gt_gemm2 / gt_gemm_multi (the adapter-carrying projection as one product);
+//   fused kernels of the launch-deferring mirror: gt_glu_fwd / gt_glu_bwd, gt_glu_linear_fwd, gt_add_rmsnorm_fwd,
+//     gt_rmsnorm_bwd_add, gt_gemm_grouped (projections of one input; the weight gradients of a layer), gt_linear_rope_grouped,
+//     gt_rmsnorm_heads_rope_fwd and gt_attention_bwd_rope (the rotary embedding applied by its neighbours);
 //   gt_newton_schulz (newtonSchulzGpu, src/backend/muon-gpu.ts:258-282), gt_attention_bwd_static, gt_selftest_bounded_wait.
 // gguf_trainer_b200/train.py (CudaStep, DataParallel), ingest.py and lora.py show each sequence of calls.
