@@ -819,6 +819,8 @@ class CudaBackend:
     # ------------------------------------------------------------------ raw buffers (optimizers, checkpoints)
     def buffersFor(self, t: Tensor):
         e = self._entryFor(t)
+        if e.copyFrom:                  # the caller is about to look at the gradient buffer itself
+            self._materializeCopy(e)
         return {"data": e.data, "grad": e.grad}
 
     def keepGradOnDevice(self, t: Tensor):
