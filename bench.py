@@ -599,6 +599,17 @@ def run_micro(args):
         cases = [("ffn entry, one launch (gate, up, gated unit)", lambda: lib.gt_glu_linear_fwd(ctx, 2, rows, f, h, x, wg, wu, gate, up, hid), fl_f),
                  ("ffn entry, three launches", fwd_sep, fl_f)]
         unit, peak = "TFLOP/s", pk["tflops_sustained"]
+    elif name == "norm":
+        # the HBM-bound passes around a residual connection at the benchmark shape, in bytes moved per second
+        a, b2, sm, y, g, gx = buf(rows * h), buf(rows * h), buf(rows * h, False), buf(rows * h, False), buf(rows * h), buf(rows * h, False)
+        w, rinv, gw = buf(h), buf(rows, False), buf(h, False)
+        nb = rows * h * 4
+        gpu._check(lib.gt_rmsnorm_fwd(ctx, rows, h, a, w, 1e-5, y, rinv))
+        cases = [("rmsnorm forward (read x, write y)", lambda: lib.gt_rmsnorm_fwd(ctx, rows, h, a, w, 1e-5, y, rinv), 2 * nb),
+                 ("residual add + rmsnorm forward (read a, b; write sum, y)", lambda: lib.gt_add_rmsnorm_fwd(ctx, rows, h, a, b2, w, 1e-5, sm, y, rinv), 4 * nb),
+                 ("rmsnorm backward on top of the residual gradient (read x, g, upstream; write dx; dw)",
+                  lambda: lib.gt_rmsnorm_bwd_add(ctx, rows, h, a, w, rinv, g, b2, gx, gw, 0), 4 * nb)]
+        unit, peak = "TB/s", pk["hbm_gbs"] / 1e3
     elif name == "gemm":
         cases = []
         for out, inn in [(q, h), (kv, h), (f, h), (h, f)]:
@@ -660,7 +671,7 @@ def main():
     ap.add_argument("--no-peak", action="store_true", help="skip the torch.matmul TF32 peak and comparator")
     ap.add_argument("--recompute", action="store_true")
     ap.add_argument("--profile", action="store_true", help="per-entry-point GPU time of one eager step")
-    ap.add_argument("--micro", default="", help="time one op of the step instead: attention | gemm | bwd-gemm | ffn | qkv")
+    ap.add_argument("--micro", default="", help="time one op of the step instead: attention | gemm | bwd-gemm | ffn | qkv | norm")
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--window", type=int, default=0)
     ap.add_argument("--layers-per-bucket", type=int, default=6, help="data parallel: layers per gradient all-reduce bucket")
