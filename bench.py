@@ -376,12 +376,20 @@ def run_ours(args):
         gpu.recordEvent(0)
         loss = None
         nxt = batch(first)
+        pending = None
         for i in range(steps):
             one_step(first + i, resident, nxt)
             if i + 1 < steps:
                 nxt = batch(first + i + 1)  # the next batch is drawn on the host while this step runs on the device
             if not resident:
-                loss = step.losses()      # device -> host read of the step's result, every step
+                # device -> host read of every step's result: started now, collected after the next step has been
+                # enqueued, so the device does not wait for the host between steps
+                ticket = step.lossesBegin()
+                if pending is not None:
+                    loss = step.lossesEnd(pending)
+                pending = ticket
+        if pending is not None:
+            loss = step.lossesEnd(pending)
         gpu.recordEvent(1)
         ms = gpu.elapsedMs(0, 1)
         barrier()

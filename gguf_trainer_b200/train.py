@@ -318,6 +318,23 @@ class CudaStep:
         self.dp.start(base + s * 4, c)
         self.dp.wait()
 
+    def lossesBegin(self) -> int:
+        """Start reading the last run's losses without waiting for them: the copy is queued behind everything enqueued
+        so far and lands in pinned memory while the host goes on to enqueue the next step (whose loss kernel waits, on
+        the device, for this copy). Returns a ticket for `lossesEnd`. A loop that reads each step's loss after it has
+        enqueued the next step never leaves the device idle between steps."""
+        gpu = self.gpu
+        e = gpu._entries[self.lossTensor]
+        ticket = gpu.readAsync(e.data, (1 + self.batch) * 4)
+        gpu.readFence()
+        return ticket
+
+    def lossesEnd(self, ticket: int) -> np.ndarray:
+        """[mean over sequences, per-sequence...] of the run `ticket` was taken after (blocks until that copy landed)."""
+        out = np.empty(1 + self.batch, np.float32)
+        self.gpu.readFinish(ticket, out)
+        return out
+
     def losses(self) -> np.ndarray:
         """[mean over sequences, per-sequence...] of the last run (blocks)."""
         gpu = self.gpu

@@ -122,3 +122,35 @@ def test_step_fed_by_window_starts_equals_step_fed_by_arrays(gpu, oracle, captur
     if capture:
         with pytest.raises(ValueError, match="out of range"):
             step.runWindows([0, 1, 476])
+
+
+@pytest.mark.parametrize("capture", [False, True])
+def test_losses_read_one_step_late_are_the_steps_own(gpu, oracle, capture):
+    """`lossesBegin` after a step and `lossesEnd` after the NEXT step has been enqueued (the loop that keeps the device
+    busy between steps) returns the first step's losses, not the second's: the copy is ordered behind the first step and
+    the second step's loss kernel waits for it."""
+    cfg = ModelConfig("qwen3", 300, 32, 2, 4, 2, 8, 64, 1_000_000.0, 1e-6)
+    B, T = 3, 24
+    rng = np.random.default_rng(11)
+    tokens = rng.integers(0, cfg.vocabSize, 500)
+    m = buildModel(cfg, 9)
+    for p in m.params():
+        gpu.keepGradOnDevice(p)
+    step = CudaStep(m, gpu, B, T, capture=capture)
+    batches = [host_windows(tokens, None, starts, T) for starts in ([5, 100, 475], [0, 17, 300], [9, 200, 31])]
+    blocking = []
+    for ids, tg in batches:
+        step.run(ids, tg)
+        blocking.append(step.losses().copy())
+    late, pending = [], None
+    for ids, tg in batches:
+        step.run(ids, tg)
+        ticket = step.lossesBegin()
+        if pending is not None:
+            late.append(step.lossesEnd(pending))
+        pending = ticket
+    late.append(step.lossesEnd(pending))
+    gpu.sync([])
+    assert not np.array_equal(blocking[0], blocking[1])
+    for a, b in zip(blocking, late):
+        assert np.array_equal(a, b)
