@@ -1,0 +1,212 @@
+"""The host side (`autograd.py` tape + `backend.py` bookkeeping) driven on a CPU-only machine: `CudaBackend` talks to a
+numpy stand-in for the C ABI (`tests/fake_cabi.py`) and whole small models are held to the CPU oracle, once with every
+launch-merging decision of the backend switched on and once with every op launched as recorded. What this pins down
+without a GPU: which entry points the backend calls and how often, the accumulate flags and addresses it passes (a
+wrong one shows as a wrong gradient, an unwritten buffer reads as NaN), the projections and norms it leaves unwritten
+until asked, and that recompute regions replay through the same decisions.
+
+The shape of the whole-model check follows the reference's parity case (tests/gpu-parity.ts:333-392), as the GPU depth
+suite does; the stand-in computes in f64 and stores f32 like the oracle, so the bound is the strict one (1e-5)."""
+import numpy as np
+import pytest
+
+import fake_cabi
+from depth_cases import run_case
+from gguf_trainer_b200.arch import ModelConfig
+
+L = 2
+CONFIGS = {
+    "llama": (ModelConfig("llama", 96, 128, L, 2, 1, 64, 192, 10_000.0, 1e-5), 64),
+    "qwen3": (ModelConfig("qwen3", 96, 128, L, 2, 1, 64, 192, 1_000_000.0, 1e-6), 64),
+    "gemma3": (ModelConfig("gemma3", 96, 128, 3, 2, 1, 64, 192, 1_000_000.0, 1e-6, ropeBaseLocal=10_000.0, slidingWindow=8,
+                           swaPattern=3), 64),
+}
+FLAGS = ("mergeInputGradients", "fuseResidualNorm", "groupWeightGradients", "groupForward", "fuseGatedUnits", "fuseRope", "fuseLora")
+
+
+@pytest.fixture
+def dev(monkeypatch):
+    fake = fake_cabi.install(monkeypatch)
+    from gguf_trainer_b200.backend import CudaBackend
+    gpu = CudaBackend(0, "tf32")
+    yield gpu, fake
+    gpu.destroy()
+
+
+def check(res, what, bound=1e-5):
+    got, ref = res["loss"]
+    assert res["finite"], f"{what}: a gradient is not finite (something read a buffer nobody wrote)"
+    assert abs(got - ref) <= bound * abs(ref), f"{what}: loss {got} vs {ref}"
+    for l, e in enumerate(res["layers"]):
+        assert e <= bound, f"{what}: output of layer {l}: relative L2 {e:.3e}"
+    for i, (shape, e) in enumerate(res["grads"]):
+        assert e <= bound, f"{what}: gradient {i} {shape}: relative L2 {e:.3e}"
+
+
+@pytest.mark.parametrize("arch", list(CONFIGS))
+@pytest.mark.parametrize("merged", [True, False])
+@pytest.mark.parametrize("recompute", [False, True])
+def test_whole_model_against_the_oracle(dev, oracle, arch, merged, recompute):
+    gpu, fake = dev
+    cfg, T = CONFIGS[arch]
+    for f in FLAGS:
+        setattr(gpu, f, merged)
+    check(run_case(gpu, oracle, cfg, T, adamw=False, recompute=recompute), f"{arch}, merged launches {merged}, recompute {recompute}")
+    if merged and not recompute:
+        # what a merged step must not contain: rotations, residual adds, gated units and gradient copies of their own
+        for name in ("gt_rope_fwd", "gt_copy", "gt_glu_fwd"):
+            assert fake.count(name) == 0, (name, fake.count(name))
+        assert not [c for c in fake.calls("gt_ew_fwd") if c["op"] == 0], "a residual add was launched on its own"
+        assert fake.count("gt_glu_linear_fwd") == cfg.nLayers
+        assert fake.count("gt_gemm_multi") == 2 * cfg.nLayers          # dX of q/k/v and of gate/up, one product each
+        assert fake.count("gt_add_rmsnorm_fwd") >= 2 * cfg.nLayers - 1
+        if arch == "llama":
+            assert fake.count("gt_linear_rope_grouped") == cfg.nLayers and fake.count("gt_attention_bwd_rope") == cfg.nLayers
+            assert fake.count("gt_rope_bwd") == 0
+        else:
+            assert fake.count("gt_rmsnorm_heads_rope_fwd") == 2 * cfg.nLayers and fake.count("gt_attention_bwd_rope") == cfg.nLayers
+    if not merged:
+        assert fake.count("gt_rope_fwd") == 2 * cfg.nLayers * (2 if recompute else 1)
+        for name in ("gt_gemm_multi", "gt_gemm_grouped", "gt_linear_rope_grouped", "gt_glu_linear_fwd", "gt_add_rmsnorm_fwd",
+                     "gt_rmsnorm_bwd_add", "gt_attention_bwd_rope", "gt_rmsnorm_heads_rope_fwd"):
+            assert fake.count(name) == 0, (name, fake.count(name))
+
+
+@pytest.mark.parametrize("merged", [True, False])
+def test_adapters_on_a_frozen_base(dev, oracle, merged):
+    """Rank-4 adapters on all seven projections of the Qwen3 block, half of the targets masked, recompute on: the
+    adapter gradients against the oracle; merged, the thin products of projections that share an input are one grouped
+    launch and the adapters' own gradients go through the grouped weight-gradient launch."""
+    gpu, fake = dev
+    cfg, T = CONFIGS["qwen3"]
+    for f in FLAGS:
+        setattr(gpu, f, merged)
+    check(run_case(gpu, oracle, cfg, T, adamw=False, lora=(4, 8.0), mask_frac=0.5, recompute=True), f"adapters, merged {merged}")
+    if merged:
+        assert fake.count("gt_gemm_grouped_scaled") == 2 * cfg.nLayers * 2      # q/k/v and gate/up, forward and replay
+        assert not [c for c in fake.calls("gt_gemm") if c["kind"] == fake_cabi.TN], "an adapter gradient was launched on its own"
+    else:
+        assert fake.count("gt_gemm_grouped_scaled") == 0 and fake.count("gt_gemm2") == 0
+
+
+def test_projection_left_unwritten_is_written_when_read(dev, oracle):
+    """`rope(linear(x, W))` merged into one launch never writes the projection itself; a later reader gets it from a
+    product launched then, and the values are the projection's."""
+    from gguf_trainer_b200 import autograd as ag
+    from gguf_trainer_b200.autograd import Tensor
+    gpu, fake = dev
+    rng = np.random.default_rng(3)
+    T, din, H, hd = 32, 48, 2, 64
+    x = Tensor(rng.standard_normal(T * din).astype(np.float32), [T, din], True)
+    wq = Tensor((rng.standard_normal(H * hd * din) * 0.1).astype(np.float32), [H * hd, din], True)
+    wv = Tensor((rng.standard_normal(H * hd * din) * 0.1).astype(np.float32), [H * hd, din], True)
+    gpu.install()
+    try:
+        q0, v = ag.linear(x, wq), ag.linear(x, wv)
+        q = ag.rope(q0, T, H, hd, 10_000.0)
+        assert fake.launches == 0                                 # three ops recorded, nothing launched yet
+        gpu.sync([q, v])
+        assert fake.count("gt_linear_rope_grouped") == 1 and fake.count("gt_gemm") == 0
+        assert np.isnan(fake.f32(gpu._entries[q0].data, T, H * hd)).all()   # the unrotated projection: never written
+    finally:
+        gpu.uninstall()
+    X, W = x.data.astype(np.float64).reshape(T, din), wq.data.astype(np.float64).reshape(H * hd, din)
+    gpu.install()
+    try:
+        q0, v = ag.linear(x, wq), ag.linear(x, wv)
+        q = ag.rope(q0, T, H, hd, 10_000.0)
+        gpu.sync([q, q0])                                         # this time someone asks for it
+        assert fake.count("gt_gemm") == 1
+        assert np.allclose(q0.data.reshape(T, H * hd), X @ W.T, rtol=1e-6, atol=1e-6)
+    finally:
+        gpu.uninstall()
+
+
+def test_precision_names_and_refusals(dev):
+    gpu, _fake = dev
+    gpu.setPrecision("fp32")
+    assert gpu.precision == "fp32"
+    with pytest.raises(KeyError):
+        gpu.setPrecision("bf16")                                  # not a mode of this library
+    assert gpu.precision == "fp32"
+
+
+def test_batched_step_is_the_mean_of_its_sequences(dev, oracle):
+    """`CudaStep` (eager form) over 3 sequences of 64 tokens: per-sequence losses equal the oracle's loss of each sequence
+    run alone, and every gradient is the mean of the three single-sequence gradients (the loss seed is 1/sequences per
+    sequence, as the reference's accumulation over micro-batches scales it, src/backend/train-gpu.ts:206-215)."""
+    from gguf_trainer_b200.arch import buildModel
+    from gguf_trainer_b200.train import CudaStep
+    gpu, fake = dev
+    cfg, T = CONFIGS["llama"]
+    B = 3
+    om = oracle.Model(cfg.oracle_dict(), 77)
+    m = buildModel(cfg, 77)
+    ps = m.params()
+    for i, p in enumerate(ps):
+        p.data[:] = om.data(i).reshape(-1)
+        gpu.keepGradOnDevice(p)
+    ids = oracle.Mulberry32(3).randint(B * T, cfg.vocabSize)
+    tg = oracle.Mulberry32(4).randint(B * T, cfg.vocabSize)
+    tg[5], tg[T + 9] = -1, -1
+    step = CudaStep(m, gpu, B, T, capture=False)
+    step.run(ids, tg)
+    losses = step.losses().copy()
+    grads = [gpu.readStateBuffer(gpu.buffersFor(p)["grad"], p.size) for p in ps]
+    gpu.sync([])
+    want_losses = []
+    for s in range(B):   # the oracle's gradients accumulate over calls, as the reference's do over micro-batches
+        want_losses.append(float(om.loss_backward(ids[s * T:(s + 1) * T], tg[s * T:(s + 1) * T], seed=1.0 / B)))
+    want_grads = [om.grad(i).astype(np.float64).reshape(-1) for i in range(len(ps))]
+    om.close()
+    assert np.allclose(losses[1:], want_losses, rtol=1e-5, atol=0)
+    assert abs(losses[0] - np.mean(want_losses)) <= 1e-5 * abs(np.mean(want_losses))
+    for p, g, w in zip(ps, grads, want_grads):
+        e = float(np.linalg.norm(g - w) / max(np.linalg.norm(w), 1e-30))
+        assert e <= 1e-5, f"gradient {tuple(p.shape)}: relative L2 {e:.3e}"
+    assert fake.count("gt_copy") == 0
+
+
+def test_the_stand_in_follows_the_header():
+    """Every entry point the stand-in offers is declared in include/gguftrain.h with the same number of parameters, so a
+    call the backend makes against it is a call the library accepts."""
+    import inspect
+    from gguf_trainer_b200 import _lib
+    declared = {name: len(types) for name, _ret, types in _lib.declared_functions()}
+    mine = [n for n in dir(fake_cabi.FakeLib) if n.startswith("gt_")]
+    assert len(mine) >= 45
+    for n in mine:
+        assert n in declared, f"{n} is not in the header"
+        params = [p for p in inspect.signature(getattr(fake_cabi.FakeLib, n)).parameters.values()
+                  if p.name != "self" and not p.name.startswith("_")]
+        assert len(params) == declared[n], f"{n}: {len(params)} parameters here, {declared[n]} in the header"
+
+
+def test_forward_only_caller_gets_no_gradient_work(dev, oracle):
+    """A frozen model scored window by window (the evaluation loop, src/train/eval.ts): no backward, so no gradient
+    buffer is cleared, nothing but the loss comes back, and the logits are the oracle's."""
+    from gguf_trainer_b200 import autograd as ag
+    from gguf_trainer_b200.arch import buildModel
+    from gguf_trainer_b200.train import freezeForScoring, sequenceLoss
+    gpu, fake = dev
+    cfg, T = CONFIGS["qwen3"]
+    om = oracle.Model(cfg.oracle_dict(), 5)
+    m = buildModel(cfg, 5)
+    for i, p in enumerate(m.params()):
+        p.data[:] = om.data(i).reshape(-1)
+    freezeForScoring(m)
+    ids = oracle.Mulberry32(3).randint(T, cfg.vocabSize)
+    tg = oracle.Mulberry32(4).randint(T, cfg.vocabSize)
+    want = float(om.loss_backward(ids, tg))
+    om.close()
+    gpu.install()
+    try:
+        for _ in range(2):
+            loss = sequenceLoss(m, ids, tg)
+            gpu.sync([loss])
+            assert abs(float(loss.data[0]) - want) <= 1e-5 * abs(want)
+    finally:
+        gpu.uninstall()
+    assert gpu.gradClearsIssued == 0 and fake.count("gt_zero") == 0
+    assert gpu.lastSyncReadbackBytes == 4
+    assert all(fake.count(n) == 0 for n in ("gt_attention_bwd", "gt_attention_bwd_rope", "gt_ce_bwd", "gt_rmsnorm_bwd"))
