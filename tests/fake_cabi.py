@@ -496,6 +496,54 @@ class FakeLib:
         self._store(glogits, G, accum)
         return self._called("gt_ce_bwd", rows=rows, V=V, accum=accum)
 
+    # ------------------------------------------------------------------ the same loss over vocabulary spans (chunked readout)
+    def gt_ce_chunk_stats(self, ctx, rows, n, v0, first, chunk, targets, run):
+        Z = self.f32(chunk, rows, n).astype(np.float64)
+        tg = self._view(targets, rows, np.uint32).astype(np.int64)
+        R = self.f32(run, rows, 3)
+        m_c = Z.max(axis=1)
+        if first:
+            m_prev, s_prev = np.full(rows, -np.inf), np.zeros(rows)
+        else:
+            m_prev, s_prev = R[:, 0].astype(np.float64), R[:, 1].astype(np.float64)
+        m_new = np.maximum(m_prev, m_c)
+        s_new = s_prev * np.exp(m_prev - m_new) + np.exp(Z - m_new[:, None]).sum(axis=1)
+        inside = (tg >= v0) & (tg < v0 + n)
+        R[:, 0], R[:, 1] = m_new, s_new
+        R[inside, 2] = Z[np.arange(rows)[inside], tg[inside] - v0]
+        return self._called("gt_ce_chunk_stats", rows=rows, n=n, v0=v0, first=first)
+
+    def gt_ce_loss_from_stats(self, ctx, rows, run, targets, loss, inv_kept):
+        T, nseq = self._seq(rows)
+        R = self.f32(run, rows, 3).astype(np.float64)
+        kept = self._view(targets, rows, np.uint32) != IGNORE
+        rl = np.where(kept, np.log(R[:, 1]) + R[:, 0] - np.where(kept, R[:, 2], 0.0), 0.0)
+        L, ik = self.f32(loss, 1 + nseq), self.f32(inv_kept, nseq)
+        total = 0.0
+        for s in range(nseq):
+            rows_s = slice(s * T, (s + 1) * T)
+            c = int(kept[rows_s].sum())
+            denom = float(c) if c > 0 else 1.0
+            L[1 + s] = rl[rows_s][kept[rows_s]].sum() / denom
+            ik[s] = 1.0 / denom
+            total += float(L[1 + s])
+        L[0] = total / nseq
+        return self._called("gt_ce_loss_from_stats", rows=rows)
+
+    def gt_ce_chunk_grad(self, ctx, rows, n, v0, chunk, targets, run, inv_kept, gloss):
+        T, nseq = self._seq(rows)
+        Zv = self.f32(chunk, rows, n)
+        Z = Zv.astype(np.float64)
+        tg = self._view(targets, rows, np.uint32)
+        R = self.f32(run, rows, 3).astype(np.float64)
+        sc = float(self.f32(gloss, 1)[0]) * self.f32(inv_kept, nseq).astype(np.float64)[np.arange(rows) // T] / nseq
+        P = np.exp(Z - R[:, 0:1]) / R[:, 1:2]
+        kept = tg != IGNORE
+        inside = kept & (tg >= v0) & (tg.astype(np.int64) < v0 + n)
+        P[np.arange(rows)[inside], tg[inside].astype(np.int64) - v0] -= 1.0
+        Zv[...] = np.where(kept[:, None], sc[:, None] * P, 0.0).astype(np.float32)      # in place, as the library does
+        return self._called("gt_ce_chunk_grad", rows=rows, n=n, v0=v0)
+
 
 def install(monkeypatch):
     """Make `CudaBackend()` come up on a fresh FakeLib; returns it."""

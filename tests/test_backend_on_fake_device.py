@@ -210,3 +210,15 @@ def test_forward_only_caller_gets_no_gradient_work(dev, oracle):
     assert gpu.gradClearsIssued == 0 and fake.count("gt_zero") == 0
     assert gpu.lastSyncReadbackBytes == 4
     assert all(fake.count(n) == 0 for n in ("gt_attention_bwd", "gt_attention_bwd_rope", "gt_ce_bwd", "gt_rmsnorm_bwd"))
+
+
+@pytest.mark.parametrize("arch", ["llama", "gemma3"])
+def test_readout_loss_over_vocabulary_spans(dev, oracle, arch):
+    """`fusedCrossEntropy` with spans of 40 over a vocabulary of 96 (a ragged last span of 16) and a third of the targets
+    ignored: loss and every gradient against the oracle's chunked loss; the [T, V] logits are never formed."""
+    gpu, fake = dev
+    cfg, T = CONFIGS[arch]
+    check(run_case(gpu, oracle, cfg, T, adamw=False, loss_chunk=40, mask_frac=0.33), f"{arch}, readout in spans")
+    assert fake.count("gt_ce_fwd") == 0 and fake.count("gt_ce_chunk_stats") == 3 and fake.count("gt_ce_chunk_grad") == 3
+    assert [c["n"] for c in fake.calls("gt_ce_chunk_stats")] == [40, 40, 16]
+    assert not [c for c in fake.calls("gt_gemm") if c["N"] == cfg.vocabSize or c["M"] == cfg.vocabSize]
