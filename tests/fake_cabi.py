@@ -544,6 +544,57 @@ class FakeLib:
         Zv[...] = np.where(kept[:, None], sc[:, None] * P, 0.0).astype(np.float32)      # in place, as the library does
         return self._called("gt_ce_chunk_grad", rows=rows, n=n, v0=v0)
 
+    # ------------------------------------------------------------------ AdamW over a group of tensors, global-norm clip
+    def gt_adamw_create(self, ctx, n, data, grad, sizes, lr, b1, b2, eps, wd, clip, ref):
+        if not hasattr(self, "_adamw"):
+            self._adamw = {}
+        h = len(self._adamw) + 1
+        sz = _ints(sizes, n)
+        self._adamw[h] = dict(data=_ints(data, n), grad=_ints(grad, n), sizes=sz, lr=float(lr), b1=float(b1), b2=float(b2),
+                              eps=float(eps), wd=float(wd), clip=float(clip), t=0,
+                              m=[self._new(4 * k, zero=True) for k in sz], v=[self._new(4 * k, zero=True) for k in sz])
+        ref._obj.value = h
+        return 0
+
+    def gt_adamw_set_lr(self, ctx, h, lr):
+        self._adamw[int(h)]["lr"] = float(lr)
+        return 0
+
+    def gt_adamw_state(self, ctx, h, i, mref, vref):
+        a = self._adamw[int(h)]
+        mref._obj.value, vref._obj.value = a["m"][i], a["v"][i]
+        return 0
+
+    def gt_adamw_get_t(self, ctx, h, ref):
+        ref._obj.value = self._adamw[int(h)]["t"]
+        return 0
+
+    def gt_adamw_set_t(self, ctx, h, t):
+        self._adamw[int(h)]["t"] = int(t)
+        return 0
+
+    def gt_adamw_step(self, ctx, h):
+        a = self._adamw[int(h)]
+        a["t"] += 1
+        scale = 1.0
+        if a["clip"] > 0:
+            norm = math.sqrt(sum(float((self.f32(g, k).astype(np.float64) ** 2).sum()) for g, k in zip(a["grad"], a["sizes"])))
+            if norm > a["clip"]:
+                scale = a["clip"] / (norm + 1e-12)
+        bc1, bc2 = 1.0 - a["b1"] ** a["t"], 1.0 - a["b2"] ** a["t"]
+        for w, g, m, v, k in zip(a["data"], a["grad"], a["m"], a["v"], a["sizes"]):
+            G = self.f32(g, k).astype(np.float64) * scale
+            M = a["b1"] * self.f32(m, k).astype(np.float64) + (1.0 - a["b1"]) * G
+            V = a["b2"] * self.f32(v, k).astype(np.float64) + (1.0 - a["b2"]) * G * G
+            W = self.f32(w, k).astype(np.float64)
+            u = (M / bc1) / (np.sqrt(V / bc2) + a["eps"])
+            if a["wd"] > 0:
+                u = u + a["wd"] * W
+            self._store(m, M)
+            self._store(v, V)
+            self._store(w, W - a["lr"] * u)
+        return self._called("gt_adamw_step", h=int(h), t=a["t"])
+
 
 def install(monkeypatch):
     """Make `CudaBackend()` come up on a fresh FakeLib; returns it."""

@@ -222,3 +222,18 @@ def test_readout_loss_over_vocabulary_spans(dev, oracle, arch):
     assert fake.count("gt_ce_fwd") == 0 and fake.count("gt_ce_chunk_stats") == 3 and fake.count("gt_ce_chunk_grad") == 3
     assert [c["n"] for c in fake.calls("gt_ce_chunk_stats")] == [40, 40, 16]
     assert not [c for c in fake.calls("gt_gemm") if c["N"] == cfg.vocabSize or c["M"] == cfg.vocabSize]
+
+
+def test_step_with_adamw_matches_the_oracle_weights(dev, oracle):
+    """Forward, backward and one AdamW step (lr 1e-3, betas 0.9 / 0.95, weight decay 0.1, clip 1.0) through `AdamWGpu`: the
+    optimizer flushes whatever launches were still put off before it reads the gradients, and the weights after the
+    step are the oracle's."""
+    gpu, fake = dev
+    cfg, T = CONFIGS["llama"]
+    res = run_case(gpu, oracle, cfg, T, adamw=True)
+    check(res, "llama with adamw")
+    for i, (shape, e) in enumerate(res["weights"]):
+        assert e <= 1e-5, f"weight {i} {shape} after the step: relative L2 {e:.3e}"
+    assert fake.count("gt_adamw_step") == 1
+    order = [n for n, _kw in fake.log]
+    assert max(i for i, n in enumerate(order) if n in ("gt_gemm_grouped", "gt_gemm_multi")) < order.index("gt_adamw_step")
