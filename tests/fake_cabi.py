@@ -39,8 +39,64 @@ class FakeLib:
         self.precision = 0
         self._tickets = {}
         self._nextTicket = 1
+        self._recording = None      # the list a recording in progress appends to
         self.state_bytes = 0
         self.pool_bytes = 0
+
+    # ------------------------------------------------------------------ recording and replay (gt_graph_*)
+    # While a recording is open, device work is not run: the call and its arguments are appended to the recording, and
+    # gt_graph_launch runs them in order, as a CUDA graph would. Host-side calls (allocation, statistics) run at once;
+    # host transfers are refused, as the library refuses them.
+    _HOST_SIDE = {"gt_init", "gt_destroy", "gt_last_error", "gt_device_name", "gt_set_precision", "gt_set_batch", "gt_alloc",
+                  "gt_alloc_state", "gt_free", "gt_stats", "gt_graph_begin", "gt_graph_end", "gt_graph_launch", "gt_graph_destroy",
+                  "gt_adamw_create", "gt_adamw_set_lr", "gt_adamw_state", "gt_adamw_get_t", "gt_adamw_set_t"}
+    _REFUSED_WHILE_RECORDING = {"gt_write", "gt_read", "gt_read_async", "gt_read_fence", "gt_sync"}
+
+    def __getattribute__(self, name):
+        attr = object.__getattribute__(self, name)
+        if not name.startswith("gt_"):
+            return attr
+        rec = object.__getattribute__(self, "__dict__").get("_recording")
+        if rec is None or name in FakeLib._HOST_SIDE:
+            return attr
+        if name in FakeLib._REFUSED_WHILE_RECORDING:
+            return lambda *a, **k: 4
+        batch = self.batch
+
+        def record(*args):
+            rec.append((name, args, batch))
+            self.launches += 1
+            return 0
+        return record
+
+    def gt_graph_begin(self, ctx):
+        if self.__dict__.get("_recording") is not None:
+            return 4
+        self._recording = []
+        return 0
+
+    def gt_graph_end(self, ctx, ref):
+        if not hasattr(self, "_graphs"):
+            self._graphs = {}
+        h = len(self._graphs) + 1
+        self._graphs[h] = self._recording
+        self._recording = None
+        ref._obj.value = h
+        return 0
+
+    def gt_graph_launch(self, ctx, h):
+        saved = self.batch
+        for name, args, batch in self._graphs[int(h)]:
+            self.batch = batch                       # the shapes a recorded kernel was launched with are part of the recording
+            st = getattr(FakeLib, name)(self, *args)
+            if st:
+                return st
+        self.batch = saved
+        return 0
+
+    def gt_graph_destroy(self, ctx, h):
+        self._graphs.pop(int(h), None)
+        return 0
 
     # ------------------------------------------------------------------ memory model
     def _new(self, nbytes, zero):

@@ -237,3 +237,40 @@ def test_step_with_adamw_matches_the_oracle_weights(dev, oracle):
     assert fake.count("gt_adamw_step") == 1
     order = [n for n, _kw in fake.log]
     assert max(i for i, n in enumerate(order) if n in ("gt_gemm_grouped", "gt_gemm_multi")) < order.index("gt_adamw_step")
+
+
+def test_recorded_step_replays_to_the_eager_steps_results(dev, oracle):
+    """`CudaStep` with recording: the first call runs eagerly once and records, later calls only rewrite the inputs and
+    replay. Losses and gradients of three different batches equal the eager form's bit for bit (same arithmetic, same
+    order), the replay records nothing new, and ids outside the vocabulary are refused before they reach the recording."""
+    from gguf_trainer_b200.arch import buildModel
+    from gguf_trainer_b200.train import CudaStep
+    gpu, fake = dev
+    cfg, T = CONFIGS["qwen3"]
+    B = 2
+    batches = [(oracle.Mulberry32(10 + i).randint(B * T, cfg.vocabSize), oracle.Mulberry32(20 + i).randint(B * T, cfg.vocabSize)) for i in range(3)]
+    results = {}
+    for capture in (False, True):
+        m = buildModel(cfg, 9)
+        for p in m.params():
+            gpu.keepGradOnDevice(p)
+        step = CudaStep(m, gpu, B, T, capture=capture)
+        out = []
+        for ids, tg in batches:
+            before = len(fake.log)
+            step.run(ids, tg)
+            out.append((step.losses().copy(), [gpu.readStateBuffer(gpu.buffersFor(p)["grad"], p.size) for p in m.params()], len(fake.log) - before))
+        gpu.sync([])
+        results[capture] = out
+        if capture:
+            assert step.launchesPerReplay > 0
+            bad = batches[0][0].copy()
+            bad[3] = cfg.vocabSize
+            with pytest.raises(ValueError, match="not an integer in \\[0,96\\)"):
+                step.run(bad, batches[0][1])
+    for (la, ga, _na), (lb, gb, _nb) in zip(results[False], results[True]):
+        assert np.array_equal(la, lb)
+        for a, b in zip(ga, gb):
+            assert np.array_equal(a, b) and np.isfinite(a).all()
+    # the first call ran the step eagerly and then replayed its recording; later calls only replay
+    assert results[True][1][2] == results[True][2][2] and results[True][0][2] == 2 * results[True][1][2]
