@@ -49,8 +49,11 @@ class FakeLib:
     # host transfers are refused, as the library refuses them.
     _HOST_SIDE = {"gt_init", "gt_destroy", "gt_last_error", "gt_device_name", "gt_set_precision", "gt_set_batch", "gt_alloc",
                   "gt_alloc_state", "gt_free", "gt_stats", "gt_graph_begin", "gt_graph_end", "gt_graph_launch", "gt_graph_destroy",
-                  "gt_adamw_create", "gt_adamw_set_lr", "gt_adamw_state", "gt_adamw_get_t", "gt_adamw_set_t"}
-    _REFUSED_WHILE_RECORDING = {"gt_write", "gt_read", "gt_read_async", "gt_read_fence", "gt_sync"}
+                  "gt_adamw_create", "gt_adamw_set_lr", "gt_adamw_state", "gt_adamw_get_t", "gt_adamw_set_t", "gt_dp_unique_id",
+                  "gt_dp_init", "gt_dp_reserve_sms", "gt_dp_destroy"}
+    # (the exchange is issued by the host between recorded segments, never into one)
+    _REFUSED_WHILE_RECORDING = {"gt_write", "gt_read", "gt_read_async", "gt_read_fence", "gt_sync", "gt_dp_allreduce_start",
+                                "gt_dp_wait", "gt_dp_wait_host"}
 
     def __getattribute__(self, name):
         attr = object.__getattribute__(self, name)
@@ -650,6 +653,37 @@ class FakeLib:
             self._store(v, V)
             self._store(w, W - a["lr"] * u)
         return self._called("gt_adamw_step", h=int(h), t=a["t"])
+
+    # ------------------------------------------------------------------ gradient exchange, as seen by ONE rank
+    # A single process cannot hold the other ranks; the stand-in plays a world whose ranks all hold the same numbers:
+    # the sum over `world` ranks is then `world` times this rank's buffer (exact in f32 for a power of two).
+    def gt_dp_unique_id(self, buf):
+        for i in range(128):
+            buf[i] = i
+        return 0
+
+    def gt_dp_init(self, ctx, rank, world, buf):
+        self.dp_world = int(world)
+        return 0
+
+    def gt_dp_allreduce_start(self, ctx, addr, n):
+        v = self.f32(addr, int(n))
+        v[...] = (v.astype(np.float64) * self.dp_world).astype(np.float32)
+        self.log.append(("gt_dp_allreduce_start", dict(addr=int(addr), n=int(n))))
+        return 0
+
+    def gt_dp_wait(self, ctx):
+        self.log.append(("gt_dp_wait", {}))
+        return 0
+
+    def gt_dp_wait_host(self, ctx, timeout_ms):
+        return 0
+
+    def gt_dp_reserve_sms(self, ctx, n):
+        return 0
+
+    def gt_dp_destroy(self, ctx):
+        return 0
 
 
 def install(monkeypatch):

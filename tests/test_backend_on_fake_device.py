@@ -274,3 +274,48 @@ def test_recorded_step_replays_to_the_eager_steps_results(dev, oracle):
             assert np.array_equal(a, b) and np.isfinite(a).all()
     # the first call ran the step eagerly and then replayed its recording; later calls only replay
     assert results[True][1][2] == results[True][2][2] and results[True][0][2] == 2 * results[True][1][2]
+
+
+@pytest.mark.parametrize("capture", [False, True])
+def test_gradient_exchange_in_buckets_leaves_the_single_process_gradients(dev, oracle, capture):
+    """The data-parallel step as one of two ranks holding the same batch: the loss is seeded with 1/2, the gradient arena
+    is summed bucket by bucket (one bucket per layer, each started when backward leaves the bucket's first layer; the
+    stand-in's sum over two equal ranks is a doubling), and the result is bit for bit the gradient of the plain step.
+    Recorded, the step is one graph per bucket boundary and the exchange is issued between the segments."""
+    from gguf_trainer_b200.arch import buildModel
+    from gguf_trainer_b200.train import CudaStep, DataParallel
+    gpu, fake = dev
+    cfg, T = CONFIGS["gemma3"]
+    B = 2
+    batches = [(oracle.Mulberry32(10 + i).randint(B * T, cfg.vocabSize), oracle.Mulberry32(20 + i).randint(B * T, cfg.vocabSize)) for i in range(2)]
+
+    def run(with_dp):
+        m = buildModel(cfg, 9)
+        ps = m.params()
+        arena = gpu.reserveGradArena(list(reversed(ps))) if with_dp else None
+        if not with_dp:
+            for p in ps:
+                gpu.keepGradOnDevice(p)
+        dp = DataParallel(gpu, 0, 2, DataParallel.uniqueId()) if with_dp else None
+        step = CudaStep(m, gpu, B, T, world=2 if with_dp else 1, capture=capture, dp=dp, arena=arena, layersPerBucket=1)
+        out = []
+        for ids, tg in batches:
+            before = len(fake.log)
+            step.run(ids, tg)
+            grads = [gpu.readStateBuffer(gpu.buffersFor(p)["grad"], p.size) for p in ps]
+            out.append((step.losses().copy(), grads, [n for n, _kw in fake.log[before:]]))
+        gpu.sync([])
+        return out, (step.bucketPlan() if with_dp else None)
+
+    plain, _ = run(False)
+    exchanged, plan = run(True)
+    assert len(plan) == cfg.nLayers and sum(c for _l, _s, c in plan) == sum(p.size + (-p.size) % 64 for p in buildModel(cfg, 9).params())
+    for (la, ga, _), (lb, gb, names) in zip(plain, exchanged):
+        assert np.array_equal(la, lb)
+        for a, b in zip(ga, gb):
+            assert np.array_equal(a, b) and np.isfinite(a).all()
+    names = exchanged[1][2]
+    starts = [i for i, n in enumerate(names) if n == "gt_dp_allreduce_start"]
+    assert len(starts) == cfg.nLayers and names.count("gt_dp_wait") == 1
+    # the first reduction starts while backward still has work to launch; the wait comes after the last one
+    assert any(n.startswith("gt_attention_bwd") for n in names[starts[0]:]) and names.index("gt_dp_wait") > starts[-1]
