@@ -654,6 +654,27 @@ class FakeLib:
             self._store(w, W - a["lr"] * u)
         return self._called("gt_adamw_step", h=int(h), t=a["t"])
 
+    # ------------------------------------------------------------------ token windows gathered from a resident corpus
+    def gt_tokens_max(self, ctx, tokens, bpt, count, ref):
+        dt = np.uint16 if int(bpt) == 2 else np.uint32
+        ref._obj.value = int(self._view(tokens, count, dt).max()) if count else 0
+        return self._called("gt_tokens_max", count=int(count))
+
+    def gt_gather_windows(self, ctx, tokens, mask, bpt, count, starts, B, T, ids, targets):
+        dt = np.uint16 if int(bpt) == 2 else np.uint32
+        tok = self._view(tokens, count, dt).astype(np.uint32)
+        msk = self._view(mask, count, dt) if mask else None
+        st = self._view(starts, B, np.uint64).astype(np.int64)
+        I, G = self._view(ids, B * T, np.uint32).reshape(B, T), self._view(targets, B * T, np.uint32).reshape(B, T)
+        for b in range(B):
+            s = int(st[b])
+            assert 0 <= s and s + T + 1 <= int(count), "window start past corpus length"
+            I[b] = tok[s:s + T]
+            G[b] = tok[s + 1:s + 1 + T]
+            if msk is not None:
+                G[b][msk[s + 1:s + 1 + T] == 0] = IGNORE
+        return self._called("gt_gather_windows", B=int(B), T=int(T))
+
     # ------------------------------------------------------------------ gradient exchange, as seen by ONE rank
     # A single process cannot hold the other ranks; the stand-in plays a world whose ranks all hold the same numbers:
     # the sum over `world` ranks is then `world` times this rank's buffer (exact in f32 for a power of two).

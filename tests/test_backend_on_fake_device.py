@@ -319,3 +319,54 @@ def test_gradient_exchange_in_buckets_leaves_the_single_process_gradients(dev, o
     assert len(starts) == cfg.nLayers and names.count("gt_dp_wait") == 1
     # the first reduction starts while backward still has work to launch; the wait comes after the last one
     assert any(n.startswith("gt_attention_bwd") for n in names[starts[0]:]) and names.index("gt_dp_wait") > starts[-1]
+
+
+@pytest.mark.parametrize("capture", [False, True])
+def test_step_fed_by_window_starts(dev, oracle, capture):
+    """`CudaStep.runWindows(starts)` over a corpus resident on the device equals `run(ids, targets)` on the windows the
+    host would have cut (`window` twice + `maskWindow`, src/data/tokens.ts:158-185, src/train/trainer.ts:45-49), bit for
+    bit; starts past the end and a corpus outside the vocabulary are refused on the host."""
+    from gguf_trainer_b200.arch import buildModel
+    from gguf_trainer_b200.ingest import DeviceTokenSource
+    from gguf_trainer_b200.train import CudaStep, maskWindow
+    gpu, fake = dev
+    cfg, T = CONFIGS["llama"]
+    B = 2
+    rng = np.random.default_rng(5)
+    tokens = rng.integers(0, cfg.vocabSize, 400)
+    supervised = (rng.random(400) < 0.6).astype(np.int64)
+    with pytest.raises(ValueError, match="not in \\[0,90\\)"):
+        DeviceTokenSource(gpu, np.concatenate([tokens, [95]]), 90)
+
+    def host_windows(starts):
+        ids, tgs = [], []
+        for s in starts:
+            ids.append(np.array(tokens[s:s + T], dtype=np.int64))
+            t = np.array(tokens[s + 1:s + 1 + T], dtype=np.int64)
+            maskWindow(t, supervised, s + 1)
+            tgs.append(t)
+        return np.concatenate(ids), np.concatenate(tgs)
+
+    out = []
+    for windows in (False, True):
+        m = buildModel(cfg, 9)
+        for p in m.params():
+            gpu.keepGradOnDevice(p)
+        src = DeviceTokenSource(gpu, tokens, cfg.vocabSize, supervised) if windows else None
+        step = CudaStep(m, gpu, B, T, capture=capture, source=src)
+        res = []
+        for starts in ([5, 300], [0, 400 - T - 1]):
+            if windows:
+                step.runWindows(starts)
+            else:
+                step.run(*host_windows(starts))
+            res.append((step.losses().copy(), [gpu.readStateBuffer(gpu.buffersFor(p)["grad"], p.size) for p in m.params()]))
+        gpu.sync([])
+        out.append(res)
+        if windows:
+            with pytest.raises(ValueError, match="out of range"):
+                step.runWindows([0, 400 - T])
+    for (la, ga), (lb, gb) in zip(out[0], out[1]):
+        assert np.array_equal(la, lb)
+        for a, b in zip(ga, gb):
+            assert np.array_equal(a, b)
