@@ -50,7 +50,8 @@ class FakeLib:
     _HOST_SIDE = {"gt_init", "gt_destroy", "gt_last_error", "gt_device_name", "gt_set_precision", "gt_set_batch", "gt_alloc",
                   "gt_alloc_state", "gt_free", "gt_stats", "gt_graph_begin", "gt_graph_end", "gt_graph_launch", "gt_graph_destroy",
                   "gt_adamw_create", "gt_adamw_set_lr", "gt_adamw_state", "gt_adamw_get_t", "gt_adamw_set_t", "gt_dp_unique_id",
-                  "gt_dp_init", "gt_dp_reserve_sms", "gt_dp_destroy"}
+                  "gt_dp_init", "gt_dp_reserve_sms", "gt_dp_destroy", "gt_muon_create", "gt_muon_set_lr", "gt_muon_state",
+                  "gt_muon_set_sharded"}
     # (the exchange is issued by the host between recorded segments, never into one)
     _REFUSED_WHILE_RECORDING = {"gt_write", "gt_read", "gt_read_async", "gt_read_fence", "gt_sync", "gt_dp_allreduce_start",
                                 "gt_dp_wait", "gt_dp_wait_host"}
@@ -653,6 +654,55 @@ class FakeLib:
             self._store(v, V)
             self._store(w, W - a["lr"] * u)
         return self._called("gt_adamw_step", h=int(h), t=a["t"])
+
+    # ------------------------------------------------------------------ Muon: momentum, five quintic Newton-Schulz steps, apply
+    @staticmethod
+    def _newton_schulz(G, steps):
+        X = G / (np.sqrt((G * G).sum()) + 1e-7)
+        flip = X.shape[0] > X.shape[1]
+        if flip:
+            X = X.T
+        for _ in range(steps):
+            A = X @ X.T
+            X = 3.4445 * X + (-4.7750 * A + 2.0315 * (A @ A)) @ X
+        return X.T if flip else X
+
+    def gt_newton_schulz(self, ctx, m, n, steps, g, out):
+        self._store(out, self._newton_schulz(self.f32(g, m, n).astype(np.float64), steps))
+        return self._called("gt_newton_schulz", m=m, n=n, steps=steps)
+
+    def gt_muon_create(self, ctx, n, data, grad, rows, cols, lr, momentum, nesterov, ns_steps, ref):
+        if not hasattr(self, "_muon"):
+            self._muon = {}
+        h = len(self._muon) + 1
+        r, c = _ints(rows, n), _ints(cols, n)
+        self._muon[h] = dict(data=_ints(data, n), grad=_ints(grad, n), rows=r, cols=c, lr=float(lr), mu=float(momentum),
+                             nesterov=int(nesterov), ns=int(ns_steps), buf=[self._new(4 * a * b, zero=True) for a, b in zip(r, c)])
+        ref._obj.value = h
+        return 0
+
+    def gt_muon_set_lr(self, ctx, h, lr):
+        self._muon[int(h)]["lr"] = float(lr)
+        return 0
+
+    def gt_muon_state(self, ctx, h, i, ref):
+        ref._obj.value = self._muon[int(h)]["buf"][i]
+        return 0
+
+    def gt_muon_set_sharded(self, ctx, h, on):
+        return 0
+
+    def gt_muon_step(self, ctx, h):
+        m = self._muon[int(h)]
+        for w, g, b, r, c in zip(m["data"], m["grad"], m["buf"], m["rows"], m["cols"]):
+            G = self.f32(g, r, c).astype(np.float64)
+            B = m["mu"] * self.f32(b, r, c).astype(np.float64) + G
+            self._store(b, B)
+            B = self.f32(b, r, c).astype(np.float64)
+            U = G + m["mu"] * B if m["nesterov"] else B
+            X = self._newton_schulz(U.astype(np.float32).astype(np.float64), m["ns"])
+            self._store(w, self.f32(w, r, c).astype(np.float64) - m["lr"] * math.sqrt(max(1.0, r / c)) * X)
+        return self._called("gt_muon_step", h=int(h))
 
     # ------------------------------------------------------------------ token windows gathered from a resident corpus
     def gt_tokens_max(self, ctx, tokens, bpt, count, ref):

@@ -370,3 +370,34 @@ def test_step_fed_by_window_starts(dev, oracle, capture):
         assert np.array_equal(la, lb)
         for a, b in zip(ga, gb):
             assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("rows,cols", [(12, 20), (20, 12), (16, 16)])
+def test_muon_host_side_two_steps_and_state(dev, oracle, rows, cols):
+    """`MuonGpu` (src/backend/muon-gpu.ts:351-470) over two steps against the oracle's Muon (momentum 0.95, Nesterov, five
+    Newton-Schulz steps), its auxiliary AdamW group, and the .optstate round trip through device buffers
+    (tests/gpu-parity.ts:1040-1093)."""
+    from gguf_trainer_b200.autograd import Tensor
+    from gguf_trainer_b200.optim import MuonGpu, deserializeOptState, serializeOptState
+    gpu, fake = dev
+    rng = oracle.Mulberry32(0x4D4D)
+    p = Tensor(rng.randn((rows, cols), 0.5), [rows, cols], True)
+    aux = Tensor(rng.randn((9,), 0.5), [9], True)
+    w = p.data.copy().reshape(rows, cols)
+    buf = np.zeros((rows, cols), np.float32)
+    opt = MuonGpu(gpu, [p], [aux], lr=0.05, momentum=0.95, nesterov=True, nsSteps=5, aux={"lr": 1e-3})
+    for _ in range(2):
+        g = rng.randn((rows, cols), 0.3)
+        gpu.writeStateBuffer(gpu.buffersFor(p)["grad"], g)
+        gpu.writeStateBuffer(gpu.buffersFor(aux)["grad"], rng.randn((9,), 0.1))
+        opt.recordStep()
+        oracle.muon_step_array(w, g, buf, 0.05, 0.95, True, 5)
+    gpu.sync([p, aux])
+    assert np.linalg.norm(p.data.reshape(rows, cols) - w) <= 1e-5 * np.linalg.norm(w)
+    st = opt.exportState()
+    assert np.allclose(st["muonMomentum"][0].reshape(rows, cols), buf, rtol=1e-5, atol=1e-6) and st["adamT"] == 2
+    blob = serializeOptState(st)
+    opt2 = MuonGpu(gpu, [Tensor(p.data.copy(), p.shape, True)], [Tensor(aux.data.copy(), aux.shape, True)], lr=0.05, aux={"lr": 1e-3})
+    opt2.importState(deserializeOptState(blob))
+    assert serializeOptState(opt2.exportState()) == blob
+    assert fake.count("gt_muon_step") == 2 and fake.count("gt_adamw_step") == 2
