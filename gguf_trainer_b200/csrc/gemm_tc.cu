@@ -778,6 +778,8 @@ static gt_status gemm_tc_dispatch(gt_ctx* ctx, int kind, int accum, int M, int N
   struct Cfg { int mt, bn; };   // mt 1, 2: 128 / 256 rows on one CTA; mt 3: 256 rows on a CTA pair
   static const Cfg cfgs[6] = {{1, 192}, {1, 128}, {2, 256}, {2, 192}, {3, 192}, {3, 256}};
   const char* force = getenv("GT_GEMM_TILE");   // "mt,bn": forces one tile shape (read per call so tests can switch it)
+  const char* ds = getenv("GT_GEMM_DEEP_SPLIT");   // "0": never cut a product that already fills the SMs along K (for comparison)
+  const bool deep_split = !(ds && ds[0] == '0');
   const int npairs = max(0, pair_capacity(ctx) - (ctx->sm_reserved + 1) / 2);
   int best = 0, ksplit = 1;
   double best_cost = 1e30;
@@ -796,6 +798,20 @@ static gt_status gemm_tc_dispatch(gt_ctx* ctx, int kind, int accum, int M, int N
       ks = (int)min((long)(workers / tiles), (long)(kblocks / 8));
       if (ks < 1) ks = 1;
     }
+    // A very deep product whose tiles fill the SMs unevenly (the readout's dX: 384 tiles on 148 SMs are 2.6 waves,
+    // run as 3) is cut along K as well when that evens the waves out: 3 slices give 1152 units = 7.8 waves of a third
+    // of the length. The clear before it and the reduce-adds are charged below. Measured at rows 16384: the readout's
+    // dX (K 49152) 1890 -> 1292 us, dX of gate and up (K 3072) 128 -> 106 us, both moving to 256-row tiles in three
+    // slices; at K 1536 the same choice measured slower (60.5 -> 67.9 us), hence the depth limit of 64 K blocks.
+    double split_penalty = 0.0;
+    if (ks == 1 && tiles >= workers && kblocks >= 64 && deep_split) {
+      double best_w = (double)gt_cdiv(tiles, workers);
+      for (int k2 = 2; k2 <= 4; k2++) {
+        const double w2 = (double)gt_cdiv(tiles * k2, workers) / k2;
+        if (w2 < best_w - 0.05) { best_w = w2; ks = k2; }
+      }
+      if (ks > 1) split_penalty = 8000.0;
+    }
     const long units = tiles * ks;
     const long waves = gt_cdiv(units, workers);
     const double kb_unit = (double)gt_cdiv(kblocks, ks);
@@ -809,7 +825,7 @@ static gt_status gemm_tc_dispatch(gt_ctx* ctx, int kind, int accum, int M, int N
     const double smem = mt == 3 ? (bn == 192 ? 640.0 : 720.0)
                                 : 0.92 * ((bm * 128.0 + bn * 128.0) + mt * (BM1 * 128.0 + bn * 128.0)) / 128.0;
     const double epilogue = mt == 2 ? 14.0 * bn + 900.0 : 1500.0;
-    const double cost = waves * (kb_unit * (tensor > smem ? tensor : smem) + epilogue);
+    const double cost = waves * (kb_unit * (tensor > smem ? tensor : smem) + epilogue + (split_penalty > 0 ? 600.0 : 0.0)) + split_penalty;
     if (cost < best_cost) { best_cost = cost; best = i; ksplit = ks; }
   }
   if (best_cost >= 1e30) return GT_OK;
