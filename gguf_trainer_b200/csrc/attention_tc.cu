@@ -20,6 +20,9 @@
 // block are fetched as soon as the products that read the current ones have completed.
 // Waits on mbarriers are bounded in wall time: on expiry a thread raises the device flag and from then on skips
 // every wait, so all threads still run the same control flow to the end and release TMEM.
+#include <algorithm>
+#include <vector>
+
 #include "common.cuh"
 #include "tc_common.cuh"
 
@@ -469,7 +472,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
                        const __grid_constant__ CUtensorMap mapGk, const __grid_constant__ CUtensorMap mapGm,
                        const float* __restrict__ lse, const float* __restrict__ Ds, float* gk, int accum_k, float* gv, int accum_v,
                        int rows, int T, int Hq, int Hkv, int window, float scale2, float dp_scale, const float2* __restrict__ rope,
-                       int* __restrict__ flag) {
+                       const int* __restrict__ order, int* __restrict__ flag) {
   extern __shared__ uint8_t smem_raw[];
   using S = DkvSmem<HD, NQ, KBUF, MBUF, SPLIT>;
   constexpr int ATOMS = HD / 32, NH = NQ / 2, HH = HD / 2, HDF = HD * SPLIT;
@@ -485,8 +488,17 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + S::BAR_OFF + 64);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int k0 = blockIdx.y * ROWS;           // early keys are read by the most queries: heaviest first
-  const int crank = SPLIT == 2 ? (int)(blockIdx.x & 1) : 0, bx = blockIdx.x / SPLIT;   // which half of the head; tile
+  // Which (key block, kv head, sequence) this CTA takes. CTAs start in index order as SMs fall free; early key blocks are
+  // read by the most queries, so plain index order is heaviest first. `order` (one CTA per tile only) replaces it by
+  // the order a packing of the tiles into the SMs prescribes (attn_dkv_order).
+  int tile_y = blockIdx.y, tile_x = blockIdx.x;
+  if (SPLIT == 1 && order != nullptr) {
+    const int lin = order[blockIdx.y * gridDim.x + blockIdx.x];
+    tile_y = lin / (int)gridDim.x;
+    tile_x = lin % (int)gridDim.x;
+  }
+  const int k0 = tile_y * ROWS;
+  const int crank = SPLIT == 2 ? (int)(tile_x & 1) : 0, bx = tile_x / SPLIT;   // which half of the head; tile
   const int kvh = bx % Hkv, seq = bx / Hkv;
   const int group = Hq / Hkv;
   const int row0 = seq * T;
@@ -1017,6 +1029,61 @@ gt_status launch_fwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, 
   return GT_OK;
 }
 
+// The order in which the tiles of the dK/dV kernel are handed out. A tile's work is its number of (query head, query
+// block) iterations, 96 down to 6 at the benchmark shape, and the hardware gives the next tile in index order to whichever
+// SM falls free: with the tiles sorted heaviest first that is longest-processing-time-first scheduling, which at 384
+// tiles on 148 SMs ends 9 % above the mean load. Here the tiles are first packed into the SMs (first fit decreasing
+// under the smallest capacity that fits, found by bisection) and then listed by the time at which the packing starts
+// them; handing them out in that order reproduces the packing to within timing noise and ends 3 % above the mean.
+// Built once per shape on the host (not during a recording) and kept on the device.
+gt_status attn_dkv_order(gt_ctx* ctx, int nkb, int ntx, int group, int T, int NQ, int window, const int** out) {
+  std::vector<int> key = {nkb, ntx, group, T, NQ, window, ctx->sm_count};
+  auto it = ctx->attn_orders.find(key);
+  if (it == ctx->attn_orders.end()) {
+    if (ctx->capturing) return gt_fail(ctx, GT_ERR_STATE, "attention backward: the launch order of this shape is built on first use; run the step once eagerly before recording");
+    const int n = nkb * ntx, workers = ctx->sm_count;
+    std::vector<int> size(n), idx(n);
+    double total = 0.0;
+    int largest = 0;
+    for (int kb = 0; kb < nkb; kb++) {
+      const int k0 = kb * ROWS, k_last = min(k0 + ROWS - 1, T - 1);
+      const int q_max = window > 0 ? min(T - 1, k_last + window - 1) : T - 1;
+      const int w = (q_max / NQ - k0 / NQ + 1) * group + 3;       // iterations, plus about three for the tile's own prologue and epilogue
+      for (int x = 0; x < ntx; x++) { size[kb * ntx + x] = w; idx[kb * ntx + x] = kb * ntx + x; }
+      total += (double)w * ntx;
+      largest = max(largest, w);
+    }
+    std::stable_sort(idx.begin(), idx.end(), [&](int a, int b) { return size[a] > size[b]; });
+    std::vector<int> bin_of(n), start(n);
+    auto pack = [&](double cap) {
+      std::vector<double> load(workers, 0.0);
+      for (int j : idx) {
+        int b = 0;
+        while (b < workers && load[b] + size[j] > cap) b++;
+        if (b == workers) return false;
+        bin_of[j] = b; start[j] = (int)load[b];
+        load[b] += size[j];
+      }
+      return true;
+    };
+    double lo = std::max((double)largest, total / workers), hi = 2.0 * lo;
+    for (int r = 0; r < 24; r++) {
+      const double mid = 0.5 * (lo + hi);
+      if (pack(mid)) hi = mid; else lo = mid;
+    }
+    pack(hi);
+    std::vector<int> order(idx);
+    std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return start[a] != start[b] ? start[a] < start[b] : size[a] > size[b]; });
+    int* dev = nullptr;
+    GT_CUDA(ctx, cudaMalloc(&dev, sizeof(int) * n));
+    GT_CUDA(ctx, cudaMemcpy(dev, order.data(), sizeof(int) * n, cudaMemcpyHostToDevice));
+    ctx->state_bytes += sizeof(int) * n;
+    it = ctx->attn_orders.emplace(key, dev).first;
+  }
+  *out = it->second;
+  return GT_OK;
+}
+
 template <int HD, int NQ, int NK, int DKV_KBUF, int DKV_MBUF, int DQ_KBUF, bool DQ_SB, int SPLIT>
 gt_status launch_bwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, const float* q, const float* k, const float* v,
                      const float* out, const float* lse, const float* go, float* gq, int accum_q, float* gk, int accum_k, float* gv,
@@ -1046,12 +1113,17 @@ gt_status launch_bwd(gt_ctx* ctx, int rows, int T, int Hq, int Hkv, int window, 
     st = set_smem(ctx, kern, SM::TOTAL, done);
     if (st) return st;
     dim3 grid(Hkv * nseq * SPLIT, gt_cdiv(T, ROWS), 1);
+    const int* order = nullptr;
+    if (SPLIT == 1 && (int)(grid.x * grid.y) > ctx->sm_count && !getenv("GT_ATTN_INDEX_ORDER")) {   // (the variable keeps index order, for comparison)
+      st = attn_dkv_order(ctx, (int)grid.y, (int)grid.x, Hq / Hkv, T, NQ, window, &order);
+      if (st) return st;
+    }
     if (SPLIT == 1)
       kern<<<grid, THREADS, SM::TOTAL, ctx->stream>>>(mK, mV, mQk, mQm, mGk, mGm, lse, D, gk, accum_k, gv, accum_v, rows, T, Hq, Hkv, window, scale2,
-                                                      dp_scale, rope, flag);
+                                                      dp_scale, rope, order, flag);
     else
       GT_CUDA(ctx, launch_split(kern, grid, THREADS, SM::TOTAL, ctx->stream, SPLIT, mK, mV, mQk, mQm, mGk, mGm, lse, D, gk, accum_k, gv, accum_v,
-                                rows, T, Hq, Hkv, window, scale2, dp_scale, rope, flag));
+                                rows, T, Hq, Hkv, window, scale2, dp_scale, rope, order, flag));
     GT_LAUNCHED(ctx, "attn_bwd_dkv_tc_kernel");
   }
   if (gq) {

@@ -39,6 +39,9 @@ struct gt_ctx {
     }
   };
   std::map<RopeKey, float*> rope_tables;  // [T, hd/2, 2] (cos, sin)
+  // launch orders of the attention dK/dV kernel, keyed by (key blocks, (kv head, sequence) pairs, query blocks per key block
+  // step, window): see attn_dkv_order
+  std::map<std::vector<int>, int*> attn_orders;
   // small scratch for reductions (never pooled)
   float* scratch = nullptr;
   uint64_t scratch_bytes = 0;

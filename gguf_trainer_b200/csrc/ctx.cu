@@ -85,6 +85,7 @@ gt_status gt_destroy(gt_ctx* ctx) {
   for (auto& kv : ctx->live) cudaFree(kv.first);
   for (auto& kv : ctx->state) cudaFree(kv.first);
   for (auto& kv : ctx->rope_tables) cudaFree(kv.second);
+  for (auto& kv : ctx->attn_orders) cudaFree(kv.second);
   for (auto ev : ctx->events) if (ev) cudaEventDestroy(ev);
   if (ctx->scratch) cudaFree(ctx->scratch);
   for (float* p : ctx->retired_scratch) cudaFree(p);
