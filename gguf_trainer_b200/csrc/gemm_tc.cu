@@ -783,6 +783,8 @@ static gt_status gemm_tc_dispatch(gt_ctx* ctx, int kind, int accum, int M, int N
   const int npairs = max(0, pair_capacity(ctx) - (ctx->sm_reserved + 1) / 2);
   int best = 0, ksplit = 1;
   double best_cost = 1e30;
+  int best_deep = 0, ks_deep = 1;      // the best choice that also cuts a product with enough tiles along K (see below)
+  double cost_deep = 1e30;
   for (int i = 0; i < 6; i++) {
     const int mt = cfgs[i].mt, bn = cfgs[i].bn, bm = mt == 1 ? BM1 : 2 * BM1;
     if (mt == 3 && (npairs < 8 || nparts > 1)) continue;   // (the pair kernel takes one product)
@@ -798,23 +800,6 @@ static gt_status gemm_tc_dispatch(gt_ctx* ctx, int kind, int accum, int M, int N
       ks = (int)min((long)(workers / tiles), (long)(kblocks / 8));
       if (ks < 1) ks = 1;
     }
-    // A very deep product whose tiles fill the SMs unevenly (the readout's dX: 384 tiles on 148 SMs are 2.6 waves,
-    // run as 3) is cut along K as well when that evens the waves out: 3 slices give 1152 units = 7.8 waves of a third
-    // of the length. The clear before it and the reduce-adds are charged below. Measured at rows 16384: the readout's
-    // dX (K 49152) 1890 -> 1292 us, dX of gate and up (K 3072) 128 -> 106 us, both moving to 256-row tiles in three
-    // slices; at K 1536 the same choice measured slower (60.5 -> 67.9 us), hence the depth limit of 64 K blocks.
-    double split_penalty = 0.0;
-    if (ks == 1 && tiles >= workers && kblocks >= 64 && deep_split) {
-      double best_w = (double)gt_cdiv(tiles, workers);
-      for (int k2 = 2; k2 <= 4; k2++) {
-        const double w2 = (double)gt_cdiv(tiles * k2, workers) / k2;
-        if (w2 < best_w - 0.05) { best_w = w2; ks = k2; }
-      }
-      if (ks > 1) split_penalty = 8000.0;
-    }
-    const long units = tiles * ks;
-    const long waves = gt_cdiv(units, workers);
-    const double kb_unit = (double)gt_cdiv(kblocks, ks);
     // One K block costs the slower of its MMAs (N/2 cycles each) and its shared-memory traffic at 128 B/clk: the stage
     // is written once by TMA and read once per 128-row half by the MMAs (measured: 0.9 of that bound). The epilogue
     // of a 256-row tile is exposed, that of a 128-row tile mostly hidden.
@@ -824,10 +809,30 @@ static gt_status gemm_tc_dispatch(gt_ctx* ctx, int kind, int accum, int M, int N
     const double tensor = (mt == 2 ? 2 : 1) * 4.0 * (bn / 2);
     const double smem = mt == 3 ? (bn == 192 ? 640.0 : 720.0)
                                 : 0.92 * ((bm * 128.0 + bn * 128.0) + mt * (BM1 * 128.0 + bn * 128.0)) / 128.0;
+    const double per_kb = tensor > smem ? tensor : smem;
     const double epilogue = mt == 2 ? 14.0 * bn + 900.0 : 1500.0;
-    const double cost = waves * (kb_unit * (tensor > smem ? tensor : smem) + epilogue + (split_penalty > 0 ? 600.0 : 0.0)) + split_penalty;
+    const double cost = gt_cdiv(tiles * ks, workers) * ((double)gt_cdiv(kblocks, ks) * per_kb + epilogue);
     if (cost < best_cost) { best_cost = cost; best = i; ksplit = ks; }
+    // A deep product whose tiles fill the SMs unevenly (the readout's dX: 384 tiles of 128 x 192 on 148 SMs are 2.6
+    // waves, run as 3) may be cut along K as well when that evens the waves out: as 192 tiles of 256 x 192 in three
+    // slices it is 576 units = 3.9 waves of a third of the length. The clear before it and the reduce-adds are
+    // charged; the candidate is taken after the loop only if it is predicted well ahead. Measured at rows 16384: the
+    // readout's dX (K 49152) 1890 -> 1292 us, dX of gate and up (K 3072) 128 -> 106 us; at K 1536 the same choice
+    // measured slower (60.5 -> 67.9 us), hence the depth limit of 64 K blocks.
+    if (ks == 1 && tiles >= workers && kblocks >= 64 && deep_split && mt != 3) {
+      double best_w = (double)gt_cdiv(tiles, workers);
+      int k2best = 1;
+      for (int k2 = 2; k2 <= 4; k2++) {
+        const double w2 = (double)gt_cdiv(tiles * k2, workers) / k2;
+        if (w2 < best_w - 0.05) { best_w = w2; k2best = k2; }
+      }
+      if (k2best > 1) {
+        const double c2 = gt_cdiv(tiles * k2best, workers) * ((double)gt_cdiv(kblocks, k2best) * per_kb + epilogue + 600.0) + 8000.0;
+        if (c2 < cost_deep) { cost_deep = c2; best_deep = i; ks_deep = k2best; }
+      }
+    }
   }
+  if (cost_deep < 0.92 * best_cost) { best_cost = cost_deep; best = best_deep; ksplit = ks_deep; }
   if (best_cost >= 1e30) return GT_OK;
   const int mt = cfgs[best].mt, bn = cfgs[best].bn;
   const int a_box = mt == 2 ? 2 * BM1 : BM1, b_box = mt == 3 ? bn / 2 : bn;   // rows one TMA copy brings
