@@ -27,7 +27,7 @@ extern "C" {
 
 gt_status gt_attention_fwd(gt_ctx* ctx, int32_t rows, int32_t Hq, int32_t Hkv, int32_t hd, int32_t window, gt_buf q, gt_buf k,
                            gt_buf v, gt_buf out, gt_buf lse) {
-  int T;
+  int T = 0;
   gt_status s = check_shape(ctx, rows, Hq, Hkv, hd, window, &T);
   if (s) return s;
   GT_REQUIRE(ctx, q && k && v && out && lse, "gt_attention_fwd: null operand");
@@ -44,7 +44,7 @@ gt_status gt_attention_fwd(gt_ctx* ctx, int32_t rows, int32_t Hq, int32_t Hkv, i
 gt_status gt_attention_bwd(gt_ctx* ctx, int32_t rows, int32_t Hq, int32_t Hkv, int32_t hd, int32_t window, gt_buf q, gt_buf k,
                            gt_buf v, gt_buf out, gt_buf lse, gt_buf gout, gt_buf gq, int32_t accum_q, gt_buf gk, int32_t accum_k,
                            gt_buf gv, int32_t accum_v) {
-  int T;
+  int T = 0;
   gt_status s = check_shape(ctx, rows, Hq, Hkv, hd, window, &T);
   if (s) return s;
   GT_REQUIRE(ctx, q && k && v && out && lse && gout, "gt_attention_bwd: null operand");
@@ -67,7 +67,7 @@ gt_status gt_attention_bwd(gt_ctx* ctx, int32_t rows, int32_t Hq, int32_t Hkv, i
 gt_status gt_attention_bwd_rope(gt_ctx* ctx, int32_t rows, int32_t Hq, int32_t Hkv, int32_t hd, int32_t window, gt_buf q, gt_buf k,
                                 gt_buf v, gt_buf out, gt_buf lse, gt_buf gout, gt_buf gq, int32_t accum_q, gt_buf gk, int32_t accum_k,
                                 gt_buf gv, int32_t accum_v, double base, int32_t pos_offset) {
-  int T;
+  int T = 0;
   gt_status s = check_shape(ctx, rows, Hq, Hkv, hd, window, &T);
   if (s) return s;
   GT_REQUIRE(ctx, q && k && v && out && lse && gout, "gt_attention_bwd_rope: null operand");

@@ -506,7 +506,6 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
   } else {
     // ---- epilogue (both CTAs): this CTA's 128 rows ----
     const int q = warp & 3;
-    const bool vec = (N & 3) == 0;
     uint32_t tl = 0, nst = 0;
     for (int t = pair; t < ntiles; t += npairs, tl++) {
       const int bi = t / per_mat, tt = t % per_mat;

@@ -109,16 +109,6 @@ __global__ void __launch_bounds__(OT) adamw_kernel(const Chunk* __restrict__ chu
 }
 
 // ---- Muon elementwise pieces ----
-// buf = mu*buf + g ; U = nesterov ? g + mu*buf : buf     (muon.ts:78-85, srcMomentum muon-gpu.ts:51-64)
-__global__ void muon_momentum_kernel(size_t n, const float* __restrict__ g, float* __restrict__ buf, float* __restrict__ U,
-                                     float mu, int nesterov) {
-  size_t stride = (size_t)gridDim.x * blockDim.x;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-    float b = mu * buf[i] + g[i];
-    buf[i] = b;
-    U[i] = nesterov ? g[i] + mu * b : b;
-  }
-}
 // X[r,c] = (flip ? U^T : U) * inv[0], U is [m,n]   (srcNormalize muon-gpu.ts:100-135)
 __global__ void muon_normalize_kernel(int m, int n, int flip, const float* __restrict__ U, const float* __restrict__ inv,
                                       float* __restrict__ X) {
