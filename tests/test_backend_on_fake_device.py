@@ -401,3 +401,44 @@ def test_muon_host_side_two_steps_and_state(dev, oracle, rows, cols):
     opt2.importState(deserializeOptState(blob))
     assert serializeOptState(opt2.exportState()) == blob
     assert fake.count("gt_muon_step") == 2 and fake.count("gt_adamw_step") == 2
+
+
+def _trajectory(oracle, gpu, cfg, reclaim, loss_chunk=0, recompute=False, steps=3, seq=8, batch=3):
+    from gguf_trainer_b200 import autograd as ag
+    from gguf_trainer_b200.arch import buildModel
+    from gguf_trainer_b200.optim import MuonGpu
+    from gguf_trainer_b200.train import trainLMGpuResident
+    rng_tok = oracle.Mulberry32(0x5EC1)
+    tokens = np.array([int(rng_tok() * cfg.vocabSize) for _ in range(160)])
+    ag.setCheckpointing(recompute)
+    try:
+        m = buildModel(cfg, 5)
+        g = m.paramGroups()
+        opt = MuonGpu(gpu, g["muon"], g["aux"], lr=0.02, momentum=0.95, aux={"lr": 3e-3, "weightDecay": 0.0, "clip": 1.0})
+        hist = trainLMGpuResident(m, gpu, tokens, seq, steps, batch, opt, logEvery=1, rng=oracle.Mulberry32(7),
+                                  reclaimTransients=reclaim, lossChunk=loss_chunk)
+    finally:
+        ag.setCheckpointing(False)
+    return hist, [p.data.copy() for p in m.params()]
+
+
+def test_training_loop_reclaim_recompute_and_chunked_loss(dev, oracle):
+    """The step loop of src/backend/train-gpu.ts:162-258 (`trainLMGpuResident`: three Muon + AdamW steps of three
+    micro-batches each, windows drawn as floor(rng() * maxStart)) on the stand-in, following tests/gpu-parity.ts:438-564:
+    reclaiming the transients at every micro-batch boundary changes nothing, recompute gives the plain run's losses and
+    parameters bit for bit, and the chunked loss follows the dense one."""
+    gpu, _fake = dev
+    cfg = ModelConfig("gemma3", 50, 32, 2, 4, 2, 8, 64, 1_000_000.0, 1e-6, ropeBaseLocal=10_000.0, slidingWindow=32, swaPattern=2)
+    off = _trajectory(oracle, gpu, cfg, False)
+    assert len(off[0]) == 3 and all(np.isfinite(h["loss"]) for h in off[0]) and off[0][-1]["loss"] < off[0][0]["loss"]
+    for name, run in (("reclaim", _trajectory(oracle, gpu, cfg, True)), ("recompute", _trajectory(oracle, gpu, cfg, False, 0, True)),
+                      ("recompute + reclaim", _trajectory(oracle, gpu, cfg, True, 0, True))):
+        for a, b in zip(run[0], off[0]):
+            assert a["loss"] == b["loss"], f"{name}, step {a['step']}: {a['loss']} vs {b['loss']}"
+        for i, (a, b) in enumerate(zip(run[1], off[1])):
+            assert np.array_equal(a, b), f"{name} changed parameter {i}"
+    chunked = _trajectory(oracle, gpu, cfg, True, 16)
+    for a, b in zip(chunked[0], off[0]):
+        assert abs(a["loss"] - b["loss"]) <= 1e-5 * abs(b["loss"])
+    for a, b in zip(chunked[1], off[1]):
+        assert np.linalg.norm(a - b) <= 1e-4 * max(np.linalg.norm(b), 1e-30)
