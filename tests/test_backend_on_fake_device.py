@@ -442,3 +442,97 @@ def test_training_loop_reclaim_recompute_and_chunked_loss(dev, oracle):
         assert abs(a["loss"] - b["loss"]) <= 1e-5 * abs(b["loss"])
     for a, b in zip(chunked[1], off[1]):
         assert np.linalg.norm(a - b) <= 1e-4 * max(np.linalg.norm(b), 1e-30)
+
+
+def test_checkpoint_taken_while_the_next_step_runs(oracle, monkeypatch):
+    """`beginCheckpoint` after step k, `finish` after step k + 1 (src/backend/muon-gpu.ts:440-470 through the asynchronous
+    read): the weights and the .optstate bytes are those of step k, although step k + 1 has overwritten both."""
+    from gguf_trainer_b200 import autograd as ag
+    from gguf_trainer_b200.arch import buildModel
+    from gguf_trainer_b200.backend import CudaBackend
+    from gguf_trainer_b200.optim import MuonGpu, deserializeOptState, serializeOptState
+    from gguf_trainer_b200.train import sequenceLoss
+    cfg = ModelConfig("gemma3", 50, 32, 2, 4, 2, 8, 64, 1_000_000.0, 1e-6, ropeBaseLocal=10_000.0, slidingWindow=32, swaPattern=2)
+    tokens = oracle.Mulberry32(23).randint(400, cfg.vocabSize)
+
+    def run(overlapped):
+        fake_cabi.install(monkeypatch)
+        gpu = CudaBackend(0, "fp32")
+        try:
+            m = buildModel(cfg, 5)
+            g = m.paramGroups()
+            opt = MuonGpu(gpu, g["muon"], g["aux"], lr=0.02, aux={"lr": 1e-2, "clip": 1.0, "weightDecay": 0.0})
+            T, rng = 9, oracle.Mulberry32(7)
+
+            def step():
+                gpu.install()
+                try:
+                    st = int(rng() * (len(tokens) - T - 1))
+                    loss = sequenceLoss(m, tokens[st:st + T], tokens[st + 1:st + 1 + T])
+                    ag.backward(loss, 1.0)
+                    gpu.sync([loss])
+                finally:
+                    gpu.uninstall()
+                opt.recordStep()
+
+            step(); step()
+            if overlapped:
+                ck = opt.beginCheckpoint()
+                step()
+                state = ck.finish()
+            else:
+                opt.syncWeightsToHost()
+                state = opt.exportState()
+            return [p.data.copy() for p in m.params()], serializeOptState(state)
+        finally:
+            gpu.destroy()
+
+    w_sync, s_sync = run(False)
+    w_late, s_late = run(True)
+    for i, (a, b) in enumerate(zip(w_late, w_sync)):
+        assert np.array_equal(a, b), f"weight {i}"
+    assert s_late == s_sync and deserializeOptState(s_late)["adamT"] == 2
+
+
+def test_clears_and_the_refusal_of_a_late_backward(dev):
+    """tests/gpu-parity.ts:1752-1900: a training window clears fewer gradient buffers than there are parameters (first
+    writers overwrite), a frozen model clears none, a forward-only window clears only what its sync stages back, and a
+    backward over a graph that a sync has already recycled is refused."""
+    from gguf_trainer_b200 import autograd as ag
+    from gguf_trainer_b200.arch import buildModel
+    from gguf_trainer_b200.train import freezeForScoring, sequenceLoss
+    gpu, _fake = dev
+    cfg = ModelConfig("gemma3", 64, 64, 2, 4, 2, 16, 256, 1_000_000.0, 1e-6, ropeBaseLocal=10_000.0, slidingWindow=16, swaPattern=2)
+    ids = np.array([(i * 11 + 5) % cfg.vocabSize for i in range(33)])
+    out = {}
+    for freeze in (False, True):
+        m = buildModel(cfg, 5)
+        if freeze:
+            freezeForScoring(m)
+        gpu.install()
+        try:
+            gpu.uploadParams(m.params())
+
+            def window():
+                loss = sequenceLoss(m, ids[:-1], ids[1:], 0)
+                ag.backward(loss, 1.0)
+                gpu.sync([loss])
+                return float(loss.data[0])
+
+            window()
+            before = gpu.gradClearsIssued
+            out[freeze] = (window(), gpu.gradClearsIssued - before, len(m.params()))
+        finally:
+            gpu.uninstall()
+    assert out[False][1] < out[False][2] and out[True][1] == 0 and out[False][0] == out[True][0]
+    m = buildModel(cfg, 5)
+    gpu.install()
+    try:
+        before = gpu.gradClearsIssued
+        loss = sequenceLoss(m, ids[:-1], ids[1:], 0)
+        gpu.sync([loss])
+        assert gpu.gradClearsIssued - before == len(m.params())
+        with pytest.raises(RuntimeError, match="graph built before a sync"):
+            ag.backward(loss, 1.0)
+    finally:
+        gpu.uninstall()
