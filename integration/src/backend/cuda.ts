@@ -15,8 +15,11 @@
 //
 // The Python mirror also defers some launches so that neighbouring ops run as one kernel (an activation whose only use
 // is a product: _gatedUnit; a residual add whose first use is a norm: add/_rmsNormRows; the input-gradient products of
-// an activation that feeds several projections: _deferDx; add's backward without a copy: _materializeCopy). They change
-// no value, only launch counts; they are left out here to keep the port short and can be carried over method by method.
+// an activation that feeds several projections: _deferDx; the weight gradients of a layer: _deferDw; projections of
+// one input, with the gated unit or the rotary embedding that follows them: _deferLinear, rope; a per-head norm and
+// the rotation after it: _deferHeadNorm; add's backward without a copy: _materializeCopy). They change no value, only
+// launch counts (550 instead of 1183 per step of a 30-layer model); they are left out here to keep the port short and
+// can be carried over method by method: INTEGRATION.md lists the entry point behind each.
 import { type OpsBackend, setOpsBackend, Tensor } from "../model/autograd.ts";
 
 const LIB_PATH = Deno.env.get("GGUFTRAIN_CUDA_LIB") ?? new URL("../../libgguftrain_cuda.so", import.meta.url).pathname;
